@@ -1,0 +1,741 @@
+// gemm_fused.cu — persistent, warp-specialised bf16 GEMM for sm_100a with the collective fused into it.
+//
+//   C[M, N] = A[M, K] * B[N, K]^T        (both operands K-contiguous, fp32 accumulation, bf16 output)
+//
+// Data path per CTA (one CTA per SM, 128 x 256 output tile):
+//   warp 0      TMA producer: cp.async.bulk.tensor loads of A (128 x 64) and B (256 x 64) slices into a
+//               4-deep shared-memory ring, completion on mbarriers.  Every CTA loads for itself; there is
+//               no cluster multicast.
+//   warp 1      one thread issues tcgen05.mma (M128 N256 K16, cta_group::1); accumulators live in tensor
+//               memory, two of them, so the epilogue of tile i overlaps the main loop of tile i+1.
+//   warps 2-5   epilogue: tcgen05.ld -> bf16 -> swizzled shared memory -> the collective:
+//                 store     TMA store of the tile into the C buffer of every rank       (GEMM + all-scatter)
+//                 reduce    TMA reduce-add of the tile into the C buffer of every rank  (GEMM + atomic all-reduce)
+//                 one-shot  tile -> own partial buffer, per-tile flag on every rank, then pull the tile
+//                           from all ranks and sum in fp32                              (GEMM + one-shot all-reduce)
+//                 two-shot  as one-shot, but only rank (tile % world) sums and pushes the result
+//   warps 6-7   all-gather prologue (optional): push this rank's rows of A to every peer in slices, each
+//               followed by a release increment of the peer's chunk flag; the producer warp waits for a
+//               chunk's flag before it loads rows that came from a peer (data is read from LOCAL memory).
+//
+// What it replaces in the reference: the persistent Triton kernels
+// examples/07_gemm_all_scatter/gemm_all_scatter.py:97-255,
+// examples/08_gemm_atomics_all_reduce/gemm_atomics_all_reduce.py:94-252 and
+// examples/09_gemm_one_shot_all_reduce/gemm_one_shot_all_reduce.py:94-275.
+//
+// Every wait (mbarrier, flag) is bounded by timeout_ns; on expiry the CTA records a status, raises its
+// abort word, lets every role leave its loop, frees its tensor memory and returns.
+//
+// Several ranks can be simulated by ONE launch on one GPU (num_local > 1, cooperative launch): CTA b works
+// as rank rank0 + b / ctas_per_rank.  That is how the multi-rank protocols are tested on a single GPU.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <mutex>
+#include <new>
+
+#include "gemm_fused.cuh"
+#include "iris/iris.cuh"
+#include "iris/ptx_sm100.cuh"
+
+namespace iris {
+namespace gemm {
+
+using namespace iris::ptx;
+
+// Sites reported in StatusBlock::where.
+enum Site : uint32_t {
+  kSiteProducerEmpty = 10,
+  kSiteProducerAgFlag = 11,
+  kSiteMmaAccEmpty = 20,
+  kSiteMmaFull = 21,
+  kSiteEpiAccFull = 30,
+  kSiteEpiEntry = 31,
+  kSiteEpiTileFlag = 32,
+  kSiteDone = 40,
+};
+
+struct TileCoord {
+  int m_idx, n_idx;
+};
+
+// Grouped raster: consecutive tile ids walk down `group_m` m-tiles before moving to the next n-tile, so
+// the CTAs of one wave share A rows and B columns in L2 (the reference's GROUP_SIZE_M swizzle,
+// examples/07_gemm_all_scatter/gemm_all_scatter.py:158-163).
+__device__ __forceinline__ TileCoord raster(int tile, int tiles_m, int tiles_n, int group_m) {
+  const int per_group = group_m * tiles_n;
+  const int g = tile / per_group;
+  const int first_m = g * group_m;
+  const int gsz = min(tiles_m - first_m, group_m);
+  const int in_g = tile - g * per_group;
+  TileCoord c;
+  c.m_idx = first_m + in_g % gsz;
+  c.n_idx = in_g / gsz;
+  return c;
+}
+
+// With the all-gather prologue the m-tiles are visited shard by shard starting with the rank's own rows:
+// logical shard position sp maps to source rank (rank + sp) % world.
+__device__ __forceinline__ int ag_actual_m(int logical_m, int tiles_per_shard, int rank, int world) {
+  const int sp = logical_m / tiles_per_shard;
+  const int within = logical_m - sp * tiles_per_shard;
+  const int s = (rank + sp) % world;
+  return s * tiles_per_shard + within;
+}
+
+__device__ __forceinline__ uint32_t* flag_ptr(const FusedGemmParams& p, int rank, int index) {
+  return reinterpret_cast<uint32_t*>(p.heap_base[rank] + p.flags_off) + index;
+}
+__device__ __forceinline__ StatusBlock* status_ptr(const FusedGemmParams& p, int rank) {
+  return reinterpret_cast<StatusBlock*>(p.heap_base[rank] + p.status_off);
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ void acc_bf16x8(float* acc, uint4 v) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 f = __bfloat1622float2(h[i]);
+    acc[2 * i] += f.x;
+    acc[2 * i + 1] += f.y;
+  }
+}
+
+__global__ void __launch_bounds__(kThreads, 1) fused_gemm_kernel(const __grid_constant__ FusedGemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  // 128-byte-swizzled tiles need 1024-byte alignment.
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t epi_base = smem_base + kStages * kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kSmemTiles);
+  const uint32_t bar_base = smem_u32(bars);
+  // barrier slots: full[kStages], empty[kStages], acc_full[kAccBufs], acc_empty[kAccBufs]
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+  auto acc_full_bar = [&](int b) { return bar_base + 8u * (2 * kStages + b); };
+  auto acc_empty_bar = [&](int b) { return bar_base + 8u * (2 * kStages + kAccBufs + b); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * kStages + 2 * kAccBufs);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+  volatile uint32_t* epi_ok = tmem_slot + 2;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int lr = blockIdx.x / p.ctas_per_rank;   // local rank index
+  const int cta = blockIdx.x - lr * p.ctas_per_rank;
+  const int G = p.ctas_per_rank;
+  const int rank = p.rank0 + lr;
+  const int W = p.world;
+  StatusBlock* status = status_ptr(p, rank);
+
+  const int tiles_m = (p.M + BM - 1) / BM;
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int total_tiles = tiles_m * tiles_n;
+  const int kblocks = (p.K + BK - 1) / BK;
+  const int tiles_per_shard = p.ag ? (p.M / W) / BM : 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < kAccBufs; ++b) {
+      mbar_init(acc_full_bar(b), 1);
+      mbar_init(acc_empty_bar(b), 4);  // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    *epi_ok = 1;
+    mbar_fence_init();
+    prefetch_tensormap(&p.tmA[lr]);
+    prefetch_tensormap(&p.tmB[lr]);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // Entry flag: tell every rank that this rank has started call `epoch` (its output buffers are ready to be
+  // written by peers).  One thread of one CTA per rank.
+  if (W > 1 && cta == 0 && threadIdx.x == 0) {
+    for (int i = 0; i < W; ++i) {
+      const int t = (rank + 1 + i) % W;
+      st_release_sys(flag_ptr(p, t, 8 + rank), p.epoch);
+    }
+  }
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------------------------------
+    // TMA producer
+    // ------------------------------------------------------------------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = cta; tile < total_tiles && ok; tile += G) {
+        TileCoord tc = raster(tile, tiles_m, tiles_n, p.group_m);
+        if (p.ag) {
+          tc.m_idx = ag_actual_m(tc.m_idx, tiles_per_shard, rank, W);
+          const int src = tc.m_idx / tiles_per_shard;
+          if (src != rank) {
+            const int chunk = tc.m_idx - src * tiles_per_shard;
+            const uint32_t* f = flag_ptr(p, rank, p.ag_flag_base + src * tiles_per_shard + chunk);
+            if (wait_until_ge(f, p.flag_target, p.timeout_ns, status, kSiteProducerAgFlag, rank, tile) != kOk) {
+              *abort_flag = 1;
+              ok = false;
+              break;
+            }
+            fence_proxy_async_all();  // peer wrote with ordinary stores; TMA reads through the async proxy
+          }
+        }
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1, p.timeout_ns, abort_flag)) {
+            record_status(status, kTimeout, kSiteProducerEmpty, rank, tile, kb);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          const uint32_t a_dst = smem_base + stage * kStageBytes;
+          const uint32_t b_dst = a_dst + kAStageBytes;
+          mbar_expect_tx(full_bar(stage), kStageBytes);
+          tma_load_2d(a_dst, &p.tmA[lr], kb * BK, tc.m_idx * BM, full_bar(stage));
+          tma_load_2d(b_dst, &p.tmB[lr], kb * BK, tc.n_idx * BN, full_bar(stage));
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------------------------------
+    // MMA issuer
+    // ------------------------------------------------------------------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_f16(BM, BN, true);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = cta; tile < total_tiles && ok; tile += G) {
+        if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1, p.timeout_ns, abort_flag)) {
+          record_status(status, kTimeout, kSiteMmaAccEmpty, rank, tile, acc);
+          *abort_flag = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, p.timeout_ns, abort_flag)) {
+            record_status(status, kTimeout, kSiteMmaFull, rank, tile, kb);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_base + stage * kStageBytes;
+          const uint32_t b_addr = a_addr + kAStageBytes;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t a_desc = umma_desc_k_sw128(a_addr + k * UMMA_K * 2);
+            const uint64_t b_desc = umma_desc_k_sw128(b_addr + k * UMMA_K * 2);
+            umma_f16_ss(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(empty_bar(stage));  // frees the ring slot once these MMAs have read it
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        umma_commit(acc_full_bar(acc));  // accumulator complete
+        if (++acc == kAccBufs) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+      }
+    }
+  } else if (warp < 6) {
+    // ------------------------------------------------------------------------------------------
+    // Epilogue (128 threads)
+    // ------------------------------------------------------------------------------------------
+    const int et = threadIdx.x - 64;
+    const bool issuer = (et == 0);
+    const int quad = warp & 3;          // tensor-memory lane quadrant this warp may read
+    const int row = quad * 32 + lane;   // row of the tile held by this thread
+    const bool pulls = (p.mode == kEpiOneShot || p.mode == kEpiTwoShot);
+    const bool push_all = (p.mode == kEpiStore || p.mode == kEpiReduce) && p.store_all && W > 1;
+    const bool need_entry = W > 1 && (push_all || p.mode == kEpiTwoShot);
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    int ebuf = 0;
+    int prev_tile = -1;
+    bool entered = !need_entry;
+
+    // Sum tile `t` over all ranks' partial buffers and write the result (one-/two-shot modes).
+    auto pull_reduce = [&](int t) -> bool {
+      if (p.mode == kEpiTwoShot && (t % W) != rank) return true;
+      if (issuer) {
+        const uint32_t* f = flag_ptr(p, rank, p.tile_flag_base + t);
+        *epi_ok = wait_until_ge(f, p.flag_target, p.timeout_ns, status, kSiteEpiTileFlag, rank, t) == kOk ? 1u : 0u;
+      }
+      named_barrier_sync(1, 128);
+      const bool ok = *epi_ok != 0;
+      named_barrier_sync(1, 128);
+      if (!ok) return false;
+      const TileCoord tc = raster(t, tiles_m, tiles_n, p.group_m);
+      const int m0 = tc.m_idx * BM, n0 = tc.n_idx * BN;
+      // 128 rows x 32 vectors of 8 bf16; a warp covers one 512-byte row segment per step.
+      for (int i = 0; i < (BM * BN / 8) / 128; i += 2) {
+        uint4 v[2][kMaxRanks];
+        int rr[2], cc[2];
+        bool in[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int idx = et + (i + u) * 128;
+          rr[u] = m0 + idx / (BN / 8);
+          cc[u] = n0 + (idx % (BN / 8)) * 8;
+          in[u] = rr[u] < p.M && cc[u] < p.N;
+          if (in[u]) {
+            const uint64_t off = p.partial_off + ((uint64_t)rr[u] * p.N + cc[u]) * 2;
+#pragma unroll
+            for (int s = 0; s < kMaxRanks; ++s)
+              if (s < W) v[u][s] = ld_v4(reinterpret_cast<const uint4*>(p.heap_base[(rank + s) % W] + off));
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          if (!in[u]) continue;
+          float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+          for (int s = 0; s < kMaxRanks; ++s)
+            if (s < W) acc_bf16x8(a, v[u][s]);
+          uint4 o;
+          o.x = pack_bf16x2(a[0], a[1]);
+          o.y = pack_bf16x2(a[2], a[3]);
+          o.z = pack_bf16x2(a[4], a[5]);
+          o.w = pack_bf16x2(a[6], a[7]);
+          const uint64_t ooff = p.out_off + ((uint64_t)rr[u] * p.ldo + cc[u]) * 2;
+          if (p.mode == kEpiOneShot) {
+            st_v4(reinterpret_cast<uint4*>(p.heap_base[rank] + ooff), o);
+          } else {
+            for (int s = 0; s < W; ++s) st_v4(reinterpret_cast<uint4*>(p.heap_base[(rank + 1 + s) % W] + ooff), o);
+          }
+        }
+      }
+      return true;
+    };
+
+    bool ok_all = true;
+    for (int tile = cta; tile < total_tiles; tile += G) {
+      TileCoord tc = raster(tile, tiles_m, tiles_n, p.group_m);
+      if (p.ag) tc.m_idx = ag_actual_m(tc.m_idx, tiles_per_shard, rank, W);
+      // Uniform decision for the whole epilogue group: one thread waits, everybody reads the verdict.
+      if (issuer) {
+        bool ok = mbar_wait(acc_full_bar(acc), acc_phase, p.timeout_ns, abort_flag);
+        if (!ok) record_status(status, kTimeout, kSiteEpiAccFull, rank, tile, acc);
+        if (ok && !entered) {
+          // Before the first push of this call: every peer must have entered the call.
+          for (int i = 0; i < W && ok; ++i) {
+            const int t = (rank + 1 + i) % W;
+            ok = wait_until_ge(flag_ptr(p, rank, 8 + t), p.epoch, p.timeout_ns, status, kSiteEpiEntry, rank, t) == kOk;
+          }
+        }
+        *epi_ok = ok ? 1u : 0u;
+      }
+      named_barrier_sync(1, 128);
+      const bool ok = *epi_ok != 0;
+      named_barrier_sync(1, 128);
+      if (!ok) {
+        ok_all = false;
+        break;
+      }
+      entered = true;
+      tc_fence_after();
+
+      const int x_base = (pulls ? 0 : rank * p.col_off_per_rank) + tc.n_idx * BN;
+      const int y = tc.m_idx * BM;
+#pragma unroll 1
+      for (int c = 0; c < BN / kEpiCols; ++c) {
+        const bool live = tc.n_idx * BN + c * kEpiCols < p.N;  // sub-tiles past the matrix edge are skipped
+        uint32_t v[kEpiCols];
+        const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN + c * kEpiCols;
+        tmem_ld_32x32b_x32(taddr, v);
+        tmem_ld_32x32b_x32(taddr + 32, v + 32);
+        tmem_wait_ld();
+        if (c == BN / kEpiCols - 1) {
+          // The accumulator has been read completely: hand it back to the MMA warp.
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(acc_empty_bar(acc));
+        }
+        if (!live) continue;  // uniform over the group
+        // The staging buffer was last used two sub-tiles ago: its TMA reads must have finished.
+        if (issuer) bulk_wait_read<kEpiBufs - 1>();
+        named_barrier_sync(1, 128);
+        const uint32_t sbase = epi_base + ebuf * kEpiStageBytes + row * 128;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t a = pack_bf16x2(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]));
+          const uint32_t b = pack_bf16x2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
+          const uint32_t cc = pack_bf16x2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
+          const uint32_t d = pack_bf16x2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
+          st_shared_v4(sbase + ((j ^ (row & 7)) << 4), a, b, cc, d);  // 128-byte swizzle, as the tensor map expects
+        }
+        fence_proxy_async_smem();
+        named_barrier_sync(1, 128);
+        if (issuer) {
+          const uint32_t src = epi_base + ebuf * kEpiStageBytes;
+          const int x = x_base + c * kEpiCols;
+          if (push_all) {
+            for (int i = 0; i < W; ++i) {  // peers first, starting with the next rank; own copy last
+              const int t = (rank + 1 + i) % W;
+              if (p.mode == kEpiStore) tma_store_2d(&p.tmC[t], x, y, src);
+              else tma_reduce_add_2d(&p.tmC[t], x, y, src);
+            }
+          } else if (p.mode == kEpiReduce) {
+            tma_reduce_add_2d(&p.tmC[rank], x, y, src);
+          } else {
+            tma_store_2d(&p.tmC[rank], x, y, src);
+          }
+          bulk_commit();
+        }
+        ebuf ^= 1;
+      }
+      if (++acc == kAccBufs) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+
+      if (pulls) {
+        if (issuer) {
+          // Partial tile is in this rank's buffer: publish it to every rank, then sum the previous tile.
+          bulk_wait<0>();
+          fence_proxy_async_all();
+          for (int i = 0; i < W; ++i) {
+            const int t = (rank + 1 + i) % W;
+            if (p.mode == kEpiTwoShot && t != tile % W) continue;  // only the tile's owner needs to know
+            red_release_sys_add(flag_ptr(p, t, p.tile_flag_base + tile), 1u);
+          }
+        }
+        if (prev_tile >= 0 && !pull_reduce(prev_tile)) {
+          ok_all = false;
+          break;
+        }
+        prev_tile = tile;
+      }
+    }
+    if (pulls && ok_all && prev_tile >= 0) ok_all = pull_reduce(prev_tile);
+    if (!ok_all && issuer) *abort_flag = 1;
+
+    // Completion: all pushes of this CTA have landed -> bump every rank's arrival counter; then wait until
+    // every CTA of every rank has done the same, so that at kernel end all remote tiles are in local memory.
+    const bool end_sync = W > 1 && (push_all || p.mode == kEpiTwoShot);
+    if (end_sync) {
+      if (p.mode == kEpiTwoShot) {
+        fence_sys();  // every thread pushed result vectors with ordinary stores
+      }
+      named_barrier_sync(1, 128);
+      if (issuer) {
+        bulk_wait<0>();
+        fence_proxy_async_all();
+        fence_sys();
+        for (int i = 0; i < W; ++i) red_release_sys_add(flag_ptr(p, (rank + 1 + i) % W, 0), 1u);
+        if (ok_all) wait_until_ge(flag_ptr(p, rank, 0), p.done_target, p.timeout_ns, status, kSiteDone, rank, cta);
+      }
+    } else if (issuer) {
+      bulk_wait<0>();
+    }
+  } else {
+    // ------------------------------------------------------------------------------------------
+    // All-gather push (64 threads): this rank's rows of A -> the same rows of every peer's gathered A.
+    // ------------------------------------------------------------------------------------------
+    if (p.ag && W > 1) {
+      const int ct = threadIdx.x - 192;
+      const int Ms = p.M / W;
+      const int S = p.ag_slices;
+      const int slice_elems = p.K / S;             // multiple of 8 (checked on the host)
+      const int vec_per_row = slice_elems / 8;     // 16-byte vectors per row of a slice
+      const int items = (W - 1) * tiles_per_shard * S;
+      for (int item = cta; item < items; item += G) {
+        const int pi = item / (tiles_per_shard * S);           // peer-major: finish one peer's copy first
+        const int rem = item - pi * (tiles_per_shard * S);
+        const int chunk = rem / S;
+        const int slice = rem - chunk * S;
+        const int peer = (rank - 1 - pi + 2 * W) % W;           // the peer that needs these rows earliest
+        const int r0 = rank * Ms + chunk * BM;
+        const uint64_t base_off = p.agsrc_off + ((uint64_t)r0 * p.lda_full + (uint64_t)slice * slice_elems) * 2;
+        const uint8_t* src = reinterpret_cast<const uint8_t*>(p.heap_base[rank] + base_off);
+        uint8_t* dst = reinterpret_cast<uint8_t*>(p.heap_base[peer] + base_off);
+        const int nvec = BM * vec_per_row;
+        for (int i0 = ct; i0 < nvec; i0 += 64 * 8) {
+          uint4 v[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const int i = i0 + u * 64;
+            if (i < nvec) {
+              const int r = i / vec_per_row, cv = i - r * vec_per_row;
+              v[u] = ld_v4(reinterpret_cast<const uint4*>(src + ((uint64_t)r * p.lda_full) * 2 + cv * 16));
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const int i = i0 + u * 64;
+            if (i < nvec) {
+              const int r = i / vec_per_row, cv = i - r * vec_per_row;
+              st_v4(reinterpret_cast<uint4*>(dst + ((uint64_t)r * p.lda_full) * 2 + cv * 16), v[u]);
+            }
+          }
+        }
+        fence_sys();
+        named_barrier_sync(2, 64);
+        if (ct == 0) red_release_sys_add(flag_ptr(p, peer, p.ag_flag_base + rank * tiles_per_shard + chunk), 1u);
+      }
+    }
+  }
+
+  // ---- teardown --------------------------------------------------------------------------------
+  __syncwarp();
+  if (*abort_flag) {
+    // Error path only: give copies in flight a bounded time to land before tensor memory is released.
+    const uint64_t t0 = timer_ns();
+    while (timer_ns() - t0 < 50000) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ================================================================================================
+// Host side
+// ================================================================================================
+namespace {
+
+thread_local char g_err[512] = "";
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+std::once_flag g_encode_once;
+
+EncodeTiledFn encode_fn() {
+  std::call_once(g_encode_once, []() {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    else
+      (void)cudaGetLastError();
+  });
+  return g_encode;
+}
+
+// bf16 matrix [rows, cols] with `ld` elements between rows; box = box_cols x box_rows; 128-byte swizzle.
+int encode_2d(CUtensorMap* out, uint64_t ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_cols,
+              uint32_t box_rows, const char* what) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) {
+    snprintf(g_err, sizeof(g_err), "cuTensorMapEncodeTiled is not available");
+    return -1;
+  }
+  if (ptr % 16 != 0 || (ld * 2) % 16 != 0) {
+    snprintf(g_err, sizeof(g_err), "%s: base address and row pitch must be multiples of 16 bytes", what);
+    return -2;
+  }
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, reinterpret_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    snprintf(g_err, sizeof(g_err), "cuTensorMapEncodeTiled(%s) failed with %d", what, (int)r);
+    return -3;
+  }
+  return 0;
+}
+
+}  // namespace
+}  // namespace gemm
+}  // namespace iris
+
+using namespace iris::gemm;
+
+extern "C" {
+
+// Plain-C description of one fused GEMM; mirrored field by field in iris_b200/ops/gemm.py.
+struct IrisGemmDesc {
+  uint64_t a_ptr[kMaxRanks];   // per local rank (with ag = 1: the gathered A buffer)
+  uint64_t b_ptr[kMaxRanks];   // per local rank
+  uint64_t c_ptr[kMaxRanks];   // per target rank: output (store/reduce) or partial buffer parity 0 (one-/two-shot)
+  uint64_t c2_ptr[kMaxRanks];  // partial buffer parity 1, else 0
+  uint64_t heap_base[kMaxRanks];
+  int64_t lda[kMaxRanks];      // elements
+  int64_t ldb[kMaxRanks];
+  int64_t ldc;                 // row pitch of the C / partial buffers
+  int64_t c_cols;              // logical number of columns of the C / partial buffers
+  uint64_t flags_off;
+  uint64_t partial_off[2];
+  uint64_t out_off;
+  uint64_t status_off;
+  uint64_t agsrc_off;
+  uint64_t timeout_ns;
+  int M, N, K;
+  int ldo;
+  int col_off_per_rank;
+  int world, num_local, rank0, ctas_per_rank;
+  int mode, group_m, ag, ag_slices, store_all;
+  int tile_flag_base, ag_flag_base;
+  int device;
+};
+
+struct IrisGemmPlan {
+  FusedGemmParams params[2];  // one per parity of the partial buffers
+  int grid;
+  int cooperative;
+  int device;
+};
+
+const char* iris_gemm_last_error() { return g_err; }
+int iris_gemm_smem_bytes() { return kSmemBytes; }
+int iris_gemm_desc_size() { return (int)sizeof(IrisGemmDesc); }
+
+void* iris_gemm_plan_create(const IrisGemmDesc* d) {
+  g_err[0] = 0;
+  if (d->world < 1 || d->world > kMaxRanks || d->num_local < 1 || d->num_local > kMaxRanks) {
+    snprintf(g_err, sizeof(g_err), "world and num_local must be in [1, %d]", kMaxRanks);
+    return nullptr;
+  }
+  if (d->M < 1 || d->N < 1 || d->K < 1) {
+    snprintf(g_err, sizeof(g_err), "M, N, K must be positive");
+    return nullptr;
+  }
+  if (d->N % 8 != 0 || d->K % 8 != 0) {
+    snprintf(g_err, sizeof(g_err), "N and K must be multiples of 8 (16-byte rows)");
+    return nullptr;
+  }
+  if (d->world > 1 && d->store_all && d->N % kEpiCols != 0) {
+    snprintf(g_err, sizeof(g_err), "N per rank must be a multiple of %d when tiles are pushed to peers", kEpiCols);
+    return nullptr;
+  }
+  if (d->ag) {
+    if (d->M % d->world != 0 || (d->M / d->world) % BM != 0) {
+      snprintf(g_err, sizeof(g_err), "all-gather prologue needs M / world to be a multiple of %d", BM);
+      return nullptr;
+    }
+    if (d->ag_slices < 1 || d->K % d->ag_slices != 0 || (d->K / d->ag_slices) % 8 != 0) {
+      snprintf(g_err, sizeof(g_err), "ag_slices must divide K into multiples of 8 elements");
+      return nullptr;
+    }
+  }
+  cudaSetDevice(d->device);
+  int sms = 0;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, d->device);
+  const int grid = d->ctas_per_rank * d->num_local;
+  if (d->ctas_per_rank < 1 || (sms > 0 && grid > sms)) {
+    snprintf(g_err, sizeof(g_err), "grid of %d CTAs does not fit %d SMs (all CTAs must be resident)", grid, sms);
+    return nullptr;
+  }
+  IrisGemmPlan* plan = new (std::nothrow) IrisGemmPlan();
+  if (!plan) return nullptr;
+  memset(plan, 0, sizeof(*plan));
+  plan->grid = grid;
+  plan->cooperative = d->num_local > 1;
+  plan->device = d->device;
+  for (int par = 0; par < 2; ++par) {
+    FusedGemmParams& p = plan->params[par];
+    for (int l = 0; l < d->num_local; ++l) {
+      if (encode_2d(&p.tmA[l], d->a_ptr[l], d->M, d->K, d->lda[l], BK, BM, "A") ||
+          encode_2d(&p.tmB[l], d->b_ptr[l], d->N, d->K, d->ldb[l], BK, BN, "B")) {
+        delete plan;
+        return nullptr;
+      }
+    }
+    for (int t = 0; t < d->world; ++t) {
+      const uint64_t cp = (par == 1 && d->c2_ptr[t]) ? d->c2_ptr[t] : d->c_ptr[t];
+      if (!cp) continue;
+      if (encode_2d(&p.tmC[t], cp, d->M, d->c_cols, d->ldc, kEpiCols, BM, "C")) {
+        delete plan;
+        return nullptr;
+      }
+    }
+    for (int t = 0; t < kMaxRanks; ++t) p.heap_base[t] = d->heap_base[t];
+    p.flags_off = d->flags_off;
+    p.partial_off = d->partial_off[par];
+    p.out_off = d->out_off;
+    p.status_off = d->status_off;
+    p.agsrc_off = d->agsrc_off;
+    p.timeout_ns = d->timeout_ns;
+    p.M = d->M;
+    p.N = d->N;
+    p.K = d->K;
+    p.ldo = d->ldo;
+    p.lda_full = (int)d->lda[0];
+    p.col_off_per_rank = d->col_off_per_rank;
+    p.world = d->world;
+    p.num_local = d->num_local;
+    p.rank0 = d->rank0;
+    p.ctas_per_rank = d->ctas_per_rank;
+    p.mode = d->mode;
+    p.group_m = d->group_m < 1 ? 1 : d->group_m;
+    p.ag = d->ag;
+    p.ag_slices = d->ag_slices;
+    p.store_all = d->store_all;
+    p.tile_flag_base = d->tile_flag_base;
+    p.ag_flag_base = d->ag_flag_base;
+  }
+  cudaError_t e = cudaFuncSetAttribute(fused_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+  if (e != cudaSuccess) {
+    snprintf(g_err, sizeof(g_err), "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    delete plan;
+    return nullptr;
+  }
+  return plan;
+}
+
+void iris_gemm_plan_destroy(void* h) { delete static_cast<IrisGemmPlan*>(h); }
+
+// Launch one call.  `parity` selects the partial-buffer set; epoch / flag_target / done_target are the
+// cumulative values this call drives the flags to (kept by the caller).
+int iris_gemm_plan_launch(void* h, int parity, uint32_t epoch, uint32_t flag_target, uint32_t done_target,
+                          void* stream) {
+  IrisGemmPlan* plan = static_cast<IrisGemmPlan*>(h);
+  FusedGemmParams& p = plan->params[parity & 1];
+  p.epoch = epoch;
+  p.flag_target = flag_target;
+  p.done_target = done_target;
+  cudaError_t e;
+  if (plan->cooperative) {
+    void* args[] = {&p};
+    e = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(fused_gemm_kernel), dim3(plan->grid), dim3(kThreads),
+                                    args, kSmemBytes, static_cast<cudaStream_t>(stream));
+  } else {
+    fused_gemm_kernel<<<plan->grid, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(p);
+    e = cudaGetLastError();
+  }
+  if (e != cudaSuccess) {
+    snprintf(g_err, sizeof(g_err), "launch failed: %s", cudaGetErrorString(e));
+    return -1;
+  }
+  return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,81 @@
+// gemm_fused.cuh — parameters shared by the host launcher and the device code of the fused
+// GEMM + collective kernels (gemm_fused.cu).
+//
+// One kernel family replaces the reference's three Triton kernels:
+//   * examples/07_gemm_all_scatter/gemm_all_scatter.py:97-255        -> kEpiStore   (push tile to every rank)
+//   * examples/08_gemm_atomics_all_reduce/gemm_atomics_all_reduce.py:94-252 -> kEpiReduce (add tile into every rank)
+//   * examples/09_gemm_one_shot_all_reduce/gemm_one_shot_all_reduce.py:94-275 -> kEpiOneShot / kEpiTwoShot
+// plus the all-gather -> GEMM prologue that the reference does not have.
+#pragma once
+#include <cuda.h>
+#include <stdint.h>
+
+namespace iris {
+namespace gemm {
+
+constexpr int kMaxRanks = 8;
+
+// Tile shape of one CTA: 128 x 256 output elements, 64-deep K slices (128 bytes of bf16: one swizzle row).
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int kStages = 4;   // shared-memory ring of (A,B) slices
+constexpr int kAccBufs = 2;  // TMEM accumulators: epilogue of tile i overlaps main loop of tile i+1
+constexpr int kEpiCols = 64; // epilogue works on 128 x 64 sub-tiles (128-byte rows of bf16)
+constexpr int kEpiBufs = 2;
+
+constexpr int kAStageBytes = BM * BK * 2;
+constexpr int kBStageBytes = BN * BK * 2;
+constexpr int kStageBytes = kAStageBytes + kBStageBytes;
+constexpr int kEpiStageBytes = BM * kEpiCols * 2;
+constexpr int kSmemTiles = kStages * kStageBytes + kEpiBufs * kEpiStageBytes;
+constexpr int kSmemBarriers = 256;
+constexpr int kSmemBytes = kSmemTiles + kSmemBarriers + 1024;  // + slack to align the base to 1024 B
+
+constexpr int kThreads = 256;  // warp 0: TMA producer, warp 1: MMA issuer, warps 2-5: epilogue, warps 6-7: comm
+
+enum EpiMode : int {
+  kEpiStore = 0,    // C tile -> TMA store into the C buffer of every rank (world 1: plain GEMM)
+  kEpiReduce = 1,   // C tile -> TMA reduce-add into the C buffer of every rank (C must start at zero)
+  kEpiOneShot = 2,  // partial tile -> own partial buffer; flags; every rank pulls all partials and sums
+  kEpiTwoShot = 3,  // as one-shot, but tile t is summed only by rank t % world, which pushes the result
+};
+
+struct FusedGemmParams {
+  // Tensor maps (host-encoded).  Index = local rank for A and B, target rank for C.
+  CUtensorMap tmA[kMaxRanks];  // [rows M, cols K] bf16, K contiguous, box 64 x 128, 128-byte swizzle
+  CUtensorMap tmB[kMaxRanks];  // [rows N, cols K] bf16, K contiguous, box 64 x 256, 128-byte swizzle
+  CUtensorMap tmC[kMaxRanks];  // [rows M, cols ldc] bf16, box 64 x 128, 128-byte swizzle
+                               //   store/reduce: the output of rank t; one-/two-shot: the partial buffer of rank t
+  uint64_t heap_base[kMaxRanks];  // base address of every rank's heap in this process
+  // Symmetric offsets (bytes from the heap base) of the communication state.
+  uint64_t flags_off;    // uint32[...]: [0] arrival counter, [8 + r] entry flag of rank r, then per-tile /
+                         // per-chunk flags at tile_flag_base / ag_flag_base
+  uint64_t partial_off;  // one-/two-shot: bf16 [M, N] partial buffer of the current parity
+  uint64_t out_off;      // one-/two-shot: bf16 [M, ldo] final output
+  uint64_t status_off;   // iris::StatusBlock
+  uint64_t agsrc_off;    // all-gather prologue: gathered A [M, K] (row stride lda_full elements)
+  uint64_t timeout_ns;
+  int M, N, K;           // per-rank GEMM problem: C[M, N] = A[M, K] * B[N, K]^T
+  int ldo;               // row stride (elements) of the final output in one-/two-shot mode
+  int lda_full;          // row stride (elements) of the gathered A
+  int col_off_per_rank;  // store/reduce: rank r writes columns [r * col_off_per_rank, ... + N) of C
+  int world;             // ranks taking part in the collective
+  int num_local;         // ranks simulated by this launch (1 on real multi-GPU runs)
+  int rank0;             // rank of local index 0
+  int ctas_per_rank;
+  int mode;              // EpiMode
+  int group_m;           // raster: m-tiles per group
+  int ag;                // 1: A is gathered by the comm warps of this kernel (rows sharded M / world per rank)
+  int ag_slices;         // column slices per 128-row chunk in the all-gather push
+  int store_all;         // store/reduce modes: 1 = push the tile to every rank, 0 = own rank only
+  int tile_flag_base;    // index (uint32 units from flags_off) of the per-tile flags
+  int ag_flag_base;      // index of the all-gather chunk flags: [src rank][chunk]
+  uint32_t epoch;        // call number (1, 2, ...): value of the entry flags in this call
+  uint32_t flag_target;  // value per-tile / per-chunk flags reach in this call (cumulative over calls)
+  uint32_t done_target;  // value the arrival counter reaches when every CTA of every rank has finished
+};
+
+}  // namespace gemm
+}  // namespace iris

@@ -1,0 +1,294 @@
+"""Fused bf16 GEMM + collective operators on the tcgen05 kernel of ``csrc/kernels/gemm_fused.cu``.
+
+Role in the reference: the ``matmul`` autograd-Function wrappers that launch the persistent Triton kernels
+(``examples/07_gemm_all_scatter/matmul_wrapper.py:19-219`` and its copies in 08/09) together with the buffer
+set-up of the drivers (``examples/07_gemm_all_scatter/benchmark.py:103-142``).
+
+Operand convention (as the reference: ``A = randn(m, k)``, ``B = randn(n, k).T``,
+``examples/07_gemm_all_scatter/benchmark.py:103-104``): ``A`` is ``[M, K]`` and ``B`` is given as ``Bt = [N, K]``,
+both K-contiguous with an arbitrary 16-byte-aligned row pitch, so K-shards that are views work without copies.
+
+A ``FusedGemm`` is built once for fixed buffers (tensor maps are encoded at construction) and called many
+times; flags are cumulative counters, so nothing is reset between calls.
+
+``ctxs`` is one :class:`~iris_b200.context.Iris` (one process per GPU) or the list returned by
+``Iris.local_world`` (several ranks simulated by ONE launch on one GPU).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import List, Optional, Sequence, Union
+
+import torch
+
+from .. import _native
+from ..context import Iris
+
+MAX_RANKS = 8
+BM, BN, BK = 128, 256, 64
+MODES = {"store": 0, "reduce": 1, "one_shot": 2, "two_shot": 3}
+FLAG_HEADER = 16  # [0] arrival counter, [8 + r] entry flags
+
+
+class _Desc(ctypes.Structure):
+    _fields_ = [
+        ("a_ptr", ctypes.c_uint64 * MAX_RANKS), ("b_ptr", ctypes.c_uint64 * MAX_RANKS),
+        ("c_ptr", ctypes.c_uint64 * MAX_RANKS), ("c2_ptr", ctypes.c_uint64 * MAX_RANKS),
+        ("heap_base", ctypes.c_uint64 * MAX_RANKS),
+        ("lda", ctypes.c_int64 * MAX_RANKS), ("ldb", ctypes.c_int64 * MAX_RANKS),
+        ("ldc", ctypes.c_int64), ("c_cols", ctypes.c_int64),
+        ("flags_off", ctypes.c_uint64), ("partial_off", ctypes.c_uint64 * 2), ("out_off", ctypes.c_uint64),
+        ("status_off", ctypes.c_uint64), ("agsrc_off", ctypes.c_uint64), ("timeout_ns", ctypes.c_uint64),
+        ("M", ctypes.c_int), ("N", ctypes.c_int), ("K", ctypes.c_int), ("ldo", ctypes.c_int),
+        ("col_off_per_rank", ctypes.c_int),
+        ("world", ctypes.c_int), ("num_local", ctypes.c_int), ("rank0", ctypes.c_int), ("ctas_per_rank", ctypes.c_int),
+        ("mode", ctypes.c_int), ("group_m", ctypes.c_int), ("ag", ctypes.c_int), ("ag_slices", ctypes.c_int),
+        ("store_all", ctypes.c_int), ("tile_flag_base", ctypes.c_int), ("ag_flag_base", ctypes.c_int),
+        ("device", ctypes.c_int),
+    ]
+
+
+def _lib():
+    lib = _native.kernels()
+    if not getattr(lib, "_gemm_typed", False):
+        lib.iris_gemm_last_error.restype = ctypes.c_char_p
+        lib.iris_gemm_plan_create.restype = ctypes.c_void_p
+        lib.iris_gemm_plan_create.argtypes = [ctypes.POINTER(_Desc)]
+        lib.iris_gemm_plan_destroy.argtypes = [ctypes.c_void_p]
+        lib.iris_gemm_plan_launch.restype = ctypes.c_int
+        lib.iris_gemm_plan_launch.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_uint32, ctypes.c_uint32,
+                                              ctypes.c_uint32, ctypes.c_void_p]
+        if lib.iris_gemm_desc_size() != ctypes.sizeof(_Desc):
+            raise RuntimeError("IrisGemmDesc layout mismatch between Python and the native library")
+        lib._gemm_typed = True
+    return lib
+
+
+def _check_operand(t: torch.Tensor, name: str):
+    if t.dtype != torch.bfloat16:
+        raise TypeError(f"{name} must be bfloat16, got {t.dtype}")
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise ValueError(f"{name} must be 2-D with a contiguous last dimension (K-major)")
+    if t.data_ptr() % 16 or (t.stride(0) * 2) % 16:
+        raise ValueError(f"{name}: base address and row pitch must be multiples of 16 bytes")
+
+
+def as_kmajor_bt(b: torch.Tensor) -> torch.Tensor:
+    """Accept ``B`` as ``[K, N]`` with strides ``(1, ld)`` (the reference's ``randn(n, k).T``) or as ``Bt = [N, K]``
+    with a contiguous last dimension, and return the ``[N, K]`` K-major view."""
+    if b.dim() != 2:
+        raise ValueError("B must be 2-D")
+    if b.stride(1) == 1:
+        return b
+    if b.stride(0) == 1:
+        return b.t()
+    raise ValueError("B must be K-contiguous (pass randn(n, k).T or an [N, K] tensor)")
+
+
+class FusedGemm:
+    """One fused GEMM + collective on fixed buffers.
+
+    Args:
+        ctxs: one ``Iris`` or the list from ``Iris.local_world``.
+        a: per local rank, ``[M, K]`` K-major (with ``ag=True``: ignored, the gathered buffer ``a_full`` is used).
+        bt: per local rank, ``[N, K]`` K-major.
+        mode: ``"store"`` (all-scatter when ``store_all``), ``"reduce"`` (atomic all-reduce), ``"one_shot"``,
+            ``"two_shot"``.
+        store_all: push each tile to every rank (``store`` / ``reduce``).
+        c_cols / col_off_per_rank: width of the output buffer and column offset per rank (all-scatter:
+            ``c_cols = world * N``, ``col_off_per_rank = N``).
+        ag: run the all-gather prologue (A rows sharded M / world per rank; see ``a_full``).
+    """
+
+    def __init__(self, ctxs: Union[Iris, Sequence[Iris]], a: Optional[Sequence[torch.Tensor]],
+                 bt: Sequence[torch.Tensor], mode: str = "store", *, M: Optional[int] = None,
+                 store_all: bool = False, c_cols: Optional[int] = None, col_off_per_rank: int = 0,
+                 out: Optional[Sequence[torch.Tensor]] = None, ag: bool = False, ag_slices: int = 8,
+                 ctas_per_rank: Optional[int] = None, group_m: int = 8, timeout_ms: float = 2000.0):
+        self.ctxs: List[Iris] = [ctxs] if isinstance(ctxs, Iris) else list(ctxs)
+        c0 = self.ctxs[0]
+        if c0.backend != "cuda":
+            raise RuntimeError("FusedGemm needs a CUDA context (the kernel is sm_100a only)")
+        self.world = c0.get_num_ranks()
+        self.num_local = len(self.ctxs)
+        if self.num_local != 1 and self.num_local != self.world:
+            raise ValueError("pass one context, or all members of a local world")
+        if mode not in MODES:
+            raise ValueError(f"mode must be one of {sorted(MODES)}")
+        self.mode = mode
+        self.rank0 = c0.get_rank()
+        bt = [as_kmajor_bt(x) for x in bt]
+        for x in bt:
+            _check_operand(x, "B")
+        self.N, self.K = bt[0].shape
+        self.ag = bool(ag)
+        if mode in ("one_shot", "two_shot") and ag:
+            raise ValueError("the all-gather prologue is combined with mode='store' only")
+        if self.ag:
+            if M is None:
+                raise ValueError("ag=True needs M (rows of the gathered A)")
+            self.M = int(M)
+            # gathered A lives on the heap: peers write their rows into it
+            self.a_full = [c.zeros((self.M, self.K), dtype=torch.bfloat16) for c in self.ctxs]
+            a_use = self.a_full
+        else:
+            a_use = list(a)
+            for x in a_use:
+                _check_operand(x, "A")
+            self.M = a_use[0].shape[0]
+            if a_use[0].shape[1] != self.K:
+                raise ValueError(f"K mismatch: A has {a_use[0].shape[1]}, B has {self.K}")
+        self.a, self.bt = a_use, bt
+        dev = c0.device
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        self.ctas_per_rank = int(ctas_per_rank) if ctas_per_rank else sms // self.num_local
+        tiles_m, tiles_n = -(-self.M // BM), -(-self.N // BN)
+        self.total_tiles = tiles_m * tiles_n
+        self.ctas_per_rank = max(1, min(self.ctas_per_rank, max(self.total_tiles, 1 if not self.ag else 8)))
+        self.store_all = bool(store_all) and self.world > 1
+        pulls = mode in ("one_shot", "two_shot")
+        tiles_per_shard = (self.M // self.world) // BM if self.ag else 0
+        nflags = FLAG_HEADER + (self.total_tiles if pulls else 0) + self.world * tiles_per_shard
+        # ---- symmetric allocations (identical sequence on every rank) ----
+        self.flags = [c.zeros(nflags, dtype=torch.int32) for c in self.ctxs]
+        self.c_cols = int(c_cols) if c_cols else self.N
+        if pulls:
+            self.partial = [[c.zeros((self.M, self.N), dtype=torch.bfloat16) for c in self.ctxs] for _ in range(2)]
+            self.out = list(out) if out is not None else [c.zeros((self.M, self.N), dtype=torch.bfloat16)
+                                                          for c in self.ctxs]
+            c_bufs, c2_bufs = self.partial[0], self.partial[1]
+            ldc, c_cols_eff = self.N, self.N
+        else:
+            self.out = list(out) if out is not None else [c.zeros((self.M, self.c_cols), dtype=torch.bfloat16)
+                                                          for c in self.ctxs]
+            c_bufs, c2_bufs = self.out, None
+            ldc, c_cols_eff = self.out[0].stride(0), self.c_cols
+        for o in self.out:
+            _check_operand(o, "output")
+        d = _Desc()
+        for l, ctx in enumerate(self.ctxs):
+            d.a_ptr[l], d.lda[l] = a_use[l].data_ptr(), a_use[l].stride(0)
+            d.b_ptr[l], d.ldb[l] = bt[l].data_ptr(), bt[l].stride(0)
+        for t in range(self.world):
+            d.heap_base[t] = c0.heap_base(t)
+        if pulls or self.store_all:
+            # buffers that peers touch are named by their symmetric offset
+            c_off = c0.offset_of(c_bufs[0])
+            c2_off = c0.offset_of(c2_bufs[0]) if c2_bufs else 0
+            for t in range(self.world):
+                d.c_ptr[t] = c0.heap_base(t) + c_off
+                d.c2_ptr[t] = c0.heap_base(t) + c2_off if c2_bufs else 0
+        else:
+            # output stays on the computing rank: any device buffer will do
+            c_off = c2_off = 0
+            for l in range(self.num_local):
+                d.c_ptr[self.rank0 + l] = c_bufs[l].data_ptr()
+        d.ldc, d.c_cols = ldc, c_cols_eff
+        d.flags_off = c0.offset_of(self.flags[0])
+        d.partial_off[0] = c_off if pulls else 0
+        d.partial_off[1] = c2_off if pulls else 0
+        d.out_off = c0.offset_of(self.out[0]) if pulls else 0
+        d.status_off = c0.offset_of(c0.status)
+        d.agsrc_off = c0.offset_of(self.a_full[0]) if self.ag else 0
+        d.timeout_ns = int(timeout_ms * 1e6)
+        d.M, d.N, d.K = self.M, self.N, self.K
+        d.ldo = self.out[0].stride(0)
+        d.col_off_per_rank = int(col_off_per_rank)
+        d.world, d.num_local, d.rank0, d.ctas_per_rank = self.world, self.num_local, self.rank0, self.ctas_per_rank
+        d.mode, d.group_m, d.ag, d.ag_slices = MODES[mode], int(group_m), int(self.ag), int(ag_slices)
+        d.store_all = int(self.store_all)
+        d.tile_flag_base = FLAG_HEADER
+        d.ag_flag_base = FLAG_HEADER + (self.total_tiles if pulls else 0)
+        d.device = c0.gpu_id
+        self.ag_slices = int(ag_slices)
+        lib = _lib()
+        self._plan = lib.iris_gemm_plan_create(ctypes.byref(d))
+        if not self._plan:
+            raise RuntimeError("fused GEMM plan: " + lib.iris_gemm_last_error().decode())
+        self.calls = 0
+        self.launches = 0
+
+    # every rank of a real multi-process world must call this the same number of times
+    def __call__(self, stream=None) -> List[torch.Tensor]:
+        c0 = self.ctxs[0]
+        st = torch.cuda.current_stream(c0.device).cuda_stream if stream is None else stream
+        if self.mode == "reduce":
+            for o in self.out[:self.num_local]:
+                o.zero_()  # partial sums are added into the output: it has to start at zero
+            self.launches += self.num_local
+        self.calls += 1
+        per_flag = self.world if self.mode in ("one_shot", "two_shot") else self.ag_slices
+        rc = _lib().iris_gemm_plan_launch(self._plan, self.calls & 1, self.calls & 0xFFFFFFFF,
+                                          (per_flag * self.calls) & 0xFFFFFFFF,
+                                          (self.calls * self.world * self.ctas_per_rank) & 0xFFFFFFFF,
+                                          ctypes.c_void_p(st))
+        if rc != 0:
+            raise RuntimeError("fused GEMM launch: " + _lib().iris_gemm_last_error().decode())
+        self.launches += 1
+        return self.out
+
+    def check(self) -> None:
+        """Synchronise and raise if a bounded wait of the last calls expired."""
+        torch.cuda.synchronize(self.ctxs[0].device)
+        for c in self.ctxs:
+            c.check_status()
+
+    def close(self) -> None:
+        if getattr(self, "_plan", None):
+            _lib().iris_gemm_plan_destroy(self._plan)
+            self._plan = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+# --------------------------------------------------------------------------------------------------
+# convenience constructors for the named workloads
+# --------------------------------------------------------------------------------------------------
+def gemm_all_scatter(ctxs, a, bt, **kw) -> FusedGemm:
+    """``C[M, world * N] = A @ [B_0 | B_1 | ...]``: every rank computes its column block and pushes each
+    finished tile into the C of every rank (``examples/07_gemm_all_scatter``)."""
+    lst = [ctxs] if isinstance(ctxs, Iris) else list(ctxs)
+    world = lst[0].get_num_ranks()
+    n = as_kmajor_bt(bt[0]).shape[0]
+    return FusedGemm(ctxs, a, bt, "store", store_all=True, c_cols=world * n, col_off_per_rank=n, **kw)
+
+
+def gemm_all_reduce(ctxs, a, bt, variant: str = "one_shot", **kw) -> FusedGemm:
+    """``C[M, N] = sum over ranks of A_r @ B_r`` (K sharded).  ``variant``: ``"atomic"``
+    (``examples/08_gemm_atomics_all_reduce``), ``"one_shot"`` (``examples/09_gemm_one_shot_all_reduce``) or
+    ``"two_shot"`` (each tile summed by one owner rank and pushed: the bandwidth-optimal extra)."""
+    if variant == "atomic":
+        return FusedGemm(ctxs, a, bt, "reduce", store_all=True, **kw)
+    if variant in ("one_shot", "two_shot"):
+        return FusedGemm(ctxs, a, bt, variant, **kw)
+    raise ValueError("variant must be 'atomic', 'one_shot' or 'two_shot'")
+
+
+def all_gather_gemm(ctxs, M: int, bt, **kw) -> FusedGemm:
+    """``C_r[M, N_r] = all_gather(A rows) @ B_r``: peers' rows are pushed into ``op.a_full`` by the kernel's
+    communication warps while the tiles of rows already present are computed (no counterpart in the reference)."""
+    return FusedGemm(ctxs, None, bt, "store", M=M, ag=True, **kw)
+
+
+_private_ctx = {}
+
+
+def matmul(a: torch.Tensor, bt: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Single-GPU ``a @ bt.T`` on the tcgen05 kernel (world of one, no communication)."""
+    dev = a.device
+    ctx = _private_ctx.get(dev)
+    if ctx is None:
+        with torch.cuda.device(dev):
+            ctx = Iris.local_world(1, heap_size=1 << 20, backend="cuda", device=dev.index)[0]
+        _private_ctx[dev] = ctx
+    n = as_kmajor_bt(bt).shape[0]
+    if out is None:
+        out = torch.empty((a.shape[0], n), dtype=torch.bfloat16, device=dev)
+    op = FusedGemm(ctx, [a], [bt], "store", out=[out])
+    op()
+    op.close()
+    return out

@@ -1,0 +1,124 @@
+"""Host-side control plane: rank discovery, all-gather of small byte strings, scalar broadcast, barrier.
+
+Role in the reference: ``iris/_mpi_helpers.py:8-51`` (mpi4py: ``init_mpi``, ``mpi_allgather``,
+``mpi_broadcast_scalar``, ``world_barrier``).  Neither ``mpirun`` nor ``mpi4py`` is assumed here: ranks are
+ordinary processes started by ``torchrun`` or by :mod:`iris_b200.launch`, and they meet through a
+``torch.distributed`` *gloo* group (TCP on 127.0.0.1).  Data never moves through this plane; it only carries
+handles, base addresses and barriers.
+"""
+from __future__ import annotations
+
+import datetime
+import os
+import pickle
+from typing import Any, List, Optional
+
+import torch
+import torch.distributed as dist
+
+
+class BootstrapError(RuntimeError):
+    pass
+
+
+class Bootstrap:
+    """Interface of a control-plane back end."""
+
+    rank: int = 0
+    world: int = 1
+
+    def allgather_bytes(self, payload: bytes) -> List[bytes]:
+        raise NotImplementedError
+
+    def broadcast_object(self, obj: Any, root: int) -> Any:
+        raise NotImplementedError
+
+    def barrier(self, timeout_s: Optional[float] = None) -> None:
+        raise NotImplementedError
+
+    def local_rank(self) -> int:
+        return int(os.environ.get("LOCAL_RANK", self.rank))
+
+
+class SingleBootstrap(Bootstrap):
+    """World of one process (no launcher)."""
+
+    def allgather_bytes(self, payload: bytes) -> List[bytes]:
+        return [bytes(payload)]
+
+    def broadcast_object(self, obj: Any, root: int) -> Any:
+        if root != 0:
+            raise BootstrapError(f"root {root} does not exist in a world of 1")
+        return obj
+
+    def barrier(self, timeout_s: Optional[float] = None) -> None:
+        return None
+
+
+class TorchDistBootstrap(Bootstrap):
+    """Control plane over a gloo process group.
+
+    When the default group is NCCL-only a gloo group over the same ranks is created once, so that
+    handle exchange and host barriers never touch the GPUs.
+    """
+
+    def __init__(self, timeout_s: float = 120.0):
+        if not dist.is_initialized():
+            raise BootstrapError("torch.distributed is not initialised")
+        self.rank = dist.get_rank()
+        self.world = dist.get_world_size()
+        self._timeout = datetime.timedelta(seconds=timeout_s)
+        backend = str(dist.get_backend())
+        if "gloo" in backend:
+            self._group = dist.group.WORLD
+        else:
+            self._group = dist.new_group(backend="gloo", timeout=self._timeout)
+
+    def allgather_bytes(self, payload: bytes) -> List[bytes]:
+        out: List[Any] = [None] * self.world
+        dist.all_gather_object(out, bytes(payload), group=self._group)
+        return out
+
+    def broadcast_object(self, obj: Any, root: int) -> Any:
+        if not 0 <= root < self.world:
+            raise BootstrapError(f"root {root} outside world of {self.world}")
+        box = [obj if self.rank == root else None]
+        dist.broadcast_object_list(box, src=root, group=self._group)
+        return box[0]
+
+    def barrier(self, timeout_s: Optional[float] = None) -> None:
+        if timeout_s is None:
+            dist.barrier(group=self._group)
+            return
+        try:
+            dist.monitored_barrier(group=self._group, timeout=datetime.timedelta(seconds=timeout_s))
+        except RuntimeError as e:  # a rank did not arrive in time
+            raise BootstrapError(f"barrier timed out after {timeout_s} s on rank {self.rank}: {e}") from e
+
+
+def init_from_env(timeout_s: float = 120.0) -> Bootstrap:
+    """Pick the back end from the environment.
+
+    * ``torch.distributed`` already initialised → use it.
+    * ``RANK`` and ``WORLD_SIZE`` set (torchrun / iris_b200.launch) → initialise a process group
+      (gloo for CPU tensors, NCCL for CUDA tensors when a GPU is present) on ``MASTER_ADDR`` (default
+      127.0.0.1) and use it.
+    * otherwise → a world of one.
+    """
+    if dist.is_available() and dist.is_initialized():
+        return TorchDistBootstrap(timeout_s)
+    if "RANK" in os.environ and "WORLD_SIZE" in os.environ and int(os.environ["WORLD_SIZE"]) > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29533")
+        backend = "cpu:gloo,cuda:nccl" if torch.cuda.is_available() else "gloo"
+        dist.init_process_group(backend=backend, timeout=datetime.timedelta(seconds=timeout_s))
+        return TorchDistBootstrap(timeout_s)
+    return SingleBootstrap()
+
+
+def dumps(obj: Any) -> bytes:
+    return pickle.dumps(obj, protocol=4)
+
+
+def loads(b: bytes) -> Any:
+    return pickle.loads(b)

@@ -1,0 +1,55 @@
+"""Multi-process CPU tests: ranks are child processes meeting over gloo on 127.0.0.1; heaps are POSIX shared
+memory mapped by every rank.  These stand in for ``mpirun -np N pytest tests/unittests`` of the reference."""
+import os
+
+import pytest
+
+from conftest import run_ranks
+
+W = os.path.join(os.path.dirname(__file__), "workers")
+
+
+def _ok(code, outs):
+    assert code == 0, "\n".join(o or "" for o in outs)
+
+
+def test_cpu_plumbing_two_ranks():
+    code, outs = run_ranks(2, [os.path.join(W, "cpu_plumbing.py")])
+    _ok(code, outs)
+    assert all("OK" in o for o in outs)
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_unit_semantics_all_ranks(world):
+    code, outs = run_ranks(world, [os.path.join(W, "cpu_unit_all_ranks.py")], timeout_s=180)
+    _ok(code, outs)
+
+
+def test_message_passing_release_acquire():
+    code, outs = run_ranks(2, [os.path.join(W, "cpu_faults.py"), "message_passing"])
+    _ok(code, outs)
+
+
+def test_heap_size_mismatch_detected():
+    code, outs = run_ranks(2, [os.path.join(W, "cpu_faults.py"), "heap_size_mismatch"])
+    _ok(code, outs)
+    assert all("ValueError" in o for o in outs)
+
+
+def test_missing_rank_times_out_instead_of_hanging():
+    code, outs = run_ranks(2, [os.path.join(W, "cpu_faults.py"), "missing_rank_at_barrier"], timeout_s=60)
+    _ok(code, outs)
+    assert "BootstrapError" in outs[0]
+
+
+def test_flag_never_set_returns_status():
+    code, outs = run_ranks(2, [os.path.join(W, "cpu_faults.py"), "flag_never_set"])
+    _ok(code, outs)
+    assert all("IrisTimeoutError" in o for o in outs)
+
+
+def test_launcher_propagates_failure(tmp_path):
+    bad = tmp_path / "bad.py"
+    bad.write_text("import os, sys, time\nif os.environ['RANK'] == '1':\n    sys.exit(3)\ntime.sleep(30)\n")
+    code, _ = run_ranks(2, [str(bad)], timeout_s=20)
+    assert code == 3

@@ -1,0 +1,117 @@
+"""tcgen05 GEMM and the fused GEMM + collective kernels against a plain PyTorch fp32 reference.
+
+Multi-rank cases run as ONE cooperative launch over ranks simulated on a single GPU
+(``Iris.local_world``): the per-tile flags, entry flags, pushes and pulls go through the same code as between
+GPUs, only the transport is local.  Acceptance mirrors the reference's ``validate_gemm``
+(``examples/common/validation.py:7-23``) but with a tolerance that fits bf16 outputs instead of ``atol=1..2``.
+"""
+import pytest
+import torch
+
+import iris_b200 as iris
+from iris_b200.ops import gemm as G
+
+pytestmark = pytest.mark.gpu
+
+if not torch.cuda.is_available():
+    pytest.skip("needs a CUDA device", allow_module_level=True)
+
+
+def _rand(shape, seed, scale=1.0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(shape, generator=g, device="cuda", dtype=torch.float32) * scale).to(torch.bfloat16)
+
+
+def _assert_close(got, ref_fp32, scale=None, ulps=2.0):
+    """Element-wise bound: `ulps` bf16 roundings (2^-8 relative each) of `scale`, the magnitude the rounding acts
+    on: |ref| for a plain GEMM, the sum of the partials' magnitudes when bf16 partials are added up."""
+    ref = ref_fp32.float()
+    scale = ref.abs() if scale is None else scale
+    tol = ulps * (2.0 ** -8) * scale + 1e-3 * ref.abs().max().item() + 1e-6
+    err = (got.float() - ref).abs()
+    bad = err > tol
+    assert not bool(bad.any()), f"{int(bad.sum())} mismatches, max err {err.max().item():.4g}"
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (256, 512, 256), (384, 768, 192), (1000, 520, 1376),
+                                   (2048, 1792, 4096), (1, 4096, 1376)])
+def test_plain_gemm(m, n, k):
+    a, bt = _rand((m, k), 1), _rand((n, k), 2, 0.05)
+    out = G.matmul(a, bt)
+    torch.cuda.synchronize()
+    _assert_close(out, a.float() @ bt.float().t())
+
+
+def test_gemm_strided_views():
+    # K-shards taken as views: row pitch larger than K, base offset inside the row
+    big_a, big_b = _rand((512, 4096), 3), _rand((768, 4096), 4, 0.05)
+    a, bt = big_a[:, 1376:2752], big_b[:, 1376:2752]
+    out = G.matmul(a, bt)
+    torch.cuda.synchronize()
+    _assert_close(out, a.float() @ bt.float().t())
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_gemm_all_scatter_emulated(world):
+    m, n_local, k = 512, 512, 512
+    ranks = iris.Iris.local_world(world, heap_size=64 << 20)
+    a = _rand((m, k), 5)
+    bts = [_rand((n_local, k), 10 + r, 0.05) for r in range(world)]
+    op = G.gemm_all_scatter(ranks, [a] * world, bts)
+    for _ in range(3):  # cumulative flags must keep working call after call
+        outs = op()
+    op.check()
+    ref = torch.cat([a.float() @ b.float().t() for b in bts], dim=1)
+    for r in range(world):
+        _assert_close(outs[r], ref)
+    op.close()
+    ranks[0].close()
+
+
+@pytest.mark.parametrize("variant", ["atomic", "one_shot", "two_shot"])
+@pytest.mark.parametrize("world", [2, 4])
+def test_gemm_all_reduce_emulated(variant, world):
+    m, n, k_full = 384, 768, 2752
+    ks = k_full // world
+    ranks = iris.Iris.local_world(world, heap_size=64 << 20)
+    a_full, b_full = _rand((m, k_full), 6), _rand((n, k_full), 7, 0.05)
+    a = [a_full[:, r * ks:(r + 1) * ks] for r in range(world)]       # views: pitch k_full
+    bt = [b_full[:, r * ks:(r + 1) * ks] for r in range(world)]
+    op = G.gemm_all_reduce(ranks, a, bt, variant=variant)
+    for _ in range(3):
+        outs = op()
+    op.check()
+    parts = [a[r].float() @ bt[r].float().t() for r in range(world)]
+    ref = sum(parts)
+    scale = sum(p.abs() for p in parts)
+    for r in range(world):
+        _assert_close(outs[r], ref, scale=scale, ulps=2.0 + world)
+    op.close()
+    ranks[0].close()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_all_gather_gemm_emulated(world):
+    m, n_local, k = 1024, 256, 512
+    ms = m // world
+    ranks = iris.Iris.local_world(world, heap_size=64 << 20)
+    a_full = _rand((m, k), 8)
+    bts = [_rand((n_local, k), 20 + r, 0.05) for r in range(world)]
+    op = G.all_gather_gemm(ranks, m, bts, ag_slices=4)
+    for call in range(2):
+        for r in range(world):  # every rank owns only its rows; the kernel gathers the rest
+            op.a_full[r].zero_()
+            op.a_full[r][r * ms:(r + 1) * ms].copy_(a_full[r * ms:(r + 1) * ms])
+        outs = op()
+        op.check()
+        for r in range(world):
+            assert torch.equal(op.a_full[r], a_full), f"gathered A differs on rank {r}"
+            _assert_close(outs[r], a_full.float() @ bts[r].float().t())
+    op.close()
+    ranks[0].close()
+
+
+def test_plan_rejects_bad_shapes():
+    a, bt = _rand((128, 60), 1), _rand((256, 60), 2)
+    with pytest.raises((RuntimeError, ValueError)):
+        G.matmul(a, bt)

@@ -739,3 +739,144 @@ int iris_gemm_plan_launch(void* h, int parity, uint32_t epoch, uint32_t flag_tar
 }
 
 }  // extern "C"
+
+// ================================================================================================
+// Entry point that allocates nothing (declared and documented in gemm_noalloc.h; no counterpart in the
+// reference).  The kernel's scratch is this file-scope device array.  In host code the name `g_noalloc_scratch`
+// is only a handle for the runtime's symbol table, NOT a device address: the address the kernel needs is
+// obtained once per device with cudaGetSymbolAddress below.
+// ================================================================================================
+#include "gemm_noalloc.h"
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[IRIS_GEMM_NOALLOC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kNoAllocMaxDevices = 64;
+constexpr uint64_t kNoAllocStatusOff = 0;      // iris::StatusBlock (256 bytes reserved)
+constexpr uint64_t kNoAllocFlagsOff = 256;     // uint32[16 + max tiles]
+constexpr uint64_t kNoAllocPartialOff = IRIS_GEMM_NOALLOC_HEADER_BYTES;  // bf16 [M, N], 256-byte aligned
+static_assert(IRIS_GEMM_NOALLOC_HEADER_BYTES % 256 == 0, "partial matrix must stay 256-byte aligned");
+
+struct NoAllocDevice {
+  bool ready = false;
+  unsigned char* scratch = nullptr;  // device address of g_noalloc_scratch on this device
+  int sms = 0;
+};
+NoAllocDevice g_noalloc_dev[kNoAllocMaxDevices];
+std::mutex g_noalloc_mutex;
+
+// Once per device, with that device current.
+int noalloc_setup(int dev) {
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  NoAllocDevice& d = g_noalloc_dev[dev];
+  if (d.ready) return 0;
+  void* ptr = nullptr;
+  cudaError_t e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+  if (e != cudaSuccess || ptr == nullptr) {
+    snprintf(iris::gemm::g_err, sizeof(iris::gemm::g_err), "cudaGetSymbolAddress(scratch): %s", cudaGetErrorString(e));
+    return -3;
+  }
+  e = cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(fused_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+  if (e != cudaSuccess) {
+    snprintf(iris::gemm::g_err, sizeof(iris::gemm::g_err), "no-alloc set-up: %s", cudaGetErrorString(e));
+    return -3;
+  }
+  d.scratch = static_cast<unsigned char*>(ptr);
+  d.ready = true;
+  return 0;
+}
+}  // namespace
+
+extern "C" {
+
+int iris_gemm_noalloc(const void* a, int64_t lda, const void* bt, int64_t ldb, void* out, int64_t ldo, int M, int N,
+                      int K, void* stream) {
+  char* err = iris::gemm::g_err;
+  const size_t errn = sizeof(iris::gemm::g_err);
+  err[0] = 0;
+  if (!a || !bt || !out || M < 1 || N < 1 || K < 1 || N % 8 != 0 || K % 8 != 0) {
+    snprintf(err, errn, "iris_gemm_noalloc: need non-null buffers, positive sizes, N and K multiples of 8");
+    return -1;
+  }
+  if (reinterpret_cast<uintptr_t>(out) % 16 != 0 || (ldo * 2) % 16 != 0 || ldo < N) {
+    snprintf(err, errn, "iris_gemm_noalloc: output must be 16-byte aligned with a pitch of at least N elements");
+    return -1;
+  }
+  const long long tiles = (long long)((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  if ((unsigned long long)M * (unsigned long long)N > IRIS_GEMM_NOALLOC_MAX_ELEMS ||
+      tiles > IRIS_GEMM_NOALLOC_MAX_TILES) {
+    snprintf(err, errn,
+             "iris_gemm_noalloc: M*N = %lld (%lld tiles) exceeds the built-in scratch (max %u elements, %d tiles); "
+             "use the plan-based entry points for larger problems",
+             (long long)M * N, tiles, IRIS_GEMM_NOALLOC_MAX_ELEMS, IRIS_GEMM_NOALLOC_MAX_TILES);
+    return -2;
+  }
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kNoAllocMaxDevices) {
+    snprintf(err, errn, "iris_gemm_noalloc: no current CUDA device");
+    return -3;
+  }
+  if (!g_noalloc_dev[dev].ready) {
+    const int rc = noalloc_setup(dev);
+    if (rc != 0) return rc;
+  }
+  const NoAllocDevice& d = g_noalloc_dev[dev];
+  const uint64_t base = reinterpret_cast<uint64_t>(d.scratch);
+
+  // Parameters live on the host stack; nothing is allocated.
+  FusedGemmParams p;
+  memset(&p, 0, sizeof(p));
+  if (encode_2d(&p.tmA[0], reinterpret_cast<uint64_t>(a), M, K, lda, BK, BM, "A") ||
+      encode_2d(&p.tmB[0], reinterpret_cast<uint64_t>(bt), N, K, ldb, BK, BN, "B") ||
+      encode_2d(&p.tmC[0], base + kNoAllocPartialOff, M, N, N, kEpiCols, BM, "scratch partial"))
+    return -1;
+  p.heap_base[0] = base;                // "heap" of the single rank = the scratch array
+  p.flags_off = kNoAllocFlagsOff;
+  p.partial_off = kNoAllocPartialOff;
+  p.out_off = reinterpret_cast<uint64_t>(out) - base;  // the output is addressed relative to the same base
+  p.status_off = kNoAllocStatusOff;
+  p.timeout_ns = 2000000000ull;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.ldo = (int)ldo;
+  p.world = 1;
+  p.num_local = 1;
+  p.rank0 = 0;
+  p.ctas_per_rank = (int)(tiles < d.sms ? tiles : d.sms);
+  p.mode = kEpiOneShot;
+  p.group_m = 8;
+  p.tile_flag_base = 16;
+  p.ag_flag_base = 16;
+  p.epoch = 1;
+  p.flag_target = 1;  // one rank raises each tile's flag once; the flags are cleared just below
+  p.done_target = 0;
+
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // The scratch keeps the previous call's flags and status: clear what has to start at zero, in stream order.
+  cudaError_t e = cudaMemsetAsync(d.scratch, 0, kNoAllocPartialOff, st);
+  if (e == cudaSuccess) {
+    fused_gemm_kernel<<<p.ctas_per_rank, kThreads, kSmemBytes, st>>>(p);
+    e = cudaGetLastError();
+  }
+  if (e != cudaSuccess) {
+    snprintf(err, errn, "iris_gemm_noalloc: %s", cudaGetErrorString(e));
+    return -3;
+  }
+  return 0;
+}
+
+int iris_gemm_noalloc_status(void) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kNoAllocMaxDevices || !g_noalloc_dev[dev].ready) return 0;
+  if (cudaDeviceSynchronize() != cudaSuccess) return -3;
+  uint32_t code = 0;
+  if (cudaMemcpy(&code, g_noalloc_dev[dev].scratch + kNoAllocStatusOff, sizeof(code), cudaMemcpyDeviceToHost) !=
+      cudaSuccess)
+    return -3;
+  return (int)code;
+}
+
+}  // extern "C"

@@ -68,10 +68,10 @@ class TorchDistBootstrap(Bootstrap):
         self.rank = dist.get_rank()
         self.world = dist.get_world_size()
         self._timeout = datetime.timedelta(seconds=timeout_s)
-        backend = str(dist.get_backend())
-        if "gloo" in backend:
+        if str(dist.get_backend()) == "gloo":
             self._group = dist.group.WORLD
         else:
+            # NCCL-only or mixed default group: keep the control plane off the GPUs
             self._group = dist.new_group(backend="gloo", timeout=self._timeout)
 
     def allgather_bytes(self, payload: bytes) -> List[bytes]:

@@ -1,0 +1,133 @@
+"""Driver shared by the fused GEMM + collective examples 07 / 08 / 09.
+
+Role in the reference: ``examples/07_gemm_all_scatter/benchmark.py:24-299`` and its two copies (argument parsing,
+operand set-up with a fixed seed, sharding, validation against ``A @ B``, timing, JSON).  Differences: time is
+taken on the device around the fused launch only (plus the output clear the atomic variant needs), ranks are
+aligned by a barrier before every iteration, and the figure reported is the maximum over ranks; the unfused
+cuBLAS + NCCL time for the same shape is measured next to it; the roofline fraction is printed.
+"""
+from __future__ import annotations
+
+import argparse
+
+from .harness import iris, reduce_ranks, time_kernel_ms, torch
+from iris_b200.ops import gemm as G
+from iris_b200.utils import roofline
+from iris_b200.utils.results import JSONWriter
+
+
+def parse_args(kind: str):
+    d = {"all_scatter": dict(m=8192, n=14336, k=4096), "atomic": dict(m=8192, n=4096, k=11008),
+         "one_shot": dict(m=8192, n=4096, k=11008)}[kind]
+    ap = argparse.ArgumentParser(description=f"Fused GEMM + {kind}", formatter_class=argparse.ArgumentDefaultsHelpFormatter)
+    ap.add_argument("-m", type=int, default=d["m"])
+    ap.add_argument("-n", type=int, default=d["n"])
+    ap.add_argument("-k", type=int, default=d["k"])
+    ap.add_argument("-d", "--debug", action="store_true")
+    ap.add_argument("-v", "--validate", action="store_true")
+    ap.add_argument("-t", "--trace_tiles", action="store_true", help="accepted; per-tile traces are not recorded yet")
+    ap.add_argument("-b", "--benchmark", action="store_true")
+    ap.add_argument("--datatype", default="bf16", choices=["bf16"])
+    ap.add_argument("--output_file", default="")
+    ap.add_argument("--gsize_m", type=int, default=8, help="m-tiles per raster group")
+    ap.add_argument("--heap_size", type=int, default=1 << 31)
+    ap.add_argument("--gemm_sms", type=int, default=0, help="CTAs of the persistent grid (0: one per SM)")
+    ap.add_argument("--variant", default=None, help="all-reduce only: atomic | one_shot | two_shot")
+    ap.add_argument("--num_experiments", type=int, default=50)
+    ap.add_argument("--num_warmup", type=int, default=10)
+    ap.add_argument("--no_baseline", action="store_true")
+    # knobs of the reference that have no meaning on this hardware are accepted and ignored
+    for flag in ("--BLK_M", "--BLK_N", "--BLK_K", "--num_stages", "--num_warps", "--waves_per_eu", "--mfmaInstrSize",
+                 "--kpack", "--total_sms"):
+        ap.add_argument(flag, type=int, default=None, help=argparse.SUPPRESS)
+    ap.add_argument("--two_tiles", default="True", help=argparse.SUPPRESS)
+    ap.add_argument("--algorithm", default=None, help=argparse.SUPPRESS)
+    return vars(ap.parse_args())
+
+
+def run(kind: str, seed: int):
+    args = parse_args(kind)
+    ctx = iris.iris(args["heap_size"])
+    rank, world = ctx.get_rank(), ctx.get_num_ranks()
+    dev = ctx.get_device()
+    m, n, k = args["m"], args["n"], args["k"]
+    gen = torch.Generator(device=dev).manual_seed(seed)  # same seed everywhere -> identical A and B
+    A = (torch.randn((m, k), generator=gen, device=dev) * 0.02).to(torch.bfloat16)
+    Bt = (torch.randn((n, k), generator=gen, device=dev) * 0.02).to(torch.bfloat16)  # B = Bt.T, K-major
+    ctas = args["gemm_sms"] or None
+    peaks = roofline.load_peaks()
+    import torch.distributed as dist
+    if kind == "all_scatter":
+        if n % world:
+            raise SystemExit("N must be divisible by the number of ranks")
+        nl = n // world
+        bt_local = Bt[rank * nl:(rank + 1) * nl].contiguous()
+        op = G.gemm_all_scatter(ctx, [A], [bt_local], ctas_per_rank=ctas, group_m=args["gsize_m"])
+        roof = roofline.all_scatter_roofline_us(m, n, k, world, peaks)
+        c_part = torch.empty((m, nl), dtype=torch.bfloat16, device=dev)
+        gathered = torch.empty((world, m, nl), dtype=torch.bfloat16, device=dev)
+
+        def unfused():
+            torch.matmul(A, bt_local.t(), out=c_part)
+            if world > 1:
+                dist.all_gather_into_tensor(gathered, c_part)
+        a_local, b_local = A, bt_local
+        variant = "all_scatter"
+    else:
+        variant = args["variant"] or kind
+        if k % world or (k // world) % 8:
+            raise SystemExit("K / ranks must be a multiple of 8")
+        ks = k // world
+        a_local, b_local = A[:, rank * ks:(rank + 1) * ks], Bt[:, rank * ks:(rank + 1) * ks]  # views, pitch k
+        op = G.gemm_all_reduce(ctx, [a_local], [b_local], variant=variant, ctas_per_rank=ctas, group_m=args["gsize_m"])
+        roof = roofline.all_reduce_roofline_us(m, n, k, world, peaks,
+                                               "two_shot" if variant == "two_shot" else "one_shot")
+        c_part = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+
+        def unfused():
+            torch.matmul(a_local, b_local.t(), out=c_part)
+            if world > 1:
+                dist.all_reduce(c_part)
+    js = JSONWriter(args["output_file"] if rank == 0 else "")
+    fields = {k_: v for k_, v in args.items() if v is not None}
+    fields.update(world_size=world, variant=variant, gemm_sms=op.ctas_per_rank, tile="128x256x64")
+    js.add_fields(**fields)
+    ctx.barrier()
+    out = op()[0]
+    ctx.barrier()
+    op.check()
+    ok = True
+    if args["validate"]:
+        rows = slice(0, min(m, 1024))
+        ref = A[rows].float() @ Bt.float().t()
+        # bf16 rounding of the result and (all-reduce) of the partials, relative to the largest entry
+        err = (out[rows].float() - ref).abs().max().item()
+        ok = err <= (2.0 + world) * 2.0 ** -8 * ref.abs().max().item()
+        ctx.log(f"Validation {'successful' if ok else 'FAILED'}.")
+        js.add_field("success", ok)
+    if args["benchmark"]:
+        ms = time_kernel_ms(ctx, lambda: op(), args["num_warmup"], args["num_experiments"])
+        ms = reduce_ranks(ctx, ms, "max")
+        op.check()
+        flops = 2.0 * m * n * k
+        tflops = flops / (ms * 1e-3) / 1e12
+        frac = roof["target_us"] / (ms * 1e3)
+        js.add_fields(fused_ms=ms, fused_tflops=tflops, roofline_us=roof["target_us"], roofline_bound=roof["bound"],
+                      roofline_fraction=frac, peaks=peaks.source)
+        line = (f"{variant} W={world} M={m} N={n} K={k}: fused {ms * 1e3:.1f} us = {tflops:.1f} TFLOPS, "
+                f"roofline {roof['target_us']:.0f} us ({roof['bound']}-bound) -> {100 * frac:.0f}% of {peaks.source}")
+        if not args["no_baseline"]:
+            if world > 1 and not dist.is_initialized():
+                raise SystemExit("baseline needs torch.distributed")
+            bms = reduce_ranks(ctx, time_kernel_ms(ctx, unfused, args["num_warmup"], args["num_experiments"]), "max")
+            js.add_fields(baseline_ms=bms, baseline_tflops=flops / (bms * 1e-3) / 1e12, speedup=bms / ms)
+            line += f" | cuBLAS+NCCL {bms * 1e3:.1f} us -> speed-up {bms / ms:.2f}x"
+        if rank == 0:
+            print(line, flush=True)
+    if rank == 0:
+        js.flush()
+    op.close()
+    ctx.barrier()
+    ctx.close()
+    if not ok:
+        raise SystemExit(1)

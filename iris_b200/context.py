@@ -482,6 +482,12 @@ class Iris:
                     lib.iris_cpu_heap_unlink(name.encode())
         except Exception:  # teardown must not mask the error that led here
             pass
+        finally:
+            if self._local_world is None:
+                try:
+                    self.comm.shutdown()
+                except Exception:
+                    pass
 
     def __enter__(self):
         return self

@@ -110,20 +110,37 @@ __device__ __forceinline__ void acc_bf16x8(float* acc, uint4 v) {
   }
 }
 
+// Per-CTA-group configuration.  CG = 1: one CTA per 128 x 256 tile.  CG = 2: a pair of CTAs (one cluster on the
+// two SMs of a TPC) per 256 x 256 tile; each CTA loads its own 128 rows of A and its own 128 of the 256 B rows,
+// one thread of the leader CTA issues cta_group::2 MMAs that read both CTAs' shared memory, and each CTA ends up
+// with its 128 x 256 half of the accumulator in its own tensor memory.  Loads stay per-CTA (no multicast).
+template <int CG>
+struct Cfg {
+  static constexpr int kStages = CG == 1 ? 4 : 6;
+  static constexpr int kBRows = BN / CG;
+  static constexpr int kBStage = kBRows * BK * 2;
+  static constexpr int kStage = kAStageBytes + kBStage;
+  static constexpr int kTilesBytes = kStages * kStage + kEpiBufs * kEpiStageBytes;
+  static_assert(kTilesBytes <= kSmemTiles, "shared-memory budget");
+};
+
+template <int CG>
 __global__ void __launch_bounds__(kThreads, 1) fused_gemm_kernel(const __grid_constant__ FusedGemmParams p) {
+  using C = Cfg<CG>;
+  constexpr int kStages = C::kStages;
   extern __shared__ uint8_t smem_raw[];
-  // 128-byte-swizzled tiles need 1024-byte alignment.
+  // 128-byte-swizzled tiles need 1024-byte alignment (identical offsets in both CTAs of a pair).
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t smem_base = smem_u32(smem);
-  const uint32_t epi_base = smem_base + kStages * kStageBytes;
+  const uint32_t epi_base = smem_base + kStages * C::kStage;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kSmemTiles);
   const uint32_t bar_base = smem_u32(bars);
-  // barrier slots: full[kStages], empty[kStages], acc_full[kAccBufs], acc_empty[kAccBufs]
+  // barrier slots: full[6], empty[6], acc_full[2], acc_empty[2]
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
-  auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
-  auto acc_full_bar = [&](int b) { return bar_base + 8u * (2 * kStages + b); };
-  auto acc_empty_bar = [&](int b) { return bar_base + 8u * (2 * kStages + kAccBufs + b); };
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * kStages + 2 * kAccBufs);
+  auto empty_bar = [&](int s) { return bar_base + 8u * (6 + s); };
+  auto acc_full_bar = [&](int b) { return bar_base + 8u * (12 + b); };
+  auto acc_empty_bar = [&](int b) { return bar_base + 8u * (14 + b); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 16);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   volatile uint32_t* epi_ok = tmem_slot + 2;
 
@@ -131,16 +148,21 @@ __global__ void __launch_bounds__(kThreads, 1) fused_gemm_kernel(const __grid_co
   const int lane = threadIdx.x & 31;
   const int lr = blockIdx.x / p.ctas_per_rank;   // local rank index
   const int cta = blockIdx.x - lr * p.ctas_per_rank;
-  const int G = p.ctas_per_rank;
+  const int pr = (CG == 2) ? (int)cluster_ctarank() : 0;  // position in the CTA pair; 0 = leader
+  const bool leader = pr == 0;
+  const int unit = cta / CG;                      // tile-scheduling unit (CTA or CTA pair) within the rank
+  const int G = p.ctas_per_rank / CG;
   const int rank = p.rank0 + lr;
   const int W = p.world;
   StatusBlock* status = status_ptr(p, rank);
 
-  const int tiles_m = (p.M + BM - 1) / BM;
+  constexpr int TM = BM * CG;                     // rows of a scheduling unit's tile
+  const int tiles_m = (p.M + TM - 1) / TM;
   const int tiles_n = (p.N + BN - 1) / BN;
   const int total_tiles = tiles_m * tiles_n;
   const int kblocks = (p.K + BK - 1) / BK;
-  const int tiles_per_shard = p.ag ? (p.M / W) / BM : 0;
+  const int tiles_per_shard = p.ag ? (p.M / W) / TM : 0;
+  const int chunks_per_shard = p.ag ? (p.M / W) / BM : 0;  // all-gather flags are per 128 rows
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -149,7 +171,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_gemm_kernel(const __grid_co
     }
     for (int b = 0; b < kAccBufs; ++b) {
       mbar_init(acc_full_bar(b), 1);
-      mbar_init(acc_empty_bar(b), 4);  // one arrival per epilogue warp
+      mbar_init(acc_empty_bar(b), 4 * CG);  // one arrival per epilogue warp of every CTA of the group
     }
     *abort_flag = 0;
     *epi_ok = 1;
@@ -158,11 +180,17 @@ __global__ void __launch_bounds__(kThreads, 1) fused_gemm_kernel(const __grid_co
     prefetch_tensormap(&p.tmB[lr]);
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
-    tmem_relinquish();
+    if (CG == 1) {
+      tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
+      tmem_relinquish();
+    } else {
+      tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
+      tmem_relinquish_pair();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (CG == 2) cluster_sync_all();  // the partner's barriers exist before anything arrives on them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -177,20 +205,22 @@ __global__ void __launch_bounds__(kThreads, 1) fused_gemm_kernel(const __grid_co
 
   if (warp == 0) {
     // ------------------------------------------------------------------------------------------
-    // TMA producer
+    // TMA producer (every CTA loads its own A rows and its own share of the B rows)
     // ------------------------------------------------------------------------------------------
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = cta; tile < total_tiles && ok; tile += G) {
+      for (int tile = unit; tile < total_tiles && ok; tile += G) {
         TileCoord tc = raster(tile, tiles_m, tiles_n, p.group_m);
-        if (p.ag) {
-          tc.m_idx = ag_actual_m(tc.m_idx, tiles_per_shard, rank, W);
-          const int src = tc.m_idx / tiles_per_shard;
+        if (p.ag) tc.m_idx = ag_actual_m(tc.m_idx, tiles_per_shard, rank, W);
+        const int row0 = tc.m_idx * TM + pr * BM;
+        if (p.ag && row0 < p.M) {
+          const int Ms = p.M / W;
+          const int src = row0 / Ms;
           if (src != rank) {
-            const int chunk = tc.m_idx - src * tiles_per_shard;
-            const uint32_t* f = flag_ptr(p, rank, p.ag_flag_base + src * tiles_per_shard + chunk);
+            const int chunk = (row0 - src * Ms) / BM;
+            const uint32_t* f = flag_ptr(p, rank, p.ag_flag_base + src * chunks_per_shard + chunk);
             if (wait_until_ge(f, p.flag_target, p.timeout_ns, status, kSiteProducerAgFlag, rank, tile) != kOk) {
               *abort_flag = 1;
               ok = false;
@@ -206,11 +236,19 @@ __global__ void __launch_bounds__(kThreads, 1) fused_gemm_kernel(const __grid_co
             ok = false;
             break;
           }
-          const uint32_t a_dst = smem_base + stage * kStageBytes;
+          const uint32_t a_dst = smem_base + stage * C::kStage;
           const uint32_t b_dst = a_dst + kAStageBytes;
-          mbar_expect_tx(full_bar(stage), kStageBytes);
-          tma_load_2d(a_dst, &p.tmA[lr], kb * BK, tc.m_idx * BM, full_bar(stage));
-          tma_load_2d(b_dst, &p.tmB[lr], kb * BK, tc.n_idx * BN, full_bar(stage));
+          if (CG == 1) {
+            mbar_expect_tx(full_bar(stage), C::kStage);
+            tma_load_2d(a_dst, &p.tmA[lr], kb * BK, row0, full_bar(stage));
+            tma_load_2d(b_dst, &p.tmB[lr], kb * BK, tc.n_idx * BN, full_bar(stage));
+          } else {
+            // Both CTAs' bytes are counted on the leader's barrier, which the leader arms for the pair.
+            const uint32_t lead_full = mapa_shared(full_bar(stage), 0);
+            if (leader) mbar_expect_tx(full_bar(stage), 2 * C::kStage);
+            tma_load_2d_pair(a_dst, &p.tmA[lr], kb * BK, row0, lead_full);
+            tma_load_2d_pair(b_dst, &p.tmB[lr], kb * BK, tc.n_idx * BN + pr * C::kBRows, lead_full);
+          }
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1;
@@ -220,16 +258,16 @@ __global__ void __launch_bounds__(kThreads, 1) fused_gemm_kernel(const __grid_co
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------------------------------
-    // MMA issuer
+    // MMA issuer (one thread; with CTA pairs only the leader's)
     // ------------------------------------------------------------------------------------------
-    if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_f16(BM, BN, true);
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = umma_idesc_f16(TM, BN, true);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int tile = cta; tile < total_tiles && ok; tile += G) {
+      for (int tile = unit; tile < total_tiles && ok; tile += G) {
         if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1, p.timeout_ns, abort_flag)) {
           record_status(status, kTimeout, kSiteMmaAccEmpty, rank, tile, acc);
           *abort_flag = 1;
@@ -245,22 +283,34 @@ __global__ void __launch_bounds__(kThreads, 1) fused_gemm_kernel(const __grid_co
             break;
           }
           tc_fence_after();
-          const uint32_t a_addr = smem_base + stage * kStageBytes;
+          const uint32_t a_addr = smem_base + stage * C::kStage;
           const uint32_t b_addr = a_addr + kAStageBytes;
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint64_t a_desc = umma_desc_k_sw128(a_addr + k * UMMA_K * 2);
             const uint64_t b_desc = umma_desc_k_sw128(b_addr + k * UMMA_K * 2);
-            umma_f16_ss(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0 ? 1u : 0u);
+            if (CG == 1) umma_f16_ss(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0 ? 1u : 0u);
+            else umma_f16_ss_pair(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0 ? 1u : 0u);
           }
-          umma_commit(empty_bar(stage));  // frees the ring slot once these MMAs have read it
+          // Free the ring slot (in both CTAs of a pair) once these MMAs have read it.
+          if (CG == 1) {
+            umma_commit(empty_bar(stage));
+          } else {
+            umma_commit_pair(mapa_shared(empty_bar(stage), 0));
+            umma_commit_pair(mapa_shared(empty_bar(stage), 1));
+          }
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1;
           }
         }
         if (!ok) break;
-        umma_commit(acc_full_bar(acc));  // accumulator complete
+        if (CG == 1) {
+          umma_commit(acc_full_bar(acc));  // accumulator complete
+        } else {
+          umma_commit_pair(mapa_shared(acc_full_bar(acc), 0));
+          umma_commit_pair(mapa_shared(acc_full_bar(acc), 1));
+        }
         if (++acc == kAccBufs) {
           acc = 0;
           acc_phase ^= 1;
@@ -269,7 +319,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_gemm_kernel(const __grid_co
     }
   } else if (warp < 6) {
     // ------------------------------------------------------------------------------------------
-    // Epilogue (128 threads)
+    // Epilogue (128 threads): this CTA's 128 x 256 part of the tile
     // ------------------------------------------------------------------------------------------
     const int et = threadIdx.x - 64;
     const bool issuer = (et == 0);
@@ -284,11 +334,11 @@ __global__ void __launch_bounds__(kThreads, 1) fused_gemm_kernel(const __grid_co
     int prev_tile = -1;
     bool entered = !need_entry;
 
-    // Sum tile `t` over all ranks' partial buffers and write the result (one-/two-shot modes).
+    // Sum this CTA's part of tile `t` over all ranks' partial buffers and write the result (one-/two-shot).
     auto pull_reduce = [&](int t) -> bool {
       if (p.mode == kEpiTwoShot && (t % W) != rank) return true;
       if (issuer) {
-        const uint32_t* f = flag_ptr(p, rank, p.tile_flag_base + t);
+        const uint32_t* f = flag_ptr(p, rank, p.tile_flag_base + t * CG + pr);
         *epi_ok = wait_until_ge(f, p.flag_target, p.timeout_ns, status, kSiteEpiTileFlag, rank, t) == kOk ? 1u : 0u;
       }
       named_barrier_sync(1, 128);
@@ -296,7 +346,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_gemm_kernel(const __grid_co
       named_barrier_sync(1, 128);
       if (!ok) return false;
       const TileCoord tc = raster(t, tiles_m, tiles_n, p.group_m);
-      const int m0 = tc.m_idx * BM, n0 = tc.n_idx * BN;
+      const int m0 = tc.m_idx * TM + pr * BM, n0 = tc.n_idx * BN;
       // 128 rows x 32 vectors of 8 bf16; a warp covers one 512-byte row segment per step.
       for (int i = 0; i < (BM * BN / 8) / 128; i += 2) {
         uint4 v[2][kMaxRanks];
@@ -339,7 +389,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_gemm_kernel(const __grid_co
     };
 
     bool ok_all = true;
-    for (int tile = cta; tile < total_tiles; tile += G) {
+    for (int tile = unit; tile < total_tiles; tile += G) {
       TileCoord tc = raster(tile, tiles_m, tiles_n, p.group_m);
       if (p.ag) tc.m_idx = ag_actual_m(tc.m_idx, tiles_per_shard, rank, W);
       // Uniform decision for the whole epilogue group: one thread waits, everybody reads the verdict.
@@ -366,20 +416,23 @@ __global__ void __launch_bounds__(kThreads, 1) fused_gemm_kernel(const __grid_co
       tc_fence_after();
 
       const int x_base = (pulls ? 0 : rank * p.col_off_per_rank) + tc.n_idx * BN;
-      const int y = tc.m_idx * BM;
+      const int y = tc.m_idx * TM + pr * BM;
 #pragma unroll 1
       for (int c = 0; c < BN / kEpiCols; ++c) {
-        const bool live = tc.n_idx * BN + c * kEpiCols < p.N;  // sub-tiles past the matrix edge are skipped
+        const bool live = tc.n_idx * BN + c * kEpiCols < p.N && y < p.M;  // parts past the matrix edge are skipped
         uint32_t v[kEpiCols];
         const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN + c * kEpiCols;
         tmem_ld_32x32b_x32(taddr, v);
         tmem_ld_32x32b_x32(taddr + 32, v + 32);
         tmem_wait_ld();
         if (c == BN / kEpiCols - 1) {
-          // The accumulator has been read completely: hand it back to the MMA warp.
+          // The accumulator has been read completely: hand it back to the MMA warp (of the leader CTA).
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(acc_empty_bar(acc));
+          if (lane == 0) {
+            if (CG == 1) mbar_arrive(acc_empty_bar(acc));
+            else mbar_arrive_cluster(mapa_shared(acc_empty_bar(acc), 0));
+          }
         }
         if (!live) continue;  // uniform over the group
         // The staging buffer was last used two sub-tiles ago: its TMA reads must have finished.
@@ -427,7 +480,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_gemm_kernel(const __grid_co
           for (int i = 0; i < W; ++i) {
             const int t = (rank + 1 + i) % W;
             if (p.mode == kEpiTwoShot && t != tile % W) continue;  // only the tile's owner needs to know
-            red_release_sys_add(flag_ptr(p, t, p.tile_flag_base + tile), 1u);
+            red_release_sys_add(flag_ptr(p, t, p.tile_flag_base + tile * CG + pr), 1u);
           }
         }
         if (prev_tile >= 0 && !pull_reduce(prev_tile)) {
@@ -468,10 +521,10 @@ __global__ void __launch_bounds__(kThreads, 1) fused_gemm_kernel(const __grid_co
       const int S = p.ag_slices;
       const int slice_elems = p.K / S;             // multiple of 8 (checked on the host)
       const int vec_per_row = slice_elems / 8;     // 16-byte vectors per row of a slice
-      const int items = (W - 1) * tiles_per_shard * S;
-      for (int item = cta; item < items; item += G) {
-        const int pi = item / (tiles_per_shard * S);           // peer-major: finish one peer's copy first
-        const int rem = item - pi * (tiles_per_shard * S);
+      const int items = (W - 1) * chunks_per_shard * S;
+      for (int item = cta; item < items; item += p.ctas_per_rank) {
+        const int pi = item / (chunks_per_shard * S);          // peer-major: finish one peer's copy first
+        const int rem = item - pi * (chunks_per_shard * S);
         const int chunk = rem / S;
         const int slice = rem - chunk * S;
         const int peer = (rank - 1 - pi + 2 * W) % W;           // the peer that needs these rows earliest
@@ -501,7 +554,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_gemm_kernel(const __grid_co
         }
         fence_sys();
         named_barrier_sync(2, 64);
-        if (ct == 0) red_release_sys_add(flag_ptr(p, peer, p.ag_flag_base + rank * tiles_per_shard + chunk), 1u);
+        if (ct == 0) red_release_sys_add(flag_ptr(p, peer, p.ag_flag_base + rank * chunks_per_shard + chunk), 1u);
       }
     }
   }
@@ -515,9 +568,11 @@ __global__ void __launch_bounds__(kThreads, 1) fused_gemm_kernel(const __grid_co
   }
   tc_fence_before();
   __syncthreads();
+  if (CG == 2) cluster_sync_all();  // neither CTA of a pair leaves while the other may still touch its memory
   if (warp == 1) {
     __syncwarp();
-    tmem_dealloc(tmem_base, 512);
+    if (CG == 1) tmem_dealloc(tmem_base, 512);
+    else tmem_dealloc_pair(tmem_base, 512);
   }
 }
 
@@ -605,6 +660,7 @@ struct IrisGemmDesc {
   int mode, group_m, ag, ag_slices, store_all;
   int tile_flag_base, ag_flag_base;
   int device;
+  int cta_group;  // 1: one CTA per 128 x 256 tile; 2: a CTA pair (cluster of 2) per 256 x 256 tile
 };
 
 struct IrisGemmPlan {
@@ -612,6 +668,8 @@ struct IrisGemmPlan {
   int grid;
   int cooperative;
   int device;
+  int cta_group;
+  int ctas_per_rank;
 };
 
 const char* iris_gemm_last_error() { return g_err; }
@@ -636,9 +694,10 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
     snprintf(g_err, sizeof(g_err), "N per rank must be a multiple of %d when tiles are pushed to peers", kEpiCols);
     return nullptr;
   }
+  const int cg = d->cta_group == 2 ? 2 : 1;
   if (d->ag) {
-    if (d->M % d->world != 0 || (d->M / d->world) % BM != 0) {
-      snprintf(g_err, sizeof(g_err), "all-gather prologue needs M / world to be a multiple of %d", BM);
+    if (d->M % d->world != 0 || (d->M / d->world) % (BM * cg) != 0) {
+      snprintf(g_err, sizeof(g_err), "all-gather prologue needs M / world to be a multiple of %d", BM * cg);
       return nullptr;
     }
     if (d->ag_slices < 1 || d->K % d->ag_slices != 0 || (d->K / d->ag_slices) % 8 != 0) {
@@ -649,8 +708,42 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
   cudaSetDevice(d->device);
   int sms = 0;
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, d->device);
-  const int grid = d->ctas_per_rank * d->num_local;
-  if (d->ctas_per_rank < 1 || (sms > 0 && grid > sms)) {
+  int ctas_per_rank = d->ctas_per_rank - d->ctas_per_rank % cg;
+  {
+    cudaError_t e = cudaFuncSetAttribute(cg == 2 ? fused_gemm_kernel<2> : fused_gemm_kernel<1>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) {
+      snprintf(g_err, sizeof(g_err), "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+      return nullptr;
+    }
+  }
+  if (cg == 2) {
+    // All CTA pairs must be resident at once: ask how many clusters of 2 the device can hold.
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(ctas_per_rank * d->num_local);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = kSmemBytes;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int max_clusters = 0;
+    cudaError_t e = cudaOccupancyMaxActiveClusters(&max_clusters, fused_gemm_kernel<2>, &cfg);
+    if (e != cudaSuccess || max_clusters < d->num_local) {
+      snprintf(g_err, sizeof(g_err), "CTA pairs cannot be scheduled (%s, %d clusters)", cudaGetErrorString(e),
+               max_clusters);
+      (void)cudaGetLastError();
+      return nullptr;
+    }
+    const int per_rank = 2 * (max_clusters / d->num_local);
+    if (ctas_per_rank > per_rank) ctas_per_rank = per_rank;
+  }
+  const int grid = ctas_per_rank * d->num_local;
+  if (ctas_per_rank < 1 || (sms > 0 && grid > sms)) {
     snprintf(g_err, sizeof(g_err), "grid of %d CTAs does not fit %d SMs (all CTAs must be resident)", grid, sms);
     return nullptr;
   }
@@ -660,11 +753,13 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
   plan->grid = grid;
   plan->cooperative = d->num_local > 1;
   plan->device = d->device;
+  plan->cta_group = cg;
+  plan->ctas_per_rank = ctas_per_rank;
   for (int par = 0; par < 2; ++par) {
     FusedGemmParams& p = plan->params[par];
     for (int l = 0; l < d->num_local; ++l) {
       if (encode_2d(&p.tmA[l], d->a_ptr[l], d->M, d->K, d->lda[l], BK, BM, "A") ||
-          encode_2d(&p.tmB[l], d->b_ptr[l], d->N, d->K, d->ldb[l], BK, BN, "B")) {
+          encode_2d(&p.tmB[l], d->b_ptr[l], d->N, d->K, d->ldb[l], BK, BN / cg, "B")) {
         delete plan;
         return nullptr;
       }
@@ -693,7 +788,7 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
     p.world = d->world;
     p.num_local = d->num_local;
     p.rank0 = d->rank0;
-    p.ctas_per_rank = d->ctas_per_rank;
+    p.ctas_per_rank = ctas_per_rank;
     p.mode = d->mode;
     p.group_m = d->group_m < 1 ? 1 : d->group_m;
     p.ag = d->ag;
@@ -702,16 +797,14 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
     p.tile_flag_base = d->tile_flag_base;
     p.ag_flag_base = d->ag_flag_base;
   }
-  cudaError_t e = cudaFuncSetAttribute(fused_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-  if (e != cudaSuccess) {
-    snprintf(g_err, sizeof(g_err), "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    delete plan;
-    return nullptr;
-  }
   return plan;
 }
 
 void iris_gemm_plan_destroy(void* h) { delete static_cast<IrisGemmPlan*>(h); }
+
+// What the plan settled on: CTAs per rank (the done counter advances by world * this per call) and CTA group.
+int iris_gemm_plan_ctas_per_rank(void* h) { return static_cast<IrisGemmPlan*>(h)->ctas_per_rank; }
+int iris_gemm_plan_cta_group(void* h) { return static_cast<IrisGemmPlan*>(h)->cta_group; }
 
 // Launch one call.  `parity` selects the partial-buffer set; epoch / flag_target / done_target are the
 // cumulative values this call drives the flags to (kept by the caller).
@@ -723,12 +816,38 @@ int iris_gemm_plan_launch(void* h, int parity, uint32_t epoch, uint32_t flag_tar
   p.flag_target = flag_target;
   p.done_target = done_target;
   cudaError_t e;
-  if (plan->cooperative) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (plan->cta_group == 2) {
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(plan->grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = kSmemBytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeCooperative;
+    attr[1].val.cooperative = 1;
+    cfg.attrs = attr;
+    // Ranks simulated on one GPU wait on one another: ask for a cooperative launch on top of the clusters.
+    cfg.numAttrs = plan->cooperative ? 2 : 1;
+    e = cudaLaunchKernelEx(&cfg, fused_gemm_kernel<2>, p);
+    if (e != cudaSuccess && plan->cooperative) {
+      // Cooperative + cluster launches are not accepted everywhere; the grid was sized by
+      // cudaOccupancyMaxActiveClusters, so all pairs are resident on an otherwise idle GPU.
+      (void)cudaGetLastError();
+      cfg.numAttrs = 1;
+      e = cudaLaunchKernelEx(&cfg, fused_gemm_kernel<2>, p);
+    }
+  } else if (plan->cooperative) {
     void* args[] = {&p};
-    e = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(fused_gemm_kernel), dim3(plan->grid), dim3(kThreads),
-                                    args, kSmemBytes, static_cast<cudaStream_t>(stream));
+    e = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(fused_gemm_kernel<1>), dim3(plan->grid), dim3(kThreads),
+                                    args, kSmemBytes, st);
   } else {
-    fused_gemm_kernel<<<plan->grid, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(p);
+    fused_gemm_kernel<1><<<plan->grid, kThreads, kSmemBytes, st>>>(p);
     e = cudaGetLastError();
   }
   if (e != cudaSuccess) {
@@ -778,7 +897,7 @@ int noalloc_setup(int dev) {
   }
   e = cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev);
   if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(fused_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    e = cudaFuncSetAttribute(fused_gemm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
   if (e != cudaSuccess) {
     snprintf(iris::gemm::g_err, sizeof(iris::gemm::g_err), "no-alloc set-up: %s", cudaGetErrorString(e));
     return -3;
@@ -858,7 +977,7 @@ int iris_gemm_noalloc(const void* a, int64_t lda, const void* bt, int64_t ldb, v
   // The scratch keeps the previous call's flags and status: clear what has to start at zero, in stream order.
   cudaError_t e = cudaMemsetAsync(d.scratch, 0, kNoAllocPartialOff, st);
   if (e == cudaSuccess) {
-    fused_gemm_kernel<<<p.ctas_per_rank, kThreads, kSmemBytes, st>>>(p);
+    fused_gemm_kernel<1><<<p.ctas_per_rank, kThreads, kSmemBytes, st>>>(p);
     e = cudaGetLastError();
   }
   if (e != cudaSuccess) {

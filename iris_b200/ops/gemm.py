@@ -44,7 +44,7 @@ class _Desc(ctypes.Structure):
         ("world", ctypes.c_int), ("num_local", ctypes.c_int), ("rank0", ctypes.c_int), ("ctas_per_rank", ctypes.c_int),
         ("mode", ctypes.c_int), ("group_m", ctypes.c_int), ("ag", ctypes.c_int), ("ag_slices", ctypes.c_int),
         ("store_all", ctypes.c_int), ("tile_flag_base", ctypes.c_int), ("ag_flag_base", ctypes.c_int),
-        ("device", ctypes.c_int),
+        ("device", ctypes.c_int), ("cta_group", ctypes.c_int),
     ]
 
 
@@ -55,6 +55,8 @@ def _lib():
         lib.iris_gemm_plan_create.restype = ctypes.c_void_p
         lib.iris_gemm_plan_create.argtypes = [ctypes.POINTER(_Desc)]
         lib.iris_gemm_plan_destroy.argtypes = [ctypes.c_void_p]
+        lib.iris_gemm_plan_ctas_per_rank.argtypes = [ctypes.c_void_p]
+        lib.iris_gemm_plan_cta_group.argtypes = [ctypes.c_void_p]
         lib.iris_gemm_plan_launch.restype = ctypes.c_int
         lib.iris_gemm_plan_launch.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_uint32, ctypes.c_uint32,
                                               ctypes.c_uint32, ctypes.c_void_p]
@@ -104,7 +106,8 @@ class FusedGemm:
                  bt: Sequence[torch.Tensor], mode: str = "store", *, M: Optional[int] = None,
                  store_all: bool = False, c_cols: Optional[int] = None, col_off_per_rank: int = 0,
                  out: Optional[Sequence[torch.Tensor]] = None, ag: bool = False, ag_slices: int = 8,
-                 ctas_per_rank: Optional[int] = None, group_m: int = 8, timeout_ms: float = 2000.0):
+                 ctas_per_rank: Optional[int] = None, group_m: int = 8, timeout_ms: float = 2000.0,
+                 cta_group: Optional[int] = None):
         self.ctxs: List[Iris] = [ctxs] if isinstance(ctxs, Iris) else list(ctxs)
         c0 = self.ctxs[0]
         if c0.backend != "cuda":
@@ -141,14 +144,23 @@ class FusedGemm:
         self.a, self.bt = a_use, bt
         dev = c0.device
         sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        # CTA pairs (256 x 256 tiles, cta_group::2) for anything taller than one 128-row tile; single CTAs else
+        if cta_group is None:
+            cta_group = 2 if self.M > BM and (not self.ag or (self.M // self.world) % (2 * BM) == 0) else 1
+        if cta_group not in (1, 2):
+            raise ValueError("cta_group must be 1 or 2")
+        self.cta_group = cta_group
         self.ctas_per_rank = int(ctas_per_rank) if ctas_per_rank else sms // self.num_local
-        tiles_m, tiles_n = -(-self.M // BM), -(-self.N // BN)
+        tiles_m, tiles_n = -(-self.M // (BM * cta_group)), -(-self.N // BN)
         self.total_tiles = tiles_m * tiles_n
-        self.ctas_per_rank = max(1, min(self.ctas_per_rank, max(self.total_tiles, 1 if not self.ag else 8)))
+        self.ctas_per_rank = max(cta_group, min(self.ctas_per_rank,
+                                                 cta_group * max(self.total_tiles, 1 if not self.ag else 8)))
+        self.ctas_per_rank -= self.ctas_per_rank % cta_group
         self.store_all = bool(store_all) and self.world > 1
         pulls = mode in ("one_shot", "two_shot")
-        tiles_per_shard = (self.M // self.world) // BM if self.ag else 0
-        nflags = FLAG_HEADER + (self.total_tiles if pulls else 0) + self.world * tiles_per_shard
+        chunks_per_shard = (self.M // self.world) // BM if self.ag else 0
+        tile_flags = self.total_tiles * cta_group if pulls else 0
+        nflags = FLAG_HEADER + tile_flags + self.world * chunks_per_shard
         # ---- symmetric allocations (identical sequence on every rank) ----
         self.flags = [c.zeros(nflags, dtype=torch.int32) for c in self.ctxs]
         self.c_cols = int(c_cols) if c_cols else self.N
@@ -198,13 +210,15 @@ class FusedGemm:
         d.mode, d.group_m, d.ag, d.ag_slices = MODES[mode], int(group_m), int(self.ag), int(ag_slices)
         d.store_all = int(self.store_all)
         d.tile_flag_base = FLAG_HEADER
-        d.ag_flag_base = FLAG_HEADER + (self.total_tiles if pulls else 0)
+        d.ag_flag_base = FLAG_HEADER + tile_flags
         d.device = c0.gpu_id
+        d.cta_group = cta_group
         self.ag_slices = int(ag_slices)
         lib = _lib()
         self._plan = lib.iris_gemm_plan_create(ctypes.byref(d))
         if not self._plan:
             raise RuntimeError("fused GEMM plan: " + lib.iris_gemm_last_error().decode())
+        self.ctas_per_rank = lib.iris_gemm_plan_ctas_per_rank(self._plan)  # what fits on the device
         self.calls = 0
         self.launches = 0
 
@@ -277,7 +291,8 @@ def all_gather_gemm(ctxs, M: int, bt, **kw) -> FusedGemm:
 _private_ctx = {}
 
 
-def matmul(a: torch.Tensor, bt: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+def matmul(a: torch.Tensor, bt: torch.Tensor, out: Optional[torch.Tensor] = None,
+           cta_group: Optional[int] = None) -> torch.Tensor:
     """Single-GPU ``a @ bt.T`` on the tcgen05 kernel (world of one, no communication)."""
     dev = a.device
     ctx = _private_ctx.get(dev)
@@ -288,7 +303,7 @@ def matmul(a: torch.Tensor, bt: torch.Tensor, out: Optional[torch.Tensor] = None
     n = as_kmajor_bt(bt).shape[0]
     if out is None:
         out = torch.empty((a.shape[0], n), dtype=torch.bfloat16, device=dev)
-    op = FusedGemm(ctx, [a], [bt], "store", out=[out])
+    op = FusedGemm(ctx, [a], [bt], "store", out=[out], cta_group=cta_group)
     op()
     op.close()
     return out

@@ -39,6 +39,9 @@ class Bootstrap:
     def local_rank(self) -> int:
         return int(os.environ.get("LOCAL_RANK", self.rank))
 
+    def shutdown(self) -> None:
+        """Release what the back end created (a process group it initialised itself)."""
+
 
 class SingleBootstrap(Bootstrap):
     """World of one process (no launcher)."""
@@ -62,7 +65,8 @@ class TorchDistBootstrap(Bootstrap):
     handle exchange and host barriers never touch the GPUs.
     """
 
-    def __init__(self, timeout_s: float = 120.0):
+    def __init__(self, timeout_s: float = 120.0, owns_process_group: bool = False):
+        self.owns_process_group = owns_process_group
         if not dist.is_initialized():
             raise BootstrapError("torch.distributed is not initialised")
         self.rank = dist.get_rank()
@@ -96,6 +100,18 @@ class TorchDistBootstrap(Bootstrap):
             raise BootstrapError(f"barrier timed out after {timeout_s} s on rank {self.rank}: {e}") from e
 
 
+def _shutdown_torchdist(self) -> None:
+    if self.owns_process_group and dist.is_initialized():
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
+        self.owns_process_group = False
+
+
+TorchDistBootstrap.shutdown = _shutdown_torchdist
+
+
 def init_from_env(timeout_s: float = 120.0) -> Bootstrap:
     """Pick the back end from the environment.
 
@@ -112,7 +128,7 @@ def init_from_env(timeout_s: float = 120.0) -> Bootstrap:
         os.environ.setdefault("MASTER_PORT", "29533")
         backend = "cpu:gloo,cuda:nccl" if torch.cuda.is_available() else "gloo"
         dist.init_process_group(backend=backend, timeout=datetime.timedelta(seconds=timeout_s))
-        return TorchDistBootstrap(timeout_s)
+        return TorchDistBootstrap(timeout_s, owns_process_group=True)
     return SingleBootstrap()
 
 

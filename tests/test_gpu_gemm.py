@@ -35,9 +35,18 @@ def _assert_close(got, ref_fp32, scale=None, ulps=2.0):
 
 @pytest.mark.parametrize("m,n,k", [(128, 256, 64), (256, 512, 256), (384, 768, 192), (1000, 520, 1376),
                                    (2048, 1792, 4096), (1, 4096, 1376)])
-def test_plain_gemm(m, n, k):
+@pytest.mark.parametrize("cta_group", [1, 2])
+def test_plain_gemm(m, n, k, cta_group):
     a, bt = _rand((m, k), 1), _rand((n, k), 2, 0.05)
-    out = G.matmul(a, bt)
+    out = G.matmul(a, bt, cta_group=cta_group)
+    torch.cuda.synchronize()
+    _assert_close(out, a.float() @ bt.float().t())
+
+
+def test_many_tiles_per_cta_pair():
+    # more tiles than CTA pairs: ring and accumulator phases wrap many times
+    a, bt = _rand((4096, 512), 1), _rand((8192, 512), 2, 0.05)
+    out = G.matmul(a, bt, cta_group=2)
     torch.cuda.synchronize()
     _assert_close(out, a.float() @ bt.float().t())
 
@@ -51,13 +60,14 @@ def test_gemm_strided_views():
     _assert_close(out, a.float() @ bt.float().t())
 
 
+@pytest.mark.parametrize("cta_group", [1, 2])
 @pytest.mark.parametrize("world", [2, 4])
-def test_gemm_all_scatter_emulated(world):
-    m, n_local, k = 512, 512, 512
+def test_gemm_all_scatter_emulated(world, cta_group):
+    m, n_local, k = 1024, 512, 512
     ranks = iris.Iris.local_world(world, heap_size=64 << 20)
     a = _rand((m, k), 5)
     bts = [_rand((n_local, k), 10 + r, 0.05) for r in range(world)]
-    op = G.gemm_all_scatter(ranks, [a] * world, bts)
+    op = G.gemm_all_scatter(ranks, [a] * world, bts, cta_group=cta_group)
     for _ in range(3):  # cumulative flags must keep working call after call
         outs = op()
     op.check()
@@ -69,15 +79,16 @@ def test_gemm_all_scatter_emulated(world):
 
 
 @pytest.mark.parametrize("variant", ["atomic", "one_shot", "two_shot"])
+@pytest.mark.parametrize("cta_group", [1, 2])
 @pytest.mark.parametrize("world", [2, 4])
-def test_gemm_all_reduce_emulated(variant, world):
-    m, n, k_full = 384, 768, 2752
+def test_gemm_all_reduce_emulated(variant, world, cta_group):
+    m, n, k_full = 640, 768, 2752
     ks = k_full // world
     ranks = iris.Iris.local_world(world, heap_size=64 << 20)
     a_full, b_full = _rand((m, k_full), 6), _rand((n, k_full), 7, 0.05)
     a = [a_full[:, r * ks:(r + 1) * ks] for r in range(world)]       # views: pitch k_full
     bt = [b_full[:, r * ks:(r + 1) * ks] for r in range(world)]
-    op = G.gemm_all_reduce(ranks, a, bt, variant=variant)
+    op = G.gemm_all_reduce(ranks, a, bt, variant=variant, cta_group=cta_group)
     for _ in range(3):
         outs = op()
     op.check()
@@ -90,14 +101,15 @@ def test_gemm_all_reduce_emulated(variant, world):
     ranks[0].close()
 
 
+@pytest.mark.parametrize("cta_group", [1, 2])
 @pytest.mark.parametrize("world", [2, 4])
-def test_all_gather_gemm_emulated(world):
-    m, n_local, k = 1024, 256, 512
+def test_all_gather_gemm_emulated(world, cta_group):
+    m, n_local, k = 2048, 256, 512
     ms = m // world
     ranks = iris.Iris.local_world(world, heap_size=64 << 20)
     a_full = _rand((m, k), 8)
     bts = [_rand((n_local, k), 20 + r, 0.05) for r in range(world)]
-    op = G.all_gather_gemm(ranks, m, bts, ag_slices=4)
+    op = G.all_gather_gemm(ranks, m, bts, ag_slices=4, cta_group=cta_group)
     for call in range(2):
         for r in range(world):  # every rank owns only its rows; the kernel gathers the rest
             op.a_full[r].zero_()

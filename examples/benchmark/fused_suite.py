@@ -1,0 +1,164 @@
+#!/usr/bin/env python
+"""One launch that measures every headline number of the repository on N ranks:
+
+* P2P RMA: remote load / store between rank 0 and rank 1 from 4 KB to 1 GB, all-load / all-store plateaus,
+  remote atomic add (fp32) and exchange (int32);
+* GEMM + all-scatter on A[8192, 4096] x B[4096, 14336];
+* GEMM + all-reduce (atomic, one-shot, two-shot) on K = 11008, N = 4096 for M in {1, 128, 1024, 8192};
+
+each fused kernel next to cuBLAS + NCCL on the same operands, device-timed, maximum over ranks, with the roofline
+fraction.  Writes one JSON document (rank 0).  The reference spreads these over separate scripts and SLURM jobs
+(``examples/benchmark/bench_all_shapes.py``, ``examples/benchmark/reference/*.py``).
+
+    python -m iris_b200.launch -np 8 examples/benchmark/fused_suite.py --out gpurun_out/suite_w8.json
+"""
+import argparse
+import json
+import os
+import sys
+
+sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), ".."))
+from common.harness import GIB, device_barrier, iris, reduce_ranks, time_kernel_ms, torch  # noqa: E402
+
+import torch.distributed as dist  # noqa: E402
+
+from iris_b200.ops import gemm as G, p2p  # noqa: E402
+from iris_b200.utils import roofline  # noqa: E402
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--out", default="")
+    ap.add_argument("--reps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--skip_p2p", action="store_true")
+    ap.add_argument("--skip_gemm", action="store_true")
+    ap.add_argument("--max_p2p_bytes", type=int, default=1 << 30)
+    args = ap.parse_args()
+    ctx = iris.iris((3 << 30) + (1 << 29))
+    rank, world = ctx.get_rank(), ctx.get_num_ranks()
+    dev = ctx.get_device()
+    device_barrier(ctx)  # allocated first, so that it survives the heap rewinds below
+    base = ctx.mark()
+    peaks = roofline.load_peaks()
+    res = {"world": world, "peaks": peaks.__dict__, "p2p": {}, "gemm": []}
+    W, R = args.warmup, args.reps
+
+    def log(msg):
+        if rank == 0:
+            print(msg, flush=True)
+
+    # ------------------------------------------------------------------ P2P
+    if not args.skip_p2p and world >= 2:
+        big = ctx.zeros(args.max_p2p_bytes // 4, dtype=torch.int32)
+        loc = ctx.zeros(args.max_p2p_bytes // 4, dtype=torch.int32)
+        sweep = []
+        size = 4096
+        while size <= args.max_p2p_bytes:
+            row = {"bytes": size}
+            for name, fn in (("load", lambda: p2p.load(ctx, big, loc, target=1, nbytes=size)),
+                             ("store", lambda: p2p.store(ctx, big, target=1, nbytes=size))):
+                ms = time_kernel_ms(ctx, fn, 2, 10, active=(rank == 0))
+                row[name + "_gbs"] = ctx.broadcast(size / (ms * 1e-3) / 1e9 if rank == 0 and ms > 0 else 0.0, 0)
+            sweep.append(row)
+            log(f"p2p 0->1 {size:>11d} B  load {row['load_gbs']:8.1f} GB/s  store {row['store_gbs']:8.1f} GB/s")
+            size *= 4 if size < (1 << 20) else 2
+        res["p2p"]["pair_sweep"] = sweep
+        nb = min(args.max_p2p_bytes, 1 << 28)
+        f32 = big.view(torch.float32)
+        for name, fn, moved in (
+                ("all_load", lambda: p2p.all_load(ctx, f32, loc.view(torch.float32), nbytes=nb), (world - 1) * nb),
+                ("all_store", lambda: p2p.all_store(ctx, big, nbytes=nb), (world - 1) * nb)):
+            ms = time_kernel_ms(ctx, fn, 2, 10)
+            bw = moved / (ms * 1e-3) / 1e9
+            lo, hi = reduce_ranks(ctx, bw, "min"), reduce_ranks(ctx, bw, "max")
+            res["p2p"][name] = {"bytes_per_peer": nb, "gbs_per_gpu_min": lo, "gbs_per_gpu_max": hi}
+            log(f"{name}: {lo:.1f} .. {hi:.1f} GB/s per GPU ({nb >> 20} MiB per peer)")
+        na = 1 << 24
+        for name, fn in (("atomic_add_f32", lambda: p2p.atomic_add_f32(ctx, f32, target=1, n=na)),
+                         ("atomic_add_f32_v4", lambda: p2p.atomic_add_f32(ctx, f32, target=1, n=na, vec4=True)),
+                         ("atomic_xchg_i32", lambda: p2p.atomic_xchg_i32(ctx, big, loc, target=1, n=na))):
+            ms = time_kernel_ms(ctx, fn, 2, 10, active=(rank == 0))
+            bw = ctx.broadcast(na * 4 / (ms * 1e-3) / 1e9 if rank == 0 and ms > 0 else 0.0, 0)
+            res["p2p"][name] = {"elements": na, "gbs": bw}
+            log(f"{name} 0->1: {bw:.1f} GB/s")
+        ctx.reset(base)
+
+    # ------------------------------------------------------------------ fused GEMMs
+    def bench_pair(label, op, unfused, flops, roof):
+        ctx.barrier()
+        op()
+        ctx.barrier()
+        op.check()
+        ms = reduce_ranks(ctx, time_kernel_ms(ctx, lambda: op(), W, R, align=True), "max")
+        op.check()
+        bms = reduce_ranks(ctx, time_kernel_ms(ctx, unfused, W, R, align=True), "max")
+        rec = dict(label, world=world, fused_us=ms * 1e3, fused_tflops=flops / (ms * 1e-3) / 1e12,
+                   baseline_us=bms * 1e3, speedup=bms / ms, roofline_us=roof["target_us"], bound=roof["bound"],
+                   roofline_fraction=roof["target_us"] / (ms * 1e3), cta_group=op.cta_group, ctas=op.ctas_per_rank)
+        res["gemm"].append(rec)
+        log(f"{label}: fused {rec['fused_us']:.1f} us ({rec['fused_tflops']:.0f} TF) | cuBLAS+NCCL {rec['baseline_us']:.1f} us "
+            f"| x{rec['speedup']:.2f} | roofline {roof['target_us']:.0f} us ({roof['bound']}) -> {100 * rec['roofline_fraction']:.0f}%")
+
+    if not args.skip_gemm:
+        # config 3: GEMM + all-scatter
+        m, n, k = 8192, 14336, 4096
+        if n % world == 0:
+            gen = torch.Generator(device=dev).manual_seed(2)
+            A = (torch.randn((m, k), generator=gen, device=dev) * 0.02).to(torch.bfloat16)
+            Bt = (torch.randn((n, k), generator=gen, device=dev) * 0.02).to(torch.bfloat16)
+            nl = n // world
+            btl = Bt[rank * nl:(rank + 1) * nl].contiguous()
+            del Bt
+            op = G.gemm_all_scatter(ctx, [A], [btl])
+            c_part = torch.empty((m, nl), dtype=torch.bfloat16, device=dev)
+            gathered = torch.empty((world, m, nl), dtype=torch.bfloat16, device=dev)
+
+            def unfused():
+                torch.matmul(A, btl.t(), out=c_part)
+                if world > 1:
+                    dist.all_gather_into_tensor(gathered, c_part)
+            bench_pair({"workload": "all_scatter", "m": m, "n": n, "k": k}, op, unfused, 2.0 * m * n * k,
+                       roofline.all_scatter_roofline_us(m, n, k, world, peaks))
+            ref = A[:256].float() @ btl.float().t()
+            err = (op.out[0][:256, rank * nl:(rank + 1) * nl].float() - ref).abs().max().item()
+            assert err <= 2 ** -6 * ref.abs().max().item(), f"all_scatter validation failed: {err}"
+            op.close()
+            del A, btl, c_part, gathered
+            ctx.reset(base)
+        # config 4: GEMM + all-reduce
+        n, k = 4096, 11008
+        if k % world == 0 and (k // world) % 8 == 0:
+            ks = k // world
+            gen = torch.Generator(device=dev).manual_seed(3)
+            Bt = (torch.randn((n, k), generator=gen, device=dev) * 0.02).to(torch.bfloat16)
+            for m in (8192, 1024, 128, 1):
+                A = (torch.randn((m, k), generator=gen, device=dev) * 0.02).to(torch.bfloat16)
+                al, bl = A[:, rank * ks:(rank + 1) * ks], Bt[:, rank * ks:(rank + 1) * ks]
+                c_part = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+
+                def unfused():
+                    torch.matmul(al, bl.t(), out=c_part)
+                    if world > 1:
+                        dist.all_reduce(c_part)
+                ref = A[:128].float() @ Bt.float().t()
+                for variant in ("atomic", "one_shot", "two_shot"):
+                    op = G.gemm_all_reduce(ctx, [al], [bl], variant=variant)
+                    bench_pair({"workload": variant, "m": m, "n": n, "k": k}, op, unfused, 2.0 * m * n * k,
+                               roofline.all_reduce_roofline_us(m, n, k, world, peaks,
+                                                               "two_shot" if variant == "two_shot" else "one_shot"))
+                    err = (op.out[0][:128].float() - ref).abs().max().item()
+                    assert err <= (2 + world) * 2 ** -8 * ref.abs().max().item() + 1e-3, f"{variant} m={m}: err {err}"
+                    op.close()
+                    ctx.reset(base)
+                del A, c_part
+    if rank == 0 and args.out:
+        os.makedirs(os.path.dirname(args.out) or ".", exist_ok=True)
+        with open(args.out, "w") as f:
+            json.dump(res, f, indent=2)
+    ctx.barrier()
+    ctx.close()
+
+
+if __name__ == "__main__":
+    main()

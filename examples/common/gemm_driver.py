@@ -106,7 +106,7 @@ def run(kind: str, seed: int):
         ctx.log(f"Validation {'successful' if ok else 'FAILED'}.")
         js.add_field("success", ok)
     if args["benchmark"]:
-        ms = time_kernel_ms(ctx, lambda: op(), args["num_warmup"], args["num_experiments"])
+        ms = time_kernel_ms(ctx, lambda: op(), args["num_warmup"], args["num_experiments"], align=True)
         ms = reduce_ranks(ctx, ms, "max")
         op.check()
         flops = 2.0 * m * n * k
@@ -119,7 +119,7 @@ def run(kind: str, seed: int):
         if not args["no_baseline"]:
             if world > 1 and not dist.is_initialized():
                 raise SystemExit("baseline needs torch.distributed")
-            bms = reduce_ranks(ctx, time_kernel_ms(ctx, unfused, args["num_warmup"], args["num_experiments"]), "max")
+            bms = reduce_ranks(ctx, time_kernel_ms(ctx, unfused, args["num_warmup"], args["num_experiments"], align=True), "max")
             js.add_fields(baseline_ms=bms, baseline_tflops=flops / (bms * 1e-3) / 1e12, speedup=bms / ms)
             line += f" | cuBLAS+NCCL {bms * 1e3:.1f} us -> speed-up {bms / ms:.2f}x"
         if rank == 0:

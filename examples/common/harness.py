@@ -31,13 +31,36 @@ def dtype_from_str(name: str) -> torch.dtype:
     return DTYPES[name]
 
 
-def time_kernel_ms(ctx, fn, n_warmup: int, n_repeat: int, active: bool = True) -> float:
+_device_barriers = {}
+
+
+def device_barrier(ctx):
+    """The context's device-side barrier (created on first use: allocate it before taking a heap mark)."""
+    from iris_b200.ops.p2p import DeviceBarrier
+    if ctx.get_num_ranks() == 1:
+        return None
+    b = _device_barriers.get(id(ctx))
+    if b is None:
+        b = _device_barriers[id(ctx)] = DeviceBarrier(ctx)
+    return b
+
+
+def time_kernel_ms(ctx, fn, n_warmup: int, n_repeat: int, active: bool = True, align: bool = False) -> float:
     """Mean device time of ``fn`` in ms on the ranks where ``active``; every rank takes part in the barriers
-    (``iris/util.py:62-104``: barrier, then event / launch / event, every iteration)."""
+    (``iris/util.py:62-104``: barrier, then event / launch / event, every iteration).  With ``align`` a
+    device-side barrier kernel runs on every rank right before the start event, so the ranks' streams start the
+    timed launch together and host launch skew is not charged to a kernel that waits for its peers."""
+    dbar = device_barrier(ctx) if align else None
     e0 = [torch.cuda.Event(enable_timing=True) for _ in range(n_repeat)]
     e1 = [torch.cuda.Event(enable_timing=True) for _ in range(n_repeat)]
     for i in range(-n_warmup, n_repeat):
         ctx.barrier()
+        if align:
+            # Keep the GPU busy while the host enqueues [barrier, event, launch, event]: otherwise a short kernel is
+            # timed together with the host's launch latency.
+            torch.cuda._sleep(300000)
+        if dbar is not None:
+            dbar()
         if active:
             if i >= 0:
                 e0[i].record()

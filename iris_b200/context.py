@@ -307,9 +307,17 @@ class Iris:
     def deallocate(self, pointer) -> None:
         """No-op, as in the reference: the heap is a bump allocator."""
 
-    def reset(self, keep_status: bool = True) -> None:
-        """Rewind the bump allocator (every rank must do so at the same point of its allocation sequence)."""
-        self.heap_offset = STATUS_BYTES if keep_status else 0
+    def mark(self) -> int:
+        """Current top of the bump allocator; pass it to :meth:`reset` to free everything allocated after it."""
+        return self.heap_offset
+
+    def reset(self, to: Optional[int] = None) -> None:
+        """Rewind the bump allocator to ``to`` (a value from :meth:`mark`; default: just above the status block).
+        Every rank must do so at the same point of its allocation sequence."""
+        to = STATUS_BYTES if to is None else int(to)
+        if not STATUS_BYTES <= to <= self.heap_offset:
+            raise ValueError("reset target is not a mark of this heap")
+        self.heap_offset = to
 
     def parse_size(self, size):
         if len(size) == 1 and isinstance(size[0], (tuple, list, torch.Size)):

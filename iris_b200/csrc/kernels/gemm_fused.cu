@@ -55,6 +55,7 @@ enum Site : uint32_t {
   kSiteEpiAccFull = 30,
   kSiteEpiEntry = 31,
   kSiteEpiTileFlag = 32,
+  kSitePullFull = 33,
   kSiteDone = 40,
 };
 
@@ -93,6 +94,15 @@ __device__ __forceinline__ StatusBlock* status_ptr(const FusedGemmParams& p, int
   return reinterpret_cast<StatusBlock*>(p.heap_base[rank] + p.status_off);
 }
 
+// Per-tile timestamps (the reference's Timestamps arrays, examples/common/utils.py:45-128, filled with
+// atomic_min / atomic_max of s_memrealtime; here one thread per role writes its own slot).
+__device__ __forceinline__ void trace(const FusedGemmParams& p, int rank, int record, int slot) {
+  if (p.trace_off) {
+    uint64_t* t = reinterpret_cast<uint64_t*>(p.heap_base[rank] + p.trace_off);
+    t[(size_t)record * kTrSlots + slot] = timer_ns();
+  }
+}
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -114,33 +124,38 @@ __device__ __forceinline__ void acc_bf16x8(float* acc, uint4 v) {
 // two SMs of a TPC) per 256 x 256 tile; each CTA loads its own 128 rows of A and its own 128 of the 256 B rows,
 // one thread of the leader CTA issues cta_group::2 MMAs that read both CTAs' shared memory, and each CTA ends up
 // with its 128 x 256 half of the accumulator in its own tensor memory.  Loads stay per-CTA (no multicast).
-template <int CG>
+// PULL (one-/two-shot all-reduce): the main ring gives up stages for a ring of 16 KB "pull" buffers into which
+// the partial sub-tiles of all ranks are fetched with TMA loads (a peer's memory included, no multicast).
+template <int CG, bool PULL>
 struct Cfg {
-  static constexpr int kStages = CG == 1 ? 4 : 6;
+  static constexpr int kStages = CG == 1 ? (PULL ? 3 : 4) : (PULL ? 4 : 6);
   static constexpr int kBRows = BN / CG;
   static constexpr int kBStage = kBRows * BK * 2;
   static constexpr int kStage = kAStageBytes + kBStage;
-  static constexpr int kTilesBytes = kStages * kStage + kEpiBufs * kEpiStageBytes;
+  static constexpr int kPullBufs = PULL ? (CG == 1 ? 3 : 4) : 0;
+  static constexpr int kTilesBytes = kStages * kStage + kEpiBufs * kEpiStageBytes + kPullBufs * kEpiStageBytes;
   static_assert(kTilesBytes <= kSmemTiles, "shared-memory budget");
 };
 
-template <int CG>
+template <int CG, bool PULL>
 __global__ void __launch_bounds__(kThreads, 1) fused_gemm_kernel(const __grid_constant__ FusedGemmParams p) {
-  using C = Cfg<CG>;
+  using C = Cfg<CG, PULL>;
   constexpr int kStages = C::kStages;
   extern __shared__ uint8_t smem_raw[];
   // 128-byte-swizzled tiles need 1024-byte alignment (identical offsets in both CTAs of a pair).
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t smem_base = smem_u32(smem);
   const uint32_t epi_base = smem_base + kStages * C::kStage;
+  const uint32_t pull_base = epi_base + kEpiBufs * kEpiStageBytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kSmemTiles);
   const uint32_t bar_base = smem_u32(bars);
-  // barrier slots: full[6], empty[6], acc_full[2], acc_empty[2]
+  // barrier slots: full[6], empty[6], acc_full[2], acc_empty[2], pull_full[4]
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (6 + s); };
   auto acc_full_bar = [&](int b) { return bar_base + 8u * (12 + b); };
   auto acc_empty_bar = [&](int b) { return bar_base + 8u * (14 + b); };
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 16);
+  auto pull_full_bar = [&](int b) { return bar_base + 8u * (16 + b); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 20);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   volatile uint32_t* epi_ok = tmem_slot + 2;
 
@@ -173,6 +188,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_gemm_kernel(const __grid_co
       mbar_init(acc_full_bar(b), 1);
       mbar_init(acc_empty_bar(b), 4 * CG);  // one arrival per epilogue warp of every CTA of the group
     }
+    for (int b = 0; b < C::kPullBufs; ++b) mbar_init(pull_full_bar(b), 1);
     *abort_flag = 0;
     *epi_ok = 1;
     mbar_fence_init();
@@ -274,6 +290,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_gemm_kernel(const __grid_co
           break;
         }
         tc_fence_after();
+        trace(p, rank, tile * CG, kTrMmaBegin);
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < kblocks; ++kb) {
           if (!mbar_wait(full_bar(stage), phase, p.timeout_ns, abort_flag)) {
@@ -305,6 +322,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_gemm_kernel(const __grid_co
           }
         }
         if (!ok) break;
+        trace(p, rank, tile * CG, kTrMmaEnd);  // issue time of the last MMA, not its completion
         if (CG == 1) {
           umma_commit(acc_full_bar(acc));  // accumulator complete
         } else {
@@ -334,58 +352,123 @@ __global__ void __launch_bounds__(kThreads, 1) fused_gemm_kernel(const __grid_co
     int prev_tile = -1;
     bool entered = !need_entry;
 
-    // Sum this CTA's part of tile `t` over all ranks' partial buffers and write the result (one-/two-shot).
+    // Sum this CTA's 128 x 256 part of tile `t` over the partial buffers of all ranks (fp32) and write bf16 to the
+    // output of this rank (one-shot) or of every rank (two-shot).  The part is fetched as 4 x W units of
+    // 128 rows x 64 columns (16 KB): unit u = (column chunk u / W, rank offset u % W) is loaded by TMA into ring
+    // buffer (count % kPullBufs); kPullBufs loads are in flight, so NVLink latency is hidden without registers.
+    uint32_t pull_issued = 0, pull_done = 0;  // units issued / consumed so far by this CTA (ring position)
     auto pull_reduce = [&](int t) -> bool {
-      if (p.mode == kEpiTwoShot && (t % W) != rank) return true;
-      if (issuer) {
-        const uint32_t* f = flag_ptr(p, rank, p.tile_flag_base + t * CG + pr);
-        *epi_ok = wait_until_ge(f, p.flag_target, p.timeout_ns, status, kSiteEpiTileFlag, rank, t) == kOk ? 1u : 0u;
-      }
-      named_barrier_sync(1, 128);
-      const bool ok = *epi_ok != 0;
-      named_barrier_sync(1, 128);
-      if (!ok) return false;
-      const TileCoord tc = raster(t, tiles_m, tiles_n, p.group_m);
-      const int m0 = tc.m_idx * TM + pr * BM, n0 = tc.n_idx * BN;
-      // 128 rows x 32 vectors of 8 bf16; a warp covers one 512-byte row segment per step.
-      for (int i = 0; i < (BM * BN / 8) / 128; i += 2) {
-        uint4 v[2][kMaxRanks];
-        int rr[2], cc[2];
-        bool in[2];
+      if constexpr (!PULL) {
+        return true;
+      } else {
+        if (p.mode == kEpiTwoShot && (t % W) != rank) return true;
+        const TileCoord tc = raster(t, tiles_m, tiles_n, p.group_m);
+        const int m0 = tc.m_idx * TM + pr * BM, n0 = tc.n_idx * BN;
+        const int units = (BN / kEpiCols) * W;
+        auto issue = [&](int u) {  // issuer only
+          const int c = u / W, sft = u - c * W;
+          const uint32_t b = pull_issued % C::kPullBufs;
+          mbar_expect_tx(pull_full_bar(b), kEpiStageBytes);
+          tma_load_2d(pull_base + b * kEpiStageBytes, &p.tmC[(rank + sft) % W], n0 + c * kEpiCols, p.part_row0 + m0,
+                      pull_full_bar(b));
+          ++pull_issued;
+        };
+        if (issuer) {
+          const uint32_t* f = flag_ptr(p, rank, p.tile_flag_base + t * CG + pr);
+          trace(p, rank, t * CG + pr, kTrWaitBegin);
+          bool ok = wait_until_ge(f, p.flag_target, p.timeout_ns, status, kSiteEpiTileFlag, rank, t) == kOk;
+          trace(p, rank, t * CG + pr, kTrWaitEnd);
+          if (ok) {
+            fence_proxy_async_all();  // the flag was acquired with ordinary loads; the data is read by TMA
+            for (int u = 0; u < units && u < C::kPullBufs; ++u) issue(u);
+            ok = mbar_wait(pull_full_bar(pull_done % C::kPullBufs), (pull_done / C::kPullBufs) & 1, p.timeout_ns,
+                           abort_flag);
+            if (!ok) record_status(status, kTimeout, kSitePullFull, rank, t, 0);
+          }
+          *epi_ok = ok ? 1u : 0u;
+        }
+        float accv[kEpiCols];
+        for (int u = 0; u < units; ++u) {
+          named_barrier_sync(1, 128);  // unit u has landed (or the wait failed): verdict is in epi_ok
+          if (*epi_ok == 0) return false;
+          const int c = u / W, sft = u - c * W;
+          const uint32_t buf = pull_base + (pull_done % C::kPullBufs) * kEpiStageBytes + row * 128;
+          if (sft == 0) {
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          const int idx = et + (i + u) * 128;
-          rr[u] = m0 + idx / (BN / 8);
-          cc[u] = n0 + (idx % (BN / 8)) * 8;
-          in[u] = rr[u] < p.M && cc[u] < p.N;
-          if (in[u]) {
-            const uint64_t off = p.partial_off + ((uint64_t)rr[u] * p.N + cc[u]) * 2;
+            for (int j = 0; j < kEpiCols; ++j) accv[j] = 0.f;
+          }
 #pragma unroll
-            for (int s = 0; s < kMaxRanks; ++s)
-              if (s < W) v[u][s] = ld_v4(reinterpret_cast<const uint4*>(p.heap_base[(rank + s) % W] + off));
+          for (int j = 0; j < 8; ++j) {
+            uint4 v;
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                         : "r"(buf + ((j ^ (row & 7)) << 4)));
+            acc_bf16x8(accv + 8 * j, v);
+          }
+          ++pull_done;
+          named_barrier_sync(1, 128);  // every thread has read the buffer: it can be refilled
+          if (issuer) {
+            if (u + C::kPullBufs < units) issue(u + C::kPullBufs);
+            if (u + 1 < units) {
+              const bool ok = mbar_wait(pull_full_bar(pull_done % C::kPullBufs), (pull_done / C::kPullBufs) & 1,
+                                        p.timeout_ns, abort_flag);
+              if (!ok) record_status(status, kTimeout, kSitePullFull, rank, t, u + 1);
+              *epi_ok = ok ? 1u : 0u;
+            }
+          }
+          if (sft == W - 1) {
+            if (p.out_row0 >= 0) {
+              // Result sub-tile -> swizzled staging buffer -> TMA store into the output of this rank (one-shot)
+              // or of every rank (two-shot): full 128-byte rows on the wire instead of 16-byte fragments.
+              if (issuer) bulk_wait_read<kEpiBufs - 1>();
+              named_barrier_sync(1, 128);
+              const uint32_t sbase = epi_base + ebuf * kEpiStageBytes + row * 128;
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                st_shared_v4(sbase + ((j ^ (row & 7)) << 4), pack_bf16x2(accv[8 * j + 0], accv[8 * j + 1]),
+                             pack_bf16x2(accv[8 * j + 2], accv[8 * j + 3]), pack_bf16x2(accv[8 * j + 4], accv[8 * j + 5]),
+                             pack_bf16x2(accv[8 * j + 6], accv[8 * j + 7]));
+              fence_proxy_async_smem();
+              named_barrier_sync(1, 128);
+              if (issuer) {
+                const uint32_t src = epi_base + ebuf * kEpiStageBytes;
+                const int x = n0 + c * kEpiCols, yy = p.out_row0 + m0;
+                if (p.mode == kEpiOneShot) {
+                  tma_store_2d(&p.tmC[rank], x, yy, src);
+                } else {
+                  for (int q = 0; q < W; ++q) tma_store_2d(&p.tmC[(rank + 1 + q) % W], x, yy, src);
+                }
+                bulk_commit();
+              }
+              ebuf ^= 1;
+            } else {
+              const int r = m0 + row;
+              if (r < p.M) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  const int col = n0 + c * kEpiCols + 8 * j;
+                  if (col < p.N) {
+                    uint4 o;
+                    o.x = pack_bf16x2(accv[8 * j + 0], accv[8 * j + 1]);
+                    o.y = pack_bf16x2(accv[8 * j + 2], accv[8 * j + 3]);
+                    o.z = pack_bf16x2(accv[8 * j + 4], accv[8 * j + 5]);
+                    o.w = pack_bf16x2(accv[8 * j + 6], accv[8 * j + 7]);
+                    const uint64_t ooff = p.out_off + ((uint64_t)r * p.ldo + col) * 2;
+                    if (p.mode == kEpiOneShot) {
+                      st_v4(reinterpret_cast<uint4*>(p.heap_base[rank] + ooff), o);
+                    } else {
+                      for (int q = 0; q < W; ++q)
+                        st_v4(reinterpret_cast<uint4*>(p.heap_base[(rank + 1 + q) % W] + ooff), o);
+                    }
+                  }
+                }
+              }
+            }
           }
         }
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          if (!in[u]) continue;
-          float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-#pragma unroll
-          for (int s = 0; s < kMaxRanks; ++s)
-            if (s < W) acc_bf16x8(a, v[u][s]);
-          uint4 o;
-          o.x = pack_bf16x2(a[0], a[1]);
-          o.y = pack_bf16x2(a[2], a[3]);
-          o.z = pack_bf16x2(a[4], a[5]);
-          o.w = pack_bf16x2(a[6], a[7]);
-          const uint64_t ooff = p.out_off + ((uint64_t)rr[u] * p.ldo + cc[u]) * 2;
-          if (p.mode == kEpiOneShot) {
-            st_v4(reinterpret_cast<uint4*>(p.heap_base[rank] + ooff), o);
-          } else {
-            for (int s = 0; s < W; ++s) st_v4(reinterpret_cast<uint4*>(p.heap_base[(rank + 1 + s) % W] + ooff), o);
-          }
-        }
+        if (issuer) trace(p, rank, t * CG + pr, kTrPullEnd);
+        return true;
       }
-      return true;
     };
 
     bool ok_all = true;
@@ -414,9 +497,11 @@ __global__ void __launch_bounds__(kThreads, 1) fused_gemm_kernel(const __grid_co
       }
       entered = true;
       tc_fence_after();
+      if (issuer) trace(p, rank, tile * CG + pr, kTrEpiBegin);
 
       const int x_base = (pulls ? 0 : rank * p.col_off_per_rank) + tc.n_idx * BN;
       const int y = tc.m_idx * TM + pr * BM;
+      const int y_st = (pulls ? p.part_row0 : 0) + y;  // row inside the tmC matrix
 #pragma unroll 1
       for (int c = 0; c < BN / kEpiCols; ++c) {
         const bool live = tc.n_idx * BN + c * kEpiCols < p.N && y < p.M;  // parts past the matrix edge are skipped
@@ -455,13 +540,13 @@ __global__ void __launch_bounds__(kThreads, 1) fused_gemm_kernel(const __grid_co
           if (push_all) {
             for (int i = 0; i < W; ++i) {  // peers first, starting with the next rank; own copy last
               const int t = (rank + 1 + i) % W;
-              if (p.mode == kEpiStore) tma_store_2d(&p.tmC[t], x, y, src);
-              else tma_reduce_add_2d(&p.tmC[t], x, y, src);
+              if (p.mode == kEpiStore) tma_store_2d(&p.tmC[t], x, y_st, src);
+              else tma_reduce_add_2d(&p.tmC[t], x, y_st, src);
             }
           } else if (p.mode == kEpiReduce) {
-            tma_reduce_add_2d(&p.tmC[rank], x, y, src);
+            tma_reduce_add_2d(&p.tmC[rank], x, y_st, src);
           } else {
-            tma_store_2d(&p.tmC[rank], x, y, src);
+            tma_store_2d(&p.tmC[rank], x, y_st, src);
           }
           bulk_commit();
         }
@@ -471,21 +556,24 @@ __global__ void __launch_bounds__(kThreads, 1) fused_gemm_kernel(const __grid_co
         acc = 0;
         acc_phase ^= 1;
       }
+      if (issuer) trace(p, rank, tile * CG + pr, kTrEpiEnd);
 
       if (pulls) {
-        if (issuer) {
-          // Partial tile is in this rank's buffer: publish it to every rank, then sum the previous tile.
-          bulk_wait<0>();
-          fence_proxy_async_all();
-          for (int i = 0; i < W; ++i) {
-            const int t = (rank + 1 + i) % W;
-            if (p.mode == kEpiTwoShot && t != tile % W) continue;  // only the tile's owner needs to know
-            red_release_sys_add(flag_ptr(p, t, p.tile_flag_base + tile * CG + pr), 1u);
-          }
-        }
+        // The partial tile is on its way into this rank's buffer.  Sum the PREVIOUS tile first (its partials
+        // have had a whole main loop to arrive everywhere), then publish this one: by then its stores are done.
         if (prev_tile >= 0 && !pull_reduce(prev_tile)) {
           ok_all = false;
           break;
+        }
+        if (issuer) {
+          bulk_wait<0>();
+          fence_proxy_async_all();
+          fence_sys();  // one release fence, then relaxed increments: a single flush for all ranks
+          for (int i = 0; i < W; ++i) {
+            const int t = (rank + 1 + i) % W;
+            if (p.mode == kEpiTwoShot && t != tile % W) continue;  // only the tile's owner needs to know
+            red_relaxed_sys_add(flag_ptr(p, t, p.tile_flag_base + tile * CG + pr), 1u);
+          }
         }
         prev_tile = tile;
       }
@@ -634,6 +722,14 @@ int encode_2d(CUtensorMap* out, uint64_t ptr, uint64_t rows, uint64_t cols, uint
 
 using namespace iris::gemm;
 
+namespace {
+using KernelFn = void (*)(const FusedGemmParams);
+KernelFn kernel_for(int cta_group, bool pull) {
+  if (cta_group == 2) return pull ? fused_gemm_kernel<2, true> : fused_gemm_kernel<2, false>;
+  return pull ? fused_gemm_kernel<1, true> : fused_gemm_kernel<1, false>;
+}
+}  // namespace
+
 extern "C" {
 
 // Plain-C description of one fused GEMM; mirrored field by field in iris_b200/ops/gemm.py.
@@ -647,14 +743,18 @@ struct IrisGemmDesc {
   int64_t ldb[kMaxRanks];
   int64_t ldc;                 // row pitch of the C / partial buffers
   int64_t c_cols;              // logical number of columns of the C / partial buffers
+  int64_t c_rows;              // rows covered by the C tensor maps (0: M)
   uint64_t flags_off;
   uint64_t partial_off[2];
   uint64_t out_off;
   uint64_t status_off;
   uint64_t agsrc_off;
+  uint64_t trace_off;
   uint64_t timeout_ns;
   int M, N, K;
   int ldo;
+  int part_row0[2];            // per parity
+  int out_row0;
   int col_off_per_rank;
   int world, num_local, rank0, ctas_per_rank;
   int mode, group_m, ag, ag_slices, store_all;
@@ -670,6 +770,7 @@ struct IrisGemmPlan {
   int device;
   int cta_group;
   int ctas_per_rank;
+  int pull;
 };
 
 const char* iris_gemm_last_error() { return g_err; }
@@ -708,9 +809,10 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
   cudaSetDevice(d->device);
   int sms = 0;
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, d->device);
+  const bool pull = d->mode == kEpiOneShot || d->mode == kEpiTwoShot;
   int ctas_per_rank = d->ctas_per_rank - d->ctas_per_rank % cg;
   {
-    cudaError_t e = cudaFuncSetAttribute(cg == 2 ? fused_gemm_kernel<2> : fused_gemm_kernel<1>,
+    cudaError_t e = cudaFuncSetAttribute(kernel_for(cg, pull),
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) {
       snprintf(g_err, sizeof(g_err), "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
@@ -732,7 +834,7 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     int max_clusters = 0;
-    cudaError_t e = cudaOccupancyMaxActiveClusters(&max_clusters, fused_gemm_kernel<2>, &cfg);
+    cudaError_t e = cudaOccupancyMaxActiveClusters(&max_clusters, kernel_for(2, pull), &cfg);
     if (e != cudaSuccess || max_clusters < d->num_local) {
       snprintf(g_err, sizeof(g_err), "CTA pairs cannot be scheduled (%s, %d clusters)", cudaGetErrorString(e),
                max_clusters);
@@ -754,6 +856,7 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
   plan->cooperative = d->num_local > 1;
   plan->device = d->device;
   plan->cta_group = cg;
+  plan->pull = pull ? 1 : 0;
   plan->ctas_per_rank = ctas_per_rank;
   for (int par = 0; par < 2; ++par) {
     FusedGemmParams& p = plan->params[par];
@@ -767,7 +870,7 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
     for (int t = 0; t < d->world; ++t) {
       const uint64_t cp = (par == 1 && d->c2_ptr[t]) ? d->c2_ptr[t] : d->c_ptr[t];
       if (!cp) continue;
-      if (encode_2d(&p.tmC[t], cp, d->M, d->c_cols, d->ldc, kEpiCols, BM, "C")) {
+      if (encode_2d(&p.tmC[t], cp, d->c_rows > 0 ? d->c_rows : d->M, d->c_cols, d->ldc, kEpiCols, BM, "C")) {
         delete plan;
         return nullptr;
       }
@@ -778,11 +881,14 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
     p.out_off = d->out_off;
     p.status_off = d->status_off;
     p.agsrc_off = d->agsrc_off;
+    p.trace_off = d->trace_off;
     p.timeout_ns = d->timeout_ns;
     p.M = d->M;
     p.N = d->N;
     p.K = d->K;
     p.ldo = d->ldo;
+    p.part_row0 = d->part_row0[par];
+    p.out_row0 = d->out_row0;
     p.lda_full = (int)d->lda[0];
     p.col_off_per_rank = d->col_off_per_rank;
     p.world = d->world;
@@ -834,21 +940,23 @@ int iris_gemm_plan_launch(void* h, int parity, uint32_t epoch, uint32_t flag_tar
     cfg.attrs = attr;
     // Ranks simulated on one GPU wait on one another: ask for a cooperative launch on top of the clusters.
     cfg.numAttrs = plan->cooperative ? 2 : 1;
-    e = cudaLaunchKernelEx(&cfg, fused_gemm_kernel<2>, p);
+    void* kargs[] = {&p};
+    e = cudaLaunchKernelExC(&cfg, reinterpret_cast<const void*>(kernel_for(2, plan->pull != 0)), kargs);
     if (e != cudaSuccess && plan->cooperative) {
       // Cooperative + cluster launches are not accepted everywhere; the grid was sized by
       // cudaOccupancyMaxActiveClusters, so all pairs are resident on an otherwise idle GPU.
       (void)cudaGetLastError();
       cfg.numAttrs = 1;
-      e = cudaLaunchKernelEx(&cfg, fused_gemm_kernel<2>, p);
+      e = cudaLaunchKernelExC(&cfg, reinterpret_cast<const void*>(kernel_for(2, plan->pull != 0)), kargs);
     }
   } else if (plan->cooperative) {
     void* args[] = {&p};
-    e = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(fused_gemm_kernel<1>), dim3(plan->grid), dim3(kThreads),
-                                    args, kSmemBytes, st);
+    e = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(kernel_for(1, plan->pull != 0)), dim3(plan->grid),
+                                    dim3(kThreads), args, kSmemBytes, st);
   } else {
-    fused_gemm_kernel<1><<<plan->grid, kThreads, kSmemBytes, st>>>(p);
-    e = cudaGetLastError();
+    void* args[] = {&p};
+    e = cudaLaunchKernel(reinterpret_cast<void*>(kernel_for(1, plan->pull != 0)), dim3(plan->grid), dim3(kThreads),
+                         args, kSmemBytes, st);
   }
   if (e != cudaSuccess) {
     snprintf(g_err, sizeof(g_err), "launch failed: %s", cudaGetErrorString(e));
@@ -897,7 +1005,7 @@ int noalloc_setup(int dev) {
   }
   e = cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev);
   if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(fused_gemm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    e = cudaFuncSetAttribute(fused_gemm_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
   if (e != cudaSuccess) {
     snprintf(iris::gemm::g_err, sizeof(iris::gemm::g_err), "no-alloc set-up: %s", cudaGetErrorString(e));
     return -3;
@@ -961,6 +1069,8 @@ int iris_gemm_noalloc(const void* a, int64_t lda, const void* bt, int64_t ldb, v
   p.N = N;
   p.K = K;
   p.ldo = (int)ldo;
+  p.part_row0 = 0;
+  p.out_row0 = -1;  // the caller's output is a separate buffer: ordinary stores
   p.world = 1;
   p.num_local = 1;
   p.rank0 = 0;
@@ -977,7 +1087,7 @@ int iris_gemm_noalloc(const void* a, int64_t lda, const void* bt, int64_t ldb, v
   // The scratch keeps the previous call's flags and status: clear what has to start at zero, in stream order.
   cudaError_t e = cudaMemsetAsync(d.scratch, 0, kNoAllocPartialOff, st);
   if (e == cudaSuccess) {
-    fused_gemm_kernel<1><<<p.ctas_per_rank, kThreads, kSmemBytes, st>>>(p);
+    fused_gemm_kernel<1, true><<<p.ctas_per_rank, kThreads, kSmemBytes, st>>>(p);
     e = cudaGetLastError();
   }
   if (e != cudaSuccess) {

@@ -33,6 +33,10 @@ constexpr int kSmemTiles = kStages * kStageBytes + kEpiBufs * kEpiStageBytes;
 constexpr int kSmemBarriers = 256;
 constexpr int kSmemBytes = kSmemTiles + kSmemBarriers + 1024;  // + slack to align the base to 1024 B
 
+// Slots of one per-tile trace record (nanoseconds of the global timer).
+enum TraceSlot : int { kTrMmaBegin = 0, kTrMmaEnd = 1, kTrEpiBegin = 2, kTrEpiEnd = 3, kTrWaitBegin = 4, kTrWaitEnd = 5,
+                       kTrPullEnd = 6, kTrSlots = 8 };
+
 constexpr int kThreads = 256;  // warp 0: TMA producer, warp 1: MMA issuer, warps 2-5: epilogue, warps 6-7: comm
 
 enum EpiMode : int {
@@ -56,8 +60,12 @@ struct FusedGemmParams {
   uint64_t out_off;      // one-/two-shot: bf16 [M, ldo] final output
   uint64_t status_off;   // iris::StatusBlock
   uint64_t agsrc_off;    // all-gather prologue: gathered A [M, K] (row stride lda_full elements)
+  uint64_t trace_off;    // 0, or int64[tiles * cta_group][8] per rank: per-tile device timestamps (ns)
   uint64_t timeout_ns;
   int M, N, K;           // per-rank GEMM problem: C[M, N] = A[M, K] * B[N, K]^T
+  int part_row0;         // one-/two-shot: first row, inside the tmC matrices, of this call's partial buffer
+  int out_row0;          // one-/two-shot: first row of the final output inside the tmC matrices, or -1 when the
+                         // output is a separate buffer written with ordinary stores (out_off, ldo)
   int ldo;               // row stride (elements) of the final output in one-/two-shot mode
   int lda_full;          // row stride (elements) of the gathered A
   int col_off_per_rank;  // store/reduce: rank r writes columns [r * col_off_per_rank, ... + N) of C

@@ -229,6 +229,20 @@ __global__ void mp_kernel(MpArgs a) {
   }
 }
 
+// Device-side barrier across ranks: one thread adds 1 to counter[0] of every rank (release, system scope),
+// then waits (bounded) until its own counter reaches `target` = calls * world.  Streams of different GPUs are
+// aligned to within a few microseconds when this kernel completes.
+__global__ void device_barrier_kernel(const uint64_t* hb, uint64_t counter_off, uint64_t status_off, int rank,
+                                      int world, uint32_t target, uint64_t timeout_ns) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  for (int i = 0; i < world; ++i) {
+    const int t = (rank + 1 + i) % world;
+    red_release_sys_add(reinterpret_cast<uint32_t*>(hb[t] + counter_off), 1u);
+  }
+  wait_until_ge(reinterpret_cast<const uint32_t*>(hb[rank] + counter_off), target, timeout_ns,
+                reinterpret_cast<StatusBlock*>(hb[rank] + status_off), /*where=*/70, (uint32_t)rank, target);
+}
+
 int check_launch() { return cudaGetLastError() == cudaSuccess ? 0 : -1; }
 
 }  // namespace
@@ -282,6 +296,13 @@ int iris_k_memset_i32(void* p, int value, uint64_t n, void* stream) {
   const int block = 256;
   const int grid = (int)((n + block - 1) / block < 1184 ? (n + block - 1) / block : 1184);
   memset_i32_kernel<<<grid, block, 0, (cudaStream_t)stream>>>((int*)p, value, n);
+  return check_launch();
+}
+
+int iris_k_device_barrier(const uint64_t* hb, uint64_t counter_off, uint64_t status_off, int rank, int world,
+                          uint32_t target, uint64_t timeout_ns, void* stream) {
+  device_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(hb, counter_off, status_off, rank, world, target,
+                                                            timeout_ns);
   return check_launch();
 }
 

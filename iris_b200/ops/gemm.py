@@ -36,10 +36,12 @@ class _Desc(ctypes.Structure):
         ("c_ptr", ctypes.c_uint64 * MAX_RANKS), ("c2_ptr", ctypes.c_uint64 * MAX_RANKS),
         ("heap_base", ctypes.c_uint64 * MAX_RANKS),
         ("lda", ctypes.c_int64 * MAX_RANKS), ("ldb", ctypes.c_int64 * MAX_RANKS),
-        ("ldc", ctypes.c_int64), ("c_cols", ctypes.c_int64),
+        ("ldc", ctypes.c_int64), ("c_cols", ctypes.c_int64), ("c_rows", ctypes.c_int64),
         ("flags_off", ctypes.c_uint64), ("partial_off", ctypes.c_uint64 * 2), ("out_off", ctypes.c_uint64),
-        ("status_off", ctypes.c_uint64), ("agsrc_off", ctypes.c_uint64), ("timeout_ns", ctypes.c_uint64),
+        ("status_off", ctypes.c_uint64), ("agsrc_off", ctypes.c_uint64), ("trace_off", ctypes.c_uint64),
+        ("timeout_ns", ctypes.c_uint64),
         ("M", ctypes.c_int), ("N", ctypes.c_int), ("K", ctypes.c_int), ("ldo", ctypes.c_int),
+        ("part_row0", ctypes.c_int * 2), ("out_row0", ctypes.c_int),
         ("col_off_per_rank", ctypes.c_int),
         ("world", ctypes.c_int), ("num_local", ctypes.c_int), ("rank0", ctypes.c_int), ("ctas_per_rank", ctypes.c_int),
         ("mode", ctypes.c_int), ("group_m", ctypes.c_int), ("ag", ctypes.c_int), ("ag_slices", ctypes.c_int),
@@ -107,7 +109,7 @@ class FusedGemm:
                  store_all: bool = False, c_cols: Optional[int] = None, col_off_per_rank: int = 0,
                  out: Optional[Sequence[torch.Tensor]] = None, ag: bool = False, ag_slices: int = 8,
                  ctas_per_rank: Optional[int] = None, group_m: int = 8, timeout_ms: float = 2000.0,
-                 cta_group: Optional[int] = None):
+                 cta_group: Optional[int] = None, trace: bool = False):
         self.ctxs: List[Iris] = [ctxs] if isinstance(ctxs, Iris) else list(ctxs)
         c0 = self.ctxs[0]
         if c0.backend != "cuda":
@@ -163,18 +165,26 @@ class FusedGemm:
         nflags = FLAG_HEADER + tile_flags + self.world * chunks_per_shard
         # ---- symmetric allocations (identical sequence on every rank) ----
         self.flags = [c.zeros(nflags, dtype=torch.int32) for c in self.ctxs]
+        self.trace = [c.zeros((self.total_tiles * cta_group, 8), dtype=torch.int64) for c in self.ctxs] if trace else None
         self.c_cols = int(c_cols) if c_cols else self.N
         if pulls:
-            self.partial = [[c.zeros((self.M, self.N), dtype=torch.bfloat16) for c in self.ctxs] for _ in range(2)]
-            self.out = list(out) if out is not None else [c.zeros((self.M, self.N), dtype=torch.bfloat16)
-                                                          for c in self.ctxs]
-            c_bufs, c2_bufs = self.partial[0], self.partial[1]
+            # One matrix per rank holds both partial buffers (call parity) and, unless the caller brings its own,
+            # the output: [partial 0 | partial 1 | out], each padded to whole 256-row tiles, so that one tensor
+            # map per rank serves partial stores, partial loads and output stores.
+            mp = -(-self.M // (2 * BM)) * (2 * BM)
+            regions = 2 if out is not None else 3
+            self._pull_buf = [c.zeros((regions * mp, self.N), dtype=torch.bfloat16) for c in self.ctxs]
+            self.partial = [[b[q * mp:q * mp + self.M] for b in self._pull_buf] for q in range(2)]
+            self.out = list(out) if out is not None else [b[2 * mp:2 * mp + self.M] for b in self._pull_buf]
+            c_bufs, c2_bufs = self._pull_buf, None
             ldc, c_cols_eff = self.N, self.N
+            c_rows, part_row0, out_row0 = regions * mp, (0, mp), (2 * mp if out is None else -1)
         else:
             self.out = list(out) if out is not None else [c.zeros((self.M, self.c_cols), dtype=torch.bfloat16)
                                                           for c in self.ctxs]
             c_bufs, c2_bufs = self.out, None
             ldc, c_cols_eff = self.out[0].stride(0), self.c_cols
+            c_rows, part_row0, out_row0 = 0, (0, 0), -1
         for o in self.out:
             _check_operand(o, "output")
         d = _Desc()
@@ -195,13 +205,14 @@ class FusedGemm:
             c_off = c2_off = 0
             for l in range(self.num_local):
                 d.c_ptr[self.rank0 + l] = c_bufs[l].data_ptr()
-        d.ldc, d.c_cols = ldc, c_cols_eff
+        d.ldc, d.c_cols, d.c_rows = ldc, c_cols_eff, c_rows
+        d.part_row0[0], d.part_row0[1], d.out_row0 = part_row0[0], part_row0[1], out_row0
         d.flags_off = c0.offset_of(self.flags[0])
-        d.partial_off[0] = c_off if pulls else 0
-        d.partial_off[1] = c2_off if pulls else 0
+        d.partial_off[0] = d.partial_off[1] = 0
         d.out_off = c0.offset_of(self.out[0]) if pulls else 0
         d.status_off = c0.offset_of(c0.status)
         d.agsrc_off = c0.offset_of(self.a_full[0]) if self.ag else 0
+        d.trace_off = c0.offset_of(self.trace[0]) if self.trace else 0
         d.timeout_ns = int(timeout_ms * 1e6)
         d.M, d.N, d.K = self.M, self.N, self.K
         d.ldo = self.out[0].stride(0)
@@ -240,6 +251,26 @@ class FusedGemm:
             raise RuntimeError("fused GEMM launch: " + _lib().iris_gemm_last_error().decode())
         self.launches += 1
         return self.out
+
+    def trace_records(self, local: int = 0):
+        """Per-tile timestamps of the last call in microseconds relative to the earliest one: a list of dicts with
+        ``mma_begin, mma_end, epi_begin, epi_end, wait_begin, wait_end, pull_end`` (the reference's per-tile trace
+        JSON, ``examples/common/utils.py:66-128``).  Needs ``trace=True`` at construction."""
+        if self.trace is None:
+            raise RuntimeError("construct the op with trace=True")
+        torch.cuda.synchronize(self.ctxs[0].device)
+        t = self.trace[local].cpu()
+        names = ["mma_begin", "mma_end", "epi_begin", "epi_end", "wait_begin", "wait_end", "pull_end"]
+        nz = t[t > 0]
+        t0 = int(nz.min()) if nz.numel() else 0
+        recs = []
+        for i in range(t.shape[0]):
+            rec = {"record": i, "tile_id": i // self.cta_group, "cta_in_pair": i % self.cta_group}
+            for j, nm in enumerate(names):
+                v = int(t[i, j])
+                rec[nm] = (v - t0) / 1e3 if v else None
+            recs.append(rec)
+        return recs
 
     def check(self) -> None:
         """Synchronise and raise if a bounded wait of the last calls expired."""

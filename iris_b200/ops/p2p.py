@@ -155,3 +155,32 @@ class MessagePassing:
             ctx.offset_of(self.flags), ctx.offset_of(ctx.status), self.chunk_bytes, self.nchunks, self.producer,
             self.consumer, roles, int(use_put), self.epoch, self.timeout_ns, block, _stream(ctx, stream))
         _check(rc, "message_passing")
+
+
+class DeviceBarrier:
+    """Barrier across ranks executed on the GPUs (one tiny kernel per rank): every rank bumps a counter in every
+    peer's heap and waits, bounded, for its own to reach ``calls * world``.  Used to align the ranks' streams
+    before a timed region so that host-side launch skew is not charged to the kernel under test.  One process
+    per GPU only (kernels that wait on one another must not share a GPU)."""
+
+    def __init__(self, ctx, timeout_ms: float = 5000.0):
+        if getattr(ctx, "_local_world", None) is not None:
+            raise RuntimeError("DeviceBarrier is for one process per GPU")
+        self.ctx = ctx
+        self.counter = ctx.zeros(16, dtype=torch.int32)
+        self.calls = 0
+        self.timeout_ns = int(timeout_ms * 1e6)
+
+    def __call__(self, stream=None) -> None:
+        ctx = self.ctx
+        self.calls += 1
+        if ctx.get_num_ranks() == 1:
+            return
+        lib = _native.kernels()
+        lib.iris_k_device_barrier.argtypes = [ctypes.c_void_p, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_int,
+                                              ctypes.c_int, ctypes.c_uint32, ctypes.c_uint64, ctypes.c_void_p]
+        rc = lib.iris_k_device_barrier(_hb(ctx), ctx.offset_of(self.counter), ctx.offset_of(ctx.status),
+                                       ctx.get_rank(), ctx.get_num_ranks(),
+                                       (self.calls * ctx.get_num_ranks()) & 0xFFFFFFFF, self.timeout_ns,
+                                       _stream(ctx, stream))
+        _check(rc, "device_barrier")

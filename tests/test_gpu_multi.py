@@ -23,3 +23,14 @@ def test_real_ranks(world):
                            env={"NCCL_NVLS_ENABLE": "0"})
     assert code == 0, "\n".join(o or "" for o in outs)
     assert all("OK" in (o or "") for o in outs)
+
+
+@pytest.mark.parametrize("nvls", ["0", "1"])
+def test_vmm_heap(nvls):
+    """Heap on CUDA virtual memory management (descriptor passing, contiguous mapping); with nvls=1 also the
+    NVLink-switch multicast path when the machine offers it.  Every rank exits normally, between steps."""
+    world = min(4, torch.cuda.device_count())
+    code, outs = run_ranks(world, [os.path.join(W, "gpu_vmm_nvls.py")], timeout_s=240,
+                           env={"IRIS_NVLS": nvls, "NCCL_NVLS_ENABLE": "0"})
+    assert code == 0, "\n".join(o or "" for o in outs)
+    assert all("VMM OK" in (o or "") for o in outs)

@@ -1,0 +1,91 @@
+#!/usr/bin/env python
+"""Tensor-parallel Llama-style decoder stack: hidden 4096, 32 heads x 128, SwiGLU 11008, RMSNorm eps 1e-6, bf16
+weights N(0, 0.02) from seed 4, activations N(0, 1) of batch 8 x seq 2048, 4 layers, forward only.
+Column-parallel projections run as fused all-gather->GEMM, row-parallel ones as fused GEMM->all-reduce
+(``iris_b200/models/tp_block.py``); the same network with cuBLAS + NCCL is timed next to it.  No counterpart in the
+reference, whose fused kernels are the ingredients.
+
+    python -m iris_b200.launch -np 8 examples/10_tp_block/tp_block.py -v -b
+"""
+import argparse
+import json
+import os
+import sys
+
+sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), ".."))
+from common.harness import device_barrier, iris, reduce_ranks, time_kernel_ms, torch  # noqa: E402
+
+from iris_b200.models.tp_block import TPConfig, TPDecoder, TPDecoderBaseline, reference_forward  # noqa: E402
+
+
+def main():
+    ap = argparse.ArgumentParser(formatter_class=argparse.ArgumentDefaultsHelpFormatter)
+    ap.add_argument("--hidden", type=int, default=4096)
+    ap.add_argument("--heads", type=int, default=32)
+    ap.add_argument("--head_dim", type=int, default=128)
+    ap.add_argument("--intermediate", type=int, default=11008)
+    ap.add_argument("--layers", type=int, default=4)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--seq", type=int, default=2048)
+    ap.add_argument("--variant", default="two_shot", choices=["two_shot", "one_shot", "atomic"])
+    ap.add_argument("-v", "--validate", action="store_true", help="compare with the unsharded fp32 oracle (1 layer subset)")
+    ap.add_argument("-b", "--benchmark", action="store_true")
+    ap.add_argument("--num_experiments", type=int, default=10)
+    ap.add_argument("--num_warmup", type=int, default=3)
+    ap.add_argument("--heap_size", type=int, default=12 << 30)
+    ap.add_argument("--output_file", default="")
+    args = ap.parse_args()
+    cfg = TPConfig(hidden=args.hidden, n_heads=args.heads, head_dim=args.head_dim, intermediate=args.intermediate,
+                   n_layers=args.layers, batch=args.batch, seq=args.seq)
+    ctx = iris.iris(args.heap_size)
+    rank, world = ctx.get_rank(), ctx.get_num_ranks()
+    dev = ctx.get_device()
+    device_barrier(ctx)
+    model = TPDecoder(ctx, cfg, variant=args.variant)
+    base = TPDecoderBaseline(cfg, rank, world, dev)
+    g = torch.Generator(device=dev).manual_seed(cfg.seed)
+    x = torch.randn((cfg.tokens, cfg.hidden), generator=g, device=dev).to(torch.bfloat16)
+    ts = cfg.tokens // world
+    mine = x[rank * ts:(rank + 1) * ts]
+    res = {"world": world, "variant": args.variant, "config": cfg.__dict__}
+    ok = True
+    if args.validate:
+        a, b = mine.clone(), mine.clone()
+        ctx.barrier()
+        model.forward([a])
+        model.check()
+        base.forward(b)
+        torch.cuda.synchronize()
+        d_fb = (a.float() - b.float()).abs()
+        res["fused_vs_baseline_max"], res["fused_vs_baseline_mean"] = d_fb.max().item(), d_fb.mean().item()
+        ok = d_fb.mean().item() < 3e-2
+        if cfg.tokens * cfg.hidden <= 1 << 24:  # the oracle needs the full fp32 network on one GPU
+            ref = reference_forward(x, cfg)[rank * ts:(rank + 1) * ts]
+            err = (a.float() - ref).abs()
+            res["fused_vs_oracle_max"], res["fused_vs_oracle_mean"] = err.max().item(), err.mean().item()
+            ok = ok and err.mean().item() < 3e-2
+        ctx.log(f"Validation {'successful' if ok else 'FAILED'}: {json.dumps({k: v for k, v in res.items() if 'vs' in k})}")
+    if args.benchmark:
+        a, b = mine.clone(), mine.clone()
+        f_ms = reduce_ranks(ctx, time_kernel_ms(ctx, lambda: model.forward([a]), args.num_warmup,
+                                                args.num_experiments, align=True), "max")
+        model.check()
+        b_ms = reduce_ranks(ctx, time_kernel_ms(ctx, lambda: base.forward(b), args.num_warmup,
+                                                args.num_experiments, align=True), "max")
+        res.update(fused_us=f_ms * 1e3, baseline_us=b_ms * 1e3, speedup=b_ms / f_ms)
+        if rank == 0:
+            print(f"TP decoder x{cfg.n_layers} layers, W={world}, {cfg.tokens} tokens: fused {f_ms * 1e3:.0f} us | "
+                  f"cuBLAS+NCCL {b_ms * 1e3:.0f} us | x{b_ms / f_ms:.2f}", flush=True)
+    if rank == 0 and args.output_file:
+        os.makedirs(os.path.dirname(args.output_file) or ".", exist_ok=True)
+        with open(args.output_file, "w") as f:
+            json.dump(res, f, indent=2, default=str)
+    model.close()
+    ctx.barrier()
+    ctx.close()
+    if not ok:
+        raise SystemExit(1)
+
+
+if __name__ == "__main__":
+    main()

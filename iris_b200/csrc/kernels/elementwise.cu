@@ -1,0 +1,131 @@
+// elementwise.cu — the memory-bound pieces of the tensor-parallel decoder block: RMSNorm, SwiGLU and the
+// residual add, bf16 in / bf16 out with fp32 arithmetic, 16-byte vector accesses.
+//
+// No counterpart in the reference (it has no model code); they exist for the tensor-parallel block built on
+// the fused GEMM + collective kernels.  RMSNorm writes straight into the row block that the all-gather -> GEMM
+// kernel pushes to the peers, so the normalised activations are never copied.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace {
+
+__device__ __forceinline__ void unpack8(uint4 v, float* f) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 t = __bfloat1622float2(h[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float* f) {
+  uint4 o;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return o;
+}
+
+// One CTA per row; cols % 8 == 0.  out[r, :] = x[r, :] * rsqrt(mean(x^2) + eps) * w
+template <int kThreads>
+__global__ void __launch_bounds__(kThreads) rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx,
+                                                           const __nv_bfloat16* __restrict__ w,
+                                                           __nv_bfloat16* __restrict__ out, int64_t ldo, int cols,
+                                                           float eps) {
+  __shared__ float red[kThreads / 32];
+  const int r = blockIdx.x;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + (int64_t)r * ldx);
+  const uint4* wv = reinterpret_cast<const uint4*>(w);
+  uint4* orow = reinterpret_cast<uint4*>(out + (int64_t)r * ldo);
+  const int nv = cols / 8;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < nv; i += kThreads) {
+    float f[8];
+    unpack8(xr[i], f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss += f[j] * f[j];
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < kThreads / 32; ++i) tot += red[i];
+  const float scale = rsqrtf(tot / (float)cols + eps);
+  for (int i = threadIdx.x; i < nv; i += kThreads) {
+    float f[8], g[8];
+    unpack8(xr[i], f);  // second read hits L1/L2
+    unpack8(wv[i], g);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = f[j] * scale * g[j];
+    orow[i] = pack8(f);
+  }
+}
+
+// out[r, c] = silu(gu[r, c]) * gu[r, inter + c]
+__global__ void swiglu_kernel(const __nv_bfloat16* __restrict__ gu, int64_t ldg, __nv_bfloat16* __restrict__ out,
+                              int64_t ldo, int rows, int inter) {
+  const int nv = inter / 8;
+  const int64_t total = (int64_t)rows * nv;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int r = (int)(i / nv), c = (int)(i - (int64_t)r * nv);
+    const uint4 g = *reinterpret_cast<const uint4*>(gu + (int64_t)r * ldg + c * 8);
+    const uint4 u = *reinterpret_cast<const uint4*>(gu + (int64_t)r * ldg + inter + c * 8);
+    float a[8], b[8];
+    unpack8(g, a);
+    unpack8(u, b);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) a[j] = a[j] / (1.f + __expf(-a[j])) * b[j];
+    *reinterpret_cast<uint4*>(out + (int64_t)r * ldo + c * 8) = pack8(a);
+  }
+}
+
+// x[r, :] += y[r, :]
+__global__ void residual_add_kernel(__nv_bfloat16* __restrict__ x, int64_t ldx, const __nv_bfloat16* __restrict__ y,
+                                    int64_t ldy, int rows, int cols) {
+  const int nv = cols / 8;
+  const int64_t total = (int64_t)rows * nv;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int r = (int)(i / nv), c = (int)(i - (int64_t)r * nv);
+    uint4* xp = reinterpret_cast<uint4*>(x + (int64_t)r * ldx + c * 8);
+    float a[8], b[8];
+    unpack8(*xp, a);
+    unpack8(*reinterpret_cast<const uint4*>(y + (int64_t)r * ldy + c * 8), b);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) a[j] += b[j];
+    *xp = pack8(a);
+  }
+}
+
+int grid_for(int64_t work_items, int block) {
+  int64_t g = (work_items + block - 1) / block;
+  return (int)(g < 1 ? 1 : (g > 148 * 8 ? 148 * 8 : g));
+}
+
+}  // namespace
+
+extern "C" {
+
+int iris_k_rmsnorm_bf16(const void* x, int64_t ldx, const void* w, void* out, int64_t ldo, int rows, int cols,
+                        float eps, void* stream) {
+  if (cols % 8 != 0 || rows < 1) return -2;
+  rmsnorm_kernel<256><<<rows, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w,
+                                                              (__nv_bfloat16*)out, ldo, cols, eps);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+int iris_k_swiglu_bf16(const void* gu, int64_t ldg, void* out, int64_t ldo, int rows, int inter, void* stream) {
+  if (inter % 8 != 0 || rows < 1) return -2;
+  swiglu_kernel<<<grid_for((int64_t)rows * inter / 8, 256), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)gu, ldg, (__nv_bfloat16*)out, ldo, rows, inter);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+int iris_k_residual_add_bf16(void* x, int64_t ldx, const void* y, int64_t ldy, int rows, int cols, void* stream) {
+  if (cols % 8 != 0 || rows < 1) return -2;
+  residual_add_kernel<<<grid_for((int64_t)rows * cols / 8, 256), 256, 0, (cudaStream_t)stream>>>(
+      (__nv_bfloat16*)x, ldx, (const __nv_bfloat16*)y, ldy, rows, cols);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+}  // extern "C"

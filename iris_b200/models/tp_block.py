@@ -1,0 +1,232 @@
+"""Tensor-parallel Llama-style decoder stack built on the fused GEMM + collective kernels.
+
+Per layer, on every rank (W ranks, tokens T = batch x seq, hidden H, SwiGLU width I):
+
+    x_shard [T/W, H]   (the residual stream is token-sharded between blocks)
+      RMSNorm -> written straight into this rank's rows of the gathered activation matrix
+      all-gather -> GEMM   qkv   = gather(xn) [T, H]   @ Wqkv_r^T [H, 3H/W]       (column-parallel, fused)
+      causal attention over this rank's H/W / head_dim heads
+      GEMM -> all-reduce   o     = attn [T, H/W]       @ Wo_r^T   [H/W, H]        (row-parallel, fused)
+      x_shard += o[own rows]
+      RMSNorm -> gathered matrix; all-gather -> GEMM  gate|up = gather(xn) @ Wgu_r^T [H, 2I/W]
+      SwiGLU; GEMM -> all-reduce  down = h [T, I/W] @ Wd_r^T [I/W, H];  x_shard += down[own rows]
+
+The reference has no model code; its fused kernels are the ingredients (``docs/FINEGRAINED_OVERLAP.md:23-31``
+describes the row-parallel and column-parallel splits).  ``TPDecoderBaseline`` is the same network with cuBLAS GEMMs
+and NCCL ``all_gather_into_tensor`` / ``all_reduce``; ``reference_forward`` is the unsharded fp32 oracle.
+The attention core is ``torch.nn.functional.scaled_dot_product_attention`` (a library kernel) in both.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Sequence, Union
+
+import torch
+import torch.nn.functional as F
+
+from ..context import Iris
+from ..ops import elementwise as E
+from ..ops import gemm as G
+
+
+@dataclass
+class TPConfig:
+    hidden: int = 4096
+    n_heads: int = 32
+    head_dim: int = 128
+    intermediate: int = 11008
+    eps: float = 1e-6
+    n_layers: int = 4
+    batch: int = 8
+    seq: int = 2048
+    seed: int = 4
+    std: float = 0.02
+
+    @property
+    def tokens(self) -> int:
+        return self.batch * self.seq
+
+
+def layer_weights(cfg: TPConfig, layer: int, device) -> dict:
+    """Full (unsharded) bf16 weights of one layer, identical on every rank: N(0, std) from ``seed + layer``."""
+    g = torch.Generator(device=device).manual_seed(cfg.seed * 1000 + layer)
+    H, I = cfg.hidden, cfg.intermediate
+
+    def w(rows, cols):
+        return (torch.randn((rows, cols), generator=g, device=device) * cfg.std).to(torch.bfloat16)
+    return {"wq": w(H, H), "wk": w(H, H), "wv": w(H, H), "wo": w(H, H), "wg": w(I, H), "wu": w(I, H), "wd": w(H, I),
+            "norm1": torch.ones(H, device=device, dtype=torch.bfloat16),
+            "norm2": torch.ones(H, device=device, dtype=torch.bfloat16)}
+
+
+def shard_weights(full: dict, cfg: TPConfig, rank: int, world: int) -> dict:
+    H, I = cfg.hidden, cfg.intermediate
+    hs, is_ = H // world, I // world
+    r0, r1 = rank * hs, (rank + 1) * hs
+    i0, i1 = rank * is_, (rank + 1) * is_
+    return {
+        "wqkv": torch.cat([full["wq"][r0:r1], full["wk"][r0:r1], full["wv"][r0:r1]], 0).contiguous(),  # [3H/W, H]
+        "wo": full["wo"][:, r0:r1].contiguous(),                                                     # [H, H/W]
+        "wgu": torch.cat([full["wg"][i0:i1], full["wu"][i0:i1]], 0).contiguous(),                      # [2I/W, H]
+        "wd": full["wd"][:, i0:i1].contiguous(),                                                     # [H, I/W]
+        "norm1": full["norm1"], "norm2": full["norm2"]}
+
+
+def attention(qkv: torch.Tensor, cfg: TPConfig, heads_local: int, out: torch.Tensor) -> torch.Tensor:
+    """Causal self-attention over the local heads.  qkv: [T, 3 * heads_local * d]; out: [T, heads_local * d]."""
+    B, S, d = cfg.batch, cfg.seq, cfg.head_dim
+    hl = heads_local * d
+    q = qkv[:, :hl].view(B, S, heads_local, d).transpose(1, 2)
+    k = qkv[:, hl:2 * hl].view(B, S, heads_local, d).transpose(1, 2)
+    v = qkv[:, 2 * hl:].view(B, S, heads_local, d).transpose(1, 2)
+    o = F.scaled_dot_product_attention(q, k, v, is_causal=True)
+    out.view(B, S, heads_local, d).copy_(o.transpose(1, 2))
+    return out
+
+
+class TPDecoder:
+    """Fused implementation.  ``ctxs``: one ``Iris`` (one process per GPU) or all members of ``Iris.local_world``."""
+
+    def __init__(self, ctxs: Union[Iris, Sequence[Iris]], cfg: TPConfig, variant: str = "two_shot", ag_slices: int = 8):
+        self.ctxs: List[Iris] = [ctxs] if isinstance(ctxs, Iris) else list(ctxs)
+        self.cfg = cfg
+        c0 = self.ctxs[0]
+        self.world = c0.get_num_ranks()
+        self.ranks = [c.get_rank() for c in self.ctxs]
+        dev = c0.device
+        W, T, H, I = self.world, cfg.tokens, cfg.hidden, cfg.intermediate
+        if cfg.n_heads % W or I % W or T % W or (I // W) % 8:
+            raise ValueError("heads, intermediate size and tokens must divide by the number of ranks")
+        self.heads_local = cfg.n_heads // W
+        self.ts = T // W
+        nl = len(self.ctxs)
+        self.attn = [torch.empty((T, H // W), dtype=torch.bfloat16, device=dev) for _ in range(nl)]
+        self.h = [torch.empty((T, I // W), dtype=torch.bfloat16, device=dev) for _ in range(nl)]
+        self.layers = []
+        for layer in range(cfg.n_layers):
+            full = layer_weights(cfg, layer, dev)
+            sh = [shard_weights(full, cfg, r, W) for r in self.ranks]
+            del full
+            ops = {
+                "w": sh,
+                "qkv": G.all_gather_gemm(self.ctxs, T, [s["wqkv"] for s in sh], ag_slices=ag_slices),
+                "o": G.gemm_all_reduce(self.ctxs, self.attn, [s["wo"] for s in sh], variant=variant),
+                "gu": G.all_gather_gemm(self.ctxs, T, [s["wgu"] for s in sh], ag_slices=ag_slices),
+                "down": G.gemm_all_reduce(self.ctxs, self.h, [s["wd"] for s in sh], variant=variant),
+            }
+            self.layers.append(ops)
+        self.kernel_launches = 0
+
+    def rows(self, local: int) -> slice:
+        r = self.ranks[local]
+        return slice(r * self.ts, (r + 1) * self.ts)
+
+    def forward(self, x_shards: Sequence[torch.Tensor]) -> Sequence[torch.Tensor]:
+        """``x_shards[l]``: [T/W, H] bf16 of local rank l; updated in place and returned."""
+        cfg, nl = self.cfg, len(self.ctxs)
+        n = 0
+        for ops in self.layers:
+            for l in range(nl):
+                E.rmsnorm(x_shards[l], ops["w"][l]["norm1"], ops["qkv"].a_full[l][self.rows(l)], cfg.eps)
+            qkv = ops["qkv"]()
+            for l in range(nl):
+                attention(qkv[l], cfg, self.heads_local, self.attn[l])
+            o = ops["o"]()
+            for l in range(nl):
+                E.residual_add(x_shards[l], o[l][self.rows(l)])
+                E.rmsnorm(x_shards[l], ops["w"][l]["norm2"], ops["gu"].a_full[l][self.rows(l)], cfg.eps)
+            gu = ops["gu"]()
+            for l in range(nl):
+                E.swiglu(gu[l], self.h[l])
+            d = ops["down"]()
+            for l in range(nl):
+                E.residual_add(x_shards[l], d[l][self.rows(l)])
+            n += 4 + 5 * nl
+        self.kernel_launches += n
+        return x_shards
+
+    def check(self) -> None:
+        torch.cuda.synchronize(self.ctxs[0].device)
+        for c in self.ctxs:
+            c.check_status()
+
+    def close(self) -> None:
+        for ops in self.layers:
+            for k in ("qkv", "o", "gu", "down"):
+                ops[k].close()
+
+
+class TPDecoderBaseline:
+    """Same network, one process per GPU: cuBLAS GEMMs + NCCL all_gather_into_tensor / all_reduce."""
+
+    def __init__(self, cfg: TPConfig, rank: int, world: int, device):
+        self.cfg, self.rank, self.world = cfg, rank, world
+        T, H, I = cfg.tokens, cfg.hidden, cfg.intermediate
+        self.heads_local = cfg.n_heads // world
+        self.ts = T // world
+        self.w = []
+        for layer in range(cfg.n_layers):
+            full = layer_weights(cfg, layer, device)
+            self.w.append(shard_weights(full, cfg, rank, world))
+            del full
+        bf = dict(dtype=torch.bfloat16, device=device)
+        self.xn = torch.empty((self.ts, H), **bf)
+        self.full = torch.empty((T, H), **bf)
+        self.qkv = torch.empty((T, 3 * H // world), **bf)
+        self.attn = torch.empty((T, H // world), **bf)
+        self.part = torch.empty((T, H), **bf)
+        self.gu = torch.empty((T, 2 * I // world), **bf)
+        self.h = torch.empty((T, I // world), **bf)
+
+    def forward(self, x_shard: torch.Tensor) -> torch.Tensor:
+        import torch.distributed as dist
+        cfg = self.cfg
+        rows = slice(self.rank * self.ts, (self.rank + 1) * self.ts)
+
+        def gather(t):
+            if self.world > 1:
+                dist.all_gather_into_tensor(self.full, t)
+            else:
+                self.full.copy_(t)
+
+        def reduce(t):
+            if self.world > 1:
+                dist.all_reduce(t)
+        for w in self.w:
+            E.rmsnorm(x_shard, w["norm1"], self.xn, cfg.eps)
+            gather(self.xn)
+            torch.matmul(self.full, w["wqkv"].t(), out=self.qkv)
+            attention(self.qkv, cfg, self.heads_local, self.attn)
+            torch.matmul(self.attn, w["wo"].t(), out=self.part)
+            reduce(self.part)
+            E.residual_add(x_shard, self.part[rows])
+            E.rmsnorm(x_shard, w["norm2"], self.xn, cfg.eps)
+            gather(self.xn)
+            torch.matmul(self.full, w["wgu"].t(), out=self.gu)
+            E.swiglu(self.gu, self.h)
+            torch.matmul(self.h, w["wd"].t(), out=self.part)
+            reduce(self.part)
+            E.residual_add(x_shard, self.part[rows])
+        return x_shard
+
+
+def reference_forward(x: torch.Tensor, cfg: TPConfig) -> torch.Tensor:
+    """Unsharded fp32 oracle: x [T, H] (any float dtype) -> [T, H] fp32, with the same bf16 weights."""
+    dev = x.device
+    x = x.float().clone()
+    B, S, nh, d = cfg.batch, cfg.seq, cfg.n_heads, cfg.head_dim
+
+    def norm(t, w):
+        return t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + cfg.eps) * w.float()
+    for layer in range(cfg.n_layers):
+        w = layer_weights(cfg, layer, dev)
+        xn = norm(x, w["norm1"])
+        q = (xn @ w["wq"].float().t()).view(B, S, nh, d).transpose(1, 2)
+        k = (xn @ w["wk"].float().t()).view(B, S, nh, d).transpose(1, 2)
+        v = (xn @ w["wv"].float().t()).view(B, S, nh, d).transpose(1, 2)
+        a = F.scaled_dot_product_attention(q, k, v, is_causal=True).transpose(1, 2).reshape(B * S, nh * d)
+        x = x + a @ w["wo"].float().t()
+        xn = norm(x, w["norm2"])
+        hidden = F.silu(xn @ w["wg"].float().t()) * (xn @ w["wu"].float().t())
+        x = x + hidden @ w["wd"].float().t()
+    return x

@@ -47,6 +47,8 @@ def cpu() -> ctypes.CDLL:
                                      c_int, c_int, c_int, c_double, c_int64, c_int64, c_int]
         lib.iris_cpu_mp_produce.restype = None
         lib.iris_cpu_mp_produce.argtypes = [c_void_p, c_void_p, c_uint64, c_void_p, c_uint32, c_void_p, c_int, c_int]
+        lib.iris_cpu_translate_checked.restype = c_uint64
+        lib.iris_cpu_translate_checked.argtypes = [c_uint64, c_void_p, c_uint64, c_int, c_int, c_int, c_void_p]
         lib.iris_cpu_wait_flag.restype = c_uint32
         lib.iris_cpu_wait_flag.argtypes = [c_void_p, c_uint32, c_uint64, c_void_p, c_uint32]
         lib._iris_typed = True

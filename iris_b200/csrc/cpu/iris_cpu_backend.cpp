@@ -128,6 +128,14 @@ int iris_cpu_rma(int op, int dtype, int sem, int scope, void* a, void* b, void* 
   return -1;
 }
 
+// Checking pointer translation (iris::translate_checked): returns the translated address, or 0 after recording
+// kBadPointer / kBadRank in `st` when `ptr` is outside the caller's heap or `target` is not a rank.
+uint64_t iris_cpu_translate_checked(uint64_t ptr, const uint64_t* heap_bases, uint64_t heap_size, int rank, int world,
+                                    int target, StatusBlock* st) {
+  Context c{heap_bases, heap_size, 0, st, rank, world};
+  return reinterpret_cast<uint64_t>(translate_checked(reinterpret_cast<char*>(ptr), c, target, /*where=*/90));
+}
+
 // Producer side of the message-passing protocol (examples/06): copy `bytes` from local `src` into the
 // consumer's `dst`, then raise the consumer's flag to `epoch` with release semantics.
 void iris_cpu_mp_produce(const void* src, void* dst_sym, uint64_t bytes, uint32_t* flag_sym, uint32_t epoch,

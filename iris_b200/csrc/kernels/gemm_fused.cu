@@ -120,6 +120,56 @@ __device__ __forceinline__ void acc_bf16x8(float* acc, uint4 v) {
   }
 }
 
+// One piece of work of a scheduling unit: k-blocks [kb0, kb1) of `tile`.
+struct Work {
+  int tile, kb0, kb1;
+};
+
+// Persistent + stream-K schedule.  Tiles [0, dp_tiles) are taken whole, round-robin over the units (the reference's
+// `for tile_id in range(pid, total_tiles, NUM_SMS)`, examples/07_gemm_all_scatter/gemm_all_scatter.py:153).  The
+// remaining tiles form one long sequence of (tile, k-block) iterations that is cut into `sk_units` equal ranges —
+// the stream-K decomposition the reference only sketches (matmul_wrapper.py:73-103 computes its statistics, the
+// kernels never use them).  A unit's range may end in the middle of a tile; such a tile is finished by whichever
+// unit adds the last missing k-blocks (see the epilogue).
+struct WorkIter {
+  int G, dp_tiles, kblocks, next_dp;
+  long long it, end;
+  __device__ WorkIter(int unit, int G_, int total_tiles, int kblocks_, const FusedGemmParams& p)
+      : G(G_), dp_tiles(p.dp_tiles), kblocks(kblocks_), next_dp(unit), it(0), end(0) {
+    const long long S = (long long)(total_tiles - p.dp_tiles) * kblocks_;
+    if (S > 0 && unit < p.sk_units) {
+      it = S * unit / p.sk_units;
+      end = S * (unit + 1) / p.sk_units;
+    }
+  }
+  __device__ bool next(Work& w) {
+    if (next_dp < dp_tiles) {
+      w.tile = next_dp;
+      w.kb0 = 0;
+      w.kb1 = kblocks;
+      next_dp += G;
+      return true;
+    }
+    if (it < end) {
+      const int t = (int)(it / kblocks);
+      const int kb0 = (int)(it - (long long)t * kblocks);
+      const long long left = end - it;
+      const int len = (int)((long long)(kblocks - kb0) < left ? (kblocks - kb0) : left);
+      w.tile = dp_tiles + t;
+      w.kb0 = kb0;
+      w.kb1 = kb0 + len;
+      it += len;
+      return true;
+    }
+    return false;
+  }
+};
+
+__device__ __forceinline__ void red_add_v4_f32_gpu(float* p, float a, float b, float c, float d) {
+  asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
+}
+
 // Per-CTA-group configuration.  CG = 1: one CTA per 128 x 256 tile.  CG = 2: a pair of CTAs (one cluster on the
 // two SMs of a TPC) per 256 x 256 tile; each CTA loads its own 128 rows of A and its own 128 of the 256 B rows,
 // one thread of the leader CTA issues cta_group::2 MMAs that read both CTAs' shared memory, and each CTA ends up
@@ -227,7 +277,10 @@ __global__ void __launch_bounds__(kThreads, 1) fused_gemm_kernel(const __grid_co
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = unit; tile < total_tiles && ok; tile += G) {
+      WorkIter sched(unit, G, total_tiles, kblocks, p);
+      Work w;
+      while (ok && sched.next(w)) {
+        const int tile = w.tile;
         TileCoord tc = raster(tile, tiles_m, tiles_n, p.group_m);
         if (p.ag) tc.m_idx = ag_actual_m(tc.m_idx, tiles_per_shard, rank, W);
         const int row0 = tc.m_idx * TM + pr * BM;
@@ -245,7 +298,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_gemm_kernel(const __grid_co
             fence_proxy_async_all();  // peer wrote with ordinary stores; TMA reads through the async proxy
           }
         }
-        for (int kb = 0; kb < kblocks; ++kb) {
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1, p.timeout_ns, abort_flag)) {
             record_status(status, kTimeout, kSiteProducerEmpty, rank, tile, kb);
             *abort_flag = 1;
@@ -283,7 +336,10 @@ __global__ void __launch_bounds__(kThreads, 1) fused_gemm_kernel(const __grid_co
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int tile = unit; tile < total_tiles && ok; tile += G) {
+      WorkIter sched(unit, G, total_tiles, kblocks, p);
+      Work w;
+      while (ok && sched.next(w)) {
+        const int tile = w.tile;
         if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1, p.timeout_ns, abort_flag)) {
           record_status(status, kTimeout, kSiteMmaAccEmpty, rank, tile, acc);
           *abort_flag = 1;
@@ -292,7 +348,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_gemm_kernel(const __grid_co
         tc_fence_after();
         trace(p, rank, tile * CG, kTrMmaBegin);
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < kblocks; ++kb) {
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!mbar_wait(full_bar(stage), phase, p.timeout_ns, abort_flag)) {
             record_status(status, kTimeout, kSiteMmaFull, rank, tile, kb);
             *abort_flag = 1;
@@ -306,8 +362,9 @@ __global__ void __launch_bounds__(kThreads, 1) fused_gemm_kernel(const __grid_co
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint64_t a_desc = umma_desc_k_sw128(a_addr + k * UMMA_K * 2);
             const uint64_t b_desc = umma_desc_k_sw128(b_addr + k * UMMA_K * 2);
-            if (CG == 1) umma_f16_ss(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0 ? 1u : 0u);
-            else umma_f16_ss_pair(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0 ? 1u : 0u);
+            const uint32_t accumulate = (kb > w.kb0 || k > 0) ? 1u : 0u;  // the first MMA of a piece overwrites
+            if (CG == 1) umma_f16_ss(d_tmem, a_desc, b_desc, idesc, accumulate);
+            else umma_f16_ss_pair(d_tmem, a_desc, b_desc, idesc, accumulate);
           }
           // Free the ring slot (in both CTAs of a pair) once these MMAs have read it.
           if (CG == 1) {
@@ -356,12 +413,15 @@ __global__ void __launch_bounds__(kThreads, 1) fused_gemm_kernel(const __grid_co
     // output of this rank (one-shot) or of every rank (two-shot).  The part is fetched as 4 x W units of
     // 128 rows x 64 columns (16 KB): unit u = (column chunk u / W, rank offset u % W) is loaded by TMA into ring
     // buffer (count % kPullBufs); kPullBufs loads are in flight, so NVLink latency is hidden without registers.
+    // Two-shot: the rank that sums tile t.  A scheduling unit visits tiles u, u + G, u + 2G, ...; rotating the owner
+    // with the visit number gives every unit of every rank the same share of the summing work.
+    auto owner_of = [&](int t) { return ((t % G) + (t / G)) % W; };
     uint32_t pull_issued = 0, pull_done = 0;  // units issued / consumed so far by this CTA (ring position)
     auto pull_reduce = [&](int t) -> bool {
       if constexpr (!PULL) {
         return true;
       } else {
-        if (p.mode == kEpiTwoShot && (t % W) != rank) return true;
+        if (p.mode == kEpiTwoShot && owner_of(t) != rank) return true;
         const TileCoord tc = raster(t, tiles_m, tiles_n, p.group_m);
         const int m0 = tc.m_idx * TM + pr * BM, n0 = tc.n_idx * BN;
         const int units = (BN / kEpiCols) * W;
@@ -472,7 +532,10 @@ __global__ void __launch_bounds__(kThreads, 1) fused_gemm_kernel(const __grid_co
     };
 
     bool ok_all = true;
-    for (int tile = unit; tile < total_tiles; tile += G) {
+    WorkIter sched(unit, G, total_tiles, kblocks, p);
+    Work w;
+    while (sched.next(w)) {
+      const int tile = w.tile;
       TileCoord tc = raster(tile, tiles_m, tiles_n, p.group_m);
       if (p.ag) tc.m_idx = ag_actual_m(tc.m_idx, tiles_per_shard, rank, W);
       // Uniform decision for the whole epilogue group: one thread waits, everybody reads the verdict.
@@ -502,15 +565,73 @@ __global__ void __launch_bounds__(kThreads, 1) fused_gemm_kernel(const __grid_co
       const int x_base = (pulls ? 0 : rank * p.col_off_per_rank) + tc.n_idx * BN;
       const int y = tc.m_idx * TM + pr * BM;
       const int y_st = (pulls ? p.part_row0 : 0) + y;  // row inside the tmC matrix
+
+      // Stream-K: a piece that covers only part of the tile's k-blocks adds its fp32 accumulator into the tile's
+      // workspace and bumps the tile's k-block counter; the unit whose addition completes the count finishes the
+      // tile from the workspace (and leaves workspace and counter at zero for the next call).  Nobody waits.
+      const bool whole = (w.kb0 == 0 && w.kb1 == kblocks);
+      float* ws_row = nullptr;
+      if (!whole) {
+        const size_t slot = (size_t)(tile - p.dp_tiles) * CG + pr;
+        ws_row = reinterpret_cast<float*>(p.heap_base[rank] + p.ws_off) + (slot * BM + row) * BN;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN + c * 32, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            red_add_v4_f32_gpu(ws_row + c * 32 + 4 * j, __uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                               __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          if (CG == 1) mbar_arrive(acc_empty_bar(acc));
+          else mbar_arrive_cluster(mapa_shared(acc_empty_bar(acc), 0));
+        }
+        if (++acc == kAccBufs) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+        __threadfence();  // this thread's additions are visible before the count says so
+        named_barrier_sync(1, 128);
+        if (issuer) {
+          uint32_t* cnt = flag_ptr(p, rank, p.sk_flag_base + (int)slot);
+          const uint32_t len = (uint32_t)(w.kb1 - w.kb0);
+          const uint32_t old = atomic_add<Sem::acq_rel, Scope::gpu>(cnt, len, 0, 0, p.heap_base);
+          const bool fin = old + len == (uint32_t)kblocks;
+          if (fin) *cnt = 0;
+          *epi_ok = fin ? 1u : 0u;
+        }
+        named_barrier_sync(1, 128);
+        const bool fin = *epi_ok != 0;
+        named_barrier_sync(1, 128);
+        if (!fin) continue;  // another unit completes this tile
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / kEpiCols; ++c) {
         const bool live = tc.n_idx * BN + c * kEpiCols < p.N && y < p.M;  // parts past the matrix edge are skipped
         uint32_t v[kEpiCols];
+        if (!whole) {
+          // finishing a split tile: the sum of all pieces is in the workspace; read it and put zeros back
+#pragma unroll
+          for (int j = 0; j < kEpiCols / 4; ++j) {
+            float4* q = reinterpret_cast<float4*>(ws_row + c * kEpiCols + 4 * j);
+            const float4 f = __ldcg(q);
+            __stcg(q, make_float4(0.f, 0.f, 0.f, 0.f));
+            v[4 * j] = __float_as_uint(f.x);
+            v[4 * j + 1] = __float_as_uint(f.y);
+            v[4 * j + 2] = __float_as_uint(f.z);
+            v[4 * j + 3] = __float_as_uint(f.w);
+          }
+        } else {
         const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN + c * kEpiCols;
         tmem_ld_32x32b_x32(taddr, v);
         tmem_ld_32x32b_x32(taddr + 32, v + 32);
         tmem_wait_ld();
-        if (c == BN / kEpiCols - 1) {
+        }
+        if (whole && c == BN / kEpiCols - 1) {
           // The accumulator has been read completely: hand it back to the MMA warp (of the leader CTA).
           tc_fence_before();
           __syncwarp();
@@ -552,29 +673,35 @@ __global__ void __launch_bounds__(kThreads, 1) fused_gemm_kernel(const __grid_co
         }
         ebuf ^= 1;
       }
-      if (++acc == kAccBufs) {
+      if (whole && ++acc == kAccBufs) {
         acc = 0;
         acc_phase ^= 1;
       }
       if (issuer) trace(p, rank, tile * CG + pr, kTrEpiEnd);
 
       if (pulls) {
-        // The partial tile is on its way into this rank's buffer.  Sum the PREVIOUS tile first (its partials
-        // have had a whole main loop to arrive everywhere), then publish this one: by then its stores are done.
+        auto publish = [&]() {
+          if (issuer) {
+            bulk_wait<0>();
+            fence_proxy_async_all();
+            fence_sys();  // one release fence, then relaxed increments: a single flush for all ranks
+            for (int i = 0; i < W; ++i) {
+              const int t = (rank + 1 + i) % W;
+              if (p.mode == kEpiTwoShot && t != owner_of(tile)) continue;  // only the tile's owner needs to know
+              red_relaxed_sys_add(flag_ptr(p, t, p.tile_flag_base + tile * CG + pr), 1u);
+            }
+          }
+        };
+        // The partial tile is on its way into this rank's buffer.  Without split tiles every rank finishes its
+        // tiles in the same order, so the PREVIOUS tile is summed first (its partials have had a whole main loop to
+        // arrive everywhere) and this one is published afterwards, when its stores are long done.  With split
+        // tiles the finishing order differs between ranks: publish at once, then sum the previous tile.
+        if (p.sk_units > 0) publish();
         if (prev_tile >= 0 && !pull_reduce(prev_tile)) {
           ok_all = false;
           break;
         }
-        if (issuer) {
-          bulk_wait<0>();
-          fence_proxy_async_all();
-          fence_sys();  // one release fence, then relaxed increments: a single flush for all ranks
-          for (int i = 0; i < W; ++i) {
-            const int t = (rank + 1 + i) % W;
-            if (p.mode == kEpiTwoShot && t != tile % W) continue;  // only the tile's owner needs to know
-            red_relaxed_sys_add(flag_ptr(p, t, p.tile_flag_base + tile * CG + pr), 1u);
-          }
-        }
+        if (p.sk_units == 0) publish();
         prev_tile = tile;
       }
     }
@@ -750,6 +877,7 @@ struct IrisGemmDesc {
   uint64_t status_off;
   uint64_t agsrc_off;
   uint64_t trace_off;
+  uint64_t ws_off;
   uint64_t timeout_ns;
   int M, N, K;
   int ldo;
@@ -760,7 +888,8 @@ struct IrisGemmDesc {
   int mode, group_m, ag, ag_slices, store_all;
   int tile_flag_base, ag_flag_base;
   int device;
-  int cta_group;  // 1: one CTA per 128 x 256 tile; 2: a CTA pair (cluster of 2) per 256 x 256 tile
+  int cta_group;
+  int dp_tiles, sk_units, sk_flag_base;  // stream-K schedule (dp_tiles < 0: every tile whole)  // 1: one CTA per 128 x 256 tile; 2: a CTA pair (cluster of 2) per 256 x 256 tile
 };
 
 struct IrisGemmPlan {
@@ -882,6 +1011,14 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
     p.status_off = d->status_off;
     p.agsrc_off = d->agsrc_off;
     p.trace_off = d->trace_off;
+    p.ws_off = d->ws_off;
+    {
+      const int tiles = ((d->M + BM * cg - 1) / (BM * cg)) * ((d->N + BN - 1) / BN);
+      p.dp_tiles = (d->dp_tiles < 0 || d->dp_tiles > tiles || d->sk_units <= 0) ? tiles : d->dp_tiles;
+      p.sk_units = p.dp_tiles == tiles ? 0 : d->sk_units;
+      if (p.sk_units > ctas_per_rank / cg) p.sk_units = ctas_per_rank / cg;  // only units that exist take a range
+      p.sk_flag_base = d->sk_flag_base;
+    }
     p.timeout_ns = d->timeout_ns;
     p.M = d->M;
     p.N = d->N;
@@ -1077,6 +1214,8 @@ int iris_gemm_noalloc(const void* a, int64_t lda, const void* bt, int64_t ldb, v
   p.ctas_per_rank = (int)(tiles < d.sms ? tiles : d.sms);
   p.mode = kEpiOneShot;
   p.group_m = 8;
+  p.dp_tiles = (int)tiles;  // every tile is computed whole by one CTA
+  p.sk_units = 0;
   p.tile_flag_base = 16;
   p.ag_flag_base = 16;
   p.epoch = 1;

@@ -60,6 +60,7 @@ struct FusedGemmParams {
   uint64_t out_off;      // one-/two-shot: bf16 [M, ldo] final output
   uint64_t status_off;   // iris::StatusBlock
   uint64_t agsrc_off;    // all-gather prologue: gathered A [M, K] (row stride lda_full elements)
+  uint64_t ws_off;       // stream-K: fp32 workspace [split tiles * cta_group][128][256] per rank, zero between calls
   uint64_t trace_off;    // 0, or int64[tiles * cta_group][8] per rank: per-tile device timestamps (ns)
   uint64_t timeout_ns;
   int M, N, K;           // per-rank GEMM problem: C[M, N] = A[M, K] * B[N, K]^T
@@ -77,6 +78,10 @@ struct FusedGemmParams {
   int group_m;           // raster: m-tiles per group
   int ag;                // 1: A is gathered by the comm warps of this kernel (rows sharded M / world per rank)
   int ag_slices;         // column slices per 128-row chunk in the all-gather push
+  int dp_tiles;          // tiles [0, dp_tiles) are computed whole (tile = unit + i * units); the others are split
+                         // by k-blocks over `sk_units` scheduling units (stream-K), 0 = no split tiles
+  int sk_units;
+  int sk_flag_base;      // index of the per-(split tile, CTA of the group) k-block counters
   int store_all;         // store/reduce modes: 1 = push the tile to every rank, 0 = own rank only
   int tile_flag_base;    // index (uint32 units from flags_off) of the per-tile flags
   int ag_flag_base;      // index of the all-gather chunk flags: [src rank][chunk]

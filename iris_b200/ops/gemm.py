@@ -39,6 +39,7 @@ class _Desc(ctypes.Structure):
         ("ldc", ctypes.c_int64), ("c_cols", ctypes.c_int64), ("c_rows", ctypes.c_int64),
         ("flags_off", ctypes.c_uint64), ("partial_off", ctypes.c_uint64 * 2), ("out_off", ctypes.c_uint64),
         ("status_off", ctypes.c_uint64), ("agsrc_off", ctypes.c_uint64), ("trace_off", ctypes.c_uint64),
+        ("ws_off", ctypes.c_uint64),
         ("timeout_ns", ctypes.c_uint64),
         ("M", ctypes.c_int), ("N", ctypes.c_int), ("K", ctypes.c_int), ("ldo", ctypes.c_int),
         ("part_row0", ctypes.c_int * 2), ("out_row0", ctypes.c_int),
@@ -47,6 +48,7 @@ class _Desc(ctypes.Structure):
         ("mode", ctypes.c_int), ("group_m", ctypes.c_int), ("ag", ctypes.c_int), ("ag_slices", ctypes.c_int),
         ("store_all", ctypes.c_int), ("tile_flag_base", ctypes.c_int), ("ag_flag_base", ctypes.c_int),
         ("device", ctypes.c_int), ("cta_group", ctypes.c_int),
+        ("dp_tiles", ctypes.c_int), ("sk_units", ctypes.c_int), ("sk_flag_base", ctypes.c_int),
     ]
 
 
@@ -109,7 +111,7 @@ class FusedGemm:
                  store_all: bool = False, c_cols: Optional[int] = None, col_off_per_rank: int = 0,
                  out: Optional[Sequence[torch.Tensor]] = None, ag: bool = False, ag_slices: int = 8,
                  ctas_per_rank: Optional[int] = None, group_m: int = 8, timeout_ms: float = 2000.0,
-                 cta_group: Optional[int] = None, trace: bool = False):
+                 cta_group: Optional[int] = None, trace: bool = False, stream_k: Optional[bool] = None):
         self.ctxs: List[Iris] = [ctxs] if isinstance(ctxs, Iris) else list(ctxs)
         c0 = self.ctxs[0]
         if c0.backend != "cuda":
@@ -153,19 +155,38 @@ class FusedGemm:
             raise ValueError("cta_group must be 1 or 2")
         self.cta_group = cta_group
         self.ctas_per_rank = int(ctas_per_rank) if ctas_per_rank else sms // self.num_local
+        self.ctas_per_rank -= self.ctas_per_rank % cta_group
         tiles_m, tiles_n = -(-self.M // (BM * cta_group)), -(-self.N // BN)
         self.total_tiles = tiles_m * tiles_n
-        self.ctas_per_rank = max(cta_group, min(self.ctas_per_rank,
-                                                 cta_group * max(self.total_tiles, 1 if not self.ag else 8)))
-        self.ctas_per_rank -= self.ctas_per_rank % cta_group
+        kblocks = -(-self.K // BK)
+        # ---- schedule: whole tiles round-robin, plus (stream-K) a tail of tiles split by k-blocks ----
+        units = max(1, self.ctas_per_rank // cta_group)
+        T = self.total_tiles
+        waves = -(-T // units)
+        if stream_k is None:  # worth it when the last wave is poorly filled
+            stream_k = T % units != 0 and T / (waves * units) < 0.9 and not self.ag
+        self.dp_tiles, self.sk_units, sk_tiles = T, 0, 0
+        if stream_k and T % units != 0:
+            sk_tiles = T % units + (units if T >= units else 0)   # the ragged wave plus one full wave
+            sk_tiles = min(sk_tiles, T)
+            self.dp_tiles = T - sk_tiles
+            self.sk_units = max(1, min(units, (sk_tiles * kblocks) // 4))  # at least 4 k-blocks per unit
+        if self.dp_tiles == 0:
+            units = self.sk_units if self.sk_units else min(units, max(T, 1 if not self.ag else 8))
+        elif not self.sk_units:
+            units = min(units, max(T, 1 if not self.ag else 8))
+        self.ctas_per_rank = max(1, units) * cta_group
         self.store_all = bool(store_all) and self.world > 1
         pulls = mode in ("one_shot", "two_shot")
         chunks_per_shard = (self.M // self.world) // BM if self.ag else 0
         tile_flags = self.total_tiles * cta_group if pulls else 0
-        nflags = FLAG_HEADER + tile_flags + self.world * chunks_per_shard
+        sk_flags = sk_tiles * cta_group
+        nflags = FLAG_HEADER + tile_flags + self.world * chunks_per_shard + sk_flags
         # ---- symmetric allocations (identical sequence on every rank) ----
         self.flags = [c.zeros(nflags, dtype=torch.int32) for c in self.ctxs]
         self.trace = [c.zeros((self.total_tiles * cta_group, 8), dtype=torch.int64) for c in self.ctxs] if trace else None
+        self.workspace = [c.zeros((max(sk_tiles, 1) * cta_group * BM, BN), dtype=torch.float32)
+                          for c in self.ctxs] if sk_tiles else None
         self.c_cols = int(c_cols) if c_cols else self.N
         if pulls:
             # One matrix per rank holds both partial buffers (call parity) and, unless the caller brings its own,
@@ -224,6 +245,10 @@ class FusedGemm:
         d.ag_flag_base = FLAG_HEADER + tile_flags
         d.device = c0.gpu_id
         d.cta_group = cta_group
+        d.dp_tiles = self.dp_tiles if self.sk_units else -1
+        d.sk_units = self.sk_units
+        d.sk_flag_base = FLAG_HEADER + tile_flags + self.world * chunks_per_shard
+        d.ws_off = c0.offset_of(self.workspace[0]) if self.workspace else 0
         self.ag_slices = int(ag_slices)
         lib = _lib()
         self._plan = lib.iris_gemm_plan_create(ctypes.byref(d))
@@ -329,12 +354,15 @@ def matmul(a: torch.Tensor, bt: torch.Tensor, out: Optional[torch.Tensor] = None
     ctx = _private_ctx.get(dev)
     if ctx is None:
         with torch.cuda.device(dev):
-            ctx = Iris.local_world(1, heap_size=1 << 20, backend="cuda", device=dev.index)[0]
+            ctx = Iris.local_world(1, heap_size=64 << 20, backend="cuda", device=dev.index)[0]
         _private_ctx[dev] = ctx
     n = as_kmajor_bt(bt).shape[0]
     if out is None:
         out = torch.empty((a.shape[0], n), dtype=torch.bfloat16, device=dev)
+    mark = ctx.mark()
     op = FusedGemm(ctx, [a], [bt], "store", out=[out], cta_group=cta_group)
     op()
     op.close()
+    torch.cuda.current_stream(dev).synchronize()  # the plan's flags and workspace are released just below
+    ctx.reset(mark)
     return out

@@ -51,6 +51,26 @@ def test_many_tiles_per_cta_pair():
     _assert_close(out, a.float() @ bt.float().t())
 
 
+@pytest.mark.parametrize("m,n,k,cta_group", [(128, 4096, 1376, 1), (1, 4096, 1376, 1), (1024, 4096, 1376, 2),
+                                               (2304, 2560, 2048, 2), (8192, 1792, 1024, 2), (640, 1280, 4160, 1)])
+def test_stream_k_schedule(m, n, k, cta_group):
+    """Tiles split by k-blocks across CTAs, fp32 fix-up through the workspace, last contributor finishes the tile;
+    called twice: the workspace and the counters must be back at zero after every call."""
+    a, bt = _rand((m, k), 1), _rand((n, k), 2, 0.05)
+    ctx = iris.Iris.local_world(1, heap_size=256 << 20)[0]
+    out = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
+    op = G.FusedGemm(ctx, [a], [bt], "store", out=[out], cta_group=cta_group, stream_k=True)
+    assert op.sk_units > 0, "shape does not exercise the split schedule"
+    for _ in range(2):
+        out.zero_()
+        op()
+        op.check()
+        _assert_close(out, a.float() @ bt.float().t())
+    assert float(op.workspace[0].abs().sum()) == 0.0
+    op.close()
+    ctx.close()
+
+
 def test_gemm_strided_views():
     # K-shards taken as views: row pitch larger than K, base offset inside the row
     big_a, big_b = _rand((512, 4096), 3), _rand((768, 4096), 4, 0.05)
@@ -60,14 +80,15 @@ def test_gemm_strided_views():
     _assert_close(out, a.float() @ bt.float().t())
 
 
+@pytest.mark.parametrize("stream_k", [False, True])
 @pytest.mark.parametrize("cta_group", [1, 2])
 @pytest.mark.parametrize("world", [2, 4])
-def test_gemm_all_scatter_emulated(world, cta_group):
+def test_gemm_all_scatter_emulated(world, cta_group, stream_k):
     m, n_local, k = 1024, 512, 512
     ranks = iris.Iris.local_world(world, heap_size=64 << 20)
     a = _rand((m, k), 5)
     bts = [_rand((n_local, k), 10 + r, 0.05) for r in range(world)]
-    op = G.gemm_all_scatter(ranks, [a] * world, bts, cta_group=cta_group)
+    op = G.gemm_all_scatter(ranks, [a] * world, bts, cta_group=cta_group, stream_k=stream_k)
     for _ in range(3):  # cumulative flags must keep working call after call
         outs = op()
     op.check()
@@ -79,16 +100,17 @@ def test_gemm_all_scatter_emulated(world, cta_group):
 
 
 @pytest.mark.parametrize("variant", ["atomic", "one_shot", "two_shot"])
+@pytest.mark.parametrize("stream_k", [False, True])
 @pytest.mark.parametrize("cta_group", [1, 2])
 @pytest.mark.parametrize("world", [2, 4])
-def test_gemm_all_reduce_emulated(variant, world, cta_group):
+def test_gemm_all_reduce_emulated(variant, world, cta_group, stream_k):
     m, n, k_full = 640, 768, 2752
     ks = k_full // world
     ranks = iris.Iris.local_world(world, heap_size=64 << 20)
     a_full, b_full = _rand((m, k_full), 6), _rand((n, k_full), 7, 0.05)
     a = [a_full[:, r * ks:(r + 1) * ks] for r in range(world)]       # views: pitch k_full
     bt = [b_full[:, r * ks:(r + 1) * ks] for r in range(world)]
-    op = G.gemm_all_reduce(ranks, a, bt, variant=variant, cta_group=cta_group)
+    op = G.gemm_all_reduce(ranks, a, bt, variant=variant, cta_group=cta_group, stream_k=stream_k)
     for _ in range(3):
         outs = op()
     op.check()

@@ -60,8 +60,8 @@ def test_noalloc_matches_plan_entry_twice_in_a_row():
         assert rc == 0, lib.iris_gemm_last_error().decode()
         torch.cuda.synchronize()
         assert lib.iris_gemm_noalloc_status() == 0
-        # existing entry point, same mode of the same kernel, scratch on a heap
-        plan = G.FusedGemm(ctx, [a], [bt], "one_shot")
+        # existing entry point, same mode and schedule of the same kernel (single CTAs, whole tiles), scratch on a heap
+        plan = G.FusedGemm(ctx, [a], [bt], "one_shot", cta_group=1, stream_k=False)
         ref_entry = plan()[0]
         plan.check()
         _close(out, ref_entry)

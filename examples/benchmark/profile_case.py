@@ -1,0 +1,65 @@
+#!/usr/bin/env python
+"""Run a few launches of one fused kernel on ONE GPU, sized for a profiler capture (inputs above the L2 size,
+well under a few GB).  With ``--world W > 1`` the W ranks are simulated by one launch on the GPU, so the
+collective epilogue (pushes, flags, pulls) shows up in the same capture as the tensor-core tiles.
+
+    python examples/benchmark/profile_case.py --workload one_shot --world 2
+    ncu --set full --clock-control none -k regex:fused_gemm_kernel -s 1 -c 2 -o prof \\
+        python examples/benchmark/profile_case.py --workload one_shot --world 2
+
+Role in the reference: ``scripts/profile.sh`` (a rocprof-sys wrapper around one example run).
+"""
+import argparse
+import os
+import sys
+
+sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), ".."))
+from common.harness import iris, torch  # noqa: E402
+
+from iris_b200.ops import gemm as G  # noqa: E402
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--workload", default="gemm", choices=["gemm", "all_scatter", "atomic", "one_shot", "two_shot", "ag"])
+    ap.add_argument("--world", type=int, default=1)
+    ap.add_argument("-m", type=int, default=8192)
+    ap.add_argument("-n", type=int, default=3584)
+    ap.add_argument("-k", type=int, default=4096)
+    ap.add_argument("--launches", type=int, default=3)
+    ap.add_argument("--cta_group", type=int, default=0)
+    args = ap.parse_args()
+    W = args.world
+    ranks = iris.Iris.local_world(W, heap_size=(1 << 30) // max(1, W // 2))
+    g = torch.Generator(device="cuda").manual_seed(0)
+
+    def rand(r, c):
+        return (torch.randn((r, c), generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    cg = args.cta_group or None
+    m, n, k = args.m, args.n, args.k
+    if args.workload in ("gemm", "all_scatter"):
+        a = rand(m, k)
+        bts = [rand(n // W, k) for _ in range(W)]
+        op = G.gemm_all_scatter(ranks, [a] * W, bts, cta_group=cg)
+    elif args.workload == "ag":
+        bts = [rand(n // W, k) for _ in range(W)]
+        op = G.all_gather_gemm(ranks, m, bts, cta_group=cg)
+        for r in range(W):
+            op.a_full[r][r * (m // W):(r + 1) * (m // W)].copy_(rand(m // W, k))
+    else:
+        ks = k // W
+        a_full, b_full = rand(m, k), rand(n, k)
+        op = G.gemm_all_reduce(ranks, [a_full[:, r * ks:(r + 1) * ks] for r in range(W)],
+                               [b_full[:, r * ks:(r + 1) * ks] for r in range(W)], variant=args.workload,
+                               cta_group=cg)
+    for _ in range(args.launches):
+        op()
+    op.check()
+    print(f"{args.workload} W={W} {m}x{n}x{k}: {args.launches} launches, cta_group={op.cta_group}, "
+          f"ctas/rank={op.ctas_per_rank}")
+    op.close()
+    ranks[0].close()
+
+
+if __name__ == "__main__":
+    main()

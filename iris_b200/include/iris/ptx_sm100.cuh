@@ -97,6 +97,12 @@ __device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* m, int x, i
                "r"(x), "r"(y), "r"(smem_src)
                : "memory");
 }
+// 1-D bulk reduction: add `bytes` (multiple of 16) of fp32 values from shared memory into global memory.
+__device__ __forceinline__ void bulk_reduce_add_f32(void* gptr, uint32_t smem_src, uint32_t bytes) {
+  asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(gptr), "r"(smem_src),
+               "r"(bytes)
+               : "memory");
+}
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void bulk_wait_read() {

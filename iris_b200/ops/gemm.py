@@ -162,9 +162,11 @@ class FusedGemm:
         # ---- schedule: whole tiles round-robin, plus (stream-K) a tail of tiles split by k-blocks ----
         units = max(1, self.ctas_per_rank // cta_group)
         T = self.total_tiles
-        waves = -(-T // units)
-        if stream_k is None:  # worth it when the last wave is poorly filled
-            stream_k = T % units != 0 and T / (waves * units) < 0.9 and not self.ag
+        if stream_k is None:
+            # Off unless asked for: on B200 the fix-up of a split tile (fp32 partials through L2 plus a second
+            # epilogue for the finishing unit) costs more than the ragged last wave it removes, for every shape
+            # measured so far; the whole-tile schedule is the default.
+            stream_k = False
         self.dp_tiles, self.sk_units, sk_tiles = T, 0, 0
         if stream_k and T % units != 0:
             sk_tiles = T % units + (units if T >= units else 0)   # the ragged wave plus one full wave

@@ -182,13 +182,16 @@ struct Cfg {
   static constexpr int kBRows = BN / CG;
   static constexpr int kBStage = kBRows * BK * 2;
   static constexpr int kStage = kAStageBytes + kBStage;
-  static constexpr int kPullBufs = PULL ? (CG == 1 ? 3 : 4) : 0;
-  static constexpr int kTilesBytes = kStages * kStage + kEpiBufs * kEpiStageBytes + kPullBufs * kEpiStageBytes;
+  static constexpr int kPullBufs = PULL ? (CG == 1 ? 2 : 3) : 0;  // ring of fetched partial sub-tiles
+  static constexpr int kRedOutBufs = PULL ? 1 : 0;                // reducer's staging buffer for result stores
+  static constexpr int kTilesBytes =
+      kStages * kStage + (kEpiBufs + kPullBufs + kRedOutBufs) * kEpiStageBytes;
   static_assert(kTilesBytes <= kSmemTiles, "shared-memory budget");
 };
 
 template <int CG, bool PULL>
-__global__ void __launch_bounds__(kThreads, 1) fused_gemm_kernel(const __grid_constant__ FusedGemmParams p) {
+__global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
+    fused_gemm_kernel(const __grid_constant__ FusedGemmParams p) {
   using C = Cfg<CG, PULL>;
   constexpr int kStages = C::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -197,6 +200,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_gemm_kernel(const __grid_co
   const uint32_t smem_base = smem_u32(smem);
   const uint32_t epi_base = smem_base + kStages * C::kStage;
   const uint32_t pull_base = epi_base + kEpiBufs * kEpiStageBytes;
+  const uint32_t redout_base = pull_base + C::kPullBufs * kEpiStageBytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kSmemTiles);
   const uint32_t bar_base = smem_u32(bars);
   // barrier slots: full[6], empty[6], acc_full[2], acc_empty[2], pull_full[4]
@@ -208,6 +212,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_gemm_kernel(const __grid_co
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 20);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   volatile uint32_t* epi_ok = tmem_slot + 2;
+  volatile uint32_t* red_ok = tmem_slot + 3;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -228,6 +233,9 @@ __global__ void __launch_bounds__(kThreads, 1) fused_gemm_kernel(const __grid_co
   const int kblocks = (p.K + BK - 1) / BK;
   const int tiles_per_shard = p.ag ? (p.M / W) / TM : 0;
   const int chunks_per_shard = p.ag ? (p.M / W) / BM : 0;  // all-gather flags are per 128 rows
+  // Two-shot: the rank that sums tile t.  A scheduling unit visits tiles u, u + G, u + 2G, ...; rotating the owner
+  // with the visit number gives every unit of every rank the same share of the summing work.
+  auto owner_of = [&](int t) { return ((t % G) + (t / G)) % W; };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -241,6 +249,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_gemm_kernel(const __grid_co
     for (int b = 0; b < C::kPullBufs; ++b) mbar_init(pull_full_bar(b), 1);
     *abort_flag = 0;
     *epi_ok = 1;
+    *red_ok = 1;
     mbar_fence_init();
     prefetch_tensormap(&p.tmA[lr]);
     prefetch_tensormap(&p.tmB[lr]);
@@ -402,135 +411,24 @@ __global__ void __launch_bounds__(kThreads, 1) fused_gemm_kernel(const __grid_co
     const int row = quad * 32 + lane;   // row of the tile held by this thread
     const bool pulls = (p.mode == kEpiOneShot || p.mode == kEpiTwoShot);
     const bool push_all = (p.mode == kEpiStore || p.mode == kEpiReduce) && p.store_all && W > 1;
-    const bool need_entry = W > 1 && (push_all || p.mode == kEpiTwoShot);
+    const bool need_entry = W > 1 && push_all;  // two-shot pushes are made (and guarded) by the reducer warps
     int acc = 0;
     uint32_t acc_phase = 0;
     int ebuf = 0;
-    int prev_tile = -1;
+    int pending_tile = -1;  // one-/two-shot: tile whose partial is stored but not yet published
     bool entered = !need_entry;
 
-    // Sum this CTA's 128 x 256 part of tile `t` over the partial buffers of all ranks (fp32) and write bf16 to the
-    // output of this rank (one-shot) or of every rank (two-shot).  The part is fetched as 4 x W units of
-    // 128 rows x 64 columns (16 KB): unit u = (column chunk u / W, rank offset u % W) is loaded by TMA into ring
-    // buffer (count % kPullBufs); kPullBufs loads are in flight, so NVLink latency is hidden without registers.
-    // Two-shot: the rank that sums tile t.  A scheduling unit visits tiles u, u + G, u + 2G, ...; rotating the owner
-    // with the visit number gives every unit of every rank the same share of the summing work.
-    auto owner_of = [&](int t) { return ((t % G) + (t / G)) % W; };
-    uint32_t pull_issued = 0, pull_done = 0;  // units issued / consumed so far by this CTA (ring position)
-    auto pull_reduce = [&](int t) -> bool {
-      if constexpr (!PULL) {
-        return true;
-      } else {
-        if (p.mode == kEpiTwoShot && owner_of(t) != rank) return true;
-        const TileCoord tc = raster(t, tiles_m, tiles_n, p.group_m);
-        const int m0 = tc.m_idx * TM + pr * BM, n0 = tc.n_idx * BN;
-        const int units = (BN / kEpiCols) * W;
-        auto issue = [&](int u) {  // issuer only
-          const int c = u / W, sft = u - c * W;
-          const uint32_t b = pull_issued % C::kPullBufs;
-          mbar_expect_tx(pull_full_bar(b), kEpiStageBytes);
-          tma_load_2d(pull_base + b * kEpiStageBytes, &p.tmC[(rank + sft) % W], n0 + c * kEpiCols, p.part_row0 + m0,
-                      pull_full_bar(b));
-          ++pull_issued;
-        };
-        if (issuer) {
-          const uint32_t* f = flag_ptr(p, rank, p.tile_flag_base + t * CG + pr);
-          trace(p, rank, t * CG + pr, kTrWaitBegin);
-          bool ok = wait_until_ge(f, p.flag_target, p.timeout_ns, status, kSiteEpiTileFlag, rank, t) == kOk;
-          trace(p, rank, t * CG + pr, kTrWaitEnd);
-          if (ok) {
-            fence_proxy_async_all();  // the flag was acquired with ordinary loads; the data is read by TMA
-            for (int u = 0; u < units && u < C::kPullBufs; ++u) issue(u);
-            ok = mbar_wait(pull_full_bar(pull_done % C::kPullBufs), (pull_done / C::kPullBufs) & 1, p.timeout_ns,
-                           abort_flag);
-            if (!ok) record_status(status, kTimeout, kSitePullFull, rank, t, 0);
-          }
-          *epi_ok = ok ? 1u : 0u;
-        }
-        float accv[kEpiCols];
-        for (int u = 0; u < units; ++u) {
-          named_barrier_sync(1, 128);  // unit u has landed (or the wait failed): verdict is in epi_ok
-          if (*epi_ok == 0) return false;
-          const int c = u / W, sft = u - c * W;
-          const uint32_t buf = pull_base + (pull_done % C::kPullBufs) * kEpiStageBytes + row * 128;
-          if (sft == 0) {
-#pragma unroll
-            for (int j = 0; j < kEpiCols; ++j) accv[j] = 0.f;
-          }
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            uint4 v;
-            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                         : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                         : "r"(buf + ((j ^ (row & 7)) << 4)));
-            acc_bf16x8(accv + 8 * j, v);
-          }
-          ++pull_done;
-          named_barrier_sync(1, 128);  // every thread has read the buffer: it can be refilled
-          if (issuer) {
-            if (u + C::kPullBufs < units) issue(u + C::kPullBufs);
-            if (u + 1 < units) {
-              const bool ok = mbar_wait(pull_full_bar(pull_done % C::kPullBufs), (pull_done / C::kPullBufs) & 1,
-                                        p.timeout_ns, abort_flag);
-              if (!ok) record_status(status, kTimeout, kSitePullFull, rank, t, u + 1);
-              *epi_ok = ok ? 1u : 0u;
-            }
-          }
-          if (sft == W - 1) {
-            if (p.out_row0 >= 0) {
-              // Result sub-tile -> swizzled staging buffer -> TMA store into the output of this rank (one-shot)
-              // or of every rank (two-shot): full 128-byte rows on the wire instead of 16-byte fragments.
-              if (issuer) bulk_wait_read<kEpiBufs - 1>();
-              named_barrier_sync(1, 128);
-              const uint32_t sbase = epi_base + ebuf * kEpiStageBytes + row * 128;
-#pragma unroll
-              for (int j = 0; j < 8; ++j)
-                st_shared_v4(sbase + ((j ^ (row & 7)) << 4), pack_bf16x2(accv[8 * j + 0], accv[8 * j + 1]),
-                             pack_bf16x2(accv[8 * j + 2], accv[8 * j + 3]), pack_bf16x2(accv[8 * j + 4], accv[8 * j + 5]),
-                             pack_bf16x2(accv[8 * j + 6], accv[8 * j + 7]));
-              fence_proxy_async_smem();
-              named_barrier_sync(1, 128);
-              if (issuer) {
-                const uint32_t src = epi_base + ebuf * kEpiStageBytes;
-                const int x = n0 + c * kEpiCols, yy = p.out_row0 + m0;
-                if (p.mode == kEpiOneShot) {
-                  tma_store_2d(&p.tmC[rank], x, yy, src);
-                } else {
-                  for (int q = 0; q < W; ++q) tma_store_2d(&p.tmC[(rank + 1 + q) % W], x, yy, src);
-                }
-                bulk_commit();
-              }
-              ebuf ^= 1;
-            } else {
-              const int r = m0 + row;
-              if (r < p.M) {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                  const int col = n0 + c * kEpiCols + 8 * j;
-                  if (col < p.N) {
-                    uint4 o;
-                    o.x = pack_bf16x2(accv[8 * j + 0], accv[8 * j + 1]);
-                    o.y = pack_bf16x2(accv[8 * j + 2], accv[8 * j + 3]);
-                    o.z = pack_bf16x2(accv[8 * j + 4], accv[8 * j + 5]);
-                    o.w = pack_bf16x2(accv[8 * j + 6], accv[8 * j + 7]);
-                    const uint64_t ooff = p.out_off + ((uint64_t)r * p.ldo + col) * 2;
-                    if (p.mode == kEpiOneShot) {
-                      st_v4(reinterpret_cast<uint4*>(p.heap_base[rank] + ooff), o);
-                    } else {
-                      for (int q = 0; q < W; ++q)
-                        st_v4(reinterpret_cast<uint4*>(p.heap_base[(rank + 1 + q) % W] + ooff), o);
-                    }
-                  }
-                }
-              }
-            }
-          }
-        }
-        if (issuer) trace(p, rank, t * CG + pr, kTrPullEnd);
-        return true;
+    // Make a stored partial tile known: one release fence, then a relaxed increment of the tile's flag on every rank
+    // (two-shot: only on the rank that sums the tile).  Called by the issuer after the tile's stores completed.
+    auto publish_tile = [&](int t) {
+      fence_proxy_async_all();
+      fence_sys();
+      for (int i = 0; i < W; ++i) {
+        const int dst = (rank + 1 + i) % W;
+        if (p.mode == kEpiTwoShot && dst != owner_of(t)) continue;
+        red_relaxed_sys_add(flag_ptr(p, dst, p.tile_flag_base + t * CG + pr), 1u);
       }
     };
-
     bool ok_all = true;
     WorkIter sched(unit, G, total_tiles, kblocks, p);
     Work w;
@@ -569,6 +467,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_gemm_kernel(const __grid_co
       // Stream-K: a piece that covers only part of the tile's k-blocks adds its fp32 accumulator into the tile's
       // workspace and bumps the tile's k-block counter; the unit whose addition completes the count finishes the
       // tile from the workspace (and leaves workspace and counter at zero for the next call).  Nobody waits.
+      int groups_this_tile = 0;  // bulk groups the issuer committed for this tile
       const bool whole = (w.kb0 == 0 && w.kb1 == kblocks);
       float* ws_row = nullptr;
       if (!whole) {
@@ -670,6 +569,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_gemm_kernel(const __grid_co
             tma_store_2d(&p.tmC[rank], x, y_st, src);
           }
           bulk_commit();
+          ++groups_this_tile;
         }
         ebuf ^= 1;
       }
@@ -680,41 +580,29 @@ __global__ void __launch_bounds__(kThreads, 1) fused_gemm_kernel(const __grid_co
       if (issuer) trace(p, rank, tile * CG + pr, kTrEpiEnd);
 
       if (pulls) {
-        auto publish = [&]() {
-          if (issuer) {
-            bulk_wait<0>();
-            fence_proxy_async_all();
-            fence_sys();  // one release fence, then relaxed increments: a single flush for all ranks
-            for (int i = 0; i < W; ++i) {
-              const int t = (rank + 1 + i) % W;
-              if (p.mode == kEpiTwoShot && t != owner_of(tile)) continue;  // only the tile's owner needs to know
-              red_relaxed_sys_add(flag_ptr(p, t, p.tile_flag_base + tile * CG + pr), 1u);
-            }
+        // The partial tile is on its way into this rank's buffer.  Publishing needs its stores to be complete;
+        // rather than wait for them now, publish the PREVIOUS tile (its stores are the ones before the up to four
+        // groups just committed) and keep this one pending.  The reducer warps do the summing, concurrently.
+        if (issuer) {
+          if (pending_tile >= 0) {
+            if (groups_this_tile == BN / kEpiCols) bulk_wait<BN / kEpiCols>();
+            else bulk_wait<0>();
+            publish_tile(pending_tile);
           }
-        };
-        // The partial tile is on its way into this rank's buffer.  Without split tiles every rank finishes its
-        // tiles in the same order, so the PREVIOUS tile is summed first (its partials have had a whole main loop to
-        // arrive everywhere) and this one is published afterwards, when its stores are long done.  With split
-        // tiles the finishing order differs between ranks: publish at once, then sum the previous tile.
-        if (p.sk_units > 0) publish();
-        if (prev_tile >= 0 && !pull_reduce(prev_tile)) {
-          ok_all = false;
-          break;
         }
-        if (p.sk_units == 0) publish();
-        prev_tile = tile;
+        pending_tile = tile;
       }
     }
-    if (pulls && ok_all && prev_tile >= 0) ok_all = pull_reduce(prev_tile);
+    if (pulls && issuer && pending_tile >= 0) {
+      bulk_wait<0>();
+      publish_tile(pending_tile);
+    }
     if (!ok_all && issuer) *abort_flag = 1;
 
     // Completion: all pushes of this CTA have landed -> bump every rank's arrival counter; then wait until
     // every CTA of every rank has done the same, so that at kernel end all remote tiles are in local memory.
-    const bool end_sync = W > 1 && (push_all || p.mode == kEpiTwoShot);
+    const bool end_sync = push_all;
     if (end_sync) {
-      if (p.mode == kEpiTwoShot) {
-        fence_sys();  // every thread pushed result vectors with ordinary stores
-      }
       named_barrier_sync(1, 128);
       if (issuer) {
         bulk_wait<0>();
@@ -727,6 +615,155 @@ __global__ void __launch_bounds__(kThreads, 1) fused_gemm_kernel(const __grid_co
       bulk_wait<0>();
     }
   } else {
+    if constexpr (PULL) {
+      // ------------------------------------------------------------------------------------------
+      // Reducer (128 threads, warps 6-9): sums partial tiles over all ranks while the other warps keep computing.
+      // It handles tiles unit, unit + G, ... (two-shot: those this rank owns).  For each, it waits (bounded) for
+      // the tile's flag, fetches this CTA's 128 x 256 part as 4 x W units of 128 rows x 64 columns (16 KB) with
+      // TMA loads into a ring of pull buffers (a peer's memory included, no multicast), adds in fp32, and writes
+      // the bf16 result with TMA stores into the output of this rank (one-shot) or of every rank (two-shot).
+      // ------------------------------------------------------------------------------------------
+      const int rt = threadIdx.x - 192;
+      const bool rissuer = (rt == 0);
+      const int row = rt;
+      const bool two_shot = p.mode == kEpiTwoShot;
+      uint32_t pull_issued = 0, pull_done = 0;  // units issued / consumed so far (ring position)
+      bool entered = !(two_shot && W > 1);
+      bool ok_all = true;
+      float accv[kEpiCols];
+      for (int t = unit; t < total_tiles && ok_all; t += G) {
+        if (two_shot && owner_of(t) != rank) continue;
+        const TileCoord tc = raster(t, tiles_m, tiles_n, p.group_m);
+        const int m0 = tc.m_idx * TM + pr * BM, n0 = tc.n_idx * BN;
+        const int units = (BN / kEpiCols) * W;
+        auto issue = [&](int u) {  // reducer's issuer only
+          const int c = u / W, sft = u - c * W;
+          const uint32_t b = pull_issued % C::kPullBufs;
+          mbar_expect_tx(pull_full_bar(b), kEpiStageBytes);
+          tma_load_2d(pull_base + b * kEpiStageBytes, &p.tmC[(rank + sft) % W], n0 + c * kEpiCols, p.part_row0 + m0,
+                      pull_full_bar(b));
+          ++pull_issued;
+        };
+        if (rissuer) {
+          const uint32_t* f = flag_ptr(p, rank, p.tile_flag_base + t * CG + pr);
+          trace(p, rank, t * CG + pr, kTrWaitBegin);
+          bool ok = wait_until_ge(f, p.flag_target, p.timeout_ns, status, kSiteEpiTileFlag, rank, t) == kOk;
+          if (ok && !entered) {
+            // before the first push of this call: every peer must have entered the call
+            for (int i = 0; i < W && ok; ++i) {
+              const int q = (rank + 1 + i) % W;
+              ok = wait_until_ge(flag_ptr(p, rank, 8 + q), p.epoch, p.timeout_ns, status, kSiteEpiEntry, rank, q) == kOk;
+            }
+          }
+          trace(p, rank, t * CG + pr, kTrWaitEnd);
+          if (ok) {
+            fence_proxy_async_all();  // the flag was acquired with ordinary loads; the data is read by TMA
+            for (int u = 0; u < units && u < C::kPullBufs; ++u) issue(u);
+            ok = mbar_wait(pull_full_bar(pull_done % C::kPullBufs), (pull_done / C::kPullBufs) & 1, p.timeout_ns,
+                           abort_flag);
+            if (!ok) record_status(status, kTimeout, kSitePullFull, rank, t, 0);
+          }
+          *red_ok = ok ? 1u : 0u;
+        }
+        entered = true;
+        for (int u = 0; u < units; ++u) {
+          named_barrier_sync(3, 128);  // unit u has landed (or the wait failed): the verdict is in red_ok
+          if (*red_ok == 0) {
+            ok_all = false;
+            break;
+          }
+          const int c = u / W, sft = u - c * W;
+          const uint32_t buf = pull_base + (pull_done % C::kPullBufs) * kEpiStageBytes + row * 128;
+          if (sft == 0) {
+#pragma unroll
+            for (int j = 0; j < kEpiCols; ++j) accv[j] = 0.f;
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            uint4 v;
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                         : "r"(buf + ((j ^ (row & 7)) << 4)));
+            acc_bf16x8(accv + 8 * j, v);
+          }
+          ++pull_done;
+          if (sft == W - 1 && p.out_row0 >= 0) {
+            // the result staging buffer must have been read by the previous chunk's stores
+            if (rissuer) bulk_wait_read<0>();
+          }
+          named_barrier_sync(3, 128);  // every thread has read the pull buffer: it can be refilled
+          if (rissuer) {
+            if (u + C::kPullBufs < units) issue(u + C::kPullBufs);
+            if (u + 1 < units) {
+              const bool ok = mbar_wait(pull_full_bar(pull_done % C::kPullBufs), (pull_done / C::kPullBufs) & 1,
+                                        p.timeout_ns, abort_flag);
+              if (!ok) record_status(status, kTimeout, kSitePullFull, rank, t, u + 1);
+              *red_ok = ok ? 1u : 0u;
+            }
+          }
+          if (sft != W - 1) continue;
+          if (p.out_row0 >= 0) {
+            // Result sub-tile -> swizzled staging buffer -> TMA store: full 128-byte rows on the wire.
+            const uint32_t sbase = redout_base + row * 128;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              st_shared_v4(sbase + ((j ^ (row & 7)) << 4), pack_bf16x2(accv[8 * j + 0], accv[8 * j + 1]),
+                           pack_bf16x2(accv[8 * j + 2], accv[8 * j + 3]), pack_bf16x2(accv[8 * j + 4], accv[8 * j + 5]),
+                           pack_bf16x2(accv[8 * j + 6], accv[8 * j + 7]));
+            fence_proxy_async_smem();
+            named_barrier_sync(3, 128);
+            if (rissuer) {
+              const int x = n0 + c * kEpiCols, yy = p.out_row0 + m0;
+              if (!two_shot) {
+                tma_store_2d(&p.tmC[rank], x, yy, redout_base);
+              } else {
+                for (int q = 0; q < W; ++q) tma_store_2d(&p.tmC[(rank + 1 + q) % W], x, yy, redout_base);
+              }
+              bulk_commit();
+            }
+          } else {
+            // the output is a separate buffer of the caller: ordinary 16-byte stores
+            const int r = m0 + row;
+            if (r < p.M) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const int col = n0 + c * kEpiCols + 8 * j;
+                if (col < p.N) {
+                  uint4 o;
+                  o.x = pack_bf16x2(accv[8 * j + 0], accv[8 * j + 1]);
+                  o.y = pack_bf16x2(accv[8 * j + 2], accv[8 * j + 3]);
+                  o.z = pack_bf16x2(accv[8 * j + 4], accv[8 * j + 5]);
+                  o.w = pack_bf16x2(accv[8 * j + 6], accv[8 * j + 7]);
+                  const uint64_t ooff = p.out_off + ((uint64_t)r * p.ldo + col) * 2;
+                  if (!two_shot) {
+                    st_v4(reinterpret_cast<uint4*>(p.heap_base[rank] + ooff), o);
+                  } else {
+                    for (int q = 0; q < W; ++q) st_v4(reinterpret_cast<uint4*>(p.heap_base[(rank + 1 + q) % W] + ooff), o);
+                  }
+                }
+              }
+            }
+          }
+        }
+        if (rissuer && ok_all) trace(p, rank, t * CG + pr, kTrPullEnd);
+      }
+      if (!ok_all && rissuer) *abort_flag = 1;
+      // Two-shot: when this CTA's pushes have landed, bump every rank's arrival counter and wait (bounded) until
+      // every CTA of every rank has done so: at kernel end all result tiles are in local memory.
+      if (two_shot && W > 1) {
+        fence_sys();
+        named_barrier_sync(3, 128);
+        if (rissuer) {
+          bulk_wait<0>();
+          fence_proxy_async_all();
+          fence_sys();
+          for (int i = 0; i < W; ++i) red_release_sys_add(flag_ptr(p, (rank + 1 + i) % W, 0), 1u);
+          if (ok_all) wait_until_ge(flag_ptr(p, rank, 0), p.done_target, p.timeout_ns, status, kSiteDone, rank, cta);
+        }
+      } else if (rissuer) {
+        bulk_wait<0>();
+      }
+    } else {
     // ------------------------------------------------------------------------------------------
     // All-gather push (64 threads): this rank's rows of A -> the same rows of every peer's gathered A.
     // ------------------------------------------------------------------------------------------
@@ -771,6 +808,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_gemm_kernel(const __grid_co
         named_barrier_sync(2, 64);
         if (ct == 0) red_release_sys_add(flag_ptr(p, peer, p.ag_flag_base + rank * chunks_per_shard + chunk), 1u);
       }
+    }
     }
   }
 
@@ -953,7 +991,7 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3(ctas_per_rank * d->num_local);
-    cfg.blockDim = dim3(kThreads);
+    cfg.blockDim = dim3(pull ? kThreadsPull : kThreads);
     cfg.dynamicSmemBytes = kSmemBytes;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -1064,7 +1102,7 @@ int iris_gemm_plan_launch(void* h, int parity, uint32_t epoch, uint32_t flag_tar
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3(plan->grid);
-    cfg.blockDim = dim3(kThreads);
+    cfg.blockDim = dim3(plan->pull ? kThreadsPull : kThreads);
     cfg.dynamicSmemBytes = kSmemBytes;
     cfg.stream = st;
     cudaLaunchAttribute attr[2];
@@ -1089,11 +1127,11 @@ int iris_gemm_plan_launch(void* h, int parity, uint32_t epoch, uint32_t flag_tar
   } else if (plan->cooperative) {
     void* args[] = {&p};
     e = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(kernel_for(1, plan->pull != 0)), dim3(plan->grid),
-                                    dim3(kThreads), args, kSmemBytes, st);
+                                    dim3(plan->pull ? kThreadsPull : kThreads), args, kSmemBytes, st);
   } else {
     void* args[] = {&p};
-    e = cudaLaunchKernel(reinterpret_cast<void*>(kernel_for(1, plan->pull != 0)), dim3(plan->grid), dim3(kThreads),
-                         args, kSmemBytes, st);
+    e = cudaLaunchKernel(reinterpret_cast<void*>(kernel_for(1, plan->pull != 0)), dim3(plan->grid),
+                         dim3(plan->pull ? kThreadsPull : kThreads), args, kSmemBytes, st);
   }
   if (e != cudaSuccess) {
     snprintf(g_err, sizeof(g_err), "launch failed: %s", cudaGetErrorString(e));
@@ -1226,7 +1264,7 @@ int iris_gemm_noalloc(const void* a, int64_t lda, const void* bt, int64_t ldb, v
   // The scratch keeps the previous call's flags and status: clear what has to start at zero, in stream order.
   cudaError_t e = cudaMemsetAsync(d.scratch, 0, kNoAllocPartialOff, st);
   if (e == cudaSuccess) {
-    fused_gemm_kernel<1, true><<<p.ctas_per_rank, kThreads, kSmemBytes, st>>>(p);
+    fused_gemm_kernel<1, true><<<p.ctas_per_rank, kThreadsPull, kSmemBytes, st>>>(p);
     e = cudaGetLastError();
   }
   if (e != cudaSuccess) {

@@ -639,7 +639,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
         auto issue = [&](int u) {  // reducer's issuer only
           const int c = u / W, sft = u - c * W;
           const uint32_t b = pull_issued % C::kPullBufs;
-          mbar_expect_tx(pull_full_bar(b), kEpiStageBytes);
+          mbar_expect_tx(pull_full_bar(b), p.c_box_bytes);
           tma_load_2d(pull_base + b * kEpiStageBytes, &p.tmC[(rank + sft) % W], n0 + c * kEpiCols, p.part_row0 + m0,
                       pull_full_bar(b));
           ++pull_issued;
@@ -977,6 +977,8 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
   int sms = 0;
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, d->device);
   const bool pull = d->mode == kEpiOneShot || d->mode == kEpiTwoShot;
+  // Short matrices move short sub-tiles: the C / partial box has only as many rows as M needs (multiple of 8).
+  const uint32_t c_box_rows = d->M >= BM ? BM : (uint32_t)((d->M + 7) / 8 * 8);
   int ctas_per_rank = d->ctas_per_rank - d->ctas_per_rank % cg;
   {
     cudaError_t e = cudaFuncSetAttribute(kernel_for(cg, pull),
@@ -1037,7 +1039,7 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
     for (int t = 0; t < d->world; ++t) {
       const uint64_t cp = (par == 1 && d->c2_ptr[t]) ? d->c2_ptr[t] : d->c_ptr[t];
       if (!cp) continue;
-      if (encode_2d(&p.tmC[t], cp, d->c_rows > 0 ? d->c_rows : d->M, d->c_cols, d->ldc, kEpiCols, BM, "C")) {
+      if (encode_2d(&p.tmC[t], cp, d->c_rows > 0 ? d->c_rows : d->M, d->c_cols, d->ldc, kEpiCols, c_box_rows, "C")) {
         delete plan;
         return nullptr;
       }
@@ -1049,6 +1051,7 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
     p.status_off = d->status_off;
     p.agsrc_off = d->agsrc_off;
     p.trace_off = d->trace_off;
+    p.c_box_bytes = c_box_rows * 128u;
     p.ws_off = d->ws_off;
     {
       const int tiles = ((d->M + BM * cg - 1) / (BM * cg)) * ((d->N + BN - 1) / BN);
@@ -1244,6 +1247,7 @@ int iris_gemm_noalloc(const void* a, int64_t lda, const void* bt, int64_t ldb, v
   p.N = N;
   p.K = K;
   p.ldo = (int)ldo;
+  p.c_box_bytes = BM * 128u;
   p.part_row0 = 0;
   p.out_row0 = -1;  // the caller's output is a separate buffer: ordinary stores
   p.world = 1;

@@ -86,6 +86,7 @@ struct FusedGemmParams {
   int store_all;         // store/reduce modes: 1 = push the tile to every rank, 0 = own rank only
   int tile_flag_base;    // index (uint32 units from flags_off) of the per-tile flags
   int ag_flag_base;      // index of the all-gather chunk flags: [src rank][chunk]
+  uint32_t c_box_bytes;  // bytes of one C / partial sub-tile transfer: rows of the tmC box (128, fewer when M < 128) x 128
   uint32_t epoch;        // call number (1, 2, ...): value of the entry flags in this call
   uint32_t flag_target;  // value per-tile / per-chunk flags reach in this call (cumulative over calls)
   uint32_t done_target;  // value the arrival counter reaches when every CTA of every rank has finished

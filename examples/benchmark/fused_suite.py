@@ -58,7 +58,7 @@ def main():
             row = {"bytes": size}
             for name, fn in (("load", lambda: p2p.load(ctx, big, loc, target=1, nbytes=size)),
                              ("store", lambda: p2p.store(ctx, big, target=1, nbytes=size))):
-                ms = time_kernel_ms(ctx, fn, 2, 10, active=(rank == 0))
+                ms = time_kernel_ms(ctx, fn, 2, 10, active=(rank == 0), busy=True)
                 row[name + "_gbs"] = ctx.broadcast(size / (ms * 1e-3) / 1e9 if rank == 0 and ms > 0 else 0.0, 0)
             sweep.append(row)
             log(f"p2p 0->1 {size:>11d} B  load {row['load_gbs']:8.1f} GB/s  store {row['store_gbs']:8.1f} GB/s")

@@ -45,17 +45,19 @@ def device_barrier(ctx):
     return b
 
 
-def time_kernel_ms(ctx, fn, n_warmup: int, n_repeat: int, active: bool = True, align: bool = False) -> float:
+def time_kernel_ms(ctx, fn, n_warmup: int, n_repeat: int, active: bool = True, align: bool = False,
+                   busy: bool = False) -> float:
     """Mean device time of ``fn`` in ms on the ranks where ``active``; every rank takes part in the barriers
     (``iris/util.py:62-104``: barrier, then event / launch / event, every iteration).  With ``align`` a
     device-side barrier kernel runs on every rank right before the start event, so the ranks' streams start the
-    timed launch together and host launch skew is not charged to a kernel that waits for its peers."""
+    timed launch together and host launch skew is not charged to a kernel that waits for its peers.  ``busy`` alone
+    only keeps the GPU occupied while the host enqueues, so that a short kernel is not timed with launch latency."""
     dbar = device_barrier(ctx) if align else None
     e0 = [torch.cuda.Event(enable_timing=True) for _ in range(n_repeat)]
     e1 = [torch.cuda.Event(enable_timing=True) for _ in range(n_repeat)]
     for i in range(-n_warmup, n_repeat):
         ctx.barrier()
-        if align:
+        if align or busy:
             # Keep the GPU busy while the host enqueues [barrier, event, launch, event]: otherwise a short kernel is
             # timed together with the host's launch latency.
             torch.cuda._sleep(300000)

@@ -123,6 +123,7 @@ __device__ __forceinline__ void acc_bf16x8(float* acc, uint4 v) {
 // One piece of work of a scheduling unit: k-blocks [kb0, kb1) of `tile`.
 struct Work {
   int tile, kb0, kb1;
+  int piece;  // K-split piece of the tile (0 when tiles are not K-split into slots)
 };
 
 // Persistent + stream-K schedule.  Tiles [0, dp_tiles) are taken whole, round-robin over the units (the reference's
@@ -132,10 +133,11 @@ struct Work {
 // kernels never use them).  A unit's range may end in the middle of a tile; such a tile is finished by whichever
 // unit adds the last missing k-blocks (see the epilogue).
 struct WorkIter {
-  int G, dp_tiles, kblocks, next_dp;
+  int G, dp_tiles, kblocks, next_dp, ksplit, items;
   long long it, end;
   __device__ WorkIter(int unit, int G_, int total_tiles, int kblocks_, const FusedGemmParams& p)
-      : G(G_), dp_tiles(p.dp_tiles), kblocks(kblocks_), next_dp(unit), it(0), end(0) {
+      : G(G_), dp_tiles(p.dp_tiles), kblocks(kblocks_), next_dp(unit), ksplit(p.ksplit > 1 ? p.ksplit : 1),
+        items(total_tiles * (p.ksplit > 1 ? p.ksplit : 1)), it(0), end(0) {
     const long long S = (long long)(total_tiles - p.dp_tiles) * kblocks_;
     if (S > 0 && unit < p.sk_units) {
       it = S * unit / p.sk_units;
@@ -143,6 +145,17 @@ struct WorkIter {
     }
   }
   __device__ bool next(Work& w) {
+    w.piece = 0;
+    if (ksplit > 1) {
+      // K-split into inbox slots: item i = (tile i / ksplit, piece i % ksplit), each a fixed slice of the k-blocks
+      if (next_dp >= items) return false;
+      w.tile = next_dp / ksplit;
+      w.piece = next_dp - w.tile * ksplit;
+      w.kb0 = (int)((long long)kblocks * w.piece / ksplit);
+      w.kb1 = (int)((long long)kblocks * (w.piece + 1) / ksplit);
+      next_dp += G;
+      return true;
+    }
     if (next_dp < dp_tiles) {
       w.tile = next_dp;
       w.kb0 = 0;
@@ -410,8 +423,11 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
     const int quad = warp & 3;          // tensor-memory lane quadrant this warp may read
     const int row = quad * 32 + lane;   // row of the tile held by this thread
     const bool pulls = (p.mode == kEpiOneShot || p.mode == kEpiTwoShot);
-    const bool push_all = (p.mode == kEpiStore || p.mode == kEpiReduce) && p.store_all && W > 1;
-    const bool need_entry = W > 1 && push_all;  // two-shot pushes are made (and guarded) by the reducer warps
+    const bool push_all =
+        ((p.mode == kEpiStore || p.mode == kEpiReduce) && p.store_all && W > 1) || (pulls && p.push_partials && W > 1);
+    // Pushes into a peer's output wait for the peer to enter the call; inbox slots alternate by call parity and need
+    // no such guard; two-shot result pushes are made (and guarded) by the reducer warps.
+    const bool need_entry = W > 1 && push_all && !pulls;
     int acc = 0;
     uint32_t acc_phase = 0;
     int ebuf = 0;
@@ -462,13 +478,15 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
 
       const int x_base = (pulls ? 0 : rank * p.col_off_per_rank) + tc.n_idx * BN;
       const int y = tc.m_idx * TM + pr * BM;
-      const int y_st = (pulls ? p.part_row0 : 0) + y;  // row inside the tmC matrix
+      // row inside the tmC matrix: partial buffer of this call's parity, inbox slot of (rank, piece) when pushing
+      const int slot = p.push_partials ? rank * (p.ksplit > 1 ? p.ksplit : 1) + w.piece : 0;
+      const int y_st = (pulls ? p.part_row0 + slot * p.part_slot_rows : 0) + y;
 
       // Stream-K: a piece that covers only part of the tile's k-blocks adds its fp32 accumulator into the tile's
       // workspace and bumps the tile's k-block counter; the unit whose addition completes the count finishes the
       // tile from the workspace (and leaves workspace and counter at zero for the next call).  Nobody waits.
       int groups_this_tile = 0;  // bulk groups the issuer committed for this tile
-      const bool whole = (w.kb0 == 0 && w.kb1 == kblocks);
+      const bool whole = (w.kb0 == 0 && w.kb1 == kblocks) || p.ksplit > 1;  // a K-split piece is a slot of its own
       float* ws_row = nullptr;
       if (!whole) {
         const size_t slot = (size_t)(tile - p.dp_tiles) * CG + pr;
@@ -560,8 +578,8 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
           if (push_all) {
             for (int i = 0; i < W; ++i) {  // peers first, starting with the next rank; own copy last
               const int t = (rank + 1 + i) % W;
-              if (p.mode == kEpiStore) tma_store_2d(&p.tmC[t], x, y_st, src);
-              else tma_reduce_add_2d(&p.tmC[t], x, y_st, src);
+              if (p.mode == kEpiReduce) tma_reduce_add_2d(&p.tmC[t], x, y_st, src);
+              else tma_store_2d(&p.tmC[t], x, y_st, src);
             }
           } else if (p.mode == kEpiReduce) {
             tma_reduce_add_2d(&p.tmC[rank], x, y_st, src);
@@ -601,7 +619,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
 
     // Completion: all pushes of this CTA have landed -> bump every rank's arrival counter; then wait until
     // every CTA of every rank has done the same, so that at kernel end all remote tiles are in local memory.
-    const bool end_sync = push_all;
+    const bool end_sync = push_all && !pulls;
     if (end_sync) {
       named_barrier_sync(1, 128);
       if (issuer) {
@@ -631,17 +649,33 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
       bool entered = !(two_shot && W > 1);
       bool ok_all = true;
       float accv[kEpiCols];
-      for (int t = unit; t < total_tiles && ok_all; t += G) {
+      // Sources summed per column chunk: W partial buffers fetched from their owners, or (push_partials) the W x ksplit
+      // inbox slots in local memory.  With K-split pieces the unit of reducer work is one column chunk of a tile, so
+      // that the summing of a short matrix is spread over as many CTAs as its computation.
+      const int ks = p.ksplit > 1 ? p.ksplit : 1;
+      const int NS = p.push_partials ? W * ks : W;
+      const bool by_chunk = p.ksplit > 1;
+      constexpr int kChunks = BN / kEpiCols;
+      const int n_items = by_chunk ? total_tiles * kChunks : total_tiles;
+      for (int item = unit; item < n_items && ok_all; item += G) {
+        const int t = by_chunk ? item / kChunks : item;
+        const int c0 = by_chunk ? item - t * kChunks : 0;
+        const int c1 = by_chunk ? c0 + 1 : kChunks;
         if (two_shot && owner_of(t) != rank) continue;
         const TileCoord tc = raster(t, tiles_m, tiles_n, p.group_m);
         const int m0 = tc.m_idx * TM + pr * BM, n0 = tc.n_idx * BN;
-        const int units = (BN / kEpiCols) * W;
+        if (by_chunk && (n0 + c0 * kEpiCols >= p.N || m0 >= p.M)) continue;
+        const int units = (c1 - c0) * NS;
         auto issue = [&](int u) {  // reducer's issuer only
-          const int c = u / W, sft = u - c * W;
+          const int c = c0 + u / NS, sft = u % NS;
           const uint32_t b = pull_issued % C::kPullBufs;
           mbar_expect_tx(pull_full_bar(b), p.c_box_bytes);
-          tma_load_2d(pull_base + b * kEpiStageBytes, &p.tmC[(rank + sft) % W], n0 + c * kEpiCols, p.part_row0 + m0,
-                      pull_full_bar(b));
+          if (p.push_partials)
+            tma_load_2d(pull_base + b * kEpiStageBytes, &p.tmC[rank], n0 + c * kEpiCols,
+                        p.part_row0 + sft * p.part_slot_rows + m0, pull_full_bar(b));
+          else
+            tma_load_2d(pull_base + b * kEpiStageBytes, &p.tmC[(rank + sft) % W], n0 + c * kEpiCols, p.part_row0 + m0,
+                        pull_full_bar(b));
           ++pull_issued;
         };
         if (rissuer) {
@@ -672,7 +706,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
             ok_all = false;
             break;
           }
-          const int c = u / W, sft = u - c * W;
+          const int c = c0 + u / NS, sft = u % NS;
           const uint32_t buf = pull_base + (pull_done % C::kPullBufs) * kEpiStageBytes + row * 128;
           if (sft == 0) {
 #pragma unroll
@@ -687,7 +721,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
             acc_bf16x8(accv + 8 * j, v);
           }
           ++pull_done;
-          if (sft == W - 1 && p.out_row0 >= 0) {
+          if (sft == NS - 1 && p.out_row0 >= 0) {
             // the result staging buffer must have been read by the previous chunk's stores
             if (rissuer) bulk_wait_read<0>();
           }
@@ -701,7 +735,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
               *red_ok = ok ? 1u : 0u;
             }
           }
-          if (sft != W - 1) continue;
+          if (sft != NS - 1) continue;
           if (p.out_row0 >= 0) {
             // Result sub-tile -> swizzled staging buffer -> TMA store: full 128-byte rows on the wire.
             const uint32_t sbase = redout_base + row * 128;
@@ -927,7 +961,8 @@ struct IrisGemmDesc {
   int tile_flag_base, ag_flag_base;
   int device;
   int cta_group;
-  int dp_tiles, sk_units, sk_flag_base;  // stream-K schedule (dp_tiles < 0: every tile whole)  // 1: one CTA per 128 x 256 tile; 2: a CTA pair (cluster of 2) per 256 x 256 tile
+  int dp_tiles, sk_units, sk_flag_base;  // stream-K schedule (dp_tiles < 0: every tile whole)
+  int push_partials, part_slot_rows, ksplit;  // 1: one CTA per 128 x 256 tile; 2: a CTA pair (cluster of 2) per 256 x 256 tile
 };
 
 struct IrisGemmPlan {
@@ -1078,6 +1113,9 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
     p.ag = d->ag;
     p.ag_slices = d->ag_slices;
     p.store_all = d->store_all;
+    p.push_partials = d->push_partials;
+    p.part_slot_rows = d->part_slot_rows;
+    p.ksplit = d->ksplit > 1 ? d->ksplit : 1;
     p.tile_flag_base = d->tile_flag_base;
     p.ag_flag_base = d->ag_flag_base;
   }
@@ -1255,6 +1293,7 @@ int iris_gemm_noalloc(const void* a, int64_t lda, const void* bt, int64_t ldb, v
   p.rank0 = 0;
   p.ctas_per_rank = (int)(tiles < d.sms ? tiles : d.sms);
   p.mode = kEpiOneShot;
+  p.ksplit = 1;
   p.group_m = 8;
   p.dp_tiles = (int)tiles;  // every tile is computed whole by one CTA
   p.sk_units = 0;

@@ -83,6 +83,11 @@ struct FusedGemmParams {
                          // by k-blocks over `sk_units` scheduling units (stream-K), 0 = no split tiles
   int sk_units;
   int sk_flag_base;      // index of the per-(split tile, CTA of the group) k-block counters
+  int push_partials;     // one-shot: 1 = every rank's partial tile is pushed into a slot of every rank's inbox and summed
+                         // from local memory; 0 = partials stay home and are fetched by the reducers
+  int part_slot_rows;    // rows between consecutive inbox slots inside the tmC matrices
+  int ksplit;            // one-shot with push: each tile's K range is cut into `ksplit` pieces computed by different
+                         // CTAs, each piece a slot of its own (slot = rank * ksplit + piece); 1 = no split
   int store_all;         // store/reduce modes: 1 = push the tile to every rank, 0 = own rank only
   int tile_flag_base;    // index (uint32 units from flags_off) of the per-tile flags
   int ag_flag_base;      // index of the all-gather chunk flags: [src rank][chunk]

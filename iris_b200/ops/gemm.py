@@ -49,6 +49,7 @@ class _Desc(ctypes.Structure):
         ("store_all", ctypes.c_int), ("tile_flag_base", ctypes.c_int), ("ag_flag_base", ctypes.c_int),
         ("device", ctypes.c_int), ("cta_group", ctypes.c_int),
         ("dp_tiles", ctypes.c_int), ("sk_units", ctypes.c_int), ("sk_flag_base", ctypes.c_int),
+        ("push_partials", ctypes.c_int), ("part_slot_rows", ctypes.c_int), ("ksplit", ctypes.c_int),
     ]
 
 
@@ -111,7 +112,8 @@ class FusedGemm:
                  store_all: bool = False, c_cols: Optional[int] = None, col_off_per_rank: int = 0,
                  out: Optional[Sequence[torch.Tensor]] = None, ag: bool = False, ag_slices: int = 8,
                  ctas_per_rank: Optional[int] = None, group_m: int = 8, timeout_ms: float = 2000.0,
-                 cta_group: Optional[int] = None, trace: bool = False, stream_k: Optional[bool] = None):
+                 cta_group: Optional[int] = None, trace: bool = False, stream_k: Optional[bool] = None,
+                 push: Optional[bool] = None, ksplit: Optional[int] = None):
         self.ctxs: List[Iris] = [ctxs] if isinstance(ctxs, Iris) else list(ctxs)
         c0 = self.ctxs[0]
         if c0.backend != "cuda":
@@ -178,6 +180,20 @@ class FusedGemm:
         elif not self.sk_units:
             units = min(units, max(T, 1 if not self.ag else 8))
         self.ctas_per_rank = max(1, units) * cta_group
+        # ---- one-shot for short matrices: partials pushed into every rank's inbox, K cut into pieces ----
+        max_units = max(1, (sms // self.num_local) // cta_group)
+        self.push = bool(push) if push is not None else (mode == "one_shot" and self.M <= 2 * BM)
+        if mode != "one_shot":
+            self.push = False
+        self.ksplit = 1
+        if self.push:
+            if ksplit is None:
+                per_w = max(1, 16 // self.world)            # keep (ranks x pieces) summed per chunk at <= 16
+                ksplit = max(1, min(max_units // max(T, 1), per_w, kblocks // 4))
+            self.ksplit = max(1, int(ksplit))
+            if self.ksplit > 1:
+                self.dp_tiles, self.sk_units, sk_tiles = T, 0, 0
+                self.ctas_per_rank = min(max_units, T * self.ksplit) * cta_group
         self.store_all = bool(store_all) and self.world > 1
         pulls = mode in ("one_shot", "two_shot")
         chunks_per_shard = (self.M // self.world) // BM if self.ag else 0
@@ -195,13 +211,17 @@ class FusedGemm:
             # the output: [partial 0 | partial 1 | out], each padded to whole 256-row tiles, so that one tensor
             # map per rank serves partial stores, partial loads and output stores.
             mp = -(-self.M // (2 * BM)) * (2 * BM)
-            regions = 2 if out is not None else 3
+            slots = self.world * self.ksplit if self.push else 1   # inbox slots per parity
+            regions = 2 * slots + (0 if out is not None else 1)
             self._pull_buf = [c.zeros((regions * mp, self.N), dtype=torch.bfloat16) for c in self.ctxs]
-            self.partial = [[b[q * mp:q * mp + self.M] for b in self._pull_buf] for q in range(2)]
-            self.out = list(out) if out is not None else [b[2 * mp:2 * mp + self.M] for b in self._pull_buf]
+            self.partial = [[b[q * slots * mp:q * slots * mp + self.M] for b in self._pull_buf] for q in range(2)]
+            self.out = list(out) if out is not None else [b[2 * slots * mp:2 * slots * mp + self.M]
+                                                          for b in self._pull_buf]
             c_bufs, c2_bufs = self._pull_buf, None
             ldc, c_cols_eff = self.N, self.N
-            c_rows, part_row0, out_row0 = regions * mp, (0, mp), (2 * mp if out is None else -1)
+            c_rows, part_row0 = regions * mp, (0, slots * mp)
+            out_row0 = 2 * slots * mp if out is None else -1
+            self._slot_rows = mp
         else:
             self.out = list(out) if out is not None else [c.zeros((self.M, self.c_cols), dtype=torch.bfloat16)
                                                           for c in self.ctxs]
@@ -247,6 +267,9 @@ class FusedGemm:
         d.ag_flag_base = FLAG_HEADER + tile_flags
         d.device = c0.gpu_id
         d.cta_group = cta_group
+        d.push_partials = int(self.push)
+        d.part_slot_rows = getattr(self, "_slot_rows", 0)
+        d.ksplit = self.ksplit
         d.dp_tiles = self.dp_tiles if self.sk_units else -1
         d.sk_units = self.sk_units
         d.sk_flag_base = FLAG_HEADER + tile_flags + self.world * chunks_per_shard
@@ -269,7 +292,7 @@ class FusedGemm:
                 o.zero_()  # partial sums are added into the output: it has to start at zero
             self.launches += self.num_local
         self.calls += 1
-        per_flag = self.world if self.mode in ("one_shot", "two_shot") else self.ag_slices
+        per_flag = self.world * self.ksplit if self.mode in ("one_shot", "two_shot") else self.ag_slices
         rc = _lib().iris_gemm_plan_launch(self._plan, self.calls & 1, self.calls & 0xFFFFFFFF,
                                           (per_flag * self.calls) & 0xFFFFFFFF,
                                           (self.calls * self.world * self.ctas_per_rank) & 0xFFFFFFFF,

@@ -123,6 +123,30 @@ def test_gemm_all_reduce_emulated(variant, world, cta_group, stream_k):
     ranks[0].close()
 
 
+@pytest.mark.parametrize("m,ksplit", [(1, None), (100, None), (128, 3), (256, None), (128, 1)])
+@pytest.mark.parametrize("world", [2, 4])
+def test_one_shot_push_short_matrices(world, m, ksplit):
+    """Short matrices: every rank's partial (per K piece) is pushed into an inbox slot of every rank and summed from
+    local memory, the reducer work is split by column chunk."""
+    n, k_full = 1024, 5504
+    ks = k_full // world
+    ranks = iris.Iris.local_world(world, heap_size=96 << 20)
+    a_full, b_full = _rand((m, k_full), 16), _rand((n, k_full), 17, 0.05)
+    a = [a_full[:, r * ks:(r + 1) * ks] for r in range(world)]
+    bt = [b_full[:, r * ks:(r + 1) * ks] for r in range(world)]
+    op = G.gemm_all_reduce(ranks, a, bt, variant="one_shot", ksplit=ksplit)
+    assert op.push
+    for _ in range(3):
+        outs = op()
+    op.check()
+    parts = [a[r].float() @ bt[r].float().t() for r in range(world)]
+    ref, scale = sum(parts), sum(p.abs() for p in parts)
+    for r in range(world):
+        _assert_close(outs[r], ref, scale=scale, ulps=2.0 + world * op.ksplit)
+    op.close()
+    ranks[0].close()
+
+
 @pytest.mark.parametrize("cta_group", [1, 2])
 @pytest.mark.parametrize("world", [2, 4])
 def test_all_gather_gemm_emulated(world, cta_group):

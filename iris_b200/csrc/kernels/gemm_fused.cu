@@ -665,6 +665,84 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
         const TileCoord tc = raster(t, tiles_m, tiles_n, p.group_m);
         const int m0 = tc.m_idx * TM + pr * BM, n0 = tc.n_idx * BN;
         if (by_chunk && (n0 + c0 * kEpiCols >= p.N || m0 >= p.M)) continue;
+        if (p.push_partials) {
+          // Inbox slots are in LOCAL memory: read them with plain coalesced 16-byte loads, many in flight per thread
+          // (no ring, no per-unit barriers), add in fp32, and store the chunk through the staging buffer.
+          if (rissuer) {
+            const uint32_t* f = flag_ptr(p, rank, p.tile_flag_base + t * CG + pr);
+            trace(p, rank, t * CG + pr, kTrWaitBegin);
+            const bool ok = wait_until_ge(f, p.flag_target, p.timeout_ns, status, kSiteEpiTileFlag, rank, t) == kOk;
+            trace(p, rank, t * CG + pr, kTrWaitEnd);
+            *red_ok = ok ? 1u : 0u;
+          }
+          named_barrier_sync(3, 128);
+          if (*red_ok == 0) {
+            ok_all = false;
+            break;
+          }
+          const bool row_live = m0 + row < p.M;
+          for (int c = c0; c < c1; ++c) {
+            if (n0 + c * kEpiCols >= p.N) break;
+#pragma unroll
+            for (int j = 0; j < kEpiCols; ++j) accv[j] = 0.f;
+            if (row_live) {
+              const uint8_t* src = reinterpret_cast<const uint8_t*>(p.heap_base[rank] + p.partial_off) +
+                                   ((uint64_t)(p.part_row0 + m0 + row) * p.N + n0 + c * kEpiCols) * 2;
+              const uint64_t slot_bytes = (uint64_t)p.part_slot_rows * p.N * 2;
+              int sl = 0;
+              for (; sl + 1 < NS; sl += 2) {
+                uint4 v[2][8];
+#pragma unroll
+                for (int q = 0; q < 2; ++q)
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) v[q][j] = ld_v4(reinterpret_cast<const uint4*>(src + (sl + q) * slot_bytes) + j);
+#pragma unroll
+                for (int q = 0; q < 2; ++q)
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) acc_bf16x8(accv + 8 * j, v[q][j]);
+              }
+              for (; sl < NS; ++sl) {
+                uint4 v[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = ld_v4(reinterpret_cast<const uint4*>(src + sl * slot_bytes) + j);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc_bf16x8(accv + 8 * j, v[j]);
+              }
+            }
+            if (p.out_row0 >= 0) {
+              if (rissuer) bulk_wait_read<0>();  // the staging buffer's previous store has been read out
+              named_barrier_sync(3, 128);
+              const uint32_t sbase = redout_base + row * 128;
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                st_shared_v4(sbase + ((j ^ (row & 7)) << 4), pack_bf16x2(accv[8 * j + 0], accv[8 * j + 1]),
+                             pack_bf16x2(accv[8 * j + 2], accv[8 * j + 3]), pack_bf16x2(accv[8 * j + 4], accv[8 * j + 5]),
+                             pack_bf16x2(accv[8 * j + 6], accv[8 * j + 7]));
+              fence_proxy_async_smem();
+              named_barrier_sync(3, 128);
+              if (rissuer) {
+                tma_store_2d(&p.tmC[rank], n0 + c * kEpiCols, p.out_row0 + m0, redout_base);
+                bulk_commit();
+              }
+            } else if (row_live) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const int col = n0 + c * kEpiCols + 8 * j;
+                if (col < p.N) {
+                  uint4 o;
+                  o.x = pack_bf16x2(accv[8 * j + 0], accv[8 * j + 1]);
+                  o.y = pack_bf16x2(accv[8 * j + 2], accv[8 * j + 3]);
+                  o.z = pack_bf16x2(accv[8 * j + 4], accv[8 * j + 5]);
+                  o.w = pack_bf16x2(accv[8 * j + 6], accv[8 * j + 7]);
+                  st_v4(reinterpret_cast<uint4*>(p.heap_base[rank] + p.out_off +
+                                                 ((uint64_t)(m0 + row) * p.ldo + col) * 2), o);
+                }
+              }
+            }
+          }
+          if (rissuer) trace(p, rank, t * CG + pr, kTrPullEnd);
+          continue;
+        }
         const int units = (c1 - c0) * NS;
         auto issue = [&](int u) {  // reducer's issuer only
           const int c = c0 + u / NS, sft = u % NS;

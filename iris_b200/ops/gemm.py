@@ -251,7 +251,7 @@ class FusedGemm:
         d.ldc, d.c_cols, d.c_rows = ldc, c_cols_eff, c_rows
         d.part_row0[0], d.part_row0[1], d.out_row0 = part_row0[0], part_row0[1], out_row0
         d.flags_off = c0.offset_of(self.flags[0])
-        d.partial_off[0] = d.partial_off[1] = 0
+        d.partial_off[0] = d.partial_off[1] = c_off if pulls else 0  # base of [partials | out] (inbox reads)
         d.out_off = c0.offset_of(self.out[0]) if pulls else 0
         d.status_off = c0.offset_of(c0.status)
         d.agsrc_off = c0.offset_of(self.a_full[0]) if self.ag else 0

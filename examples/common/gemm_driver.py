@@ -25,7 +25,7 @@ def parse_args(kind: str):
     ap.add_argument("-k", type=int, default=d["k"])
     ap.add_argument("-d", "--debug", action="store_true")
     ap.add_argument("-v", "--validate", action="store_true")
-    ap.add_argument("-t", "--trace_tiles", action="store_true", help="accepted; per-tile traces are not recorded yet")
+    ap.add_argument("-t", "--trace_tiles", action="store_true", help="record per-tile device timestamps to trace_rank<r>.json")
     ap.add_argument("-b", "--benchmark", action="store_true")
     ap.add_argument("--datatype", default="bf16", choices=["bf16"])
     ap.add_argument("--output_file", default="")
@@ -62,7 +62,8 @@ def run(kind: str, seed: int):
             raise SystemExit("N must be divisible by the number of ranks")
         nl = n // world
         bt_local = Bt[rank * nl:(rank + 1) * nl].contiguous()
-        op = G.gemm_all_scatter(ctx, [A], [bt_local], ctas_per_rank=ctas, group_m=args["gsize_m"])
+        op = G.gemm_all_scatter(ctx, [A], [bt_local], ctas_per_rank=ctas, group_m=args["gsize_m"],
+                                trace=args["trace_tiles"])
         roof = roofline.all_scatter_roofline_us(m, n, k, world, peaks)
         c_part = torch.empty((m, nl), dtype=torch.bfloat16, device=dev)
         gathered = torch.empty((world, m, nl), dtype=torch.bfloat16, device=dev)
@@ -79,7 +80,8 @@ def run(kind: str, seed: int):
             raise SystemExit("K / ranks must be a multiple of 8")
         ks = k // world
         a_local, b_local = A[:, rank * ks:(rank + 1) * ks], Bt[:, rank * ks:(rank + 1) * ks]  # views, pitch k
-        op = G.gemm_all_reduce(ctx, [a_local], [b_local], variant=variant, ctas_per_rank=ctas, group_m=args["gsize_m"])
+        op = G.gemm_all_reduce(ctx, [a_local], [b_local], variant=variant, ctas_per_rank=ctas, group_m=args["gsize_m"],
+                               trace=args["trace_tiles"])
         roof = roofline.all_reduce_roofline_us(m, n, k, world, peaks,
                                                "two_shot" if variant == "two_shot" else "one_shot")
         c_part = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
@@ -92,10 +94,16 @@ def run(kind: str, seed: int):
     fields = {k_: v for k_, v in args.items() if v is not None}
     fields.update(world_size=world, variant=variant, gemm_sms=op.ctas_per_rank, tile="128x256x64")
     js.add_fields(**fields)
+    G.matmul.set_debug(args["debug"])
     ctx.barrier()
-    out = op()[0]
+    out = G.matmul.apply(op)
     ctx.barrier()
     op.check()
+    if args["trace_tiles"]:
+        import json
+        with open(f"trace_rank{rank}.json", "w") as f:
+            json.dump(op.trace_records(), f)
+        ctx.log(f"per-tile trace written to trace_rank{rank}.json")
     ok = True
     if args["validate"]:
         rows = slice(0, min(m, 1024))

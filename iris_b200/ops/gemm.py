@@ -372,8 +372,8 @@ def all_gather_gemm(ctxs, M: int, bt, **kw) -> FusedGemm:
 _private_ctx = {}
 
 
-def matmul(a: torch.Tensor, bt: torch.Tensor, out: Optional[torch.Tensor] = None,
-           cta_group: Optional[int] = None) -> torch.Tensor:
+def gemm(a: torch.Tensor, bt: torch.Tensor, out: Optional[torch.Tensor] = None,
+         cta_group: Optional[int] = None) -> torch.Tensor:
     """Single-GPU ``a @ bt.T`` on the tcgen05 kernel (world of one, no communication)."""
     dev = a.device
     ctx = _private_ctx.get(dev)
@@ -391,3 +391,32 @@ def matmul(a: torch.Tensor, bt: torch.Tensor, out: Optional[torch.Tensor] = None
     torch.cuda.current_stream(dev).synchronize()  # the plan's flags and workspace are released just below
     ctx.reset(mark)
     return out
+
+
+# Names of the fused algorithms (the reference keeps them as Triton constexprs, examples/common/utils.py:13-19).
+ALGORITHMS = ("all_scatter", "all_gather", "atomic", "one_shot", "two_shot")
+
+
+class matmul(torch.autograd.Function):
+    """``matmul.apply(op)``: run a prepared :class:`FusedGemm` as an autograd Function (forward only), the calling
+    convention of the reference's wrappers (``examples/07_gemm_all_scatter/matmul_wrapper.py:161-219``).
+    ``matmul.set_debug(True)`` prints the schedule the way the reference prints its Stream-K bookkeeping (:94-103)."""
+
+    _debug = False
+
+    @staticmethod
+    def set_debug(debug: bool) -> None:
+        matmul._debug = bool(debug)
+
+    @staticmethod
+    def forward(ctx, op: "FusedGemm", stream=None):
+        if matmul._debug:
+            print(f"[iris_b200.matmul] mode={op.mode} M={op.M} N={op.N} K={op.K} world={op.world} "
+                  f"cta_group={op.cta_group} ctas/rank={op.ctas_per_rank} tiles={op.total_tiles} "
+                  f"whole_tiles={op.dp_tiles} stream_k_units={op.sk_units} ksplit={op.ksplit} push={op.push}")
+        out = op(stream)
+        return out[0] if len(out) == 1 else tuple(out)
+
+    @staticmethod
+    def backward(ctx, *grads):
+        raise NotImplementedError("the fused GEMM + collective operators are forward-only, as in the reference")

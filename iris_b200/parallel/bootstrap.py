@@ -100,6 +100,41 @@ class TorchDistBootstrap(Bootstrap):
             raise BootstrapError(f"barrier timed out after {timeout_s} s on rank {self.rank}: {e}") from e
 
 
+class MpiBootstrap(Bootstrap):
+    """Control plane over mpi4py, for launches under ``mpirun`` (the reference's only back end,
+    ``iris/_mpi_helpers.py:8-51``).  Used when ``IRIS_BOOTSTRAP=mpi`` and mpi4py is importable."""
+
+    def __init__(self):
+        from mpi4py import MPI  # noqa: WPS433 (optional dependency)
+        self._mpi = MPI
+        self._comm = MPI.COMM_WORLD
+        self.rank = self._comm.Get_rank()
+        self.world = self._comm.Get_size()
+
+    def allgather_bytes(self, payload: bytes) -> List[bytes]:
+        return list(self._comm.allgather(bytes(payload)))
+
+    def broadcast_object(self, obj: Any, root: int) -> Any:
+        if not 0 <= root < self.world:
+            raise BootstrapError(f"root {root} outside world of {self.world}")
+        return self._comm.bcast(obj, root=root)
+
+    def barrier(self, timeout_s: Optional[float] = None) -> None:
+        if timeout_s is None:
+            self._comm.Barrier()
+            return
+        import time
+        req = self._comm.Ibarrier()
+        t0 = time.monotonic()
+        while not req.Test():
+            if time.monotonic() - t0 > timeout_s:
+                raise BootstrapError(f"barrier timed out after {timeout_s} s on rank {self.rank}")
+            time.sleep(0.001)
+
+    def local_rank(self) -> int:
+        return self._comm.Split_type(self._mpi.COMM_TYPE_SHARED).Get_rank()
+
+
 def _shutdown_torchdist(self) -> None:
     if self.owns_process_group and dist.is_initialized():
         try:
@@ -115,12 +150,18 @@ TorchDistBootstrap.shutdown = _shutdown_torchdist
 def init_from_env(timeout_s: float = 120.0) -> Bootstrap:
     """Pick the back end from the environment.
 
+    * ``IRIS_BOOTSTRAP=mpi`` → mpi4py (``mpirun`` launches).
     * ``torch.distributed`` already initialised → use it.
     * ``RANK`` and ``WORLD_SIZE`` set (torchrun / iris_b200.launch) → initialise a process group
       (gloo for CPU tensors, NCCL for CUDA tensors when a GPU is present) on ``MASTER_ADDR`` (default
       127.0.0.1) and use it.
     * otherwise → a world of one.
     """
+    if os.environ.get("IRIS_BOOTSTRAP", "").lower() == "mpi":
+        try:
+            return MpiBootstrap()
+        except ImportError as e:
+            raise BootstrapError("IRIS_BOOTSTRAP=mpi needs mpi4py") from e
     if dist.is_available() and dist.is_initialized():
         return TorchDistBootstrap(timeout_s)
     if "RANK" in os.environ and "WORLD_SIZE" in os.environ and int(os.environ["WORLD_SIZE"]) > 1:

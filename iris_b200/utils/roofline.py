@@ -62,3 +62,24 @@ def all_reduce_roofline_us(m, n, k, world, peaks: Peaks, variant: str = "one_sho
     link = ingress / (peaks.nvlink_gbs * 1e9) * 1e6
     return {"compute_us": compute, "link_us": link, "bound": "compute" if compute >= link else "link",
             "target_us": max(compute, link)}
+
+
+def effective_link_bandwidth(result: dict) -> dict:
+    """From one result record of a fused all-scatter run (the JSON of ``examples/07_gemm_all_scatter``): bytes every
+    rank receives, and the NVLink bandwidth that would be needed to hide them behind the measured kernel time
+    (the reference's ``scripts/link_bandwidth.py:50-54`` prints the same quantity for its sample record)."""
+    m, n, w = int(result["m"]), int(result["n"]), int(result.get("world_size", 1))
+    ms = float(result.get("fused_ms") or result.get("ms"))
+    ingress = (w - 1) * m * (n // w) * 2
+    return {"ingress_bytes_per_rank": ingress, "kernel_ms": ms, "gbs_per_rank": ingress / (ms * 1e-3) / 1e9,
+            "fraction_of_measured_link": ingress / (ms * 1e-3) / 1e9 / NVLINK_GBS_MEASURED}
+
+
+if __name__ == "__main__":
+    import sys
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python -m iris_b200.utils.roofline <result.json from examples/07_gemm_all_scatter>")
+    with open(sys.argv[1]) as f:
+        rec = json.load(f)
+    out = effective_link_bandwidth(rec)
+    print(json.dumps(out, indent=2))

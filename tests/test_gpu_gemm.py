@@ -38,7 +38,7 @@ def _assert_close(got, ref_fp32, scale=None, ulps=2.0):
 @pytest.mark.parametrize("cta_group", [1, 2])
 def test_plain_gemm(m, n, k, cta_group):
     a, bt = _rand((m, k), 1), _rand((n, k), 2, 0.05)
-    out = G.matmul(a, bt, cta_group=cta_group)
+    out = G.gemm(a, bt, cta_group=cta_group)
     torch.cuda.synchronize()
     _assert_close(out, a.float() @ bt.float().t())
 
@@ -46,7 +46,7 @@ def test_plain_gemm(m, n, k, cta_group):
 def test_many_tiles_per_cta_pair():
     # more tiles than CTA pairs: ring and accumulator phases wrap many times
     a, bt = _rand((4096, 512), 1), _rand((8192, 512), 2, 0.05)
-    out = G.matmul(a, bt, cta_group=2)
+    out = G.gemm(a, bt, cta_group=2)
     torch.cuda.synchronize()
     _assert_close(out, a.float() @ bt.float().t())
 
@@ -75,7 +75,7 @@ def test_gemm_strided_views():
     # K-shards taken as views: row pitch larger than K, base offset inside the row
     big_a, big_b = _rand((512, 4096), 3), _rand((768, 4096), 4, 0.05)
     a, bt = big_a[:, 1376:2752], big_b[:, 1376:2752]
-    out = G.matmul(a, bt)
+    out = G.gemm(a, bt)
     torch.cuda.synchronize()
     _assert_close(out, a.float() @ bt.float().t())
 
@@ -172,4 +172,4 @@ def test_all_gather_gemm_emulated(world, cta_group):
 def test_plan_rejects_bad_shapes():
     a, bt = _rand((128, 60), 1), _rand((256, 60), 2)
     with pytest.raises((RuntimeError, ValueError)):
-        G.matmul(a, bt)
+        G.gemm(a, bt)

@@ -34,3 +34,31 @@ def test_vmm_heap(nvls):
                            env={"IRIS_NVLS": nvls, "NCCL_NVLS_ENABLE": "0"})
     assert code == 0, "\n".join(o or "" for o in outs)
     assert all("VMM OK" in (o or "") for o in outs)
+
+
+EX = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "examples")
+
+
+@pytest.mark.parametrize("script,args", [
+    ("00_load/load_bench.py", ["-z", str(1 << 22), "-n", "2", "-d"]),
+    ("01_store/store_bench.py", ["-z", str(1 << 22), "-n", "2", "-d"]),
+    ("02_all_load/all_load_bench.py", ["-m", str(1 << 20), "-M", str(1 << 22), "-x", "2", "-d", "-p", str(1 << 28)]),
+    ("03_all_store/all_store_bench.py", ["-m", str(1 << 20), "-M", str(1 << 22), "-x", "2", "-d", "-p", str(1 << 28)]),
+    ("04_atomic_add/atomic_add_bench.py", ["-z", str(1 << 20), "-x", "2", "-w", "1", "-d"]),
+    ("05_atomic_xchg/atomic_xchg_bench.py", ["-z", str(1 << 20), "-x", "2", "-w", "1", "-d"]),
+    ("06_message_passing/message_passing_put.py", ["-n", "3"]),
+    ("06_message_passing/message_passing_load_store.py", ["-n", "3"]),
+    ("07_gemm_all_scatter/benchmark.py", ["-m", "1024", "-n", "2048", "-k", "512", "-v", "-b", "--num_experiments", "3",
+                                          "--num_warmup", "1", "--heap_size", str(1 << 28)]),
+    ("08_gemm_atomics_all_reduce/benchmark.py", ["-m", "1024", "-n", "1024", "-k", "1024", "-v", "--heap_size", str(1 << 28)]),
+    ("09_gemm_one_shot_all_reduce/benchmark.py", ["-m", "128", "-n", "1024", "-k", "1024", "-v", "--heap_size", str(1 << 28)]),
+    ("10_tp_block/tp_block.py", ["-v", "--hidden", "512", "--heads", "4", "--intermediate", "1024", "--batch", "2",
+                                 "--seq", "512", "--layers", "1", "--heap_size", str(1 << 29)]),
+])
+def test_examples_run_on_two_gpus(script, args):
+    """Every example script runs end to end on two ranks with its validation switched on (the reference's example
+    test only checks that ``00_load`` does not crash, tests/examples/test_load_bench.py:23-60)."""
+    code, outs = run_ranks(2, [os.path.join(EX, script)] + args, timeout_s=240, env={"NCCL_NVLS_ENABLE": "0"})
+    text = "\n".join(o or "" for o in outs)
+    assert code == 0, text
+    assert "FAILED" not in text, text

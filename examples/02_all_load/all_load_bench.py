@@ -56,6 +56,7 @@ def main():
             print(f"{size / 2**20:10.2f} MiB  {lo:10.2f} {hi:10.2f}")
         records.append({"buffer_bytes": size, "gibps_min": lo, "gibps_max": hi, "active_ranks": active})
         if args["validate"] and on:
+            run()  # the overhead kernel above wrote its own pattern into `out`: take the sum again
             torch.cuda.synchronize()
             assert float(out[: size // es].float().mean()) == float(active)
         size *= 2

@@ -34,10 +34,12 @@ def main():
     ap.add_argument("--num_warmup", type=int, default=3)
     ap.add_argument("--heap_size", type=int, default=12 << 30)
     ap.add_argument("--output_file", default="")
+    ap.add_argument("--heap_mode", default=None, choices=["ipc", "vmm"],
+                    help="vmm + IRIS_NVLS=1 in the environment binds the heap to an NVLS multicast object")
     args = ap.parse_args()
     cfg = TPConfig(hidden=args.hidden, n_heads=args.heads, head_dim=args.head_dim, intermediate=args.intermediate,
                    n_layers=args.layers, batch=args.batch, seq=args.seq)
-    ctx = iris.iris(args.heap_size)
+    ctx = iris.iris(args.heap_size, heap_mode=args.heap_mode)
     rank, world = ctx.get_rank(), ctx.get_num_ranks()
     dev = ctx.get_device()
     device_barrier(ctx)
@@ -47,7 +49,7 @@ def main():
     x = torch.randn((cfg.tokens, cfg.hidden), generator=g, device=dev).to(torch.bfloat16)
     ts = cfg.tokens // world
     mine = x[rank * ts:(rank + 1) * ts]
-    res = {"world": world, "variant": args.variant, "config": cfg.__dict__}
+    res = {"world": world, "variant": args.variant, "config": cfg.__dict__, "nvls": bool(ctx.mc_base)}
     ok = True
     if args.validate:
         a, b = mine.clone(), mine.clone()

@@ -34,14 +34,16 @@ def main():
     ap.add_argument("--skip_p2p", action="store_true")
     ap.add_argument("--skip_gemm", action="store_true")
     ap.add_argument("--max_p2p_bytes", type=int, default=1 << 30)
+    ap.add_argument("--heap_mode", default=None, choices=["ipc", "vmm"],
+                    help="vmm + IRIS_NVLS=1 in the environment binds the heap to an NVLS multicast object")
     args = ap.parse_args()
-    ctx = iris.iris((3 << 30) + (1 << 29))
+    ctx = iris.iris((3 << 30) + (1 << 29), heap_mode=args.heap_mode)
     rank, world = ctx.get_rank(), ctx.get_num_ranks()
     dev = ctx.get_device()
     device_barrier(ctx)  # allocated first, so that it survives the heap rewinds below
     base = ctx.mark()
     peaks = roofline.load_peaks()
-    res = {"world": world, "peaks": peaks.__dict__, "p2p": {}, "gemm": []}
+    res = {"heap_mode": ctx.heap_mode, "nvls": bool(ctx.mc_base), "world": world, "peaks": peaks.__dict__, "p2p": {}, "gemm": []}
     W, R = args.warmup, args.reps
 
     def log(msg):
@@ -97,7 +99,7 @@ def main():
                    baseline_us=bms * 1e3, speedup=bms / ms, roofline_us=roof["target_us"], bound=roof["bound"],
                    roofline_fraction=roof["target_us"] / (ms * 1e3), cta_group=op.cta_group, ctas=op.ctas_per_rank)
         res["gemm"].append(rec)
-        log(f"{label}: fused {rec['fused_us']:.1f} us ({rec['fused_tflops']:.0f} TF) | cuBLAS+NCCL {rec['baseline_us']:.1f} us "
+        log(f"{label}{' [nvls]' if getattr(op, 'nvls', False) else ''}: fused {rec['fused_us']:.1f} us ({rec['fused_tflops']:.0f} TF) | cuBLAS+NCCL {rec['baseline_us']:.1f} us "
             f"| x{rec['speedup']:.2f} | roofline {roof['target_us']:.0f} us ({roof['bound']}) -> {100 * rec['roofline_fraction']:.0f}%")
 
     if not args.skip_gemm:

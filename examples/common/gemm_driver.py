@@ -36,6 +36,8 @@ def parse_args(kind: str):
     ap.add_argument("--num_experiments", type=int, default=50)
     ap.add_argument("--num_warmup", type=int, default=10)
     ap.add_argument("--no_baseline", action="store_true")
+    ap.add_argument("--heap_mode", default=None, choices=["ipc", "vmm"],
+                    help="vmm + IRIS_NVLS=1 in the environment binds the heap to an NVLS multicast object")
     # knobs of the reference that have no meaning on this hardware are accepted and ignored
     for flag in ("--BLK_M", "--BLK_N", "--BLK_K", "--num_stages", "--num_warps", "--waves_per_eu", "--mfmaInstrSize",
                  "--kpack", "--total_sms"):
@@ -47,7 +49,7 @@ def parse_args(kind: str):
 
 def run(kind: str, seed: int):
     args = parse_args(kind)
-    ctx = iris.iris(args["heap_size"])
+    ctx = iris.iris(args["heap_size"], heap_mode=args["heap_mode"])
     rank, world = ctx.get_rank(), ctx.get_num_ranks()
     dev = ctx.get_device()
     m, n, k = args["m"], args["n"], args["k"]

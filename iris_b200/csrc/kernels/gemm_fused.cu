@@ -39,6 +39,7 @@
 
 #include "gemm_fused.cuh"
 #include "iris/iris.cuh"
+#include "iris/nvls.cuh"
 #include "iris/ptx_sm100.cuh"
 
 namespace iris {
@@ -665,6 +666,54 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
         const TileCoord tc = raster(t, tiles_m, tiles_n, p.group_m);
         const int m0 = tc.m_idx * TM + pr * BM, n0 = tc.n_idx * BN;
         if (by_chunk && (n0 + c0 * kEpiCols >= p.N || m0 >= p.M)) continue;
+        if (two_shot && p.mc_base != 0 && p.out_row0 >= 0 && W > 1) {
+          // NVLS two-shot: the NVLink switch does the work.  One multimem.ld_reduce per 16 bytes returns the fp32-
+          // accumulated sum of all W ranks' partials, one multimem.st delivers the result to all W outputs.  A warp
+          // covers 512 contiguous bytes (one row of the part) per instruction, eight rows in flight.
+          if (rissuer) {
+            const uint32_t* f = flag_ptr(p, rank, p.tile_flag_base + t * CG + pr);
+            trace(p, rank, t * CG + pr, kTrWaitBegin);
+            bool ok = wait_until_ge(f, p.flag_target, p.timeout_ns, status, kSiteEpiTileFlag, rank, t) == kOk;
+            if (ok && !entered) {
+              for (int i = 0; i < W && ok; ++i) {
+                const int q = (rank + 1 + i) % W;
+                ok = wait_until_ge(flag_ptr(p, rank, 8 + q), p.epoch, p.timeout_ns, status, kSiteEpiEntry, rank, q) == kOk;
+              }
+            }
+            trace(p, rank, t * CG + pr, kTrWaitEnd);
+            *red_ok = ok ? 1u : 0u;
+          }
+          entered = true;
+          named_barrier_sync(3, 128);
+          if (*red_ok == 0) {
+            ok_all = false;
+            break;
+          }
+          const int rw = rt >> 5, rl = rt & 31;
+          const int col = n0 + rl * 8;
+          if (col < p.N) {
+            const uint64_t mc = p.mc_base + p.partial_off;  // [partials | out] matrix of every rank at once
+#pragma unroll 1
+            for (int r0 = rw * 32; r0 < rw * 32 + 32; r0 += 8) {
+              uint4 v[8];
+#pragma unroll
+              for (int u = 0; u < 8; ++u) {
+                const int r = m0 + r0 + u;
+                if (r < p.M)
+                  v[u] = nvls::ld_reduce_add_bf16x8(
+                      reinterpret_cast<const void*>(mc + ((uint64_t)(p.part_row0 + r) * p.N + col) * 2));
+              }
+#pragma unroll
+              for (int u = 0; u < 8; ++u) {
+                const int r = m0 + r0 + u;
+                if (r < p.M)
+                  nvls::st_v4(reinterpret_cast<void*>(mc + ((uint64_t)(p.out_row0 + r) * p.N + col) * 2), v[u]);
+              }
+            }
+          }
+          if (rissuer) trace(p, rank, t * CG + pr, kTrPullEnd);
+          continue;
+        }
         if (p.push_partials) {
           // Inbox slots are in LOCAL memory: read them with plain coalesced 16-byte loads, many in flight per thread
           // (no ring, no per-unit barriers), add in fp32, and store the chunk through the staging buffer.
@@ -1028,6 +1077,7 @@ struct IrisGemmDesc {
   uint64_t agsrc_off;
   uint64_t trace_off;
   uint64_t ws_off;
+  uint64_t mc_base;
   uint64_t timeout_ns;
   int M, N, K;
   int ldo;
@@ -1166,6 +1216,7 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
     p.trace_off = d->trace_off;
     p.c_box_bytes = c_box_rows * 128u;
     p.ws_off = d->ws_off;
+    p.mc_base = d->mc_base;
     {
       const int tiles = ((d->M + BM * cg - 1) / (BM * cg)) * ((d->N + BN - 1) / BN);
       p.dp_tiles = (d->dp_tiles < 0 || d->dp_tiles > tiles || d->sk_units <= 0) ? tiles : d->dp_tiles;

@@ -61,6 +61,7 @@ struct FusedGemmParams {
   uint64_t out_off;      // one-/two-shot: bf16 [M, ldo] final output
   uint64_t status_off;   // iris::StatusBlock
   uint64_t agsrc_off;    // all-gather prologue: gathered A [M, K] (row stride lda_full elements)
+  uint64_t mc_base;      // NVLS multicast address of the heap (0: not bound); used by the two-shot reducer
   uint64_t ws_off;       // stream-K: fp32 workspace [split tiles * cta_group][128][256] per rank, zero between calls
   uint64_t trace_off;    // 0, or int64[tiles * cta_group][8] per rank: per-tile device timestamps (ns)
   uint64_t timeout_ns;

@@ -39,7 +39,7 @@ class _Desc(ctypes.Structure):
         ("ldc", ctypes.c_int64), ("c_cols", ctypes.c_int64), ("c_rows", ctypes.c_int64),
         ("flags_off", ctypes.c_uint64), ("partial_off", ctypes.c_uint64 * 2), ("out_off", ctypes.c_uint64),
         ("status_off", ctypes.c_uint64), ("agsrc_off", ctypes.c_uint64), ("trace_off", ctypes.c_uint64),
-        ("ws_off", ctypes.c_uint64),
+        ("ws_off", ctypes.c_uint64), ("mc_base", ctypes.c_uint64),
         ("timeout_ns", ctypes.c_uint64),
         ("M", ctypes.c_int), ("N", ctypes.c_int), ("K", ctypes.c_int), ("ldo", ctypes.c_int),
         ("part_row0", ctypes.c_int * 2), ("out_row0", ctypes.c_int),
@@ -113,7 +113,7 @@ class FusedGemm:
                  out: Optional[Sequence[torch.Tensor]] = None, ag: bool = False, ag_slices: int = 8,
                  ctas_per_rank: Optional[int] = None, group_m: int = 8, timeout_ms: float = 2000.0,
                  cta_group: Optional[int] = None, trace: bool = False, stream_k: Optional[bool] = None,
-                 push: Optional[bool] = None, ksplit: Optional[int] = None):
+                 push: Optional[bool] = None, ksplit: Optional[int] = None, nvls: Optional[bool] = None):
         self.ctxs: List[Iris] = [ctxs] if isinstance(ctxs, Iris) else list(ctxs)
         c0 = self.ctxs[0]
         if c0.backend != "cuda":
@@ -274,6 +274,12 @@ class FusedGemm:
         d.sk_units = self.sk_units
         d.sk_flag_base = FLAG_HEADER + tile_flags + self.world * chunks_per_shard
         d.ws_off = c0.offset_of(self.workspace[0]) if self.workspace else 0
+        # two-shot on a heap bound to an NVLS multicast object: the switch sums and broadcasts
+        mc = int(getattr(c0, "mc_base", 0) or 0)
+        self.nvls = bool(mc) and mode == "two_shot" and self.num_local == 1 and out is None and nvls is not False
+        if nvls and not self.nvls:
+            raise RuntimeError("nvls=True needs heap_mode='vmm' with IRIS_NVLS=1, mode='two_shot', one process per GPU")
+        d.mc_base = mc if self.nvls else 0
         self.ag_slices = int(ag_slices)
         lib = _lib()
         self._plan = lib.iris_gemm_plan_create(ctypes.byref(d))
@@ -356,11 +362,14 @@ def gemm_all_reduce(ctxs, a, bt, variant: str = "one_shot", **kw) -> FusedGemm:
     """``C[M, N] = sum over ranks of A_r @ B_r`` (K sharded).  ``variant``: ``"atomic"``
     (``examples/08_gemm_atomics_all_reduce``), ``"one_shot"`` (``examples/09_gemm_one_shot_all_reduce``) or
     ``"two_shot"`` (each tile summed by one owner rank and pushed: the bandwidth-optimal extra)."""
+    if variant == "auto":
+        # short matrices are latency-bound: one-shot with pushed partials; tall ones are bandwidth-bound: two-shot
+        variant = "one_shot" if a[0].shape[0] <= 2 * BM else "two_shot"
     if variant == "atomic":
         return FusedGemm(ctxs, a, bt, "reduce", store_all=True, **kw)
     if variant in ("one_shot", "two_shot"):
         return FusedGemm(ctxs, a, bt, variant, **kw)
-    raise ValueError("variant must be 'atomic', 'one_shot' or 'two_shot'")
+    raise ValueError("variant must be 'auto', 'atomic', 'one_shot' or 'two_shot'")
 
 
 def all_gather_gemm(ctxs, M: int, bt, **kw) -> FusedGemm:

@@ -50,6 +50,27 @@ def main():
                 ctx.check_status()
                 ref = sum(p.float() for p in parts)
                 assert (x.float() - ref).abs().max().item() <= 2 ** -7 * ref.abs().max().item(), "multimem.ld_reduce"
+            # fused GEMM + two-shot all-reduce with the switch doing the summing and the broadcast
+            from iris_b200.ops import gemm as G
+            k_full = 1024 * world
+            g = torch.Generator(device=dev).manual_seed(5)
+            a_full = torch.randn((512, k_full), generator=g, device=dev).to(torch.bfloat16)
+            b_full = (torch.randn((768, k_full), generator=g, device=dev) * 0.05).to(torch.bfloat16)
+            ks = k_full // world
+            op = G.gemm_all_reduce(ctx, [a_full[:, rank * ks:(rank + 1) * ks]], [b_full[:, rank * ks:(rank + 1) * ks]],
+                                   variant="two_shot")
+            assert op.nvls, "two-shot did not pick the NVLS reducer"
+            for _ in range(3):
+                ctx.barrier()
+                o = op()[0]
+            ctx.barrier()
+            op.check()
+            parts = [a_full[:, r * ks:(r + 1) * ks].float() @ b_full[:, r * ks:(r + 1) * ks].float().t()
+                     for r in range(world)]
+            ref, scale = sum(parts), sum(p.abs() for p in parts)
+            tol = (2 + world) * 2.0 ** -8 * scale + 1e-3 * ref.abs().max().item()
+            assert bool(((o.float() - ref).abs() <= tol).all()), "NVLS two-shot mismatch"
+            op.close()
             msg += " + NVLS OK"
     ctx.barrier()
     ctx.close()

@@ -432,6 +432,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
     int acc = 0;
     uint32_t acc_phase = 0;
     int ebuf = 0;
+    const uint64_t evict_first = l2_policy_evict_first();
     int pending_tile = -1;  // one-/two-shot: tile whose partial is stored but not yet published
     bool entered = !need_entry;
 
@@ -580,12 +581,15 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
             for (int i = 0; i < W; ++i) {  // peers first, starting with the next rank; own copy last
               const int t = (rank + 1 + i) % W;
               if (p.mode == kEpiReduce) tma_reduce_add_2d(&p.tmC[t], x, y_st, src);
+              else if (t == rank && !pulls) tma_store_2d_hint(&p.tmC[t], x, y_st, src, evict_first);
               else tma_store_2d(&p.tmC[t], x, y_st, src);
             }
           } else if (p.mode == kEpiReduce) {
             tma_reduce_add_2d(&p.tmC[rank], x, y_st, src);
+          } else if (pulls) {
+            tma_store_2d(&p.tmC[rank], x, y_st, src);  // partials are read back soon: keep them in L2
           } else {
-            tma_store_2d(&p.tmC[rank], x, y_st, src);
+            tma_store_2d_hint(&p.tmC[rank], x, y_st, src, evict_first);
           }
           bulk_commit();
           ++groups_this_tile;

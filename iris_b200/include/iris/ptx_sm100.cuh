@@ -90,6 +90,20 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, int x, int y,
                "r"(x), "r"(y), "r"(smem_src)
                : "memory");
 }
+// L2 cache policy for data that is written once and not read again by this kernel (output tiles): evict first, so
+// that the operand tiles other CTAs are about to reuse stay resident.
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ void tma_store_2d_hint(const CUtensorMap* m, int x, int y, uint32_t smem_src, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group.L2::cache_hint [%0, {%1, %2}], [%3], %4;" ::"l"(
+          reinterpret_cast<uint64_t>(m)),
+      "r"(x), "r"(y), "r"(smem_src), "l"(policy)
+      : "memory");
+}
 // 2-D tile reduction (element-wise add) from shared memory into global memory.
 __device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* m, int x, int y, uint32_t smem_src) {
   asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(

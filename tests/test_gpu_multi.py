@@ -62,3 +62,14 @@ def test_examples_run_on_two_gpus(script, args):
     text = "\n".join(o or "" for o in outs)
     assert code == 0, text
     assert "FAILED" not in text, text
+
+
+def test_rank_leaving_between_steps_is_detected_on_the_host():
+    """A rank leaves between steps; the survivors notice at the next host barrier (short time limit) and do not
+    launch the step that would wait for it.  NVLS is off and the heap is plain CUDA IPC memory."""
+    world = min(2, torch.cuda.device_count())
+    code, outs = run_ranks(world, [os.path.join(W, "gpu_rank_leaves.py")], timeout_s=120,
+                           env={"NCCL_NVLS_ENABLE": "0", "IRIS_NVLS": "0"})
+    text = "\n".join(o or "" for o in outs)
+    assert code == 0, text
+    assert "leaving after step 1" in text and "step 2 not launched" in text, text

@@ -19,9 +19,46 @@ from common.harness import iris, torch  # noqa: E402
 from iris_b200.ops import gemm as G  # noqa: E402
 
 
+def run_p2p(args):
+    """The bandwidth kernels between two heaps on ONE GPU: the 'remote' heap is local memory, so the capture shows the
+    kernels' own DRAM efficiency (256 MB buffers, larger than L2); across GPUs the same kernels are link-bound."""
+    from iris_b200.ops import p2p
+    ranks = iris.Iris.local_world(2, heap_size=(3 << 28) + (1 << 26))
+    c = ranks[0]
+    n = 1 << 26  # fp32 elements = 256 MB
+    src = [r.ones(n, dtype=torch.float32) for r in ranks]
+    dst = [r.zeros(n, dtype=torch.float32) for r in ranks]
+    for _ in range(args.launches):
+        p2p.load(c, src[0], dst[0], target=1)
+        p2p.store(c, dst[0].view(torch.int32), target=1)
+        p2p.all_load(c, src[0], dst[0])
+        p2p.atomic_add_f32(c, dst[0], target=1, n=1 << 24)
+    torch.cuda.synchronize()
+    print(f"p2p kernels on one GPU: {args.launches} rounds of load / store / all_load / atomic_add")
+    ranks[0].close()
+
+
+def run_elementwise(args):
+    """RMSNorm, SwiGLU and residual add on 16384 x 4096 (x 11008) bf16 activations: memory-bound kernels."""
+    from iris_b200.ops import elementwise as E
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn((16384, 4096), generator=g, device="cuda").to(torch.bfloat16)
+    y = torch.randn((16384, 4096), generator=g, device="cuda").to(torch.bfloat16)
+    w = torch.ones(4096, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty_like(x)
+    gu = torch.randn((16384, 2 * 1376), generator=g, device="cuda").to(torch.bfloat16)
+    h = torch.empty((16384, 1376), device="cuda", dtype=torch.bfloat16)
+    for _ in range(args.launches):
+        E.rmsnorm(x, w, out, 1e-6)
+        E.swiglu(gu, h)
+        E.residual_add(x, y)
+    torch.cuda.synchronize()
+    print(f"elementwise kernels: {args.launches} rounds of rmsnorm / swiglu / residual_add")
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="gemm", choices=["gemm", "all_scatter", "atomic", "one_shot", "two_shot", "ag"])
+    ap.add_argument("--workload", default="gemm", choices=["gemm", "all_scatter", "atomic", "one_shot", "two_shot", "ag", "p2p", "elementwise"])
     ap.add_argument("--world", type=int, default=1)
     ap.add_argument("-m", type=int, default=8192)
     ap.add_argument("-n", type=int, default=3584)
@@ -30,6 +67,10 @@ def main():
     ap.add_argument("--cta_group", type=int, default=0)
     args = ap.parse_args()
     W = args.world
+    if args.workload == "p2p":
+        return run_p2p(args)
+    if args.workload == "elementwise":
+        return run_elementwise(args)
     ranks = iris.Iris.local_world(W, heap_size=(1 << 30) // max(1, W // 2))
     g = torch.Generator(device="cuda").manual_seed(0)
 

@@ -34,6 +34,7 @@ def main():
     ap.add_argument("--num_warmup", type=int, default=3)
     ap.add_argument("--heap_size", type=int, default=12 << 30)
     ap.add_argument("--output_file", default="")
+    ap.add_argument("--breakdown", action="store_true", help="per-phase device times (max over ranks) of one forward")
     ap.add_argument("--heap_mode", default=None, choices=["ipc", "vmm"],
                     help="vmm + IRIS_NVLS=1 in the environment binds the heap to an NVLS multicast object")
     args = ap.parse_args()
@@ -79,6 +80,31 @@ def main():
         if rank == 0:
             print(f"TP decoder x{cfg.n_layers} layers, W={world}, {cfg.tokens} tokens: fused {f_ms * 1e3:.0f} us | "
                   f"cuBLAS+NCCL {b_ms * 1e3:.0f} us | x{b_ms / f_ms:.2f}", flush=True)
+    if args.breakdown:
+        def phase_times(run):
+            marks = []
+
+            def tick(name):
+                e = torch.cuda.Event(enable_timing=True)
+                e.record()
+                marks.append((name, e))
+            for _ in range(2):
+                marks.clear()
+                ctx.barrier()
+                run(tick)
+            torch.cuda.synchronize()
+            acc = {}
+            for (n0, e0), (_, e1) in zip(marks[:-1], marks[1:]):
+                acc[n0] = acc.get(n0, 0.0) + e0.elapsed_time(e1) * 1e3
+            return {k_: reduce_ranks(ctx, v, "max") for k_, v in sorted(acc.items())}
+        a, b = mine.clone(), mine.clone()
+        f_ph = phase_times(lambda tick: model.forward([a], timers=tick))
+        b_ph = phase_times(lambda tick: base.forward(b, timers=tick))
+        res["breakdown_us"] = {"fused": f_ph, "baseline": b_ph}
+        if rank == 0:
+            print("phase (us, summed over layers)      fused    cuBLAS+NCCL")
+            for k_ in f_ph:
+                print(f"  {k_:<28} {f_ph[k_]:10.0f} {b_ph.get(k_, 0.0):10.0f}", flush=True)
     if rank == 0 and args.output_file:
         os.makedirs(os.path.dirname(args.output_file) or ".", exist_ok=True)
         with open(args.output_file, "w") as f:

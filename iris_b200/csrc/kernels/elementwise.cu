@@ -64,21 +64,37 @@ __global__ void __launch_bounds__(kThreads) rmsnorm_kernel(const __nv_bfloat16* 
   }
 }
 
-// out[r, c] = silu(gu[r, c]) * gu[r, inter + c]
+// out[r, c] = silu(gu[r, c]) * gu[r, inter + c]; four independent 16-byte load pairs in flight per thread
 __global__ void swiglu_kernel(const __nv_bfloat16* __restrict__ gu, int64_t ldg, __nv_bfloat16* __restrict__ out,
                               int64_t ldo, int rows, int inter) {
+  constexpr int U = 4;
   const int nv = inter / 8;
   const int64_t total = (int64_t)rows * nv;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    const int r = (int)(i / nv), c = (int)(i - (int64_t)r * nv);
-    const uint4 g = *reinterpret_cast<const uint4*>(gu + (int64_t)r * ldg + c * 8);
-    const uint4 u = *reinterpret_cast<const uint4*>(gu + (int64_t)r * ldg + inter + c * 8);
-    float a[8], b[8];
-    unpack8(g, a);
-    unpack8(u, b);
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i0 < total; i0 += U * stride) {
+    uint4 g[U], u[U];
+    int r[U], c[U];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) a[j] = a[j] / (1.f + __expf(-a[j])) * b[j];
-    *reinterpret_cast<uint4*>(out + (int64_t)r * ldo + c * 8) = pack8(a);
+    for (int q = 0; q < U; ++q) {
+      const int64_t i = i0 + q * stride;
+      if (i < total) {
+        r[q] = (int)(i / nv);
+        c[q] = (int)(i - (int64_t)r[q] * nv);
+        g[q] = *reinterpret_cast<const uint4*>(gu + (int64_t)r[q] * ldg + c[q] * 8);
+        u[q] = *reinterpret_cast<const uint4*>(gu + (int64_t)r[q] * ldg + inter + c[q] * 8);
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < U; ++q) {
+      if (i0 + q * stride < total) {
+        float a[8], b[8];
+        unpack8(g[q], a);
+        unpack8(u[q], b);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) a[j] = a[j] / (1.f + __expf(-a[j])) * b[j];
+        *reinterpret_cast<uint4*>(out + (int64_t)r[q] * ldo + c[q] * 8) = pack8(a);
+      }
+    }
   }
 }
 

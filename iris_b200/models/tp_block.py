@@ -121,27 +121,39 @@ class TPDecoder:
         r = self.ranks[local]
         return slice(r * self.ts, (r + 1) * self.ts)
 
-    def forward(self, x_shards: Sequence[torch.Tensor]) -> Sequence[torch.Tensor]:
-        """``x_shards[l]``: [T/W, H] bf16 of local rank l; updated in place and returned."""
+    def forward(self, x_shards: Sequence[torch.Tensor], timers=None) -> Sequence[torch.Tensor]:
+        """``x_shards[l]``: [T/W, H] bf16 of local rank l; updated in place and returned.  ``timers``: optional
+        callable ``timers(name)`` invoked before every phase (per-phase breakdowns with CUDA events)."""
         cfg, nl = self.cfg, len(self.ctxs)
         n = 0
+        tick = timers if timers is not None else (lambda name: None)
         for ops in self.layers:
+            tick("norm")
             for l in range(nl):
                 E.rmsnorm(x_shards[l], ops["w"][l]["norm1"], ops["qkv"].a_full[l][self.rows(l)], cfg.eps)
+            tick("qkv_ag_gemm")
             qkv = ops["qkv"]()
+            tick("attention")
             for l in range(nl):
                 attention(qkv[l], cfg, self.heads_local, self.attn[l])
+            tick("o_gemm_ar")
             o = ops["o"]()
+            tick("norm")
             for l in range(nl):
                 E.residual_add(x_shards[l], o[l][self.rows(l)])
                 E.rmsnorm(x_shards[l], ops["w"][l]["norm2"], ops["gu"].a_full[l][self.rows(l)], cfg.eps)
+            tick("gu_ag_gemm")
             gu = ops["gu"]()
+            tick("swiglu")
             for l in range(nl):
                 E.swiglu(gu[l], self.h[l])
+            tick("down_gemm_ar")
             d = ops["down"]()
+            tick("norm")
             for l in range(nl):
                 E.residual_add(x_shards[l], d[l][self.rows(l)])
             n += 4 + 5 * nl
+        tick("end")
         self.kernel_launches += n
         return x_shards
 
@@ -178,9 +190,10 @@ class TPDecoderBaseline:
         self.gu = torch.empty((T, 2 * I // world), **bf)
         self.h = torch.empty((T, I // world), **bf)
 
-    def forward(self, x_shard: torch.Tensor) -> torch.Tensor:
+    def forward(self, x_shard: torch.Tensor, timers=None) -> torch.Tensor:
         import torch.distributed as dist
         cfg = self.cfg
+        tick = timers if timers is not None else (lambda name: None)
         rows = slice(self.rank * self.ts, (self.rank + 1) * self.ts)
 
         def gather(t):
@@ -193,20 +206,30 @@ class TPDecoderBaseline:
             if self.world > 1:
                 dist.all_reduce(t)
         for w in self.w:
+            tick("norm")
             E.rmsnorm(x_shard, w["norm1"], self.xn, cfg.eps)
+            tick("qkv_ag_gemm")
             gather(self.xn)
             torch.matmul(self.full, w["wqkv"].t(), out=self.qkv)
+            tick("attention")
             attention(self.qkv, cfg, self.heads_local, self.attn)
+            tick("o_gemm_ar")
             torch.matmul(self.attn, w["wo"].t(), out=self.part)
             reduce(self.part)
+            tick("norm")
             E.residual_add(x_shard, self.part[rows])
             E.rmsnorm(x_shard, w["norm2"], self.xn, cfg.eps)
+            tick("gu_ag_gemm")
             gather(self.xn)
             torch.matmul(self.full, w["wgu"].t(), out=self.gu)
+            tick("swiglu")
             E.swiglu(self.gu, self.h)
+            tick("down_gemm_ar")
             torch.matmul(self.h, w["wd"].t(), out=self.part)
             reduce(self.part)
+            tick("norm")
             E.residual_add(x_shard, self.part[rows])
+        tick("end")
         return x_shard
 
 

@@ -1,0 +1,100 @@
+"""Benchmark timer, result writers, roofline arithmetic, sweep driver and configuration files (no GPU needed)."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import iris_b200 as iris
+from iris_b200.utils import roofline
+from iris_b200.utils.results import JSONWriter, validate_gemm
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_do_bench_cpu_modes():
+    calls = {"fn": 0, "barrier": 0, "pre": 0}
+
+    def fn():
+        calls["fn"] += 1
+
+    def barrier():
+        calls["barrier"] += 1
+
+    def pre():
+        calls["pre"] += 1
+    ms = iris.do_bench(fn, barrier, pre, n_warmup=2, n_repeat=5)
+    assert ms >= 0.0
+    assert calls["fn"] == 1 + 2 + 5 and calls["pre"] == 1 + 2 + 5
+    assert calls["barrier"] == 2 + 2 * 7 + 1          # around the first call, twice per iteration, once at the end
+    allv = iris.do_bench(fn, n_warmup=0, n_repeat=4, return_mode="all")
+    assert len(allv) == 4
+    q = iris.do_bench(fn, n_warmup=0, n_repeat=4, quantiles=[0.5, 0.9])
+    assert len(q) == 2 and q[0] <= q[1]
+    for mode in ("min", "max", "median", "mean"):
+        assert iris.do_bench(fn, n_warmup=0, n_repeat=3, return_mode=mode) >= 0.0
+
+
+def test_memset_tensor_cpu_and_asserts():
+    t = torch.full((10,), 3, dtype=torch.int32)
+    iris.memset_tensor(t, 7)
+    assert t.tolist() == [7] * 10
+    with pytest.raises(AssertionError):
+        iris.memset_tensor(torch.zeros(4), 0)
+    with pytest.raises(AssertionError):
+        iris.memset_tensor(torch.zeros((4, 4), dtype=torch.int32).t(), 0)
+
+
+def test_json_writer(tmp_path):
+    path = tmp_path / "sub" / "log.json"
+    w = JSONWriter(str(path))
+    w.add_field("m", 8192)
+    w.add_fields(world_size=8, fused_ms=0.37)
+    w.flush()
+    assert json.loads(path.read_text()) == {"m": 8192, "world_size": 8, "fused_ms": 0.37}
+    JSONWriter("").flush()  # no file requested: nothing happens
+
+
+def test_validate_gemm_cpu():
+    a, b = torch.randn(16, 8), torch.randn(8, 4)
+    assert validate_gemm(a, b, a @ b, atol=1e-3)
+    bad = (a @ b).clone()
+    bad[3, 2] += 5
+    assert not validate_gemm(a, b, bad, atol=1e-3)
+
+
+def test_roofline_numbers():
+    pk = roofline.Peaks(6539.0, 1667.0, 1417.0, 770.0, "measured")
+    r1 = roofline.all_scatter_roofline_us(8192, 14336, 4096, 1, pk)
+    assert r1["bound"] == "compute" and abs(r1["target_us"] - 577.1) < 1.0
+    r8 = roofline.all_scatter_roofline_us(8192, 14336, 4096, 8, pk)
+    assert r8["bound"] == "link" and abs(r8["link_us"] - 267.0) < 1.0
+    one = roofline.all_reduce_roofline_us(8192, 4096, 11008, 8, pk, "one_shot")
+    two = roofline.all_reduce_roofline_us(8192, 4096, 11008, 8, pk, "two_shot")
+    assert abs(one["link_us"] - 610.1) < 1.0 and abs(two["link_us"] - 152.5) < 1.0
+    eff = roofline.effective_link_bandwidth({"m": 8192, "n": 14336, "world_size": 8, "fused_ms": 0.38})
+    assert abs(eff["gbs_per_rank"] - 540.8) < 1.0
+    assert roofline.load_peaks("/nonexistent.json").source == "fallback"
+
+
+def test_config_files_and_sweep_dry_run():
+    shapes = json.load(open(os.path.join(ROOT, "configs", "shapes.json")))["shapes"]
+    assert any(s["name"] == "config3_all_scatter" and (s["m"], s["n"], s["k"]) == (8192, 14336, 4096) for s in shapes)
+    assert {1, 128, 1024, 8192} <= {s["m"] for s in shapes if "config4" in s["name"]}
+    tiling = json.load(open(os.path.join(ROOT, "configs", "tiling_b200.json")))
+    assert tiling["default"]["BLK_M"] == 128 and tiling["default"]["BLK_N"] == 256
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "examples", "benchmark", "bench_all_shapes.py"), "-n",
+                          "--gpus", "8", "--only", "config3_all_scatter", "config4_all_reduce_m128"],
+                         capture_output=True, text=True, check=True).stdout
+    assert "07_gemm_all_scatter/benchmark.py" in out and "-np 8" in out
+    assert out.count("09_gemm_one_shot_all_reduce/benchmark.py") == 2 and "--variant two_shot" in out
+
+
+def test_launcher_time_limit(tmp_path):
+    from iris_b200.launch import launch
+    slow = tmp_path / "slow.py"
+    slow.write_text("import time\ntime.sleep(30)\n")
+    code, _ = launch(2, [str(slow)], timeout_s=1.5, capture=True)
+    assert code == 124

@@ -2,21 +2,24 @@
 //
 //   C[M, N] = A[M, K] * B[N, K]^T        (both operands K-contiguous, fp32 accumulation, bf16 output)
 //
-// Data path per CTA (one CTA per SM, 128 x 256 output tile):
-//   warp 0      TMA producer: cp.async.bulk.tensor loads of A (128 x 64) and B (256 x 64) slices into a
-//               4-deep shared-memory ring, completion on mbarriers.  Every CTA loads for itself; there is
-//               no cluster multicast.
-//   warp 1      one thread issues tcgen05.mma (M128 N256 K16, cta_group::1); accumulators live in tensor
-//               memory, two of them, so the epilogue of tile i overlaps the main loop of tile i+1.
+// Data path per CTA (one CTA per SM; 128 x 256 output tile per CTA, or 256 x 256 per pair of CTAs):
+//   warp 0      TMA producer: cp.async.bulk.tensor loads of the A (128 x 64) and B slices into a shared-memory ring,
+//               completion on mbarriers.  Every CTA loads for itself; there is no cluster multicast.
+//   warp 1      one thread issues tcgen05.mma (M128 N256 K16 with cta_group::1, M256 N256 K16 with cta_group::2);
+//               accumulators live in tensor memory, two of them, so the epilogue of tile i overlaps the main loop
+//               of tile i+1.
 //   warps 2-5   epilogue: tcgen05.ld -> bf16 -> swizzled shared memory -> the collective:
 //                 store     TMA store of the tile into the C buffer of every rank       (GEMM + all-scatter)
 //                 reduce    TMA reduce-add of the tile into the C buffer of every rank  (GEMM + atomic all-reduce)
-//                 one-shot  tile -> own partial buffer, per-tile flag on every rank, then pull the tile
-//                           from all ranks and sum in fp32                              (GEMM + one-shot all-reduce)
-//                 two-shot  as one-shot, but only rank (tile % world) sums and pushes the result
-//   warps 6-7   all-gather prologue (optional): push this rank's rows of A to every peer in slices, each
-//               followed by a release increment of the peer's chunk flag; the producer warp waits for a
-//               chunk's flag before it loads rows that came from a peer (data is read from LOCAL memory).
+//                 one-shot  tile -> partial buffer (own, or pushed into an inbox slot of every rank) + per-tile flag
+//                 two-shot  tile -> own partial buffer + flag on the rank that owns the tile
+//   warps 6-9   (one-/two-shot kernels) reducer: waits for a tile's flag, fetches the partials of all ranks (TMA
+//               loads into a ring of pull buffers, or plain loads from the local inbox, or NVLS multimem.ld_reduce),
+//               adds in fp32 and writes the result to this rank (one-shot) or to every rank (two-shot), while the
+//               other warps keep computing.
+//   warps 6-7   (other kernels) all-gather prologue: push this rank's rows of A to every peer in slices, each
+//               followed by a release increment of the peer's chunk flag; the producer warp waits for a chunk's
+//               flag before it loads rows that came from a peer (data is read from LOCAL memory).
 //
 // What it replaces in the reference: the persistent Triton kernels
 // examples/07_gemm_all_scatter/gemm_all_scatter.py:97-255,

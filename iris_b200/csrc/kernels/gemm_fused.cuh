@@ -5,7 +5,8 @@
 //   * examples/07_gemm_all_scatter/gemm_all_scatter.py:97-255        -> kEpiStore   (push tile to every rank)
 //   * examples/08_gemm_atomics_all_reduce/gemm_atomics_all_reduce.py:94-252 -> kEpiReduce (add tile into every rank)
 //   * examples/09_gemm_one_shot_all_reduce/gemm_one_shot_all_reduce.py:94-275 -> kEpiOneShot / kEpiTwoShot
-// plus the all-gather -> GEMM prologue that the reference does not have.
+// plus the all-gather -> GEMM prologue, the push / K-split form of one-shot for short matrices and the NVLS two-shot
+// reducer, which the reference does not have.
 #pragma once
 #include <cuda.h>
 #include <stdint.h>
@@ -20,7 +21,7 @@ constexpr int BM = 128;
 constexpr int BN = 256;
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
-constexpr int kStages = 4;   // shared-memory ring of (A,B) slices
+constexpr int kStages = 4;   // shared-memory ring of (A,B) slices for single CTAs (see Cfg in gemm_fused.cu for the others)
 constexpr int kAccBufs = 2;  // TMEM accumulators: epilogue of tile i overlaps main loop of tile i+1
 constexpr int kEpiCols = 64; // epilogue works on 128 x 64 sub-tiles (128-byte rows of bf16)
 constexpr int kEpiBufs = 2;

@@ -53,3 +53,10 @@ def test_launcher_propagates_failure(tmp_path):
     bad.write_text("import os, sys, time\nif os.environ['RANK'] == '1':\n    sys.exit(3)\ntime.sleep(30)\n")
     code, _ = run_ranks(2, [str(bad)], timeout_s=20)
     assert code == 3
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_native_fd_passing(world):
+    """SCM_RIGHTS descriptor exchange of the native runtime (what the VMM heap uses for allocation handles)."""
+    code, outs = run_ranks(world, [os.path.join(W, "cpu_fd_passing.py")])
+    _ok(code, outs)

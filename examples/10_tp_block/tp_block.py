@@ -27,7 +27,9 @@ def main():
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--seq", type=int, default=2048)
-    ap.add_argument("--variant", default="two_shot", choices=["two_shot", "one_shot", "atomic"])
+    ap.add_argument("--variant", default="two_shot", choices=["two_shot", "one_shot", "atomic", "reduce_scatter"],
+                    help="row-parallel projections: an all-reduce variant, or reduce_scatter (every rank receives only its "
+                         "own token rows; the baseline then uses NCCL reduce_scatter_tensor)")
     ap.add_argument("-v", "--validate", action="store_true", help="compare with the unsharded fp32 oracle (1 layer subset)")
     ap.add_argument("-b", "--benchmark", action="store_true")
     ap.add_argument("--num_experiments", type=int, default=10)
@@ -45,7 +47,7 @@ def main():
     dev = ctx.get_device()
     device_barrier(ctx)
     model = TPDecoder(ctx, cfg, variant=args.variant)
-    base = TPDecoderBaseline(cfg, rank, world, dev)
+    base = TPDecoderBaseline(cfg, rank, world, dev, scatter=args.variant == "reduce_scatter")
     g = torch.Generator(device=dev).manual_seed(cfg.seed)
     x = torch.randn((cfg.tokens, cfg.hidden), generator=g, device=dev).to(torch.bfloat16)
     ts = cfg.tokens // world

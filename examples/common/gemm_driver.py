@@ -1,4 +1,4 @@
-"""Driver shared by the fused GEMM + collective examples 07 / 08 / 09.
+"""Driver shared by the fused GEMM + collective examples 07 / 08 / 09 / 11.
 
 Role in the reference: ``examples/07_gemm_all_scatter/benchmark.py:24-299`` and its two copies (argument parsing,
 operand set-up with a fixed seed, sharding, validation against ``A @ B``, timing, JSON).  Differences: time is
@@ -18,7 +18,7 @@ from iris_b200.utils.results import JSONWriter
 
 def parse_args(kind: str):
     d = {"all_scatter": dict(m=8192, n=14336, k=4096), "atomic": dict(m=8192, n=4096, k=11008),
-         "one_shot": dict(m=8192, n=4096, k=11008)}[kind]
+         "one_shot": dict(m=8192, n=4096, k=11008), "reduce_scatter": dict(m=16384, n=4096, k=14336)}[kind]
     ap = argparse.ArgumentParser(description=f"Fused GEMM + {kind}", formatter_class=argparse.ArgumentDefaultsHelpFormatter)
     ap.add_argument("-m", type=int, default=d["m"])
     ap.add_argument("-n", type=int, default=d["n"])
@@ -76,6 +76,22 @@ def run(kind: str, seed: int):
                 dist.all_gather_into_tensor(gathered, c_part)
         a_local, b_local = A, bt_local
         variant = "all_scatter"
+    elif kind == "reduce_scatter":
+        if k % world or (k // world) % 8:
+            raise SystemExit("K / ranks must be a multiple of 8")
+        ks = k // world
+        a_local, b_local = A[:, rank * ks:(rank + 1) * ks], Bt[:, rank * ks:(rank + 1) * ks]
+        op = G.gemm_reduce_scatter(ctx, [a_local], [b_local], ctas_per_rank=ctas, group_m=args["gsize_m"],
+                                   trace=args["trace_tiles"])
+        roof = roofline.all_reduce_roofline_us(m, n, k, world, peaks, "reduce_scatter")
+        c_part = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+        c_kept = torch.empty((m // world, n), dtype=torch.bfloat16, device=dev)
+
+        def unfused():
+            torch.matmul(a_local, b_local.t(), out=c_part)
+            if world > 1:
+                dist.reduce_scatter_tensor(c_kept, c_part)
+        variant = "reduce_scatter"
     else:
         variant = args["variant"] or kind
         if k % world or (k // world) % 8:
@@ -109,9 +125,13 @@ def run(kind: str, seed: int):
     ok = True
     if args["validate"]:
         rows = slice(0, min(m, 1024))
+        got = out[rows]
+        if kind == "reduce_scatter":  # this rank holds rows [rank * m / world, ...) only
+            rows = slice(rank * (m // world), rank * (m // world) + min(m // world, 1024))
+            got = out[:rows.stop - rows.start]
         ref = A[rows].float() @ Bt.float().t()
         # bf16 rounding of the result and (all-reduce) of the partials, relative to the largest entry
-        err = (out[rows].float() - ref).abs().max().item()
+        err = (got.float() - ref).abs().max().item()
         ok = err <= (2.0 + world) * 2.0 ** -8 * ref.abs().max().item()
         ctx.log(f"Validation {'successful' if ok else 'FAILED'}.")
         js.add_field("success", ok)

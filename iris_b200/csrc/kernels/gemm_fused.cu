@@ -253,6 +253,15 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
   // Two-shot: the rank that sums tile t.  A scheduling unit visits tiles u, u + G, u + 2G, ...; rotating the owner
   // with the visit number gives every unit of every rank the same share of the summing work.
   auto owner_of = [&](int t) { return ((t % G) + (t / G)) % W; };
+  // Reduce-scatter: the tiles of one keeper's row block are contiguous in raster order (the host picks group_m so).
+  // Every rank starts with the block of the next rank and ends with its own: at any time each keeper receives from
+  // one source, and the block that needs no link is the one whose sum is wanted last.
+  const int rs_tpc = p.rs_rows > 0 ? (p.rs_rows / TM) * tiles_n : 0;  // tiles per row block
+  const int rs_rot = p.rs_rows > 0 ? ((rank + 1) % W) * rs_tpc : 0;
+  auto tile_of = [&](int t) {
+    const int x = t + rs_rot;
+    return x >= total_tiles ? x - total_tiles : x;
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -306,7 +315,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
       WorkIter sched(unit, G, total_tiles, kblocks, p);
       Work w;
       while (ok && sched.next(w)) {
-        const int tile = w.tile;
+        const int tile = tile_of(w.tile);
         TileCoord tc = raster(tile, tiles_m, tiles_n, p.group_m);
         if (p.ag) tc.m_idx = ag_actual_m(tc.m_idx, tiles_per_shard, rank, W);
         const int row0 = tc.m_idx * TM + pr * BM;
@@ -365,7 +374,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
       WorkIter sched(unit, G, total_tiles, kblocks, p);
       Work w;
       while (ok && sched.next(w)) {
-        const int tile = w.tile;
+        const int tile = tile_of(w.tile);
         if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1, p.timeout_ns, abort_flag)) {
           record_status(status, kTimeout, kSiteMmaAccEmpty, rank, tile, acc);
           *abort_flag = 1;
@@ -447,6 +456,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
       for (int i = 0; i < W; ++i) {
         const int dst = (rank + 1 + i) % W;
         if (p.mode == kEpiTwoShot && dst != owner_of(t)) continue;
+        if (p.rs_rows > 0 && dst != t / rs_tpc) continue;  // reduce-scatter: only the keeper of the rows sums them
         red_relaxed_sys_add(flag_ptr(p, dst, p.tile_flag_base + t * CG + pr), 1u);
       }
     };
@@ -454,7 +464,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
     WorkIter sched(unit, G, total_tiles, kblocks, p);
     Work w;
     while (sched.next(w)) {
-      const int tile = w.tile;
+      const int tile = tile_of(w.tile);
       TileCoord tc = raster(tile, tiles_m, tiles_n, p.group_m);
       if (p.ag) tc.m_idx = ag_actual_m(tc.m_idx, tiles_per_shard, rank, W);
       // Uniform decision for the whole epilogue group: one thread waits, everybody reads the verdict.
@@ -485,7 +495,8 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
       const int y = tc.m_idx * TM + pr * BM;
       // row inside the tmC matrix: partial buffer of this call's parity, inbox slot of (rank, piece) when pushing
       const int slot = p.push_partials ? rank * (p.ksplit > 1 ? p.ksplit : 1) + w.piece : 0;
-      const int y_st = (pulls ? p.part_row0 + slot * p.part_slot_rows : 0) + y;
+      const int keeper = p.rs_rows > 0 ? tile / rs_tpc : -1;  // reduce-scatter: the rank that keeps these rows
+      const int y_st = (pulls ? p.part_row0 + slot * p.part_slot_rows : 0) + y - (keeper > 0 ? keeper * p.rs_rows : 0);
 
       // Stream-K: a piece that covers only part of the tile's k-blocks adds its fp32 accumulator into the tile's
       // workspace and bumps the tile's k-block counter; the unit whose addition completes the count finishes the
@@ -583,6 +594,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
           if (push_all) {
             for (int i = 0; i < W; ++i) {  // peers first, starting with the next rank; own copy last
               const int t = (rank + 1 + i) % W;
+              if (keeper >= 0 && t != keeper) continue;
               if (p.mode == kEpiReduce) tma_reduce_add_2d(&p.tmC[t], x, y_st, src);
               else if (t == rank && !pulls) tma_store_2d_hint(&p.tmC[t], x, y_st, src, evict_first);
               else tma_store_2d(&p.tmC[t], x, y_st, src);
@@ -665,7 +677,11 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
       const bool by_chunk = p.ksplit > 1;
       constexpr int kChunks = BN / kEpiCols;
       const int n_items = by_chunk ? total_tiles * kChunks : total_tiles;
-      for (int item = unit; item < n_items && ok_all; item += G) {
+      // reduce-scatter: only the tiles of this rank's row block, which are [rank * rs_tpc, (rank + 1) * rs_tpc)
+      const int rs_base = p.rs_rows > 0 ? rank * p.rs_rows : 0;
+      const int item0 = p.rs_rows > 0 ? rank * rs_tpc + unit : unit;
+      const int item_end = p.rs_rows > 0 ? (rank + 1) * rs_tpc : n_items;
+      for (int item = item0; item < item_end && ok_all; item += G) {
         const int t = by_chunk ? item / kChunks : item;
         const int c0 = by_chunk ? item - t * kChunks : 0;
         const int c1 = by_chunk ? c0 + 1 : kChunks;
@@ -743,7 +759,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
             for (int j = 0; j < kEpiCols; ++j) accv[j] = 0.f;
             if (row_live) {
               const uint8_t* src = reinterpret_cast<const uint8_t*>(p.heap_base[rank] + p.partial_off) +
-                                   ((uint64_t)(p.part_row0 + m0 + row) * p.N + n0 + c * kEpiCols) * 2;
+                                   ((uint64_t)(p.part_row0 + m0 - rs_base + row) * p.N + n0 + c * kEpiCols) * 2;
               const uint64_t slot_bytes = (uint64_t)p.part_slot_rows * p.N * 2;
               int sl = 0;
               for (; sl + 1 < NS; sl += 2) {
@@ -777,7 +793,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
               fence_proxy_async_smem();
               named_barrier_sync(3, 128);
               if (rissuer) {
-                tma_store_2d(&p.tmC[rank], n0 + c * kEpiCols, p.out_row0 + m0, redout_base);
+                tma_store_2d(&p.tmC[rank], n0 + c * kEpiCols, p.out_row0 + m0 - rs_base, redout_base);
                 bulk_commit();
               }
             } else if (row_live) {
@@ -791,7 +807,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
                   o.z = pack_bf16x2(accv[8 * j + 4], accv[8 * j + 5]);
                   o.w = pack_bf16x2(accv[8 * j + 6], accv[8 * j + 7]);
                   st_v4(reinterpret_cast<uint4*>(p.heap_base[rank] + p.out_off +
-                                                 ((uint64_t)(m0 + row) * p.ldo + col) * 2), o);
+                                                 ((uint64_t)(m0 - rs_base + row) * p.ldo + col) * 2), o);
                 }
               }
             }
@@ -1097,7 +1113,8 @@ struct IrisGemmDesc {
   int device;
   int cta_group;
   int dp_tiles, sk_units, sk_flag_base;  // stream-K schedule (dp_tiles < 0: every tile whole)
-  int push_partials, part_slot_rows, ksplit;  // 1: one CTA per 128 x 256 tile; 2: a CTA pair (cluster of 2) per 256 x 256 tile
+  int push_partials, part_slot_rows, ksplit;
+  int rs_rows;                 // reduce-scatter: rows kept per rank (0 = off); see FusedGemmParams::rs_rows
 };
 
 struct IrisGemmPlan {
@@ -1133,6 +1150,22 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
     return nullptr;
   }
   const int cg = d->cta_group == 2 ? 2 : 1;
+  if (d->rs_rows > 0) {
+    const int gm = d->group_m < 1 ? 1 : d->group_m;
+    if (d->mode != kEpiOneShot || !d->push_partials || d->ksplit > 1 || d->sk_units > 0) {
+      snprintf(g_err, sizeof(g_err), "reduce-scatter runs as one-shot with pushed partials, whole tiles, no K split");
+      return nullptr;
+    }
+    if ((long long)d->rs_rows * d->world != d->M || d->rs_rows % (BM * cg) != 0 || (d->rs_rows / (BM * cg)) % gm != 0) {
+      snprintf(g_err, sizeof(g_err), "reduce-scatter needs M = world * rs_rows, rs_rows a multiple of %d x group_m",
+               BM * cg);
+      return nullptr;
+    }
+    if (d->part_slot_rows < d->rs_rows) {
+      snprintf(g_err, sizeof(g_err), "reduce-scatter: inbox slots must hold rs_rows rows");
+      return nullptr;
+    }
+  }
   if (d->ag) {
     if (d->M % d->world != 0 || (d->M / d->world) % (BM * cg) != 0) {
       snprintf(g_err, sizeof(g_err), "all-gather prologue needs M / world to be a multiple of %d", BM * cg);
@@ -1252,6 +1285,7 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
     p.push_partials = d->push_partials;
     p.part_slot_rows = d->part_slot_rows;
     p.ksplit = d->ksplit > 1 ? d->ksplit : 1;
+    p.rs_rows = d->rs_rows > 0 ? d->rs_rows : 0;
     p.tile_flag_base = d->tile_flag_base;
     p.ag_flag_base = d->ag_flag_base;
   }

@@ -97,6 +97,13 @@ class TPDecoder:
         W, T, H, I = self.world, cfg.tokens, cfg.hidden, cfg.intermediate
         if cfg.n_heads % W or I % W or T % W or (I // W) % 8:
             raise ValueError("heads, intermediate size and tokens must divide by the number of ranks")
+        # "reduce_scatter": the row-parallel projections deliver only this rank's token rows (all the layer uses)
+        self.scatter = variant == "reduce_scatter"
+
+        def row_parallel(a, bt):
+            if self.scatter:
+                return G.gemm_reduce_scatter(self.ctxs, a, bt)
+            return G.gemm_all_reduce(self.ctxs, a, bt, variant=variant)
         self.heads_local = cfg.n_heads // W
         self.ts = T // W
         nl = len(self.ctxs)
@@ -110,9 +117,9 @@ class TPDecoder:
             ops = {
                 "w": sh,
                 "qkv": G.all_gather_gemm(self.ctxs, T, [s["wqkv"] for s in sh], ag_slices=ag_slices),
-                "o": G.gemm_all_reduce(self.ctxs, self.attn, [s["wo"] for s in sh], variant=variant),
+                "o": row_parallel(self.attn, [s["wo"] for s in sh]),
                 "gu": G.all_gather_gemm(self.ctxs, T, [s["wgu"] for s in sh], ag_slices=ag_slices),
-                "down": G.gemm_all_reduce(self.ctxs, self.h, [s["wd"] for s in sh], variant=variant),
+                "down": row_parallel(self.h, [s["wd"] for s in sh]),
             }
             self.layers.append(ops)
         self.kernel_launches = 0
@@ -140,7 +147,7 @@ class TPDecoder:
             o = ops["o"]()
             tick("norm")
             for l in range(nl):
-                E.residual_add(x_shards[l], o[l][self.rows(l)])
+                E.residual_add(x_shards[l], o[l] if self.scatter else o[l][self.rows(l)])
                 E.rmsnorm(x_shards[l], ops["w"][l]["norm2"], ops["gu"].a_full[l][self.rows(l)], cfg.eps)
             tick("gu_ag_gemm")
             gu = ops["gu"]()
@@ -151,7 +158,7 @@ class TPDecoder:
             d = ops["down"]()
             tick("norm")
             for l in range(nl):
-                E.residual_add(x_shards[l], d[l][self.rows(l)])
+                E.residual_add(x_shards[l], d[l] if self.scatter else d[l][self.rows(l)])
             n += 4 + 5 * nl
         tick("end")
         self.kernel_launches += n
@@ -171,8 +178,9 @@ class TPDecoder:
 class TPDecoderBaseline:
     """Same network, one process per GPU: cuBLAS GEMMs + NCCL all_gather_into_tensor / all_reduce."""
 
-    def __init__(self, cfg: TPConfig, rank: int, world: int, device):
+    def __init__(self, cfg: TPConfig, rank: int, world: int, device, scatter: bool = False):
         self.cfg, self.rank, self.world = cfg, rank, world
+        self.scatter = bool(scatter) and world > 1   # reduce_scatter_tensor instead of all_reduce
         T, H, I = cfg.tokens, cfg.hidden, cfg.intermediate
         self.heads_local = cfg.n_heads // world
         self.ts = T // world
@@ -187,6 +195,7 @@ class TPDecoderBaseline:
         self.qkv = torch.empty((T, 3 * H // world), **bf)
         self.attn = torch.empty((T, H // world), **bf)
         self.part = torch.empty((T, H), **bf)
+        self.kept = torch.empty((self.ts, H), **bf)
         self.gu = torch.empty((T, 2 * I // world), **bf)
         self.h = torch.empty((T, I // world), **bf)
 
@@ -203,8 +212,13 @@ class TPDecoderBaseline:
                 self.full.copy_(t)
 
         def reduce(t):
+            """Sum over ranks; returns this rank's token rows of the sum."""
+            if self.scatter:
+                dist.reduce_scatter_tensor(self.kept, t)
+                return self.kept
             if self.world > 1:
                 dist.all_reduce(t)
+            return t[rows]
         for w in self.w:
             tick("norm")
             E.rmsnorm(x_shard, w["norm1"], self.xn, cfg.eps)
@@ -215,9 +229,9 @@ class TPDecoderBaseline:
             attention(self.qkv, cfg, self.heads_local, self.attn)
             tick("o_gemm_ar")
             torch.matmul(self.attn, w["wo"].t(), out=self.part)
-            reduce(self.part)
+            kept = reduce(self.part)
             tick("norm")
-            E.residual_add(x_shard, self.part[rows])
+            E.residual_add(x_shard, kept)
             E.rmsnorm(x_shard, w["norm2"], self.xn, cfg.eps)
             tick("gu_ag_gemm")
             gather(self.xn)
@@ -226,9 +240,9 @@ class TPDecoderBaseline:
             E.swiglu(self.gu, self.h)
             tick("down_gemm_ar")
             torch.matmul(self.h, w["wd"].t(), out=self.part)
-            reduce(self.part)
+            kept = reduce(self.part)
             tick("norm")
-            E.residual_add(x_shard, self.part[rows])
+            E.residual_add(x_shard, kept)
         tick("end")
         return x_shard
 

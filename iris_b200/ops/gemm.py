@@ -50,6 +50,7 @@ class _Desc(ctypes.Structure):
         ("device", ctypes.c_int), ("cta_group", ctypes.c_int),
         ("dp_tiles", ctypes.c_int), ("sk_units", ctypes.c_int), ("sk_flag_base", ctypes.c_int),
         ("push_partials", ctypes.c_int), ("part_slot_rows", ctypes.c_int), ("ksplit", ctypes.c_int),
+        ("rs_rows", ctypes.c_int),
     ]
 
 
@@ -113,7 +114,8 @@ class FusedGemm:
                  out: Optional[Sequence[torch.Tensor]] = None, ag: bool = False, ag_slices: int = 8,
                  ctas_per_rank: Optional[int] = None, group_m: int = 8, timeout_ms: float = 2000.0,
                  cta_group: Optional[int] = None, trace: bool = False, stream_k: Optional[bool] = None,
-                 push: Optional[bool] = None, ksplit: Optional[int] = None, nvls: Optional[bool] = None):
+                 push: Optional[bool] = None, ksplit: Optional[int] = None, nvls: Optional[bool] = None,
+                 reduce_scatter: bool = False):
         self.ctxs: List[Iris] = [ctxs] if isinstance(ctxs, Iris) else list(ctxs)
         c0 = self.ctxs[0]
         if c0.backend != "cuda":
@@ -153,9 +155,22 @@ class FusedGemm:
         # CTA pairs (256 x 256 tiles, cta_group::2) for anything taller than one 128-row tile; single CTAs else
         if cta_group is None:
             cta_group = 2 if self.M > BM and (not self.ag or (self.M // self.world) % (2 * BM) == 0) else 1
+            if reduce_scatter and self.M % (self.world * 2 * BM) != 0:
+                cta_group = 1
         if cta_group not in (1, 2):
             raise ValueError("cta_group must be 1 or 2")
         self.cta_group = cta_group
+        # reduce-scatter: rank r keeps rows [r * M / world, (r + 1) * M / world) of the sum
+        self.rs_rows = 0
+        if reduce_scatter:
+            if mode != "one_shot":
+                raise ValueError("reduce_scatter=True goes with mode='one_shot'")
+            if self.M % (self.world * BM * cta_group) != 0:
+                raise ValueError(f"reduce-scatter needs M to be a multiple of world x {BM * cta_group}")
+            self.rs_rows = self.M // self.world
+            push, ksplit = True, 1
+            mt = self.rs_rows // (BM * cta_group)     # m-tiles per rank: the raster groups must not straddle ranks
+            group_m = max(g for g in range(1, max(1, int(group_m)) + 1) if mt % g == 0)
         self.ctas_per_rank = int(ctas_per_rank) if ctas_per_rank else sms // self.num_local
         self.ctas_per_rank -= self.ctas_per_rank % cta_group
         tiles_m, tiles_n = -(-self.M // (BM * cta_group)), -(-self.N // BN)
@@ -210,12 +225,13 @@ class FusedGemm:
             # One matrix per rank holds both partial buffers (call parity) and, unless the caller brings its own,
             # the output: [partial 0 | partial 1 | out], each padded to whole 256-row tiles, so that one tensor
             # map per rank serves partial stores, partial loads and output stores.
-            mp = -(-self.M // (2 * BM)) * (2 * BM)
+            rows = self.rs_rows if self.rs_rows else self.M    # rows of a slot and of the output
+            mp = -(-rows // (2 * BM)) * (2 * BM)
             slots = self.world * self.ksplit if self.push else 1   # inbox slots per parity
             regions = 2 * slots + (0 if out is not None else 1)
             self._pull_buf = [c.zeros((regions * mp, self.N), dtype=torch.bfloat16) for c in self.ctxs]
-            self.partial = [[b[q * slots * mp:q * slots * mp + self.M] for b in self._pull_buf] for q in range(2)]
-            self.out = list(out) if out is not None else [b[2 * slots * mp:2 * slots * mp + self.M]
+            self.partial = [[b[q * slots * mp:q * slots * mp + rows] for b in self._pull_buf] for q in range(2)]
+            self.out = list(out) if out is not None else [b[2 * slots * mp:2 * slots * mp + rows]
                                                           for b in self._pull_buf]
             c_bufs, c2_bufs = self._pull_buf, None
             ldc, c_cols_eff = self.N, self.N
@@ -270,6 +286,7 @@ class FusedGemm:
         d.push_partials = int(self.push)
         d.part_slot_rows = getattr(self, "_slot_rows", 0)
         d.ksplit = self.ksplit
+        d.rs_rows = self.rs_rows
         d.dp_tiles = self.dp_tiles if self.sk_units else -1
         d.sk_units = self.sk_units
         d.sk_flag_base = FLAG_HEADER + tile_flags + self.world * chunks_per_shard
@@ -370,6 +387,16 @@ def gemm_all_reduce(ctxs, a, bt, variant: str = "one_shot", **kw) -> FusedGemm:
     if variant in ("one_shot", "two_shot"):
         return FusedGemm(ctxs, a, bt, variant, **kw)
     raise ValueError("variant must be 'auto', 'atomic', 'one_shot' or 'two_shot'")
+
+
+def gemm_reduce_scatter(ctxs, a, bt, **kw) -> FusedGemm:
+    """``C_r[M / world, N] = rows r of (sum over ranks of A_q @ B_q)`` (K sharded): the row-parallel projection of a
+    sequence-parallel layer, where every rank goes on with its own token rows only.  Each partial tile crosses the
+    link once, to the rank that keeps its rows, in an order that gives every keeper one sender at a time; the keeper
+    sums the ``world`` slots from local memory in fp32.  ``op.out[l]`` is the kept ``[M / world, N]`` block.  (The
+    reference stops at all-reduce, ``examples/08_gemm_atomics_all_reduce`` and ``09_gemm_one_shot_all_reduce``; its
+    baseline of this collective is ``examples/benchmark/reference/reduce_scatter.py``.)"""
+    return FusedGemm(ctxs, a, bt, "one_shot", reduce_scatter=True, **kw)
 
 
 def all_gather_gemm(ctxs, M: int, bt, **kw) -> FusedGemm:

@@ -55,10 +55,16 @@ def all_scatter_roofline_us(m, n, k, world, peaks: Peaks) -> dict:
 
 def all_reduce_roofline_us(m, n, k, world, peaks: Peaks, variant: str = "one_shot") -> dict:
     """K-sharded GEMM + all-reduce of the [m, n] bf16 partials.  one_shot / atomic: every rank moves
-    (world-1) full partials; two_shot: 2 (world-1)/world of one."""
+    (world-1) full partials; two_shot: 2 (world-1)/world of one; reduce_scatter (every rank keeps m / world rows of
+    the sum): (world-1)/world of one."""
     compute = gemm_flops(m, n, k // world) / (peaks.bf16_tflops * 1e12) * 1e6
     full = m * n * 2
-    ingress = (world - 1) * full if variant in ("one_shot", "atomic") else 2 * (world - 1) / world * full
+    if variant in ("one_shot", "atomic"):
+        ingress = (world - 1) * full
+    elif variant == "reduce_scatter":
+        ingress = (world - 1) / world * full
+    else:
+        ingress = 2 * (world - 1) / world * full
     link = ingress / (peaks.nvlink_gbs * 1e9) * 1e6
     return {"compute_us": compute, "link_us": link, "bound": "compute" if compute >= link else "link",
             "target_us": max(compute, link)}

@@ -148,6 +148,32 @@ def test_one_shot_push_short_matrices(world, m, ksplit):
 
 
 @pytest.mark.parametrize("cta_group", [1, 2])
+@pytest.mark.parametrize("world,m", [(2, 1024), (4, 2048), (4, 3072), (8, 2048)])
+def test_gemm_reduce_scatter_emulated(world, m, cta_group):
+    """GEMM + reduce-scatter: every rank keeps its own M / world rows of the sum; partial tiles go to the keeper only,
+    in a rank-dependent order."""
+    n, k_full = 768, 2048
+    ks = k_full // world
+    ranks = iris.Iris.local_world(world, heap_size=128 << 20)
+    a_full, b_full = _rand((m, k_full), 26), _rand((n, k_full), 27, 0.05)
+    a = [a_full[:, r * ks:(r + 1) * ks] for r in range(world)]
+    bt = [b_full[:, r * ks:(r + 1) * ks] for r in range(world)]
+    op = G.gemm_reduce_scatter(ranks, a, bt, cta_group=cta_group)
+    assert op.rs_rows == m // world
+    for _ in range(3):
+        outs = op()
+    op.check()
+    parts = [a[r].float() @ bt[r].float().t() for r in range(world)]
+    ref, scale = sum(parts), sum(p.abs() for p in parts)
+    for r in range(world):
+        rows = slice(r * op.rs_rows, (r + 1) * op.rs_rows)
+        assert outs[r].shape == (op.rs_rows, n)
+        _assert_close(outs[r], ref[rows], scale=scale[rows], ulps=2.0 + world)
+    op.close()
+    ranks[0].close()
+
+
+@pytest.mark.parametrize("cta_group", [1, 2])
 @pytest.mark.parametrize("world", [2, 4])
 def test_all_gather_gemm_emulated(world, cta_group):
     m, n_local, k = 2048, 256, 512

@@ -34,7 +34,7 @@ def test_elementwise_kernels():
     assert torch.equal(x2, (x.float() + y.float()).to(torch.bfloat16))
 
 
-@pytest.mark.parametrize("variant", ["one_shot", "two_shot", "atomic"])
+@pytest.mark.parametrize("variant", ["one_shot", "two_shot", "atomic", "reduce_scatter"])
 @pytest.mark.parametrize("world", [2, 4])
 def test_tp_decoder_emulated(world, variant):
     cfg = TPConfig(hidden=512, n_heads=4, head_dim=128, intermediate=1024, n_layers=2, batch=2, seq=512, seed=4)

@@ -123,6 +123,21 @@ def main():
         close(o, ref, scale=scale, ulps=2.0 + world)
         ar.close()
 
+    # GEMM + reduce-scatter: every rank keeps its own rows of the sum, back-to-back calls without host barriers
+    m_rs = 512 * world
+    a_rs = rand((m_rs, k_full), 36, dev=dev)
+    parts = [a_rs[:, r * ks:(r + 1) * ks].float() @ b_full[:, r * ks:(r + 1) * ks].float().t() for r in range(world)]
+    ref, scale = sum(parts), sum(p.abs() for p in parts)
+    rs = G.gemm_reduce_scatter(ctx, [a_rs[:, rank * ks:(rank + 1) * ks]], [b_full[:, rank * ks:(rank + 1) * ks]])
+    ctx.barrier()
+    for _ in range(4):
+        o = rs()[0]
+    ctx.barrier()
+    rs.check()
+    rows = slice(rank * 512, (rank + 1) * 512)
+    close(o, ref[rows], scale=scale[rows], ulps=2.0 + world)
+    rs.close()
+
     m2 = 256 * world
     ms = m2 // world
     a2 = rand((m2, 512), 8, dev=dev)

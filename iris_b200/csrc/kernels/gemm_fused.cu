@@ -124,6 +124,57 @@ __device__ __forceinline__ void acc_bf16x8(float* acc, uint4 v) {
   }
 }
 
+// Reduce-scatter reducer, one 128 x 256 part: sums `ns` inbox slots (local memory, `slot_rows` rows apart, first row
+// `part_row0`) over rows [mo, mo + 128) and columns [n0, n0 + 256) and writes the bf16 rows to `outp` (row pitch
+// `out_pitch` bytes).  Called by the 128 reducer threads (`rt` = 0..127).  A warp reads whole 512-byte rows (one
+// 16-byte load per lane), four rows of two slots in flight per thread.  Kept out of line so that its registers do
+// not add to those of the kernel's other roles.
+__device__ __noinline__ void rs_sum_part(const uint8_t* inbox, uint8_t* outp, uint64_t out_pitch, int N, int part_row0,
+                                         int slot_rows, int ns, int mo, int n0, int rt) {
+  const int rw = rt >> 5, rl = rt & 31;
+  const int col = n0 + rl * 8;
+  if (col >= N) return;
+  const uint64_t row_bytes = (uint64_t)N * 2;
+  const uint64_t slot_bytes = (uint64_t)slot_rows * row_bytes;
+#pragma unroll 1
+  for (int r0 = rw * 32; r0 < rw * 32 + 32; r0 += 4) {
+    float a4[4][8];
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) a4[u][j] = 0.f;
+    const uint8_t* src = inbox + (uint64_t)(part_row0 + mo + r0) * row_bytes + (uint64_t)col * 2;
+#pragma unroll 1
+    for (int sl = 0; sl < ns; sl += 2) {
+      uint4 v[2][4];  // [slot][row]: eight 16-byte loads in flight
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        if (sl + q < ns) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            v[q][u] = ld_v4_stream(reinterpret_cast<const uint4*>(src + (sl + q) * slot_bytes + u * row_bytes));
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        if (sl + q < ns) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) acc_bf16x8(a4[u], v[q][u]);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      uint4 o;
+      o.x = pack_bf16x2(a4[u][0], a4[u][1]);
+      o.y = pack_bf16x2(a4[u][2], a4[u][3]);
+      o.z = pack_bf16x2(a4[u][4], a4[u][5]);
+      o.w = pack_bf16x2(a4[u][6], a4[u][7]);
+      st_v4(reinterpret_cast<uint4*>(outp + (uint64_t)(mo + r0 + u) * out_pitch + (uint64_t)col * 2), o);
+    }
+  }
+}
+
 // One piece of work of a scheduling unit: k-blocks [kb0, kb1) of `tile`.
 struct Work {
   int tile, kb0, kb1;
@@ -253,14 +304,16 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
   // Two-shot: the rank that sums tile t.  A scheduling unit visits tiles u, u + G, u + 2G, ...; rotating the owner
   // with the visit number gives every unit of every rank the same share of the summing work.
   auto owner_of = [&](int t) { return ((t % G) + (t / G)) % W; };
-  // Reduce-scatter: the tiles of one keeper's row block are contiguous in raster order (the host picks group_m so).
-  // Every rank starts with the block of the next rank and ends with its own: at any time each keeper receives from
-  // one source, and the block that needs no link is the one whose sum is wanted last.
+  // Reduce-scatter: the tiles of one keeper's row block are contiguous in raster order (the host picks group_m so):
+  // block b is [b * rs_tpc, (b + 1) * rs_tpc).  Step i of a rank's schedule is tile i / W of block (rank + 1 + i) % W:
+  // at every step the W ranks send to W different keepers, the link is used evenly from the first tile to the last,
+  // and tile j of every block is complete on its keeper after about (j + 1) * W steps, so that the keepers' reducer
+  // warps sum while the tensor cores are still busy with later tiles.
   const int rs_tpc = p.rs_rows > 0 ? (p.rs_rows / TM) * tiles_n : 0;  // tiles per row block
-  const int rs_rot = p.rs_rows > 0 ? ((rank + 1) % W) * rs_tpc : 0;
-  auto tile_of = [&](int t) {
-    const int x = t + rs_rot;
-    return x >= total_tiles ? x - total_tiles : x;
+  auto tile_of = [&](int i) {
+    if (p.rs_rows <= 0) return i;
+    const int j = i / W;
+    return ((rank + 1 + i) % W) * rs_tpc + j;
   };
 
   if (threadIdx.x == 0) {
@@ -734,6 +787,32 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
               }
             }
           }
+          if (rissuer) trace(p, rank, t * CG + pr, kTrPullEnd);
+          continue;
+        }
+        if (p.rs_rows > 0) {
+          // Reduce-scatter: the W slots of this part are in LOCAL memory and large; rs_sum_part reads them as whole
+          // cache lines, adds in fp32 and stores the bf16 rows straight into the kept block (nothing is staged).
+          if (rissuer) {
+            const uint32_t* f = flag_ptr(p, rank, p.tile_flag_base + t * CG + pr);
+            trace(p, rank, t * CG + pr, kTrWaitBegin);
+            const bool ok = wait_until_ge(f, p.flag_target, p.timeout_ns, status, kSiteEpiTileFlag, rank, t) == kOk;
+            trace(p, rank, t * CG + pr, kTrWaitEnd);
+            *red_ok = ok ? 1u : 0u;
+          }
+          named_barrier_sync(3, 128);
+          const bool part_ok = *red_ok != 0;
+          named_barrier_sync(3, 128);  // everybody has read the verdict before the issuer writes the next one
+          if (!part_ok) {
+            ok_all = false;
+            break;
+          }
+          rs_sum_part(reinterpret_cast<const uint8_t*>(p.heap_base[rank] + p.partial_off),
+                      p.out_row0 >= 0 ? reinterpret_cast<uint8_t*>(p.heap_base[rank] + p.partial_off) +
+                                            (uint64_t)p.out_row0 * p.N * 2
+                                      : reinterpret_cast<uint8_t*>(p.heap_base[rank] + p.out_off),
+                      p.out_row0 >= 0 ? (uint64_t)p.N * 2 : (uint64_t)p.ldo * 2, p.N, p.part_row0, p.part_slot_rows, NS,
+                      m0 - rs_base, n0, rt);
           if (rissuer) trace(p, rank, t * CG + pr, kTrPullEnd);
           continue;
         }

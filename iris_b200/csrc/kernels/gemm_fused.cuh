@@ -92,8 +92,8 @@ struct FusedGemmParams {
                          // CTAs, each piece a slot of its own (slot = rank * ksplit + piece); 1 = no split
   int rs_rows;           // one-shot with push, reduce-scatter: > 0 = rank r keeps only rows [r * rs_rows, (r + 1) * rs_rows)
                          // of the sum.  A partial tile goes to the inbox of the rank that keeps its rows only (slot = source
-                         // rank, rows relative to the keeper's first row); rank r visits the row blocks in the order
-                         // r + 1, r + 2, ..., r, so that at any time every keeper is receiving from one source.  0 = off
+                         // rank, rows relative to the keeper's first row); rank r takes successive tiles from the row blocks
+                         // r + 1, r + 2, ..., r in turn, so that at any time every keeper is receiving from one source.  0 = off
   int store_all;         // store/reduce modes: 1 = push the tile to every rank, 0 = own rank only
   int tile_flag_base;    // index (uint32 units from flags_off) of the per-tile flags
   int ag_flag_base;      // index of the all-gather chunk flags: [src rank][chunk]

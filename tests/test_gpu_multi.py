@@ -54,6 +54,11 @@ EX = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "
     ("09_gemm_one_shot_all_reduce/benchmark.py", ["-m", "128", "-n", "1024", "-k", "1024", "-v", "--heap_size", str(1 << 28)]),
     ("10_tp_block/tp_block.py", ["-v", "--hidden", "512", "--heads", "4", "--intermediate", "1024", "--batch", "2",
                                  "--seq", "512", "--layers", "1", "--heap_size", str(1 << 29)]),
+    ("10_tp_block/tp_block.py", ["-v", "--variant", "reduce_scatter", "--hidden", "512", "--heads", "4",
+                                 "--intermediate", "1024", "--batch", "2", "--seq", "512", "--layers", "1",
+                                 "--heap_size", str(1 << 29)]),
+    ("11_gemm_reduce_scatter/benchmark.py", ["-m", "1024", "-n", "1024", "-k", "1024", "-v", "-b", "--num_experiments", "3",
+                                             "--num_warmup", "1", "--heap_size", str(1 << 28)]),
 ])
 def test_examples_run_on_two_gpus(script, args):
     """Every example script runs end to end on two ranks with its validation switched on (the reference's example

@@ -1,0 +1,184 @@
+// Stress program for the CPU back end of the symmetric heap, meant to be built with -fsanitize=thread and with
+// -fsanitize=address,undefined (tests/test_sanitizers_cpu.py builds and runs both).  Two "ranks" are two shared-memory
+// segments mapped into this process; threads play the ranks.  Every section ends with a check of values, so the
+// program is also a plain functional test.  Exit code 0 = all checks passed.
+//
+// What it covers: element-wise RMA primitives run by several threads (the "threads of a block" of the back end), the
+// message-passing protocol (data written with ordinary stores, flag raised with release, consumer polls with
+// acquire, then reads the data: a missing ordering shows up as a data race under the thread sanitizer), concurrent
+// atomic adds from both ranks, a bounded wait that expires, and the checking pointer translation.
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+#include <unistd.h>
+
+#include <atomic>
+#include <thread>
+#include <vector>
+
+#include "iris/rma_ops.cuh"
+
+extern "C" {
+const char* iris_cpu_last_error();
+void* iris_cpu_heap_map(const char* name, uint64_t size, int create);
+int iris_cpu_heap_unmap(void* p, uint64_t size);
+int iris_cpu_heap_unlink(const char* name);
+int iris_cpu_rma(int op, int dtype, int sem, int scope, void* a, void* b, void* c, int64_t n, const uint64_t* heap_bases,
+                 int cur, int world, int target, double fvalue, int64_t ivalue, int64_t ivalue2, int nthreads);
+uint64_t iris_cpu_translate_checked(uint64_t ptr, const uint64_t* heap_bases, uint64_t heap_size, int rank, int world,
+                                    int target, iris::StatusBlock* st);
+void iris_cpu_mp_produce(const void* src, void* dst_sym, uint64_t bytes, uint32_t* flag_sym, uint32_t epoch,
+                         const uint64_t* heap_bases, int cur, int target);
+uint32_t iris_cpu_wait_flag(const uint32_t* flag, uint32_t expected, uint64_t max_polls, iris::StatusBlock* st,
+                            uint32_t rank);
+}
+
+using namespace iris;
+using namespace iris::ops;
+
+static int g_fail = 0;
+#define CHECK(cond, ...)                   \
+  do {                                     \
+    if (!(cond)) {                         \
+      fprintf(stderr, "FAILED %s:%d: ", __FILE__, __LINE__); \
+      fprintf(stderr, __VA_ARGS__);        \
+      fprintf(stderr, "\n");               \
+      ++g_fail;                            \
+    }                                      \
+  } while (0)
+
+int main() {
+  constexpr uint64_t kHeap = 1 << 20;
+  constexpr int kWorld = 2;
+  char name[kWorld][64];
+  uint8_t* base[kWorld];
+  for (int r = 0; r < kWorld; ++r) {
+    snprintf(name[r], sizeof(name[r]), "/iris_stress_%d_%d", (int)getpid(), r);
+    base[r] = static_cast<uint8_t*>(iris_cpu_heap_map(name[r], kHeap, 1));
+    if (!base[r]) {
+      fprintf(stderr, "map: %s\n", iris_cpu_last_error());
+      return 2;
+    }
+    memset(base[r], 0, kHeap);
+  }
+  const uint64_t hb[kWorld] = {(uint64_t)base[0], (uint64_t)base[1]};
+  // The same offsets on every rank: [0, 64K) data A, [64K, 128K) data B, [128K, 192K) results, [192K, ...) flags.
+  auto sym = [&](int rank, uint64_t off) { return base[rank] + off; };
+  constexpr uint64_t kA = 0, kB = 64 << 10, kC = 128 << 10, kF = 192 << 10;
+  constexpr int64_t kN = 4096;
+
+  // ---- 1. element-wise primitives, four threads per call, every memory order ----
+  for (int sem = 0; sem < 4; ++sem) {
+    // rank 0 stores 7 into A of every rank
+    int rc = iris_cpu_rma(kStore, kI32, sem, 2, sym(0, kA), nullptr, nullptr, kN, hb, 0, kWorld, -1, 0.0, 7, 0, 4);
+    CHECK(rc == 0, "store rc %d", rc);
+    for (int r = 0; r < kWorld; ++r)
+      for (int64_t i = 0; i < kN; ++i) CHECK(reinterpret_cast<int32_t*>(sym(r, kA))[i] == 7, "store value");
+    // rank 1 loads A from every rank and sums into its C: 7 * world
+    rc = iris_cpu_rma(kLoad, kI32, sem, 2, sym(1, kA), nullptr, sym(1, kC), kN, hb, 1, kWorld, -1, 0.0, 0, 0, 4);
+    CHECK(rc == 0, "load rc %d", rc);
+    CHECK(reinterpret_cast<int32_t*>(sym(1, kC))[kN - 1] == 7 * kWorld, "load sum");
+    // rank 0 puts its A into B of rank 1
+    rc = iris_cpu_rma(kPut, kI32, sem, 2, sym(0, kA), sym(0, kB), nullptr, kN, hb, 0, kWorld, 1, 0.0, 0, 0, 4);
+    CHECK(rc == 0, "put rc %d", rc);
+    CHECK(reinterpret_cast<int32_t*>(sym(1, kB))[17] == 7, "put value");
+    // fp32 atomic add of 1.5 to C of rank 0 by rank 1, result of the old values ignored
+    memset(sym(0, kC), 0, kN * 4);
+    rc = iris_cpu_rma(kAtomicAdd, kF32, sem, 2, sym(1, kC), nullptr, nullptr, kN, hb, 1, kWorld, 0, 1.5, 0, 0, 4);
+    CHECK(rc == 0, "atomic add rc %d", rc);
+    CHECK(reinterpret_cast<float*>(sym(0, kC))[5] == 1.5f, "atomic add value");
+    // compare-and-swap 0 -> 9 on int64 words of rank 1
+    memset(sym(1, kC), 0, kN * 8);
+    rc = iris_cpu_rma(kAtomicCas, kI64, sem, 2, sym(0, kC), nullptr, nullptr, kN, hb, 0, kWorld, 1, 0.0, 0, 9, 4);
+    CHECK(rc == 0, "cas rc %d", rc);
+    CHECK(reinterpret_cast<int64_t*>(sym(1, kC))[kN - 1] == 9, "cas value");
+  }
+  CHECK(iris_cpu_rma(kAtomicAdd, kI16, 0, 2, sym(0, kA), nullptr, nullptr, 4, hb, 0, kWorld, 0, 0.0, 1, 0, 1) == -2,
+        "16-bit atomic add must be refused");
+  CHECK(iris_cpu_rma(kLoad, 99, 0, 2, sym(0, kA), nullptr, nullptr, 4, hb, 0, kWorld, 0, 0.0, 1, 0, 1) == -1,
+        "unknown dtype must be refused");
+
+  // ---- 2. both ranks add into the same counters at once ----
+  {
+    memset(sym(0, kC), 0, kN * 4);
+    memset(sym(1, kC), 0, kN * 4);
+    std::vector<std::thread> ranks;
+    for (int r = 0; r < kWorld; ++r)
+      ranks.emplace_back([&, r]() {
+        for (int rep = 0; rep < 8; ++rep)
+          iris_cpu_rma(kAtomicAdd, kI32, 0, 2, sym(r, kC), nullptr, nullptr, kN, hb, r, kWorld, -1, 0.0, 1, 0, 2);
+      });
+    for (auto& t : ranks) t.join();
+    for (int r = 0; r < kWorld; ++r)
+      CHECK(reinterpret_cast<int32_t*>(sym(r, kC))[123] == 8 * kWorld, "concurrent adds: %d",
+            reinterpret_cast<int32_t*>(sym(r, kC))[123]);
+  }
+
+  // ---- 3. message passing: rank 0 produces 16 chunks for rank 1, which doubles them and sends them back ----
+  {
+    constexpr int kChunks = 16;
+    constexpr uint64_t kChunk = 2048;  // bytes
+    std::vector<int32_t> src(kChunks * kChunk / 4), back(kChunks * kChunk / 4);
+    for (size_t i = 0; i < src.size(); ++i) src[i] = (int32_t)i;
+    uint32_t* flags0 = reinterpret_cast<uint32_t*>(sym(0, kF));
+    uint32_t* flags1 = reinterpret_cast<uint32_t*>(sym(1, kF));
+    memset(flags0, 0, kChunks * 4);
+    memset(flags1, 0, kChunks * 4);
+    StatusBlock st0{}, st1{};
+    std::thread producer([&]() {
+      for (int c = 0; c < kChunks; ++c)
+        iris_cpu_mp_produce(src.data() + c * kChunk / 4, sym(0, kA) + c * kChunk, kChunk, flags0 + c, 1, hb, 0, 1);
+      for (int c = 0; c < kChunks; ++c) {  // then collect the doubled chunks from its own B
+        const uint32_t s = iris_cpu_wait_flag(flags0 + c, 1, 1ull << 32, &st0, 0);
+        CHECK(s == kOk, "producer wait chunk %d", c);
+        memcpy(back.data() + c * kChunk / 4, sym(0, kB) + c * kChunk, kChunk);
+      }
+    });
+    std::thread consumer([&]() {
+      std::vector<int32_t> tmp(kChunk / 4);
+      for (int c = 0; c < kChunks; ++c) {
+        const uint32_t s = iris_cpu_wait_flag(flags1 + c, 1, 1ull << 32, &st1, 1);
+        CHECK(s == kOk, "consumer wait chunk %d", c);
+        const int32_t* in = reinterpret_cast<const int32_t*>(sym(1, kA) + c * kChunk);
+        for (size_t i = 0; i < tmp.size(); ++i) tmp[i] = 2 * in[i];
+        iris_cpu_mp_produce(tmp.data(), sym(1, kB) + c * kChunk, kChunk, flags1 + c, 1, hb, 1, 0);
+      }
+    });
+    producer.join();
+    consumer.join();
+    bool ok = true;
+    for (size_t i = 0; i < src.size(); ++i) ok = ok && back[i] == 2 * src[i];
+    CHECK(ok, "message passing: dst != 2 * src");
+    CHECK(st0.code == kOk && st1.code == kOk, "status after message passing");
+  }
+
+  // ---- 4. a wait on a flag that nothing sets runs out and reports where ----
+  {
+    uint32_t* flag = reinterpret_cast<uint32_t*>(sym(0, kF)) + 100;
+    *flag = 3;
+    StatusBlock st{};
+    const uint32_t s = iris_cpu_wait_flag(flag, 4, 10000, &st, 0);
+    CHECK(s == kTimeout, "wait must time out");
+    CHECK(st.code == kTimeout && st.value == 3 && st.aux == 4, "status block: code %u value %llu aux %llu", st.code,
+          (unsigned long long)st.value, (unsigned long long)st.aux);
+  }
+
+  // ---- 5. checking pointer translation ----
+  {
+    StatusBlock st{};
+    const uint64_t good = iris_cpu_translate_checked(hb[0] + 256, hb, kHeap, 0, kWorld, 1, &st);
+    CHECK(good == hb[1] + 256 && st.code == kOk, "translate inside the heap");
+    const uint64_t bad = iris_cpu_translate_checked(hb[0] + kHeap + 8, hb, kHeap, 0, kWorld, 1, &st);
+    CHECK(bad == 0 && st.code == kBadPointer, "pointer past the heap: code %u", st.code);
+    StatusBlock st2{};
+    const uint64_t bad_rank = iris_cpu_translate_checked(hb[0], hb, kHeap, 0, kWorld, 5, &st2);
+    CHECK(bad_rank == 0 && st2.code == kBadRank, "rank out of range: code %u", st2.code);
+  }
+
+  for (int r = 0; r < kWorld; ++r) {
+    CHECK(iris_cpu_heap_unmap(base[r], kHeap) == 0, "unmap");
+    CHECK(iris_cpu_heap_unlink(name[r]) == 0, "unlink");
+  }
+  if (g_fail == 0) printf("stress OK\n");
+  return g_fail == 0 ? 0 : 1;
+}

@@ -58,7 +58,8 @@ def run_elementwise(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="gemm", choices=["gemm", "all_scatter", "atomic", "one_shot", "two_shot", "ag", "p2p", "elementwise"])
+    ap.add_argument("--workload", default="gemm", choices=["gemm", "all_scatter", "atomic", "one_shot", "two_shot", "reduce_scatter", "ag", "p2p",
+                             "elementwise"])
     ap.add_argument("--world", type=int, default=1)
     ap.add_argument("-m", type=int, default=8192)
     ap.add_argument("-n", type=int, default=3584)
@@ -90,9 +91,12 @@ def main():
     else:
         ks = k // W
         a_full, b_full = rand(m, k), rand(n, k)
-        op = G.gemm_all_reduce(ranks, [a_full[:, r * ks:(r + 1) * ks] for r in range(W)],
-                               [b_full[:, r * ks:(r + 1) * ks] for r in range(W)], variant=args.workload,
-                               cta_group=cg)
+        a_sh = [a_full[:, r * ks:(r + 1) * ks] for r in range(W)]
+        b_sh = [b_full[:, r * ks:(r + 1) * ks] for r in range(W)]
+        if args.workload == "reduce_scatter":
+            op = G.gemm_reduce_scatter(ranks, a_sh, b_sh, cta_group=cg)
+        else:
+            op = G.gemm_all_reduce(ranks, a_sh, b_sh, variant=args.workload, cta_group=cg)
     for _ in range(args.launches):
         op()
     op.check()

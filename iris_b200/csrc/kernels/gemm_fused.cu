@@ -41,6 +41,7 @@
 #include <new>
 
 #include "gemm_fused.cuh"
+#include "gemm_schedule.h"
 #include "iris/iris.cuh"
 #include "iris/nvls.cuh"
 #include "iris/ptx_sm100.cuh"
@@ -62,34 +63,6 @@ enum Site : uint32_t {
   kSitePullFull = 33,
   kSiteDone = 40,
 };
-
-struct TileCoord {
-  int m_idx, n_idx;
-};
-
-// Grouped raster: consecutive tile ids walk down `group_m` m-tiles before moving to the next n-tile, so
-// the CTAs of one wave share A rows and B columns in L2 (the reference's GROUP_SIZE_M swizzle,
-// examples/07_gemm_all_scatter/gemm_all_scatter.py:158-163).
-__device__ __forceinline__ TileCoord raster(int tile, int tiles_m, int tiles_n, int group_m) {
-  const int per_group = group_m * tiles_n;
-  const int g = tile / per_group;
-  const int first_m = g * group_m;
-  const int gsz = min(tiles_m - first_m, group_m);
-  const int in_g = tile - g * per_group;
-  TileCoord c;
-  c.m_idx = first_m + in_g % gsz;
-  c.n_idx = in_g / gsz;
-  return c;
-}
-
-// With the all-gather prologue the m-tiles are visited shard by shard starting with the rank's own rows:
-// logical shard position sp maps to source rank (rank + sp) % world.
-__device__ __forceinline__ int ag_actual_m(int logical_m, int tiles_per_shard, int rank, int world) {
-  const int sp = logical_m / tiles_per_shard;
-  const int within = logical_m - sp * tiles_per_shard;
-  const int s = (rank + sp) % world;
-  return s * tiles_per_shard + within;
-}
 
 __device__ __forceinline__ uint32_t* flag_ptr(const FusedGemmParams& p, int rank, int index) {
   return reinterpret_cast<uint32_t*>(p.heap_base[rank] + p.flags_off) + index;
@@ -303,18 +276,14 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
   const int chunks_per_shard = p.ag ? (p.M / W) / BM : 0;  // all-gather flags are per 128 rows
   // Two-shot: the rank that sums tile t.  A scheduling unit visits tiles u, u + G, u + 2G, ...; rotating the owner
   // with the visit number gives every unit of every rank the same share of the summing work.
-  auto owner_of = [&](int t) { return ((t % G) + (t / G)) % W; };
+  auto owner_of = [&](int t) { return two_shot_owner(t, G, W); };
   // Reduce-scatter: the tiles of one keeper's row block are contiguous in raster order (the host picks group_m so):
   // block b is [b * rs_tpc, (b + 1) * rs_tpc).  Step i of a rank's schedule is tile i / W of block (rank + 1 + i) % W:
   // at every step the W ranks send to W different keepers, the link is used evenly from the first tile to the last,
   // and tile j of every block is complete on its keeper after about (j + 1) * W steps, so that the keepers' reducer
   // warps sum while the tensor cores are still busy with later tiles.
   const int rs_tpc = p.rs_rows > 0 ? (p.rs_rows / TM) * tiles_n : 0;  // tiles per row block
-  auto tile_of = [&](int i) {
-    if (p.rs_rows <= 0) return i;
-    const int j = i / W;
-    return ((rank + 1 + i) % W) * rs_tpc + j;
-  };
+  auto tile_of = [&](int i) { return p.rs_rows > 0 ? rs_tile_of(i, rank, W, rs_tpc) : i; };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -1206,6 +1175,20 @@ struct IrisGemmPlan {
   int pull;
 };
 
+// The schedule arithmetic of the kernel, callable on the host (no device needed): see gemm_schedule.h.
+void iris_sched_raster(int tile, int tiles_m, int tiles_n, int group_m, int* m_idx, int* n_idx) {
+  const TileCoord c = raster(tile, tiles_m, tiles_n, group_m < 1 ? 1 : group_m);
+  *m_idx = c.m_idx;
+  *n_idx = c.n_idx;
+}
+int iris_sched_ag_actual_m(int logical_m, int tiles_per_shard, int rank, int world) {
+  return ag_actual_m(logical_m, tiles_per_shard, rank, world);
+}
+int iris_sched_two_shot_owner(int tile, int units, int world) { return two_shot_owner(tile, units, world); }
+int iris_sched_rs_tile_of(int step, int rank, int world, int tiles_per_block) {
+  return rs_tile_of(step, rank, world, tiles_per_block);
+}
+
 const char* iris_gemm_last_error() { return g_err; }
 int iris_gemm_smem_bytes() { return kSmemBytes; }
 int iris_gemm_desc_size() { return (int)sizeof(IrisGemmDesc); }
@@ -1272,8 +1255,7 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
   }
   if (cg == 2) {
     // All CTA pairs must be resident at once: ask how many clusters of 2 the device can hold.
-    cudaLaunchConfig_t cfg;
-    memset(&cfg, 0, sizeof(cfg));
+    cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(ctas_per_rank * d->num_local);
     cfg.blockDim = dim3(pull ? kThreadsPull : kThreads);
     cfg.dynamicSmemBytes = kSmemBytes;
@@ -1389,8 +1371,7 @@ int iris_gemm_plan_launch(void* h, int parity, uint32_t epoch, uint32_t flag_tar
   cudaError_t e;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (plan->cta_group == 2) {
-    cudaLaunchConfig_t cfg;
-    memset(&cfg, 0, sizeof(cfg));
+    cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(plan->grid);
     cfg.blockDim = dim3(plan->pull ? kThreadsPull : kThreads);
     cfg.dynamicSmemBytes = kSmemBytes;

@@ -1,0 +1,57 @@
+// gemm_schedule.h — the pure index arithmetic of the fused GEMM's tile schedules, usable on host and device.
+// The kernel (gemm_fused.cu) calls these; the same functions are exported through C wrappers
+// (iris_sched_* in gemm_fused.cu) so that their invariants can be checked on a machine without a GPU
+// (tests/test_schedule_cpu.py): every map is a bijection, work is balanced, a keeper has one sender per step.
+#pragma once
+
+#if defined(__CUDACC__)
+#define IRIS_SCHED_HD __host__ __device__ __forceinline__
+#else
+#define IRIS_SCHED_HD inline
+#endif
+
+namespace iris {
+namespace gemm {
+
+struct TileCoord {
+  int m_idx, n_idx;
+};
+
+// Grouped raster: consecutive tile ids walk down `group_m` m-tiles before moving to the next n-tile, so
+// the CTAs of one wave share A rows and B columns in L2 (the reference's GROUP_SIZE_M swizzle,
+// examples/07_gemm_all_scatter/gemm_all_scatter.py:158-163).
+IRIS_SCHED_HD TileCoord raster(int tile, int tiles_m, int tiles_n, int group_m) {
+  const int per_group = group_m * tiles_n;
+  const int g = tile / per_group;
+  const int first_m = g * group_m;
+  const int rest = tiles_m - first_m;
+  const int gsz = rest < group_m ? rest : group_m;
+  const int in_g = tile - g * per_group;
+  TileCoord c;
+  c.m_idx = first_m + in_g % gsz;
+  c.n_idx = in_g / gsz;
+  return c;
+}
+
+// With the all-gather prologue the m-tiles are visited shard by shard starting with the rank's own rows:
+// logical shard position sp maps to source rank (rank + sp) % world.
+IRIS_SCHED_HD int ag_actual_m(int logical_m, int tiles_per_shard, int rank, int world) {
+  const int sp = logical_m / tiles_per_shard;
+  const int within = logical_m - sp * tiles_per_shard;
+  const int s = (rank + sp) % world;
+  return s * tiles_per_shard + within;
+}
+
+// Two-shot all-reduce: the rank that sums tile t.  A scheduling unit visits tiles u, u + units, u + 2 units, ...;
+// rotating the owner with the visit number gives every unit of every rank the same share of the summing work.
+IRIS_SCHED_HD int two_shot_owner(int tile, int units, int world) { return ((tile % units) + (tile / units)) % world; }
+
+// Reduce-scatter: the tiles of keeper b's row block are [b * tiles_per_block, (b + 1) * tiles_per_block) in raster
+// order.  Step i of rank `rank` is tile i / world of block (rank + 1 + i) % world: at every step the ranks send to
+// `world` different keepers, and tile j of every block has been visited by every rank after (j + 1) * world steps.
+IRIS_SCHED_HD int rs_tile_of(int step, int rank, int world, int tiles_per_block) {
+  return ((rank + 1 + step) % world) * tiles_per_block + step / world;
+}
+
+}  // namespace gemm
+}  // namespace iris

@@ -1,0 +1,81 @@
+"""Invariants of the fused GEMM's tile schedules, checked on the host through the C wrappers of the very functions
+the kernel calls (iris_b200/csrc/kernels/gemm_schedule.h).  The reference has its schedule arithmetic inline in the
+Triton kernels (examples/07_gemm_all_scatter/gemm_all_scatter.py:158-163 for the grouped raster) and no test of it."""
+import ctypes
+import itertools
+
+import pytest
+
+from iris_b200 import _build
+
+
+@pytest.fixture(scope="module")
+def lib():
+    so = ctypes.CDLL(str(_build.build_all()["kernels"]))
+    so.iris_sched_raster.argtypes = [ctypes.c_int] * 4 + [ctypes.POINTER(ctypes.c_int)] * 2
+    so.iris_sched_raster.restype = None
+    for f in (so.iris_sched_ag_actual_m, so.iris_sched_two_shot_owner, so.iris_sched_rs_tile_of):
+        f.argtypes = [ctypes.c_int] * (3 if f is so.iris_sched_two_shot_owner else 4)
+        f.restype = ctypes.c_int
+    return so
+
+
+def _raster(lib, t, tm, tn, g):
+    m, n = ctypes.c_int(), ctypes.c_int()
+    lib.iris_sched_raster(t, tm, tn, g, ctypes.byref(m), ctypes.byref(n))
+    return m.value, n.value
+
+
+@pytest.mark.parametrize("tm,tn,g", [(1, 1, 8), (32, 56, 8), (5, 3, 8), (13, 7, 4), (64, 16, 8), (7, 1, 2), (3, 9, 1)])
+def test_grouped_raster_is_a_bijection_onto_the_tile_grid(lib, tm, tn, g):
+    seen = {_raster(lib, t, tm, tn, g) for t in range(tm * tn)}
+    assert seen == set(itertools.product(range(tm), range(tn)))
+    # consecutive tiles of a full group walk down the group's m-tiles first
+    if tm >= g:
+        assert [_raster(lib, t, tm, tn, g)[0] for t in range(g)] == list(range(g))
+        assert {_raster(lib, t, tm, tn, g)[1] for t in range(g)} == {0}
+
+
+@pytest.mark.parametrize("world,per_shard", [(2, 4), (4, 2), (8, 1), (8, 8)])
+def test_all_gather_order_starts_with_own_rows_and_is_a_permutation(lib, world, per_shard):
+    for rank in range(world):
+        order = [lib.iris_sched_ag_actual_m(m, per_shard, rank, world) for m in range(world * per_shard)]
+        assert sorted(order) == list(range(world * per_shard))
+        assert order[:per_shard] == list(range(rank * per_shard, (rank + 1) * per_shard))
+        # then the peers in ring order: shard position sp holds the rows of rank (rank + sp) % world
+        for sp in range(world):
+            assert order[sp * per_shard] // per_shard == (rank + sp) % world
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("units,tiles", [(74, 512), (74, 1024), (148, 448), (37, 100)])
+def test_two_shot_owner_gives_every_unit_the_same_share(lib, world, units, tiles):
+    """Unit u visits tiles u, u + units, ...; of those, the ones it must also sum (owner == its rank) differ by at most
+    one between any two (unit, rank) pairs, and every tile has exactly one owner."""
+    share = {}
+    for t in range(tiles):
+        o = lib.iris_sched_two_shot_owner(t, units, world)
+        assert 0 <= o < world
+        share[(t % units, o)] = share.get((t % units, o), 0) + 1
+    counts = [share.get((u, r), 0) for u in range(min(units, tiles)) for r in range(world)]
+    visits = -(-tiles // units)
+    assert max(counts) - min(counts) <= 1 + (visits % world != 0)
+    assert max(counts) <= -(-visits // world)
+
+
+@pytest.mark.parametrize("world,tpb", [(1, 16), (2, 512), (4, 6), (8, 128), (8, 1)])
+def test_reduce_scatter_order(lib, world, tpb):
+    total = world * tpb
+    per_rank = [[lib.iris_sched_rs_tile_of(i, r, world, tpb) for i in range(total)] for r in range(world)]
+    for r in range(world):
+        assert sorted(per_rank[r]) == list(range(total))          # every rank computes every tile once
+    for i in range(total):
+        keepers = [per_rank[r][i] // tpb for r in range(world)]
+        assert sorted(keepers) == list(range(world))              # one sender per keeper at every step
+        assert keepers[0] == (1 + i) % world
+    for r in range(world):
+        for j in range(tpb):
+            for b in range(world):                                 # tile j of block b is done after (j + 1) * world steps
+                assert per_rank[r].index(b * tpb + j) < (j + 1) * world
+    if world > 1:
+        assert per_rank[0][0] // tpb == 1 and per_rank[0][world - 1] // tpb == 0   # next rank first, own block last

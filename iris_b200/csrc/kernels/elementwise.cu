@@ -64,24 +64,88 @@ __global__ void __launch_bounds__(kThreads) rmsnorm_kernel(const __nv_bfloat16* 
   }
 }
 
-// out[r, c] = silu(gu[r, c]) * gu[r, inter + c]; four independent 16-byte load pairs in flight per thread
-__global__ void swiglu_kernel(const __nv_bfloat16* __restrict__ gu, int64_t ldg, __nv_bfloat16* __restrict__ out,
-                              int64_t ldo, int rows, int inter) {
+// As above for rows of at most kThreads * VPT vectors: the row stays in registers between the two passes, so x is
+// read once (the generic kernel's second read hits L2 but costs a second round of load latency per row).
+template <int kThreads, int VPT>
+__global__ void __launch_bounds__(kThreads) rmsnorm_reg_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx,
+                                                               const __nv_bfloat16* __restrict__ w,
+                                                               __nv_bfloat16* __restrict__ out, int64_t ldo, int cols,
+                                                               float eps) {
+  __shared__ float red[kThreads / 32];
+  const int r = blockIdx.x;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + (int64_t)r * ldx);
+  const uint4* wv = reinterpret_cast<const uint4*>(w);
+  uint4* orow = reinterpret_cast<uint4*>(out + (int64_t)r * ldo);
+  const int nv = cols / 8;
+  uint4 xv[VPT], wr[VPT];
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) {
+    const int i = threadIdx.x + v * kThreads;
+    if (i < nv) {
+      xv[v] = xr[i];
+      wr[v] = wv[i];
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) {
+    if (threadIdx.x + v * kThreads < nv) {
+      float f[8];
+      unpack8(xv[v], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += f[j] * f[j];
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < kThreads / 32; ++i) tot += red[i];
+  const float scale = rsqrtf(tot / (float)cols + eps);
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) {
+    const int i = threadIdx.x + v * kThreads;
+    if (i < nv) {
+      float f[8], g[8];
+      unpack8(xv[v], f);
+      unpack8(wr[v], g);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = f[j] * scale * g[j];
+      orow[i] = pack8(f);
+    }
+  }
+}
+
+// silu(a) * b with two special-function operations per element (ex2 and rcp) and no IEEE division: the kernel has
+// to stay below about 25 instructions per element to be bound by memory rather than by instruction issue.
+__device__ __forceinline__ float silu_mul(float a, float b) {
+  return __fdividef(a, 1.f + __expf(-a)) * b;
+}
+
+// out[r, c] = silu(gu[r, c]) * gu[r, inter + c]; four independent 16-byte load pairs in flight per thread.
+// Index: 32-bit (fewer instructions than 64-bit division) unless the matrix has 2^31 vectors or more.
+template <class Index>
+__global__ void __launch_bounds__(256) swiglu_kernel(const __nv_bfloat16* __restrict__ gu, int64_t ldg,
+                                                     __nv_bfloat16* __restrict__ out, int64_t ldo, int rows, int inter) {
   constexpr int U = 4;
-  const int nv = inter / 8;
-  const int64_t total = (int64_t)rows * nv;
-  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t i0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i0 < total; i0 += U * stride) {
+  const Index nv = (Index)(inter / 8);
+  const Index total = (Index)rows * nv;
+  const Index stride = (Index)gridDim.x * blockDim.x;
+  for (Index i0 = (Index)blockIdx.x * blockDim.x + threadIdx.x; i0 < total; i0 += U * stride) {
     uint4 g[U], u[U];
-    int r[U], c[U];
+    int64_t oo[U];
 #pragma unroll
     for (int q = 0; q < U; ++q) {
-      const int64_t i = i0 + q * stride;
+      const Index i = i0 + q * stride;
       if (i < total) {
-        r[q] = (int)(i / nv);
-        c[q] = (int)(i - (int64_t)r[q] * nv);
-        g[q] = *reinterpret_cast<const uint4*>(gu + (int64_t)r[q] * ldg + c[q] * 8);
-        u[q] = *reinterpret_cast<const uint4*>(gu + (int64_t)r[q] * ldg + inter + c[q] * 8);
+        const Index r = i / nv;
+        const Index c = i - r * nv;
+        const __nv_bfloat16* src = gu + (int64_t)r * ldg + (int64_t)c * 8;
+        g[q] = *reinterpret_cast<const uint4*>(src);
+        u[q] = *reinterpret_cast<const uint4*>(src + inter);
+        oo[q] = (int64_t)r * ldo + (int64_t)c * 8;
       }
     }
 #pragma unroll
@@ -91,8 +155,8 @@ __global__ void swiglu_kernel(const __nv_bfloat16* __restrict__ gu, int64_t ldg,
         unpack8(g[q], a);
         unpack8(u[q], b);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) a[j] = a[j] / (1.f + __expf(-a[j])) * b[j];
-        *reinterpret_cast<uint4*>(out + (int64_t)r[q] * ldo + c[q] * 8) = pack8(a);
+        for (int j = 0; j < 8; ++j) a[j] = silu_mul(a[j], b[j]);
+        *reinterpret_cast<uint4*>(out + oo[q]) = pack8(a);
       }
     }
   }
@@ -127,14 +191,27 @@ extern "C" {
 int iris_k_rmsnorm_bf16(const void* x, int64_t ldx, const void* w, void* out, int64_t ldo, int rows, int cols,
                         float eps, void* stream) {
   if (cols % 8 != 0 || rows < 1) return -2;
-  rmsnorm_kernel<256><<<rows, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w,
-                                                              (__nv_bfloat16*)out, ldo, cols, eps);
+  const __nv_bfloat16* xp = (const __nv_bfloat16*)x;
+  const __nv_bfloat16* wp = (const __nv_bfloat16*)w;
+  __nv_bfloat16* op = (__nv_bfloat16*)out;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int nv = cols / 8;
+  if (nv <= 256) rmsnorm_reg_kernel<256, 1><<<rows, 256, 0, st>>>(xp, ldx, wp, op, ldo, cols, eps);
+  else if (nv <= 512) rmsnorm_reg_kernel<256, 2><<<rows, 256, 0, st>>>(xp, ldx, wp, op, ldo, cols, eps);
+  else if (nv <= 1024) rmsnorm_reg_kernel<256, 4><<<rows, 256, 0, st>>>(xp, ldx, wp, op, ldo, cols, eps);
+  else rmsnorm_kernel<256><<<rows, 256, 0, st>>>(xp, ldx, wp, op, ldo, cols, eps);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 int iris_k_swiglu_bf16(const void* gu, int64_t ldg, void* out, int64_t ldo, int rows, int inter, void* stream) {
   if (inter % 8 != 0 || rows < 1) return -2;
-  swiglu_kernel<<<grid_for((int64_t)rows * inter / 8, 256), 256, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)gu, ldg, (__nv_bfloat16*)out, ldo, rows, inter);
+  const int64_t vecs = (int64_t)rows * (inter / 8);
+  const int grid = grid_for((vecs + 3) / 4, 256);
+  if (vecs + 4ll * grid * 256 < (1ll << 32))
+    swiglu_kernel<uint32_t><<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)gu, ldg, (__nv_bfloat16*)out,
+                                                                     ldo, rows, inter);
+  else
+    swiglu_kernel<int64_t><<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)gu, ldg, (__nv_bfloat16*)out,
+                                                                    ldo, rows, inter);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 int iris_k_residual_add_bf16(void* x, int64_t ldx, const void* y, int64_t ldy, int rows, int cols, void* stream) {

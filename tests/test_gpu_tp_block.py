@@ -34,6 +34,39 @@ def test_elementwise_kernels():
     assert torch.equal(x2, (x.float() + y.float()).to(torch.bfloat16))
 
 
+@pytest.mark.parametrize("cols", [8, 1024, 1376, 4096, 8192, 16384])
+def test_rmsnorm_every_row_length(cols):
+    """Row lengths that take each of the kernel's forms (row kept in registers with 1, 2 or 4 vectors per thread; the
+    two-pass form for longer rows), with a strided input view and a strided output view."""
+    g = torch.Generator(device="cuda").manual_seed(cols)
+    wide = torch.randn((70, cols + 64), generator=g, device="cuda").to(torch.bfloat16)
+    x = wide[:, 32:32 + cols]
+    w = (1 + 0.1 * torch.randn(cols, generator=g, device="cuda")).to(torch.bfloat16)
+    out = torch.zeros((70, cols + 8), dtype=torch.bfloat16, device="cuda")
+    E.rmsnorm(x, w, out[:, :cols], 1e-6)
+    xf = x.float()
+    ref = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6) * w.float()
+    assert (out[:, :cols].float() - ref).abs().max().item() <= 2 ** -7 * ref.abs().max().item()
+    assert float(out[:, cols:].abs().sum()) == 0
+
+
+def test_swiglu_extreme_inputs():
+    """The sigmoid is computed with ex2 / rcp approximations: large negative gates give 0, large positive ones the
+    gate itself, and nothing turns into NaN."""
+    gate = torch.tensor([-300.0, -100.0, -88.0, -20.0, -1.0, 0.0, 1.0, 20.0, 100.0, 300.0, 3.0e38, -3.0e38] * 2,
+                        device="cuda")[:24]
+    up = torch.full((24,), 1.5, device="cuda")
+    gu = torch.cat([gate, up]).to(torch.bfloat16).view(1, 48).repeat(5, 1).contiguous()
+    h = torch.empty((5, 24), dtype=torch.bfloat16, device="cuda")
+    E.swiglu(gu, h)
+    gf = gu[:, :24].float()
+    ref = torch.nn.functional.silu(gf) * gu[:, 24:].float()
+    assert not torch.isnan(h.float()).any()
+    fin = torch.isfinite(ref.to(torch.bfloat16).float())
+    assert torch.equal(torch.isfinite(h.float()), fin)
+    assert torch.allclose(h.float()[fin], ref[fin], rtol=2 ** -7, atol=1e-30)
+
+
 @pytest.mark.parametrize("variant", ["one_shot", "two_shot", "atomic", "reduce_scatter"])
 @pytest.mark.parametrize("world", [2, 4])
 def test_tp_decoder_emulated(world, variant):

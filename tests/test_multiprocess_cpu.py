@@ -19,6 +19,30 @@ def test_cpu_plumbing_two_ranks():
     assert all("OK" in o for o in outs)
 
 
+@pytest.mark.parametrize("world", [2, 3])
+def test_cpu_plumbing_over_the_mpi_bootstrap(world):
+    """``IRIS_BOOTSTRAP=mpi``: the same worker with the control plane on mpi4py's interface (the reference's only
+    back end, iris/_mpi_helpers.py:8-51).  mpi4py is not installed here; tests/fakes/mpi4py implements the calls the
+    bootstrap makes over a TCP store, so that its MPI code path runs as real processes."""
+    fakes = os.path.join(os.path.dirname(__file__), "fakes")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code, outs = run_ranks(world, [os.path.join(W, "cpu_plumbing.py"), "--expect-bootstrap", "MpiBootstrap"],
+                           env={"IRIS_BOOTSTRAP": "mpi", "PYTHONPATH": fakes + os.pathsep + root})
+    _ok(code, outs)
+    assert all("OK" in o for o in outs)
+
+
+def test_missing_rank_times_out_over_the_mpi_bootstrap():
+    """The timed barrier of the MPI back end (a non-blocking barrier polled against a deadline) reports a rank
+    that never arrives."""
+    fakes = os.path.join(os.path.dirname(__file__), "fakes")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code, outs = run_ranks(2, [os.path.join(W, "cpu_faults.py"), "missing_rank_at_barrier"], timeout_s=60,
+                           env={"IRIS_BOOTSTRAP": "mpi", "PYTHONPATH": fakes + os.pathsep + root})
+    _ok(code, outs)
+    assert "BootstrapError" in outs[0]
+
+
 @pytest.mark.parametrize("world", [2, 4])
 def test_unit_semantics_all_ranks(world):
     code, outs = run_ranks(world, [os.path.join(W, "cpu_unit_all_ranks.py")], timeout_s=180)

@@ -12,6 +12,9 @@ def main():
     ctx = iris.iris(1 << 20, backend="cpu")
     rank, world = ctx.get_rank(), ctx.get_num_ranks()
     assert world >= 2
+    if "--expect-bootstrap" in sys.argv:  # the control plane the test asked for is the one in use
+        want = sys.argv[sys.argv.index("--expect-bootstrap") + 1]
+        assert type(ctx.comm).__name__ == want, type(ctx.comm).__name__
     n, block = 4096, 1024
     torch.manual_seed(0)
     buf = ctx.randn(n, dtype=torch.float32)

@@ -106,6 +106,11 @@ class FusedGemm:
         c_cols / col_off_per_rank: width of the output buffer and column offset per rank (all-scatter:
             ``c_cols = world * N``, ``col_off_per_rank = N``).
         ag: run the all-gather prologue (A rows sharded M / world per rank; see ``a_full``).
+        reduce_scatter: with ``mode="one_shot"``: every rank keeps only its own ``M / world`` rows of the sum
+            (``out[l]`` is that block); partial tiles are pushed to the keeper of their rows only.
+        push / ksplit: one-shot for short matrices: partials pushed into inbox slots of every rank, K cut into pieces.
+        nvls: two-shot on a heap bound to an NVLS multicast object: ``None`` = use it when available.
+        trace: record per-tile device timestamps (``trace_records()``).
     """
 
     def __init__(self, ctxs: Union[Iris, Sequence[Iris]], a: Optional[Sequence[torch.Tensor]],
@@ -430,7 +435,7 @@ def gemm(a: torch.Tensor, bt: torch.Tensor, out: Optional[torch.Tensor] = None,
 
 
 # Names of the fused algorithms (the reference keeps them as Triton constexprs, examples/common/utils.py:13-19).
-ALGORITHMS = ("all_scatter", "all_gather", "atomic", "one_shot", "two_shot")
+ALGORITHMS = ("all_scatter", "all_gather", "atomic", "one_shot", "two_shot", "reduce_scatter")
 
 
 class matmul(torch.autograd.Function):

@@ -6,7 +6,7 @@ tile sizes looked up in ``dataset/tiling.json``).  Here every point is a local m
 ``iris_b200.launch``; each writes one JSON file, and points whose file already exists are skipped, so an
 interrupted sweep resumes where it stopped.
 
-    python examples/benchmark/bench_all_shapes.py --input_json configs/shapes.json --out gpurun_out/sweep --gpus 1 2 4 8
+    python examples/benchmark/bench_all_shapes.py --input_json configs/shapes.json --out results/sweep --gpus 1 2 4 8
 """
 import argparse
 import json
@@ -33,7 +33,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--input_json", default=os.path.join(ROOT, "configs", "shapes.json"))
     ap.add_argument("--tiling_json", default=os.path.join(ROOT, "configs", "tiling_b200.json"))
-    ap.add_argument("--out", default=os.path.join(ROOT, "gpurun_out", "sweep"))
+    ap.add_argument("--out", default=os.path.join(ROOT, "results", "sweep"))
     ap.add_argument("--gpus", type=int, nargs="+", default=[1, 2, 4, 8])
     ap.add_argument("--only", nargs="*", default=None, help="restrict to these shape names")
     ap.add_argument("--timeout", type=float, default=300.0, help="seconds per point (the reference uses 5 minutes)")

@@ -10,7 +10,7 @@ each fused kernel next to cuBLAS + NCCL on the same operands, device-timed, maxi
 fraction.  Writes one JSON document (rank 0).  The reference spreads these over separate scripts and SLURM jobs
 (``examples/benchmark/bench_all_shapes.py``, ``examples/benchmark/reference/*.py``).
 
-    python -m iris_b200.launch -np 8 examples/benchmark/fused_suite.py --out gpurun_out/suite_w8.json
+    python -m iris_b200.launch -np 8 examples/benchmark/fused_suite.py --out results/suite_w8.json
 """
 import argparse
 import json

@@ -187,7 +187,7 @@ class FusedGemm:
         if stream_k is None:
             # Off unless asked for: on B200 the fix-up of a split tile (fp32 partials through L2 plus a second
             # epilogue for the finishing unit) costs more than the ragged last wave it removes, for every shape
-            # measured so far; the whole-tile schedule is the default.
+            # measured so far (8192 x 1792 x 4096: 108 us against 101 us); the whole-tile schedule is the default.
             stream_k = False
         self.dp_tiles, self.sk_units, sk_tiles = T, 0, 0
         if stream_k and T % units != 0:

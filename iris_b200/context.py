@@ -44,6 +44,17 @@ class IrisDeviceCheckError(RuntimeError):
     """A checking build of a kernel recorded a bad pointer or rank."""
 
 
+class IrisHeapCorruption(RuntimeError):
+    """Debug heap: the guard bytes behind an allocation were overwritten."""
+
+
+class IrisDivergenceError(RuntimeError):
+    """Debug heap: the ranks did not make the same sequence of allocations, so equal offsets name different objects."""
+
+
+CANARY = 0xA5        # guard byte of the debug heap
+
+
 class _DeviceMemory:
     """Exposes a raw device pointer through ``__cuda_array_interface__`` so torch can wrap it."""
 
@@ -65,11 +76,21 @@ class Iris:
         backend: ``"cuda"`` or ``"cpu"``; default ``"cuda"`` when a GPU is visible.
         heap_mode: ``"ipc"`` (cudaMalloc + CUDA IPC, default) or ``"vmm"`` (CUDA virtual memory management
             with file-descriptor export; required for NVLS multicast).  Env ``IRIS_HEAP_MODE`` overrides.
+        debug_heap: guard every allocation with ``alignment`` bytes of a known pattern and keep a record of the
+            allocation sequence; :meth:`barrier` then checks the guards (``IrisHeapCorruption``) and that every rank
+            allocated the same sequence (``IrisDivergenceError``).  Default: env ``IRIS_DEBUG_HEAP=1``.  Every rank
+            must use the same setting (checked).  The reference has neither check: a divergent allocation there
+            silently makes ``translate`` point at another object.
     """
 
     def __init__(self, heap_size: int = 1 << 30, *, bootstrap: Optional[_bs.Bootstrap] = None,
-                 backend: Optional[str] = None, heap_mode: Optional[str] = None, _local=None):
+                 backend: Optional[str] = None, heap_mode: Optional[str] = None, debug_heap: Optional[bool] = None,
+                 _local=None):
         self.alignment = 1024
+        if debug_heap is None:
+            debug_heap = os.environ.get("IRIS_DEBUG_HEAP", "0") not in ("", "0")
+        self.debug_heap = bool(debug_heap)
+        self._allocs: List[tuple] = []   # debug heap: (start, bytes asked for, bytes taken incl. guard, dtype name)
         self.heap_size = int(heap_size)
         self.heap_offset = 0
         self._closed = False
@@ -104,9 +125,13 @@ class Iris:
         self.comm = bootstrap if bootstrap is not None else _bs.init_from_env()
         self.cur_rank, self.num_ranks = self.comm.rank, self.comm.world
         # every rank must ask for the same heap size, otherwise equal offsets would not name equal objects
-        sizes = [int.from_bytes(b, "little") for b in self.comm.allgather_bytes(self.heap_size.to_bytes(8, "little"))]
+        hello = self.heap_size.to_bytes(8, "little") + bytes([int(self.debug_heap)])
+        hellos = self.comm.allgather_bytes(hello)
+        sizes = [int.from_bytes(b[:8], "little") for b in hellos]
         if any(s != self.heap_size for s in sizes):
             raise ValueError(f"heap_size differs across ranks: {sizes}")
+        if any(b[8] != int(self.debug_heap) for b in hellos):
+            raise ValueError(f"debug_heap differs across ranks: {[bool(b[8]) for b in hellos]}")
         if backend == "cuda":
             self._init_cuda()
         else:
@@ -192,10 +217,11 @@ class Iris:
     def _init_status(self) -> None:
         self.status = self.allocate(STATUS_BYTES // 4, torch.int32)
         self.status.zero_()
+        self._base_mark = self.heap_offset   # everything below belongs to the context itself
 
     @classmethod
     def local_world(cls, world: int, heap_size: int = 1 << 26, backend: Optional[str] = None,
-                    device: Optional[int] = None) -> List["Iris"]:
+                    device: Optional[int] = None, debug_heap: Optional[bool] = None) -> List["Iris"]:
         """Create ``world`` ranks inside this process, all on one device (or all on the CPU).
 
         Their heaps are separate allocations and the base-address table lists all of them, so pointer
@@ -228,7 +254,7 @@ class Iris:
             bases = torch.from_numpy(np.array(ptrs, dtype=np.uint64))
         members: List[Iris] = []
         for r in range(world):
-            members.append(cls(heap_size, backend=backend, _local=dict(
+            members.append(cls(heap_size, backend=backend, debug_heap=debug_heap, _local=dict(
                 comm=comm, rank=r, world=world, gpu_id=gpu_id, device=dev, pool=pools[r], heap_bases=bases,
                 ptr=ptrs[r], ptrs=ptrs, members=members)))
         members[0]._owns_local = True
@@ -269,6 +295,8 @@ class Iris:
         """Wait for this rank's device work, then for every rank (``iris/iris.py:272-276``)."""
         if self.backend == "cuda":
             torch.cuda.synchronize(self.device)
+        if self.debug_heap:
+            self.check_heap()
         if self._local_world is None:
             self.comm.barrier(timeout_s)
 
@@ -298,10 +326,16 @@ class Iris:
         self.log_debug(f"allocate: num_elements = {num_elements}, dtype = {dtype}")
         size_in_bytes = int(num_elements) * _element_size(dtype)
         aligned = math.ceil(size_in_bytes / self.alignment) * self.alignment
+        if self.debug_heap:
+            aligned += self.alignment  # guard bytes behind the allocation (and in its alignment slack)
         if self.heap_offset + aligned > self.heap_size:
             raise MemoryError("Heap out of memory")
         start = self.heap_offset
         self.heap_offset += aligned
+        if self.debug_heap:
+            guard0 = start + (size_in_bytes + 15) // 16 * 16   # kernels may round a store up to 16 bytes
+            self.memory_pool[guard0:start + aligned] = CANARY
+            self._allocs.append((start, size_in_bytes, aligned, str(dtype)))
         return self.memory_pool[start:start + size_in_bytes].view(dtype).reshape((int(num_elements),))
 
     def deallocate(self, pointer) -> None:
@@ -314,10 +348,53 @@ class Iris:
     def reset(self, to: Optional[int] = None) -> None:
         """Rewind the bump allocator to ``to`` (a value from :meth:`mark`; default: just above the status block).
         Every rank must do so at the same point of its allocation sequence."""
-        to = STATUS_BYTES if to is None else int(to)
-        if not STATUS_BYTES <= to <= self.heap_offset:
+        to = self._base_mark if to is None else int(to)
+        if not self._base_mark <= to <= self.heap_offset:
             raise ValueError("reset target is not a mark of this heap")
         self.heap_offset = to
+        self._allocs = [a for a in self._allocs if a[0] < to]
+
+    def allocation_digest(self) -> tuple:
+        """(number of allocations, CRC of their sizes and dtypes): equal on every rank of a correct program.  Only
+        kept by the debug heap."""
+        import zlib
+        crc = 0
+        for _, size, taken, dt in self._allocs:
+            crc = zlib.crc32(f"{size}:{taken}:{dt};".encode(), crc)
+        return len(self._allocs), crc
+
+    def check_heap(self) -> None:
+        """Debug heap: verify the guard bytes of every allocation of this rank, then that all ranks made the same
+        allocations.  Called by :meth:`barrier`; collective when the world has more than one process."""
+        if not self.debug_heap:
+            return
+        overrun = ""
+        for idx, (start, size, taken, dt) in enumerate(self._allocs):
+            guard = self.memory_pool[start + (size + 15) // 16 * 16:start + taken]
+            bad = (guard != CANARY).nonzero()
+            if bad.numel():
+                first = int(bad[0]) + (size + 15) // 16 * 16
+                overrun = (f"rank {self.cur_rank}: allocation #{idx} ({size} bytes of {dt} at heap offset {start}) was "
+                           f"overrun: byte {first - size} past its end is 0x{int(guard[int(bad[0])]):02x}")
+                break
+        mine = self.allocation_digest()
+        if self._local_world is not None:
+            if overrun:
+                raise IrisHeapCorruption(overrun)
+            theirs = [m.allocation_digest() for m in self._local_world]
+        else:
+            # the verdict travels with the digest, so that every rank leaves this collective the same way
+            blob = mine[0].to_bytes(8, "little") + mine[1].to_bytes(4, "little") + bytes([1 if overrun else 0])
+            got = self.comm.allgather_bytes(blob)
+            theirs = [(int.from_bytes(b[:8], "little"), int.from_bytes(b[8:12], "little")) for b in got]
+            hit = [r for r, b in enumerate(got) if b[12]]
+            if overrun:
+                raise IrisHeapCorruption(overrun)
+            if hit:
+                raise IrisHeapCorruption(f"rank {self.cur_rank}: guard bytes were overwritten on rank(s) {hit}")
+        if any(t != mine for t in theirs):
+            raise IrisDivergenceError(
+                f"rank {self.cur_rank}: allocation sequences differ across ranks (count, digest per rank): {theirs}")
 
     def parse_size(self, size):
         if len(size) == 1 and isinstance(size[0], (tuple, list, torch.Size)):

@@ -131,3 +131,40 @@ def test_unsupported_pairs_raise():
     b = c.zeros(4, dtype=torch.int8)
     with pytest.raises(TypeError):
         iris.atomic_add(c, b, 1)
+
+
+def test_debug_heap_guards_and_reset():
+    """Guard bytes behind every allocation: an overrun is reported at the next barrier with the allocation it
+    belongs to; ``reset`` forgets the allocations above the mark; a clean heap passes."""
+    from iris_b200.context import IrisHeapCorruption
+    ranks = iris.Iris.local_world(2, heap_size=1 << 20, backend="cpu", debug_heap=True)
+    c = ranks[0]
+    a = [r.zeros(100, dtype=torch.int32) for r in ranks]
+    mark = c.mark()
+    b = [r.ones(33, dtype=torch.float32) for r in ranks]
+    for r in ranks:
+        r.barrier()                                   # clean
+    assert c.allocation_digest() == ranks[1].allocation_digest() and c.allocation_digest()[0] == 3
+    # 132 bytes were asked for; the 16-byte round-up is tolerated, byte 144 is guarded
+    c.memory_pool[c.offset_of(b[0]) + 143] = 7
+    c.barrier()
+    c.memory_pool[c.offset_of(b[0]) + 144] = 7
+    with pytest.raises(IrisHeapCorruption, match=r"allocation #2 \(132 bytes of torch.float32"):
+        c.barrier()
+    c.reset(mark)
+    ranks[1].reset(mark)
+    c.barrier()                                       # the overrun allocation is gone
+    assert c.allocation_digest()[0] == 2
+    a[0].fill_(5)                                     # writing inside an allocation never trips a guard
+    c.barrier()
+    ranks[0].close()
+
+
+def test_debug_heap_divergence_in_a_local_world():
+    from iris_b200.context import IrisDivergenceError
+    ranks = iris.Iris.local_world(2, heap_size=1 << 20, backend="cpu", debug_heap=True)
+    ranks[0].zeros(10)
+    ranks[1].zeros(11)
+    with pytest.raises(IrisDivergenceError):
+        ranks[0].barrier()
+    ranks[0].close()

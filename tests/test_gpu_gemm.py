@@ -173,6 +173,36 @@ def test_gemm_reduce_scatter_emulated(world, m, cta_group):
     ranks[0].close()
 
 
+def test_no_kernel_writes_outside_its_buffers():
+    """Every fused variant on a debug heap (guard bytes behind each allocation), shapes with ragged edges: after the
+    calls the guards are intact and all ranks made the same allocations."""
+    world = 2
+    ranks = iris.Iris.local_world(world, heap_size=256 << 20, debug_heap=True)
+    m, n, k_full = 648, 832, 1296          # M and N end inside a tile
+    ks = k_full // world
+    a_full, b_full = _rand((m, k_full), 41), _rand((n, k_full), 42, 0.05)
+    a = [a_full[:, r * ks:(r + 1) * ks] for r in range(world)]
+    bt = [b_full[:, r * ks:(r + 1) * ks] for r in range(world)]
+    ops = [G.gemm_all_reduce(ranks, a, bt, variant=v) for v in ("atomic", "one_shot", "two_shot")]
+    ops.append(G.gemm_all_reduce(ranks, [x[:100] for x in a], bt, variant="one_shot"))            # pushed, K-split
+    ops.append(G.gemm_all_scatter(ranks, [a_full] * world, [_rand((320, k_full), 43 + r, 0.05) for r in range(world)]))
+    ops.append(G.gemm_reduce_scatter(ranks, [x[:512] for x in a], bt))
+    ag = G.all_gather_gemm(ranks, 512, [_rand((320, 512), 50 + r, 0.05) for r in range(world)], ag_slices=4)
+    for r in range(world):
+        ag.a_full[r][r * 256:(r + 1) * 256].copy_(_rand((256, 512), 60 + r))
+    ops.append(ag)
+    for _ in range(2):
+        for op in ops:
+            op()
+    for op in ops:
+        op.check()
+    for r in ranks:
+        r.barrier()      # checks guards and allocation sequences
+    for op in ops:
+        op.close()
+    ranks[0].close()
+
+
 @pytest.mark.parametrize("cta_group", [1, 2])
 @pytest.mark.parametrize("world", [2, 4])
 def test_all_gather_gemm_emulated(world, cta_group):

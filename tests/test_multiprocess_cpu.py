@@ -66,6 +66,19 @@ def test_missing_rank_times_out_instead_of_hanging():
     assert "BootstrapError" in outs[0]
 
 
+def test_debug_heap_reports_divergent_allocations():
+    code, outs = run_ranks(3, [os.path.join(W, "cpu_faults.py"), "divergent_allocation"])
+    _ok(code, outs)
+    assert all("IrisDivergenceError" in o and "differ across ranks" in o for o in outs)
+
+
+def test_debug_heap_reports_an_overrun_by_a_peer():
+    code, outs = run_ranks(2, [os.path.join(W, "cpu_faults.py"), "remote_overrun"])
+    _ok(code, outs)
+    assert "allocation #2 (1000 bytes of torch.uint8" in outs[1] and "byte 8 past its end is 0x11" in outs[1], outs[1]
+    assert "overwritten on rank(s) [1]" in outs[0], outs[0]
+
+
 def test_flag_never_set_returns_status():
     code, outs = run_ranks(2, [os.path.join(W, "cpu_faults.py"), "flag_never_set"])
     _ok(code, outs)

@@ -20,6 +20,35 @@ def main():
             print(f"rank {rank}: ValueError {e}")
             return 0
         return 1
+    if scenario == "divergent_allocation":
+        # debug heap: rank 1 allocates one buffer more than the others; the next barrier names the divergence
+        ctx = iris.iris(1 << 20, backend="cpu", debug_heap=True)
+        ctx.zeros(256, dtype=torch.float32)
+        if rank == 1:
+            ctx.zeros(8, dtype=torch.int32)
+        try:
+            ctx.barrier()
+        except iris.context.IrisDivergenceError as e:
+            print(f"rank {rank}: IrisDivergenceError {e}")
+            return 0
+        return 1
+    if scenario == "remote_overrun":
+        # debug heap: rank 0 writes 16 bytes past the end of a 1000-byte buffer of rank 1; rank 1's barrier says which
+        import ctypes
+        ctx = iris.iris(1 << 20, backend="cpu", debug_heap=True)
+        first = ctx.zeros(100, dtype=torch.int32)
+        buf = ctx.zeros(1000, dtype=torch.uint8)
+        ctx.barrier()
+        if rank == 0:
+            peer = iris.translate(buf.data_ptr(), 0, 1, ctx.get_heap_bases().tolist())
+            ctypes.memset(peer + 1008, 0x11, 16)
+        ctx.comm.barrier()          # plain host barrier: the write has happened, nothing checked yet
+        try:
+            ctx.barrier()
+        except iris.context.IrisHeapCorruption as e:   # every rank learns of it; the owner knows the details
+            print(f"rank {rank}: IrisHeapCorruption {e}")
+            return 0
+        return 1
     ctx = iris.iris(1 << 20, backend="cpu")
     if scenario == "missing_rank_at_barrier":
         # rank 1 never joins the barrier: the others must get an error within the time limit, not hang

@@ -71,9 +71,13 @@ def run(kind: str, seed: int):
         gathered = torch.empty((world, m, nl), dtype=torch.bfloat16, device=dev)
 
         def unfused():
+            torch.cuda.nvtx.range_push("GEMM")
             torch.matmul(A, bt_local.t(), out=c_part)
+            torch.cuda.nvtx.range_pop()
             if world > 1:
+                torch.cuda.nvtx.range_push("Communication")
                 dist.all_gather_into_tensor(gathered, c_part)
+                torch.cuda.nvtx.range_pop()
         a_local, b_local = A, bt_local
         variant = "all_scatter"
     elif kind == "reduce_scatter":
@@ -111,6 +115,9 @@ def run(kind: str, seed: int):
     js = JSONWriter(args["output_file"] if rank == 0 else "")
     fields = {k_: v for k_, v in args.items() if v is not None}
     fields.update(world_size=world, variant=variant, gemm_sms=op.ctas_per_rank, tile="128x256x64")
+    res = op.resources()
+    if res:  # the reference's gemm_registers / gemm_spills (examples/07_gemm_all_scatter/benchmark.py:237-242)
+        fields.update(gemm_registers=res["registers"], gemm_spills=res["spill_store_bytes"] + res["spill_load_bytes"])
     js.add_fields(**fields)
     G.matmul.set_debug(args["debug"])
     ctx.barrier()
@@ -121,7 +128,8 @@ def run(kind: str, seed: int):
         import json
         with open(f"trace_rank{rank}.json", "w") as f:
             json.dump(op.trace_records(), f)
-        ctx.log(f"per-tile trace written to trace_rank{rank}.json")
+        op.chrome_trace(f"trace_rank{rank}.chrome.json")
+        ctx.log(f"per-tile trace written to trace_rank{rank}.json (records) and trace_rank{rank}.chrome.json (timeline)")
     ok = True
     if args["validate"]:
         rows = slice(0, min(m, 1024))
@@ -136,7 +144,11 @@ def run(kind: str, seed: int):
         ctx.log(f"Validation {'successful' if ok else 'FAILED'}.")
         js.add_field("success", ok)
     if args["benchmark"]:
-        ms = time_kernel_ms(ctx, lambda: op(), args["num_warmup"], args["num_experiments"], align=True)
+        def fused():  # range names as in the reference (examples/07_gemm_all_scatter/benchmark.py:179-180)
+            torch.cuda.nvtx.range_push("GEMM + Communication")
+            op()
+            torch.cuda.nvtx.range_pop()
+        ms = time_kernel_ms(ctx, fused, args["num_warmup"], args["num_experiments"], align=True)
         ms = reduce_ranks(ctx, ms, "max")
         op.check()
         flops = 2.0 * m * n * k

@@ -8,8 +8,9 @@ Run ``python -m iris_b200._build`` (add ``-v`` for ptxas resource usage, ``-f`` 
 """
 from __future__ import annotations
 
-import hashlib
+import json
 import os
+import re
 import shutil
 import subprocess
 import sys
@@ -53,6 +54,52 @@ def _run(cmd, verbose=False):
     return p.stdout + p.stderr
 
 
+def parse_ptxas(log: str) -> dict:
+    """Resource usage per kernel from the output of ``nvcc -Xptxas -v``: ``{mangled name: {registers, barriers,
+    stack_bytes, spill_store_bytes, spill_load_bytes, smem_bytes}}`` (the figures the reference reads from Triton's
+    compiled kernel as ``n_regs`` / ``n_spills``, ``examples/07_gemm_all_scatter/matmul_wrapper.py:152-155``)."""
+    out, name, props_of = {}, None, None
+    for line in log.splitlines():
+        m = re.search(r"Compiling entry function '([^']+)'", line)
+        if m:
+            name = m.group(1)
+            out[name] = dict(registers=0, barriers=0, stack_bytes=0, spill_store_bytes=0, spill_load_bytes=0, smem_bytes=0)
+            continue
+        m = re.search(r"Function properties for (\S+)", line)
+        if m:
+            props_of = m.group(1)   # may be a device function compiled out of line: not an entry of `out`
+            continue
+        m = re.search(r"(\d+) bytes stack frame, (\d+) bytes spill stores, (\d+) bytes spill loads", line)
+        if m:
+            if props_of in out:
+                out[props_of].update(stack_bytes=int(m.group(1)), spill_store_bytes=int(m.group(2)),
+                                     spill_load_bytes=int(m.group(3)))
+            continue
+        m = re.search(r"Used (\d+) registers", line)
+        if m and name is not None:
+            out[name]["registers"] = int(m.group(1))
+            b = re.search(r"used (\d+) barriers", line)
+            s_ = re.search(r"(\d+) bytes smem", line)
+            out[name]["barriers"] = int(b.group(1)) if b else 0
+            out[name]["smem_bytes"] = int(s_.group(1)) if s_ else 0
+    return out
+
+
+def _demangle(names):
+    filt = shutil.which("c++filt")
+    if not filt or not names:
+        return {n: n for n in names}
+    p = subprocess.run([filt], input="\n".join(names), capture_output=True, text=True)
+    lines = p.stdout.splitlines()
+    return dict(zip(names, lines)) if p.returncode == 0 and len(lines) == len(names) else {n: n for n in names}
+
+
+def kernel_resources() -> dict:
+    """``{demangled kernel name: resources}`` of the kernels in ``libiris_kernels.so``, as recorded at build time."""
+    path = LIB / "kernel_resources.json"
+    return json.loads(path.read_text()) if path.exists() else {}
+
+
 def kernel_sources():
     return sorted((CSRC / "kernels").glob("*.cu"))
 
@@ -90,17 +137,22 @@ def build_kernels(force=False, verbose=False) -> Path:
         o = OBJ / (s.stem + ".o")
         objs.append(o)
         if force or _newer(o, [s] + hdrs):
-            cmd = [NVCC, *NVCC_FLAGS, "-c", s, "-o", o]
-            if verbose:
-                cmd[1:1] = ["-Xptxas", "-v"]
-            jobs.append(cmd)
+            jobs.append((s, [NVCC, "-Xptxas", "-v", *NVCC_FLAGS, "-c", s, "-o", o]))
     if jobs:
         with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
-            logs = list(ex.map(lambda c: _run(c, verbose), jobs))
-        if verbose:
-            (OBJ / "ptxas.log").write_text("\n".join(logs))
-    if jobs or force or _newer(out, objs):
+            logs = list(ex.map(lambda j: _run(j[1], verbose), jobs))
+        for (s, _), log in zip(jobs, logs):  # registers, spills, shared memory of every kernel of this source
+            (OBJ / (s.stem + ".resources.json")).write_text(json.dumps(parse_ptxas(log)))
+    res_path = LIB / "kernel_resources.json"
+    if jobs or force or _newer(out, objs) or not res_path.exists():
         _run([NVCC, *ARCH_FLAGS, "-shared", "-o", out, *objs, "-cudart", "static"], verbose)
+        merged = {}
+        for s in srcs:
+            f = OBJ / (s.stem + ".resources.json")
+            if f.exists():
+                merged.update(json.loads(f.read_text()))
+        names = _demangle(list(merged))
+        res_path.write_text(json.dumps({names[k]: dict(v, source_symbol=k) for k, v in merged.items()}, indent=1))
     return out
 
 

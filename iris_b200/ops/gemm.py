@@ -350,6 +350,25 @@ class FusedGemm:
             recs.append(rec)
         return recs
 
+    def chrome_trace(self, path: str, local: int = 0) -> None:
+        """Write the per-tile timestamps of the last call as a Chrome / Perfetto trace file."""
+        import json
+        from ..utils.results import tile_trace_to_chrome
+        with open(path, "w") as f:
+            json.dump(tile_trace_to_chrome(self.trace_records(local), self.rank0 + local), f)
+
+    def resources(self) -> dict:
+        """Registers, spill bytes and static shared memory of the kernel this op launches, as reported by ptxas when
+        the library was built (the reference records ``n_regs`` / ``n_spills`` of its Triton kernel,
+        ``examples/07_gemm_all_scatter/matmul_wrapper.py:152-155``).  Empty when the build record is missing."""
+        from .. import _build
+        pull = self.mode in ("one_shot", "two_shot")
+        want = f"fused_gemm_kernel<{self.cta_group}, {'true' if pull else 'false'}>"
+        for name, res in _build.kernel_resources().items():
+            if want in name:
+                return dict(res, kernel=want)
+        return {}
+
     def check(self) -> None:
         """Synchronise and raise if a bounded wait of the last calls expired."""
         torch.cuda.synchronize(self.ctxs[0].device)

@@ -73,6 +73,27 @@ class Timestamps:
             json.dump(self.to_records(), f)
 
 
+# Phases of a fused-GEMM tile record (``FusedGemm.trace_records``): name, begin key, end key, lane inside the CTA.
+TILE_PHASES = (("main loop", "mma_begin", "mma_end", 0), ("epilogue", "epi_begin", "epi_end", 1),
+               ("flag wait", "wait_begin", "wait_end", 2), ("sum", "wait_end", "pull_end", 2))
+
+
+def tile_trace_to_chrome(records: List[dict], rank: int = 0) -> dict:
+    """Per-tile device timestamps as a Chrome / Perfetto trace (``chrome://tracing``, ui.perfetto.dev): one process per
+    rank, one thread per (tile record, role), complete events in microseconds.  The reference dumps a flat JSON list
+    (``examples/common/utils.py:66-128``) and draws its timelines by hand (``docs/FINEGRAINED_OVERLAP.md`` figures)."""
+    events = [{"ph": "M", "name": "process_name", "pid": rank, "args": {"name": f"rank {rank}"}}]
+    for rec in records:
+        for name, kb, ke, lane in TILE_PHASES:
+            b, e = rec.get(kb), rec.get(ke)
+            if b is None or e is None or e < b:
+                continue
+            events.append({"ph": "X", "name": name, "cat": "tile", "pid": rank, "tid": 3 * int(rec["record"]) + lane,
+                           "ts": float(b), "dur": float(e - b),
+                           "args": {"tile_id": rec.get("tile_id"), "cta_in_pair": rec.get("cta_in_pair")}})
+    return {"traceEvents": events, "displayTimeUnit": "ns"}
+
+
 def validate_gemm(A: torch.Tensor, B: torch.Tensor, C: torch.Tensor, ctx=None, atol: float = 1.0) -> bool:
     """``A @ B`` against ``C`` with an absolute tolerance (``examples/common/validation.py:7-23``)."""
     expected = (A.float() @ B.float()).to(C.dtype)

@@ -98,3 +98,51 @@ def test_launcher_time_limit(tmp_path):
     slow.write_text("import time\ntime.sleep(30)\n")
     code, _ = launch(2, [str(slow)], timeout_s=1.5, capture=True)
     assert code == 124
+
+
+def test_kernel_resources_are_recorded_at_build_time():
+    """ptxas figures per kernel: parsed from the compiler's output (device functions compiled out of line do not
+    overwrite the kernel that calls them) and kept beside the library."""
+    from iris_b200 import _build
+    log = """
+ptxas info    : Compiling entry function '_Z1kv' for 'sm_100a'
+ptxas info    : Function properties for _Z1kv
+    160 bytes stack frame, 186 bytes spill stores, 336 bytes spill loads
+ptxas info    : Used 168 registers, used 4 barriers, 160 bytes cumulative stack size, 32 bytes smem
+ptxas info    : Function properties for _Z6helperv
+    0 bytes stack frame, 0 bytes spill stores, 0 bytes spill loads
+ptxas info    : Compiling entry function '_Z2k2v' for 'sm_100a'
+ptxas info    : Function properties for _Z2k2v
+    0 bytes stack frame, 0 bytes spill stores, 0 bytes spill loads
+ptxas info    : Used 32 registers, used 1 barriers
+"""
+    got = _build.parse_ptxas(log)
+    assert got["_Z1kv"] == dict(registers=168, barriers=4, stack_bytes=160, spill_store_bytes=186,
+                                spill_load_bytes=336, smem_bytes=32)
+    assert got["_Z2k2v"]["registers"] == 32 and got["_Z2k2v"]["spill_store_bytes"] == 0
+    _build.build_all()
+    res = _build.kernel_resources()
+    gemm = {k: v for k, v in res.items() if "fused_gemm_kernel<" in k}
+    assert len(gemm) == 4
+    for name, v in gemm.items():
+        # 8 warps: at most 255; 10 warps (reducer kernels): 168 per thread, or the CTA would not fit the register file
+        assert 0 < v["registers"] <= (168 if "true>" in name else 255), (name, v)
+    # the main-loop kernels without reducer warps must not spill
+    assert all(v["spill_store_bytes"] == 0 for k, v in gemm.items() if "false>" in k)
+
+
+def test_tile_trace_to_chrome():
+    from iris_b200.utils.results import tile_trace_to_chrome
+    recs = [dict(record=0, tile_id=0, cta_in_pair=0, mma_begin=1.0, mma_end=9.0, epi_begin=9.5, epi_end=12.0,
+                 wait_begin=13.0, wait_end=20.0, pull_end=31.0),
+            dict(record=1, tile_id=0, cta_in_pair=1, mma_begin=None, mma_end=None, epi_begin=9.6, epi_end=12.5,
+                 wait_begin=None, wait_end=None, pull_end=None)]
+    tr = tile_trace_to_chrome(recs, rank=3)
+    ev = [e for e in tr["traceEvents"] if e["ph"] == "X"]
+    assert {(e["name"], e["tid"]) for e in ev} == {("main loop", 0), ("epilogue", 1), ("flag wait", 2), ("sum", 2),
+                                                   ("epilogue", 4)}
+    assert all(e["pid"] == 3 and e["dur"] >= 0 for e in ev)
+    sm = next(e for e in ev if e["name"] == "sum")
+    assert sm["ts"] == 20.0 and sm["dur"] == 11.0
+    import json
+    json.dumps(tr)

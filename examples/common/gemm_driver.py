@@ -119,6 +119,7 @@ def run(kind: str, seed: int):
     if res:  # the reference's gemm_registers / gemm_spills (examples/07_gemm_all_scatter/benchmark.py:237-242)
         fields.update(gemm_registers=res["registers"], gemm_spills=res["spill_store_bytes"] + res["spill_load_bytes"])
     js.add_fields(**fields)
+    js.add_environment(dev)
     G.matmul.set_debug(args["debug"])
     ctx.barrier()
     out = G.matmul.apply(op)

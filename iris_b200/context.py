@@ -33,6 +33,23 @@ STATS = True
 LOGGING = True
 DEBUG = False
 
+# IRIS_LOG presets them: quiet (nothing), stats (log_stats only), info (log + log_stats, the default), debug (all).
+_LOG_LEVELS = {"quiet": (False, False, False), "stats": (True, False, False), "info": (True, True, False),
+               "debug": (True, True, True)}
+
+
+def set_log_level(level: str) -> None:
+    """Set the three switches at once: ``quiet``, ``stats``, ``info`` or ``debug``."""
+    global STATS, LOGGING, DEBUG
+    try:
+        STATS, LOGGING, DEBUG = _LOG_LEVELS[level.lower()]
+    except KeyError:
+        raise ValueError(f"IRIS_LOG / set_log_level: {level!r} is not one of {sorted(_LOG_LEVELS)}") from None
+
+
+if os.environ.get("IRIS_LOG"):
+    set_log_level(os.environ["IRIS_LOG"])
+
 STATUS_BYTES = 1024  # first allocation of every heap: the kernel status block (see iris.cuh StatusBlock)
 
 

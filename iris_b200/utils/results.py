@@ -27,6 +27,35 @@ class JSONWriter:
     def add_fields(self, **kw) -> None:
         self.data.update(kw)
 
+    def add_environment(self, device=None) -> None:
+        """Record where the numbers come from: time, host, package and torch versions, the source revision when the
+        package sits in a git checkout, and the GPU (name, SM count, memory) when one is given or current."""
+        import datetime
+        import platform
+        import subprocess
+        env: Dict[str, Any] = {"time_utc": datetime.datetime.now(datetime.timezone.utc).isoformat(timespec="seconds"),
+                               "host": platform.node(), "python": platform.python_version(),
+                               "torch": torch.__version__, "cuda": torch.version.cuda}
+        try:
+            from .. import __version__
+            env["iris_b200"] = __version__
+        except Exception:
+            pass
+        root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+        try:
+            rev = subprocess.run(["git", "-C", root, "rev-parse", "--short", "HEAD"], capture_output=True, text=True,
+                                 timeout=5)
+            if rev.returncode == 0:
+                env["git"] = rev.stdout.strip()
+        except Exception:
+            pass
+        if torch.cuda.is_available():
+            props = torch.cuda.get_device_properties(device if device is not None else torch.cuda.current_device())
+            env["gpu"] = {"name": props.name, "sms": props.multi_processor_count,
+                          "memory_gb": round(props.total_memory / 2 ** 30, 1),
+                          "capability": f"{props.major}.{props.minor}"}
+        self.data["environment"] = env
+
     def flush(self) -> None:
         if not self.file_path:
             return

@@ -6,13 +6,15 @@
 // What it covers: element-wise RMA primitives run by several threads (the "threads of a block" of the back end), the
 // message-passing protocol (data written with ordinary stores, flag raised with release, consumer polls with
 // acquire, then reads the data: a missing ordering shows up as a data race under the thread sanitizer), concurrent
-// atomic adds from both ranks, a bounded wait that expires, and the checking pointer translation.
+// atomic adds from both ranks, a bounded wait that expires, the checking pointer translation, and a model of the
+// fused GEMM's inbox protocol (cumulative flags, buffers alternating by call parity) run with random delays.
 #include <stdint.h>
 #include <stdio.h>
 #include <string.h>
 #include <unistd.h>
 
 #include <atomic>
+#include <chrono>
 #include <thread>
 #include <vector>
 
@@ -129,7 +131,7 @@ int main() {
       for (int c = 0; c < kChunks; ++c)
         iris_cpu_mp_produce(src.data() + c * kChunk / 4, sym(0, kA) + c * kChunk, kChunk, flags0 + c, 1, hb, 0, 1);
       for (int c = 0; c < kChunks; ++c) {  // then collect the doubled chunks from its own B
-        const uint32_t s = iris_cpu_wait_flag(flags0 + c, 1, 1ull << 32, &st0, 0);
+        const uint32_t s = iris_cpu_wait_flag(flags0 + c, 1, 1ull << 27, &st0, 0);
         CHECK(s == kOk, "producer wait chunk %d", c);
         memcpy(back.data() + c * kChunk / 4, sym(0, kB) + c * kChunk, kChunk);
       }
@@ -137,7 +139,7 @@ int main() {
     std::thread consumer([&]() {
       std::vector<int32_t> tmp(kChunk / 4);
       for (int c = 0; c < kChunks; ++c) {
-        const uint32_t s = iris_cpu_wait_flag(flags1 + c, 1, 1ull << 32, &st1, 1);
+        const uint32_t s = iris_cpu_wait_flag(flags1 + c, 1, 1ull << 27, &st1, 1);
         CHECK(s == kOk, "consumer wait chunk %d", c);
         const int32_t* in = reinterpret_cast<const int32_t*>(sym(1, kA) + c * kChunk);
         for (size_t i = 0; i < tmp.size(); ++i) tmp[i] = 2 * in[i];
@@ -173,6 +175,75 @@ int main() {
     StatusBlock st2{};
     const uint64_t bad_rank = iris_cpu_translate_checked(hb[0], hb, kHeap, 0, kWorld, 5, &st2);
     CHECK(bad_rank == 0 && st2.code == kBadRank, "rank out of range: code %u", st2.code);
+  }
+
+  // ---- 6. the inbox protocol of the fused GEMM's pushed one-shot / reduce-scatter paths, with random delays ----
+  // Every "rank" (a thread) writes its partial into its slot of EVERY rank's inbox with ordinary stores, releases it
+  // with an increment of the destination's cumulative flag, waits until its own flag has seen all ranks, and sums the
+  // slots.  Inboxes alternate by call parity and nothing is reset between calls.  A call starts with the entry
+  // handshake: every rank tells every rank that it has entered call c, and nobody pushes before all have.  Without it
+  // a rank that is one call ahead can raise a destination's cumulative flag to W * c while a slow rank's
+  // contribution to call c is still missing there (this model, run without the handshake, shows exactly that as a
+  // wrong sum).  Under the thread sanitizer a missing release / acquire is a reported race; the sums catch the rest.
+  {
+    constexpr int W = 4, kCalls = 40, kElems = 192;
+    // one "heap" per rank inside segment 0: [flag, entry flags (64 B) | inbox parity 0: W slots | inbox parity 1: W slots]
+    constexpr uint64_t kRankBytes = 64 + 2ull * W * kElems * 4;
+    static_assert(W * kRankBytes <= (64 << 10), "fits the data area A");
+    uint8_t* region = sym(0, kA);
+    memset(region, 0, W * kRankBytes);
+    uint64_t hbw[W];
+    for (int r = 0; r < W; ++r) hbw[r] = (uint64_t)(region + r * kRankBytes);
+    std::atomic<int> failures{0};
+    auto body = [&](int rank) {
+      unsigned seed = 1234u + 77u * rank;
+      auto nap = [&]() {
+        seed = seed * 1664525u + 1013904223u;
+        if ((seed >> 28) < 5) std::this_thread::sleep_for(std::chrono::microseconds((seed >> 20) & 63));
+      };
+      uint32_t* my_flag = reinterpret_cast<uint32_t*>(hbw[rank]);
+      int32_t* my_inbox = reinterpret_cast<int32_t*>(hbw[rank] + 64);
+      uint32_t* my_entry = my_flag + 8;  // entry flag of rank q at [8 + q]
+      for (int call = 1; call <= kCalls; ++call) {
+        const int par = call & 1;
+        for (int i = 0; i < W; ++i) signal_set(my_entry + rank, (uint32_t)call, rank, (rank + 1 + i) % W, hbw);
+        nap();
+        for (int q = 0; q < W; ++q) {
+          StatusBlock st{};
+          if (wait_until_ge(my_entry + q, (uint32_t)call, 1ull << 27, &st, 5, rank, q) != kOk) {
+            ++failures;
+            return;
+          }
+        }
+        for (int i = 0; i < W; ++i) {  // peers first, own copy last, as the kernel does
+          const int dst = (rank + 1 + i) % W;
+          nap();
+          int32_t* slot = translate(my_inbox, rank, dst, hbw) + (par * W + rank) * kElems;
+          for (int e = 0; e < kElems; ++e) slot[e] = call * 1000 + rank * 10 + (e & 7);
+          signal_add(my_flag, 1u, rank, dst, hbw);
+        }
+        nap();
+        StatusBlock st{};
+        if (wait_until_ge(my_flag, (uint32_t)(W * call), 1ull << 27, &st, 6, rank, call) != kOk) {
+          ++failures;
+          return;
+        }
+        for (int e = 0; e < kElems; ++e) {
+          long sum = 0;
+          for (int sl = 0; sl < W; ++sl) sum += my_inbox[(par * W + sl) * kElems + e];
+          const long want = (long)W * call * 1000 + 10 * (W * (W - 1) / 2) + (long)W * (e & 7);
+          if (sum != want) {
+            ++failures;
+            return;
+          }
+        }
+        nap();
+      }
+    };
+    std::vector<std::thread> ranks;
+    for (int r = 0; r < W; ++r) ranks.emplace_back(body, r);
+    for (auto& t : ranks) t.join();
+    CHECK(failures.load() == 0, "inbox protocol: %d rank(s) saw a wrong sum or a time-out", failures.load());
   }
 
   for (int r = 0; r < kWorld; ++r) {

@@ -168,3 +168,22 @@ def test_debug_heap_divergence_in_a_local_world():
     with pytest.raises(IrisDivergenceError):
         ranks[0].barrier()
     ranks[0].close()
+
+
+def test_log_levels(ctx, capsys):
+    from iris_b200 import context as C
+    saved = (C.STATS, C.LOGGING, C.DEBUG)
+    try:
+        C.set_log_level("quiet")
+        ctx.log("a"), ctx.log_stats("b"), ctx.log_debug("c")
+        assert capsys.readouterr().out == ""
+        C.set_log_level("stats")
+        ctx.log("a"), ctx.log_stats("b"), ctx.log_debug("c")
+        assert capsys.readouterr().out.strip().endswith("b")
+        C.set_log_level("debug")
+        ctx.log("a"), ctx.log_stats("b"), ctx.log_debug("c")
+        assert [ln[-1] for ln in capsys.readouterr().out.strip().splitlines()] == ["a", "b", "c"]
+        with pytest.raises(ValueError):
+            C.set_log_level("loud")
+    finally:
+        C.STATS, C.LOGGING, C.DEBUG = saved

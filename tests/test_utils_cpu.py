@@ -146,3 +146,15 @@ def test_tile_trace_to_chrome():
     assert sm["ts"] == 20.0 and sm["dur"] == 11.0
     import json
     json.dumps(tr)
+
+
+def test_json_writer_records_its_environment(tmp_path):
+    w = JSONWriter(str(tmp_path / "r.json"))
+    w.add_field("x", 1)
+    w.add_environment()
+    w.flush()
+    import json
+    d = json.load(open(tmp_path / "r.json"))
+    env = d["environment"]
+    assert d["x"] == 1 and env["torch"] == torch.__version__ and "time_utc" in env and "host" in env
+    assert ("gpu" in env) == torch.cuda.is_available()

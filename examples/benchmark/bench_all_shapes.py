@@ -15,18 +15,8 @@ import subprocess
 import sys
 
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
-SCRIPTS = {"all_scatter": "examples/07_gemm_all_scatter/benchmark.py",
-           "atomic": "examples/08_gemm_atomics_all_reduce/benchmark.py",
-           "one_shot": "examples/09_gemm_one_shot_all_reduce/benchmark.py",
-           "two_shot": "examples/09_gemm_one_shot_all_reduce/benchmark.py"}
-
-
-def tiling_for(table, m, n, k):
-    cfg = dict(table["default"])
-    for o in table.get("overrides", []):
-        if (o["m"], o["n"], o["k"]) == (m, n, k):
-            cfg.update({k_: v for k_, v in o.items() if k_ not in ("m", "n", "k")})
-    return cfg
+sys.path.insert(0, ROOT)
+from iris_b200.utils.config import GemmPoint, load_points  # noqa: E402
 
 
 def main():
@@ -44,31 +34,21 @@ def main():
     with open(args.tiling_json) as f:
         table = json.load(f)
     os.makedirs(args.out, exist_ok=True)
-    for s in shapes:
-        if args.only and s["name"] not in args.only:
+    for pt in load_points({"shapes": shapes}, args.gpus):
+        if args.only and pt.name not in args.only:
             continue
-        for workload in s["workloads"]:
-            for w in args.gpus:
-                m, n, k = s["m"], s["n"], s["k"]
-                if workload == "all_scatter" and n % w:
-                    continue
-                if workload != "all_scatter" and (k % w or (k // w) % 8):
-                    continue
-                per_rank = (m, n // w, k) if workload == "all_scatter" else (m, n, k // w)
-                cfg = tiling_for(table, *per_rank)
-                out = os.path.join(args.out, f"{s['name']}_{workload}_w{w}.json")
-                if os.path.exists(out):
-                    print(f"skip {out} (exists)")
-                    continue
-                cmd = [sys.executable, "-m", "iris_b200.launch", "-np", str(w), "--timeout", str(args.timeout),
-                       os.path.join(ROOT, SCRIPTS[workload]), "-m", str(m), "-n", str(n), "-k", str(k), "-v", "-b",
-                       "--gsize_m", str(cfg["gsize_m"]), "--gemm_sms", str(cfg["gemm_sms"]), "--output_file", out]
-                if workload in ("atomic", "one_shot", "two_shot") and workload != "atomic":
-                    cmd += ["--variant", workload]
-                print(" ".join(cmd), flush=True)
-                if not args.dry_run:
-                    subprocess.run(cmd, cwd=ROOT, env=dict(os.environ, PYTHONPATH=ROOT))
-
+        why = pt.problems()
+        if why:
+            print(f"skip {pt.name} {pt.workload} W={pt.world}: {'; '.join(why)}")
+            continue
+        out = os.path.join(args.out, f"{pt.name}_{pt.workload}_w{pt.world}.json")
+        if os.path.exists(out):
+            print(f"skip {out} (exists)")
+            continue
+        cmd = pt.command(ROOT, table, output_file=out, python=sys.executable, timeout_s=args.timeout)
+        print(" ".join(cmd), flush=True)
+        if not args.dry_run:
+            subprocess.run(cmd, cwd=ROOT, env=dict(os.environ, PYTHONPATH=ROOT))
 
 if __name__ == "__main__":
     main()

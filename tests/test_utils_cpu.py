@@ -158,3 +158,27 @@ def test_json_writer_records_its_environment(tmp_path):
     env = d["environment"]
     assert d["x"] == 1 and env["torch"] == torch.__version__ and "time_utc" in env and "host" in env
     assert ("gpu" in env) == torch.cuda.is_available()
+
+
+def test_benchmark_points_validate_and_build_their_command():
+    from iris_b200.utils.config import GemmPoint, TileConfig, load_points
+    table = json.load(open(os.path.join(ROOT, "configs", "tiling_b200.json")))
+    ok = GemmPoint("all_scatter", 8192, 14336, 4096, 8, name="c3")
+    assert ok.problems() == [] and ok.per_rank_shape() == (8192, 1792, 4096)
+    assert ok.tile(table) == TileConfig(gsize_m=8)
+    cmd = ok.command("/r", table, output_file="o.json")
+    assert cmd[:5] == ["python", "-m", "iris_b200.launch", "-np", "8"] and "/r/examples/07_gemm_all_scatter/benchmark.py" in cmd
+    assert cmd[cmd.index("--output_file") + 1] == "o.json"
+    assert GemmPoint("all_scatter", 8192, 14336, 4096, 3).problems() == ["N must divide by the number of ranks"]
+    assert "K per rank" in GemmPoint("one_shot", 128, 4096, 11004, 4).problems()[0]
+    assert GemmPoint("one_shot", 1, 4096, 11008, 8).problems() == []
+    assert GemmPoint("one_shot", 1, 4096, 11008, 8).per_rank_shape() == (1, 4096, 1376)
+    assert GemmPoint("one_shot", 1, 4096, 11008, 8).tile(table).gsize_m == 1       # an override of the table
+    assert "ranks x 128" in GemmPoint("reduce_scatter", 1000, 4096, 4096, 8).problems()[0]
+    assert GemmPoint("reduce_scatter", 16384, 4096, 4096, 8).problems() == []
+    assert GemmPoint("atomic", 64, 4104, 4096, 2).problems() != [] and GemmPoint("atomic", 64, 4104, 4096, 1).problems() == []
+    assert GemmPoint("nope", 1, 8, 8).problems() == ["unknown workload 'nope'"]
+    shapes = json.load(open(os.path.join(ROOT, "configs", "shapes.json")))
+    pts = load_points(shapes, (1, 2, 4, 8))
+    assert len(pts) == 4 * sum(len(s["workloads"]) for s in shapes["shapes"])
+    assert any(p.workload == "reduce_scatter" and p.world == 8 and not p.problems() for p in pts)

@@ -460,9 +460,14 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
     const bool pulls = (p.mode == kEpiOneShot || p.mode == kEpiTwoShot);
     const bool push_all =
         ((p.mode == kEpiStore || p.mode == kEpiReduce) && p.store_all && W > 1) || (pulls && p.push_partials && W > 1);
-    // Pushes into a peer's output wait for the peer to enter the call; inbox slots alternate by call parity and need
-    // no such guard; two-shot result pushes are made (and guarded) by the reducer warps.
-    const bool need_entry = W > 1 && push_all && !pulls;
+    // Nothing of this call is pushed or published before every peer has entered the call (finished the previous one).
+    // For pushes into a peer's output that keeps the previous result intact until the peer is done with it.  For the
+    // one-/two-shot and reduce-scatter partials (whose buffers alternate by call parity) it keeps the per-tile flags
+    // exact: they are cumulative counters over all sources, and a rank one call ahead could otherwise raise a flag to
+    // this call's target while a slow rank's partial of this call is still missing.  The entry flags are written at
+    // kernel start and the first publish comes a whole main loop later, so the wait is normally already satisfied.
+    // Two-shot result pushes are made (and guarded the same way) by the reducer warps.
+    const bool need_entry = W > 1 && (push_all || pulls);
     int acc = 0;
     uint32_t acc_phase = 0;
     int ebuf = 0;

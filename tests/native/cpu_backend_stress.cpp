@@ -246,6 +246,65 @@ int main() {
     CHECK(failures.load() == 0, "inbox protocol: %d rank(s) saw a wrong sum or a time-out", failures.load());
   }
 
+  // ---- 7. the all-scatter protocol: pushes into every rank's OUTPUT, entry handshake, arrival counter ----
+  // Outputs are not double-buffered: the consumer of call c's output (here: the check) runs between the calls, and
+  // a peer's pushes of call c + 1 must not land before it has finished.  The entry flag (written when a rank starts a
+  // call, i.e. after it has consumed the previous output) is what the pushers wait for; the arrival counter tells a
+  // rank that all pushes of the call have landed in its own output.
+  {
+    constexpr int W = 4, kCalls = 40, kCols = 64;  // output row per rank: W column blocks of kCols ints
+    constexpr uint64_t kRankBytes = 128 + (uint64_t)W * kCols * 4;
+    uint8_t* region = sym(1, kA);
+    memset(region, 0, W * kRankBytes);
+    uint64_t hbw[W];
+    for (int r = 0; r < W; ++r) hbw[r] = (uint64_t)(region + r * kRankBytes);
+    std::atomic<int> failures{0};
+    auto body = [&](int rank) {
+      unsigned seed = 99u + 31u * rank;
+      auto nap = [&]() {
+        seed = seed * 1664525u + 1013904223u;
+        if ((seed >> 28) < 5) std::this_thread::sleep_for(std::chrono::microseconds((seed >> 20) & 63));
+      };
+      uint32_t* done = reinterpret_cast<uint32_t*>(hbw[rank]);       // [0] arrival counter
+      uint32_t* entry = done + 8;                                      // [8 + q] entry flag of rank q
+      int32_t* out = reinterpret_cast<int32_t*>(hbw[rank] + 128);
+      for (int call = 1; call <= kCalls; ++call) {
+        for (int i = 0; i < W; ++i) signal_set(entry + rank, (uint32_t)call, rank, (rank + 1 + i) % W, hbw);
+        nap();
+        for (int q = 0; q < W; ++q) {
+          StatusBlock st{};
+          if (wait_until_ge(entry + q, (uint32_t)call, 1ull << 27, &st, 7, rank, q) != kOk) {
+            ++failures;
+            return;
+          }
+        }
+        for (int i = 0; i < W; ++i) {  // this rank's column block into every rank's output
+          const int dst = (rank + 1 + i) % W;
+          int32_t* blk = translate(out, rank, dst, hbw) + rank * kCols;
+          for (int e = 0; e < kCols; ++e) blk[e] = call * 100 + rank;
+          nap();
+        }
+        for (int i = 0; i < W; ++i) signal_add(done, 1u, rank, (rank + 1 + i) % W, hbw);
+        StatusBlock st{};
+        if (wait_until_ge(done, (uint32_t)(W * call), 1ull << 27, &st, 8, rank, call) != kOk) {
+          ++failures;
+          return;
+        }
+        nap();  // "kernel end"; the host now reads the output
+        for (int q = 0; q < W; ++q)
+          for (int e = 0; e < kCols; ++e)
+            if (out[q * kCols + e] != call * 100 + q) {
+              ++failures;
+              return;
+            }
+      }
+    };
+    std::vector<std::thread> ranks;
+    for (int r = 0; r < W; ++r) ranks.emplace_back(body, r);
+    for (auto& t : ranks) t.join();
+    CHECK(failures.load() == 0, "all-scatter protocol: %d rank(s) saw a wrong block or a time-out", failures.load());
+  }
+
   for (int r = 0; r < kWorld; ++r) {
     CHECK(iris_cpu_heap_unmap(base[r], kHeap) == 0, "unmap");
     CHECK(iris_cpu_heap_unlink(name[r]) == 0, "unlink");

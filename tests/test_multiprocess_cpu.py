@@ -79,6 +79,19 @@ def test_debug_heap_reports_an_overrun_by_a_peer():
     assert "overwritten on rank(s) [1]" in outs[0], outs[0]
 
 
+def test_a_rank_that_dies_is_noticed_at_the_next_barrier():
+    code, outs = run_ranks(3, [os.path.join(W, "cpu_faults.py"), "rank_dies"], timeout_s=60)
+    assert code != 0                    # the launcher reports the dead rank's exit code and stops the other ranks
+    assert "peer loss detected" in outs[0], outs      # rank 0 (root of the monitored barrier) had time to notice
+
+
+def test_heap_exhaustion_is_symmetric():
+    code, outs = run_ranks(2, [os.path.join(W, "cpu_faults.py"), "heap_exhaustion"])
+    _ok(code, outs)
+    offs = {o.strip().split()[-1] for o in outs}
+    assert len(offs) == 1 and all("MemoryError" in o for o in outs), outs
+
+
 def test_flag_never_set_returns_status():
     code, outs = run_ranks(2, [os.path.join(W, "cpu_faults.py"), "flag_never_set"])
     _ok(code, outs)

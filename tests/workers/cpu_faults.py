@@ -62,6 +62,31 @@ def main():
             print(f"rank {rank}: BootstrapError after {time.time() - t0:.1f}s")
             return 0
         return 1
+    if scenario == "rank_dies":
+        # rank 1 dies (no clean-up, no goodbye) after the first step; the others learn of it at their next barrier
+        ctx.barrier()
+        if rank == 1:
+            os._exit(17)
+        t0 = time.time()
+        try:
+            ctx.barrier(timeout_s=3.0)
+        except BootstrapError:
+            print(f"rank {rank}: peer loss detected after {time.time() - t0:.1f}s")
+            return 0
+        return 1
+    if scenario == "heap_exhaustion":
+        # the same allocation fails on every rank, with MemoryError and without moving the heap top
+        big = ctx.zeros(200_000, dtype=torch.float32)
+        top = ctx.mark()
+        try:
+            ctx.zeros(100_000, dtype=torch.float32)
+        except MemoryError as e:
+            assert ctx.mark() == top and str(e) == "Heap out of memory"
+            small = ctx.zeros(1000, dtype=torch.float32)   # what still fits is still served, symmetrically
+            ctx.barrier()
+            print(f"rank {rank}: MemoryError, then {small.numel()} elements at offset {ctx.offset_of(small)}")
+            return 0
+        return 1
     if scenario == "flag_never_set":
         # consumer waits on a flag nothing sets: bounded wait returns a time-out status, recorded in the block
         flag = ctx.zeros(1, dtype=torch.int32)

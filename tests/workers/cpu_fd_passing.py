@@ -30,15 +30,19 @@ def main():
         tag = ctypes.c_int(-1)
         fd = rt.iris_rt_fd_recv(sock, 10000, ctypes.byref(tag))
         assert fd >= 0, rt.iris_rt_last_error()
-        with os.fdopen(fd, "rb") as g:     # the received descriptor shares the sender's open file
-            g.seek(0)
-            got[tag.value] = g.read().decode()
+        # the received descriptor shares the sender's open file (and its offset, also with the other receivers):
+        # read by position
+        got[tag.value] = os.pread(fd, 100, 0).decode()
+        os.close(fd)
     rt.iris_rt_fd_close(sock)
     assert got == {p: f"hello from {p}" for p in range(world) if p != rank}, got
     # nothing arrives any more: the receive must time out, not block
     sock2 = rt.iris_rt_fd_listen(f"iris_b200_test_{token}_late_{rank}".encode())
     assert rt.iris_rt_fd_recv(sock2, 300, None) < 0
     rt.iris_rt_fd_close(sock2)
+    # a peer that never opened its socket: the send is refused with an error code, nothing blocks
+    assert rt.iris_rt_fd_send(f"iris_b200_test_{token}_nobody".encode(), f.fileno(), rank) != 0
+    assert rt.iris_rt_last_error()
     comm.barrier()
     comm.shutdown()
     print(f"rank {rank}: OK")

@@ -5,6 +5,7 @@
   remote atomic add (fp32) and exchange (int32);
 * GEMM + all-scatter on A[8192, 4096] x B[4096, 14336];
 * GEMM + all-reduce (atomic, one-shot, two-shot) on K = 11008, N = 4096 for M in {1, 128, 1024, 8192};
+* GEMM + reduce-scatter on M = 16384, N = 4096, K in {4096, 11008} (the decoder's row-parallel projections);
 
 each fused kernel next to cuBLAS + NCCL on the same operands, device-timed, maximum over ranks, with the roofline
 fraction.  Writes one JSON document (rank 0).  The reference spreads these over separate scripts and SLURM jobs
@@ -154,6 +155,33 @@ def main():
                     op.close()
                     ctx.reset(base)
                 del A, c_part
+        # the row-parallel projections of the decoder stack as GEMM + reduce-scatter: 16384 tokens, N = 4096
+        m, n = 16384, 4096
+        for k in (4096, 11008):
+            if k % world or (k // world) % 8 or m % (world * 256):
+                continue
+            ks = k // world
+            gen = torch.Generator(device=dev).manual_seed(5)
+            A = (torch.randn((m, k), generator=gen, device=dev) * 0.02).to(torch.bfloat16)
+            Bt = (torch.randn((n, k), generator=gen, device=dev) * 0.02).to(torch.bfloat16)
+            al, bl = A[:, rank * ks:(rank + 1) * ks], Bt[:, rank * ks:(rank + 1) * ks]
+            c_part = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+            c_kept = torch.empty((m // world, n), dtype=torch.bfloat16, device=dev)
+
+            def unfused_rs():
+                torch.matmul(al, bl.t(), out=c_part)
+                if world > 1:
+                    dist.reduce_scatter_tensor(c_kept, c_part)
+            op = G.gemm_reduce_scatter(ctx, [al], [bl])
+            bench_pair({"workload": "reduce_scatter", "m": m, "n": n, "k": k}, op, unfused_rs, 2.0 * m * n * k,
+                       roofline.all_reduce_roofline_us(m, n, k, world, peaks, "reduce_scatter"))
+            r0 = rank * (m // world)
+            ref = A[r0:r0 + 128].float() @ Bt.float().t()
+            err = (op.out[0][:128].float() - ref).abs().max().item()
+            assert err <= (2 + world) * 2 ** -8 * ref.abs().max().item() + 1e-3, f"reduce_scatter k={k}: err {err}"
+            op.close()
+            del A, Bt, c_part, c_kept
+            ctx.reset(base)
     if rank == 0 and args.out:
         os.makedirs(os.path.dirname(args.out) or ".", exist_ok=True)
         with open(args.out, "w") as f:

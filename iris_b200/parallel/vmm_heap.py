@@ -31,18 +31,27 @@ class VmmHeap:
         self._handles: List[int] = []
         self._mc_handle = 0
         self._mc_va = 0
+        self._mc_bound = False
         self._device = 0
         self._mapped: List[int] = []
+
+    def release_multicast(self) -> None:
+        """Undo whatever part of the multicast set-up exists (also the way back to plain peer access when a step of
+        the set-up failed on some rank)."""
+        rt = _native.runtime()
+        if self._mc_va:
+            rt.iris_rt_vmm_unmap(self._mc_va, self.stride)
+            rt.iris_rt_vmm_address_free(self._mc_va, self.stride)
+        if self._mc_handle:
+            if self._mc_bound:
+                rt.iris_rt_multicast_unbind(self._mc_handle, self._device, self.stride)
+            rt.iris_rt_vmm_release(self._mc_handle)
+        self._mc_va, self._mc_handle, self._mc_bound, self.mc_ptr = 0, 0, False, 0
 
     def close(self) -> None:
         rt = _native.runtime()
         try:
-            if self._mc_va:
-                rt.iris_rt_vmm_unmap(self._mc_va, self.stride)
-                rt.iris_rt_vmm_address_free(self._mc_va, self.stride)
-            if self._mc_handle:
-                rt.iris_rt_multicast_unbind(self._mc_handle, self._device, self.stride)
-                rt.iris_rt_vmm_release(self._mc_handle)
+            self.release_multicast()
             for va in self._mapped:
                 rt.iris_rt_vmm_unmap(va, self.stride)
             for h in self._handles:
@@ -50,7 +59,7 @@ class VmmHeap:
             if self._va:
                 rt.iris_rt_vmm_address_free(self._va, self._va_bytes)
         finally:
-            self._mapped, self._handles, self._va, self._mc_va, self._mc_handle = [], [], 0, 0, 0
+            self._mapped, self._handles, self._va = [], [], 0
 
 
 def _exchange_fds(ctx, token: str, own_fd: int, what: str) -> List[int]:
@@ -128,42 +137,66 @@ def create(ctx) -> VmmHeap:
     if want_mc:
         try:
             _bind_multicast(ctx, h, token, handle.value)
-        except RuntimeError as e:  # NVLS is an optimisation: fall back to plain peer access
+        except RuntimeError as e:  # NVLS is an optimisation: every rank falls back to plain peer access
             ctx.log(f"NVLS multicast not available: {e}")
-            h.mc_ptr = 0
+            h.release_multicast()
     ctx.comm.barrier()
     return h
 
 
+def _agree(ctx, error: str, what: str) -> None:
+    """Collective verdict on one step of the set-up: every rank contributes its error text (empty: fine) and all
+    ranks raise together when any failed, so that no rank is left with a binding the others do not have."""
+    got = ctx.comm.allgather_bytes(error.encode()[:240])
+    bad = {r: b.decode(errors="replace") for r, b in enumerate(got) if b}
+    if bad:
+        first = sorted(bad)[0]
+        raise RuntimeError(f"{what} failed on rank(s) {sorted(bad)}: {bad[first]}")
+
+
+def _err(rt, rc: int) -> str:
+    return "" if rc == 0 else (rt.iris_rt_last_error().decode() or f"error {rc}")
+
+
 def _bind_multicast(ctx, h: VmmHeap, token: str, mem_handle: int) -> None:
+    """Create the multicast object on rank 0, hand it to every rank, add every device, bind every heap and map the
+    object.  Each step is followed by a collective verdict (which also serves as the barrier the driver API asks for
+    between the steps): on any failure every rank raises, and the caller falls back to plain peer access everywhere."""
     rt = _native.runtime()
     rank, world, dev = ctx.cur_rank, ctx.num_ranks, ctx.gpu_id
     mc, fd = ctypes.c_uint64(0), ctypes.c_int(-1)
-    ok = 1
+    err = ""
     if rank == 0:
-        ok = 1 if rt.iris_rt_multicast_create(world, h.stride, ctypes.byref(mc), ctypes.byref(fd)) == 0 else 0
-    ok = ctx.comm.broadcast_object(ok, 0)
-    if not ok:
-        raise RuntimeError("cuMulticastCreate failed: " + rt.iris_rt_last_error().decode())
+        err = _err(rt, rt.iris_rt_multicast_create(world, h.stride, ctypes.byref(mc), ctypes.byref(fd)))
+    _agree(ctx, err, "cuMulticastCreate")
     # rank 0 hands its descriptor to everyone; the others contribute a dummy (their heap fd is closed already)
     dummy = os.open("/dev/null", os.O_RDONLY)
-    fds = _exchange_fds(ctx, token, fd.value if rank == 0 else dummy, "mc")
-    os.close(dummy)
+    try:
+        fds = _exchange_fds(ctx, token, fd.value if rank == 0 else dummy, "mc")
+    finally:
+        os.close(dummy)
+    err = ""
     if rank != 0:
-        _native.rt_check(rt.iris_rt_vmm_import(fds[0], ctypes.byref(mc)), "import multicast object")
+        err = _err(rt, rt.iris_rt_vmm_import(fds[0], ctypes.byref(mc)))
     for r, f in enumerate(fds):
         if f >= 0 and r != rank:
             rt.iris_rt_fd_close(f)
     if rank == 0:
         rt.iris_rt_fd_close(fd.value)
-    h._mc_handle = mc.value
-    _native.rt_check(rt.iris_rt_multicast_add_device(mc.value, dev), "cuMulticastAddDevice")
-    ctx.comm.barrier()  # every device has joined before anyone binds memory
-    _native.rt_check(rt.iris_rt_multicast_bind(mc.value, mem_handle, h.stride), "cuMulticastBindMem")
-    ctx.comm.barrier()
+    if not err:
+        h._mc_handle = mc.value
+        err = _err(rt, rt.iris_rt_multicast_add_device(mc.value, dev))
+    _agree(ctx, err, "import / cuMulticastAddDevice")   # every device has joined before anyone binds memory
+    err = _err(rt, rt.iris_rt_multicast_bind(mc.value, mem_handle, h.stride))
+    h._mc_bound = not err     # a rank whose bind worked must unbind when another rank's did not
+    _agree(ctx, err, "cuMulticastBindMem")
     va = ctypes.c_uint64()
-    _native.rt_check(rt.iris_rt_vmm_reserve(h.stride, h.stride if h.stride < (1 << 30) else (1 << 21), ctypes.byref(va)),
-                     "reserve multicast VA")
-    _native.rt_check(rt.iris_rt_vmm_map(va.value, h.stride, mc.value, dev), "map multicast object")
-    h._mc_va = va.value
-    h.mc_ptr = va.value
+    err = _err(rt, rt.iris_rt_vmm_reserve(h.stride, h.stride if h.stride < (1 << 30) else (1 << 21), ctypes.byref(va)))
+    if not err:
+        err = _err(rt, rt.iris_rt_vmm_map(va.value, h.stride, mc.value, dev))
+        if err:
+            rt.iris_rt_vmm_address_free(va.value, h.stride)
+        else:
+            h._mc_va = va.value
+    _agree(ctx, err, "map multicast object")
+    h.mc_ptr = h._mc_va

@@ -20,7 +20,7 @@ import ctypes
 import math
 import os
 import uuid
-from typing import List, Optional, Sequence
+from typing import List, Optional
 
 import numpy as np
 import torch

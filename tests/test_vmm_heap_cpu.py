@@ -2,7 +2,6 @@
 of the native runtime, with the ranks as threads: the order of driver calls, the contiguous mapping, and that a step
 failing on ONE rank makes EVERY rank fall back to plain peer access and release what it had created.  The real calls
 run in tests/test_gpu_multi.py::test_vmm_heap on two or more GPUs."""
-import ctypes
 import threading
 from types import SimpleNamespace
 

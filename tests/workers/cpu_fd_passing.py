@@ -5,8 +5,6 @@ import os
 import sys
 import tempfile
 
-import torch.distributed as dist
-
 from iris_b200 import _native
 from iris_b200.parallel import bootstrap
 

@@ -7,7 +7,7 @@ import sys
 import torch
 
 import iris_b200 as iris
-from iris_b200.ops import nvls, p2p
+from iris_b200.ops import nvls
 
 
 def main():

@@ -23,11 +23,9 @@ import torch
 
 from .. import _native
 from ..context import Iris
+from .gemm_plan import BK, BM, BN, FLAG_HEADER, MODES, GemmPlan, plan_gemm  # noqa: F401  (re-exported)
 
 MAX_RANKS = 8
-BM, BN, BK = 128, 256, 64
-MODES = {"store": 0, "reduce": 1, "one_shot": 2, "two_shot": 3}
-FLAG_HEADER = 16  # [0] arrival counter, [8 + r] entry flags
 
 
 class _Desc(ctypes.Structure):
@@ -157,69 +155,17 @@ class FusedGemm:
         self.a, self.bt = a_use, bt
         dev = c0.device
         sms = torch.cuda.get_device_properties(dev).multi_processor_count
-        # CTA pairs (256 x 256 tiles, cta_group::2) for anything taller than one 128-row tile; single CTAs else
-        if cta_group is None:
-            cta_group = 2 if self.M > BM and (not self.ag or (self.M // self.world) % (2 * BM) == 0) else 1
-            if reduce_scatter and self.M % (self.world * 2 * BM) != 0:
-                cta_group = 1
-        if cta_group not in (1, 2):
-            raise ValueError("cta_group must be 1 or 2")
-        self.cta_group = cta_group
-        # reduce-scatter: rank r keeps rows [r * M / world, (r + 1) * M / world) of the sum
-        self.rs_rows = 0
-        if reduce_scatter:
-            if mode != "one_shot":
-                raise ValueError("reduce_scatter=True goes with mode='one_shot'")
-            if self.M % (self.world * BM * cta_group) != 0:
-                raise ValueError(f"reduce-scatter needs M to be a multiple of world x {BM * cta_group}")
-            self.rs_rows = self.M // self.world
-            push, ksplit = True, 1
-            mt = self.rs_rows // (BM * cta_group)     # m-tiles per rank: the raster groups must not straddle ranks
-            group_m = max(g for g in range(1, max(1, int(group_m)) + 1) if mt % g == 0)
-        self.ctas_per_rank = int(ctas_per_rank) if ctas_per_rank else sms // self.num_local
-        self.ctas_per_rank -= self.ctas_per_rank % cta_group
-        tiles_m, tiles_n = -(-self.M // (BM * cta_group)), -(-self.N // BN)
-        self.total_tiles = tiles_m * tiles_n
-        kblocks = -(-self.K // BK)
-        # ---- schedule: whole tiles round-robin, plus (stream-K) a tail of tiles split by k-blocks ----
-        units = max(1, self.ctas_per_rank // cta_group)
-        T = self.total_tiles
-        if stream_k is None:
-            # Off unless asked for: on B200 the fix-up of a split tile (fp32 partials through L2 plus a second
-            # epilogue for the finishing unit) costs more than the ragged last wave it removes, for every shape
-            # measured so far (8192 x 1792 x 4096: 108 us against 101 us); the whole-tile schedule is the default.
-            stream_k = False
-        self.dp_tiles, self.sk_units, sk_tiles = T, 0, 0
-        if stream_k and T % units != 0:
-            sk_tiles = T % units + (units if T >= units else 0)   # the ragged wave plus one full wave
-            sk_tiles = min(sk_tiles, T)
-            self.dp_tiles = T - sk_tiles
-            self.sk_units = max(1, min(units, (sk_tiles * kblocks) // 4))  # at least 4 k-blocks per unit
-        if self.dp_tiles == 0:
-            units = self.sk_units if self.sk_units else min(units, max(T, 1 if not self.ag else 8))
-        elif not self.sk_units:
-            units = min(units, max(T, 1 if not self.ag else 8))
-        self.ctas_per_rank = max(1, units) * cta_group
-        # ---- one-shot for short matrices: partials pushed into every rank's inbox, K cut into pieces ----
-        max_units = max(1, (sms // self.num_local) // cta_group)
-        self.push = bool(push) if push is not None else (mode == "one_shot" and self.M <= 2 * BM)
-        if mode != "one_shot":
-            self.push = False
-        self.ksplit = 1
-        if self.push:
-            if ksplit is None:
-                per_w = max(1, 16 // self.world)            # keep (ranks x pieces) summed per chunk at <= 16
-                ksplit = max(1, min(max_units // max(T, 1), per_w, kblocks // 4))
-            self.ksplit = max(1, int(ksplit))
-            if self.ksplit > 1:
-                self.dp_tiles, self.sk_units, sk_tiles = T, 0, 0
-                self.ctas_per_rank = min(max_units, T * self.ksplit) * cta_group
-        self.store_all = bool(store_all) and self.world > 1
-        pulls = mode in ("one_shot", "two_shot")
-        chunks_per_shard = (self.M // self.world) // BM if self.ag else 0
-        tile_flags = self.total_tiles * cta_group if pulls else 0
-        sk_flags = sk_tiles * cta_group
-        nflags = FLAG_HEADER + tile_flags + self.world * chunks_per_shard + sk_flags
+        # tile shape, persistent grid, schedule, flag count and buffer layout: a pure function of the problem
+        pl = plan_gemm(self.M, self.N, self.K, self.world, self.num_local, mode, sms, ag=self.ag, cta_group=cta_group,
+                       ctas_per_rank=ctas_per_rank, group_m=group_m, stream_k=stream_k, push=push, ksplit=ksplit,
+                       reduce_scatter=reduce_scatter, store_all=store_all, own_out=out is not None)
+        self.plan = pl
+        cta_group, group_m = pl.cta_group, pl.group_m
+        self.cta_group, self.rs_rows, self.ctas_per_rank = pl.cta_group, pl.rs_rows, pl.ctas_per_rank
+        self.total_tiles, self.dp_tiles, self.sk_units = pl.total_tiles, pl.dp_tiles, pl.sk_units
+        self.push, self.ksplit, self.store_all = pl.push, pl.ksplit, pl.store_all
+        sk_tiles, pulls, chunks_per_shard, tile_flags, nflags = (pl.sk_tiles, pl.pulls, pl.chunks_per_shard,
+                                                                 pl.tile_flags, pl.nflags)
         # ---- symmetric allocations (identical sequence on every rank) ----
         self.flags = [c.zeros(nflags, dtype=torch.int32) for c in self.ctxs]
         self.trace = [c.zeros((self.total_tiles * cta_group, 8), dtype=torch.int64) for c in self.ctxs] if trace else None
@@ -230,18 +176,14 @@ class FusedGemm:
             # One matrix per rank holds both partial buffers (call parity) and, unless the caller brings its own,
             # the output: [partial 0 | partial 1 | out], each padded to whole 256-row tiles, so that one tensor
             # map per rank serves partial stores, partial loads and output stores.
-            rows = self.rs_rows if self.rs_rows else self.M    # rows of a slot and of the output
-            mp = -(-rows // (2 * BM)) * (2 * BM)
-            slots = self.world * self.ksplit if self.push else 1   # inbox slots per parity
-            regions = 2 * slots + (0 if out is not None else 1)
+            rows, mp, slots, regions = pl.rows, pl.slot_rows, pl.slots, pl.regions
             self._pull_buf = [c.zeros((regions * mp, self.N), dtype=torch.bfloat16) for c in self.ctxs]
             self.partial = [[b[q * slots * mp:q * slots * mp + rows] for b in self._pull_buf] for q in range(2)]
             self.out = list(out) if out is not None else [b[2 * slots * mp:2 * slots * mp + rows]
                                                           for b in self._pull_buf]
             c_bufs, c2_bufs = self._pull_buf, None
             ldc, c_cols_eff = self.N, self.N
-            c_rows, part_row0 = regions * mp, (0, slots * mp)
-            out_row0 = 2 * slots * mp if out is None else -1
+            c_rows, part_row0, out_row0 = pl.c_rows, pl.part_row0, pl.out_row0
             self._slot_rows = mp
         else:
             self.out = list(out) if out is not None else [c.zeros((self.M, self.c_cols), dtype=torch.bfloat16)

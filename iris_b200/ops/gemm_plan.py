@@ -1,0 +1,145 @@
+"""Schedule and buffer layout of one fused GEMM + collective, as a pure function of the problem: no device, no
+allocation.  ``FusedGemm`` builds its kernel descriptor from the result; tests exercise it on a machine without a GPU.
+
+Role in the reference: the Stream-K bookkeeping of ``examples/07_gemm_all_scatter/matmul_wrapper.py:63-103`` (tiles,
+full waves, split tiles) and the buffer set-up of ``examples/09_gemm_one_shot_all_reduce/benchmark.py:103-142``.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+BM, BN, BK = 128, 256, 64   # the compiled tile of the kernel (rows per CTA, columns, k-block)
+MODES = {"store": 0, "reduce": 1, "one_shot": 2, "two_shot": 3}
+FLAG_HEADER = 16            # flag words [0] arrival counter, [8 + r] entry flag of rank r; per-tile flags follow
+
+
+@dataclass(frozen=True)
+class GemmPlan:
+    M: int
+    N: int
+    K: int
+    world: int
+    num_local: int
+    mode: str
+    ag: bool
+    cta_group: int          # 1: one CTA per 128 x 256 tile; 2: a CTA pair per 256 x 256 tile
+    group_m: int            # raster: m-tiles per group
+    rs_rows: int            # reduce-scatter: rows kept per rank (0: off)
+    ctas_per_rank: int      # CTAs asked for (the native plan may lower it to what is resident at once)
+    total_tiles: int
+    kblocks: int
+    dp_tiles: int           # tiles computed whole; the rest is split by k-blocks (stream-K)
+    sk_units: int
+    sk_tiles: int
+    push: bool              # one-shot: partials pushed into inbox slots
+    ksplit: int             # pieces of K computed by different CTAs (push only)
+    store_all: bool
+    pulls: bool             # one-/two-shot family: partial buffers, per-tile flags, reducer warps
+    chunks_per_shard: int   # all-gather prologue: 128-row chunks per rank
+    tile_flags: int
+    sk_flags: int
+    nflags: int
+    # layout of the [partials | out] matrix of the one-/two-shot family (rows; 0 / -1 when unused)
+    rows: int               # rows of one slot and of the output
+    slot_rows: int          # the same, padded to whole 256-row tiles
+    slots: int              # inbox slots per parity
+    regions: int
+    c_rows: int
+    part_row0: Tuple[int, int]
+    out_row0: int
+
+    @property
+    def flags_per_call(self) -> int:
+        """What one call adds to a per-tile flag (arrivals from all ranks and pieces)."""
+        return self.world * self.ksplit
+
+
+def plan_gemm(M: int, N: int, K: int, world: int, num_local: int, mode: str, sms: int, *, ag: bool = False,
+              cta_group: Optional[int] = None, ctas_per_rank: Optional[int] = None, group_m: int = 8,
+              stream_k: Optional[bool] = None, push: Optional[bool] = None, ksplit: Optional[int] = None,
+              reduce_scatter: bool = False, store_all: bool = False, own_out: bool = False) -> GemmPlan:
+    """Decide tile shape, persistent grid, schedule, flag count and buffer layout.  ``sms``: SMs of the device;
+    ``own_out``: the caller brings the output buffer (the [partials | out] matrix then has no output region)."""
+    if mode not in MODES:
+        raise ValueError(f"mode must be one of {sorted(MODES)}")
+    if mode in ("one_shot", "two_shot") and ag:
+        raise ValueError("the all-gather prologue is combined with mode='store' only")
+    # CTA pairs (256 x 256 tiles, cta_group::2) for anything taller than one 128-row tile; single CTAs else
+    if cta_group is None:
+        cta_group = 2 if M > BM and (not ag or (M // world) % (2 * BM) == 0) else 1
+        if reduce_scatter and M % (world * 2 * BM) != 0:
+            cta_group = 1
+    if cta_group not in (1, 2):
+        raise ValueError("cta_group must be 1 or 2")
+    # reduce-scatter: rank r keeps rows [r * M / world, (r + 1) * M / world) of the sum
+    rs_rows = 0
+    if reduce_scatter:
+        if mode != "one_shot":
+            raise ValueError("reduce_scatter=True goes with mode='one_shot'")
+        if M % (world * BM * cta_group) != 0:
+            raise ValueError(f"reduce-scatter needs M to be a multiple of world x {BM * cta_group}")
+        rs_rows = M // world
+        push, ksplit = True, 1
+        mt = rs_rows // (BM * cta_group)     # m-tiles per rank: the raster groups must not straddle ranks
+        group_m = max(g for g in range(1, max(1, int(group_m)) + 1) if mt % g == 0)
+    ctas = int(ctas_per_rank) if ctas_per_rank else sms // num_local
+    ctas -= ctas % cta_group
+    tiles_m, tiles_n = -(-M // (BM * cta_group)), -(-N // BN)
+    T = tiles_m * tiles_n
+    kblocks = -(-K // BK)
+    # ---- schedule: whole tiles round-robin, plus (stream-K) a tail of tiles split by k-blocks ----
+    units = max(1, ctas // cta_group)
+    if stream_k is None:
+        # Off unless asked for: on B200 the fix-up of a split tile (fp32 partials through L2 plus a second
+        # epilogue for the finishing unit) costs more than the ragged last wave it removes, for every shape
+        # measured so far (8192 x 1792 x 4096: 108 us against 101 us); the whole-tile schedule is the default.
+        stream_k = False
+    dp_tiles, sk_units, sk_tiles = T, 0, 0
+    if stream_k and T % units != 0:
+        sk_tiles = T % units + (units if T >= units else 0)   # the ragged wave plus one full wave
+        sk_tiles = min(sk_tiles, T)
+        dp_tiles = T - sk_tiles
+        sk_units = max(1, min(units, (sk_tiles * kblocks) // 4))  # at least 4 k-blocks per unit
+    if dp_tiles == 0:
+        units = sk_units if sk_units else min(units, max(T, 1 if not ag else 8))
+    elif not sk_units:
+        units = min(units, max(T, 1 if not ag else 8))
+    ctas = max(1, units) * cta_group
+    # ---- one-shot for short matrices: partials pushed into every rank's inbox, K cut into pieces ----
+    max_units = max(1, (sms // num_local) // cta_group)
+    do_push = bool(push) if push is not None else (mode == "one_shot" and M <= 2 * BM)
+    if mode != "one_shot":
+        do_push = False
+    ks = 1
+    if do_push:
+        if ksplit is None:
+            per_w = max(1, 16 // world)            # keep (ranks x pieces) summed per chunk at <= 16
+            ksplit = max(1, min(max_units // max(T, 1), per_w, kblocks // 4))
+        ks = max(1, int(ksplit))
+        if ks > 1:
+            dp_tiles, sk_units, sk_tiles = T, 0, 0
+            ctas = min(max_units, T * ks) * cta_group
+    pulls = mode in ("one_shot", "two_shot")
+    chunks_per_shard = (M // world) // BM if ag else 0
+    tile_flags = T * cta_group if pulls else 0
+    sk_flags = sk_tiles * cta_group
+    nflags = FLAG_HEADER + tile_flags + world * chunks_per_shard + sk_flags
+    if pulls:
+        # One matrix per rank holds both partial buffers (call parity) and, unless the caller brings its own, the
+        # output: [partial 0 | partial 1 | out], each padded to whole 256-row tiles, so that one tensor map per rank
+        # serves partial stores, partial loads and output stores.
+        rows = rs_rows if rs_rows else M
+        mp = -(-rows // (2 * BM)) * (2 * BM)
+        slots = world * ks if do_push else 1
+        regions = 2 * slots + (0 if own_out else 1)
+        c_rows, part_row0 = regions * mp, (0, slots * mp)
+        out_row0 = -1 if own_out else 2 * slots * mp
+    else:
+        rows, mp, slots, regions, c_rows, part_row0, out_row0 = M, 0, 0, 0, 0, (0, 0), -1
+    return GemmPlan(M=M, N=N, K=K, world=world, num_local=num_local, mode=mode, ag=bool(ag), cta_group=cta_group,
+                    group_m=int(group_m), rs_rows=rs_rows, ctas_per_rank=ctas, total_tiles=T, kblocks=kblocks,
+                    dp_tiles=dp_tiles, sk_units=sk_units, sk_tiles=sk_tiles, push=do_push, ksplit=ks,
+                    store_all=bool(store_all) and world > 1, pulls=pulls, chunks_per_shard=chunks_per_shard,
+                    tile_flags=tile_flags, sk_flags=sk_flags, nflags=nflags, rows=rows, slot_rows=mp, slots=slots,
+                    regions=regions, c_rows=c_rows, part_row0=part_row0, out_row0=out_row0)

@@ -28,7 +28,8 @@ NVCC = str(CUDA_HOME / "bin" / "nvcc")
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-std=c++17", "-O3", "-lineinfo", "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC",
               "-Xcompiler", "-Wall", "-I", str(INCLUDE), "-I", str(CSRC)] + ARCH_FLAGS
-CXX_FLAGS = ["-std=c++17", "-O2", "-fPIC", "-Wall", "-Wextra", "-I", str(INCLUDE), "-I", str(CSRC)]
+# host libraries build warning-free; the reference builds its allocator the same way (csrc/finegrained_alloc/build.sh:5-15)
+CXX_FLAGS = ["-std=c++17", "-O2", "-fPIC", "-Wall", "-Wextra", "-Werror", "-I", str(INCLUDE), "-I", str(CSRC)]
 
 
 def _newer(target: Path, sources) -> bool:

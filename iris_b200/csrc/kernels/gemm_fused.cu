@@ -148,64 +148,6 @@ __device__ __noinline__ void rs_sum_part(const uint8_t* inbox, uint8_t* outp, ui
   }
 }
 
-// One piece of work of a scheduling unit: k-blocks [kb0, kb1) of `tile`.
-struct Work {
-  int tile, kb0, kb1;
-  int piece;  // K-split piece of the tile (0 when tiles are not K-split into slots)
-};
-
-// Persistent + stream-K schedule.  Tiles [0, dp_tiles) are taken whole, round-robin over the units (the reference's
-// `for tile_id in range(pid, total_tiles, NUM_SMS)`, examples/07_gemm_all_scatter/gemm_all_scatter.py:153).  The
-// remaining tiles form one long sequence of (tile, k-block) iterations that is cut into `sk_units` equal ranges —
-// the stream-K decomposition the reference only sketches (matmul_wrapper.py:73-103 computes its statistics, the
-// kernels never use them).  A unit's range may end in the middle of a tile; such a tile is finished by whichever
-// unit adds the last missing k-blocks (see the epilogue).
-struct WorkIter {
-  int G, dp_tiles, kblocks, next_dp, ksplit, items;
-  long long it, end;
-  __device__ WorkIter(int unit, int G_, int total_tiles, int kblocks_, const FusedGemmParams& p)
-      : G(G_), dp_tiles(p.dp_tiles), kblocks(kblocks_), next_dp(unit), ksplit(p.ksplit > 1 ? p.ksplit : 1),
-        items(total_tiles * (p.ksplit > 1 ? p.ksplit : 1)), it(0), end(0) {
-    const long long S = (long long)(total_tiles - p.dp_tiles) * kblocks_;
-    if (S > 0 && unit < p.sk_units) {
-      it = S * unit / p.sk_units;
-      end = S * (unit + 1) / p.sk_units;
-    }
-  }
-  __device__ bool next(Work& w) {
-    w.piece = 0;
-    if (ksplit > 1) {
-      // K-split into inbox slots: item i = (tile i / ksplit, piece i % ksplit), each a fixed slice of the k-blocks
-      if (next_dp >= items) return false;
-      w.tile = next_dp / ksplit;
-      w.piece = next_dp - w.tile * ksplit;
-      w.kb0 = (int)((long long)kblocks * w.piece / ksplit);
-      w.kb1 = (int)((long long)kblocks * (w.piece + 1) / ksplit);
-      next_dp += G;
-      return true;
-    }
-    if (next_dp < dp_tiles) {
-      w.tile = next_dp;
-      w.kb0 = 0;
-      w.kb1 = kblocks;
-      next_dp += G;
-      return true;
-    }
-    if (it < end) {
-      const int t = (int)(it / kblocks);
-      const int kb0 = (int)(it - (long long)t * kblocks);
-      const long long left = end - it;
-      const int len = (int)((long long)(kblocks - kb0) < left ? (kblocks - kb0) : left);
-      w.tile = dp_tiles + t;
-      w.kb0 = kb0;
-      w.kb1 = kb0 + len;
-      it += len;
-      return true;
-    }
-    return false;
-  }
-};
-
 __device__ __forceinline__ void red_add_v4_f32_gpu(float* p, float a, float b, float c, float d) {
   asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d)
                : "memory");
@@ -334,7 +276,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      WorkIter sched(unit, G, total_tiles, kblocks, p);
+      WorkIter sched(unit, G, total_tiles, kblocks, p.dp_tiles, p.sk_units, p.ksplit);
       Work w;
       while (ok && sched.next(w)) {
         const int tile = tile_of(w.tile);
@@ -393,7 +335,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      WorkIter sched(unit, G, total_tiles, kblocks, p);
+      WorkIter sched(unit, G, total_tiles, kblocks, p.dp_tiles, p.sk_units, p.ksplit);
       Work w;
       while (ok && sched.next(w)) {
         const int tile = tile_of(w.tile);
@@ -488,7 +430,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
       }
     };
     bool ok_all = true;
-    WorkIter sched(unit, G, total_tiles, kblocks, p);
+    WorkIter sched(unit, G, total_tiles, kblocks, p.dp_tiles, p.sk_units, p.ksplit);
     Work w;
     while (sched.next(w)) {
       const int tile = tile_of(w.tile);
@@ -1192,6 +1134,25 @@ int iris_sched_ag_actual_m(int logical_m, int tiles_per_shard, int rank, int wor
 int iris_sched_two_shot_owner(int tile, int units, int world) { return two_shot_owner(tile, units, world); }
 int iris_sched_rs_tile_of(int step, int rank, int world, int tiles_per_block) {
   return rs_tile_of(step, rank, world, tiles_per_block);
+}
+
+// The pieces of work scheduling unit `unit` of `units` goes through, as (tile, kb0, kb1, piece) quadruples; returns how
+// many there are (at most `max_items` are written).
+int iris_sched_work_list(int unit, int units, int total_tiles, int kblocks, int dp_tiles, int sk_units, int ksplit,
+                         int* out, int max_items) {
+  WorkIter it(unit, units, total_tiles, kblocks, dp_tiles, sk_units, ksplit);
+  Work w;
+  int n = 0;
+  while (it.next(w)) {
+    if (n < max_items) {
+      out[4 * n] = w.tile;
+      out[4 * n + 1] = w.kb0;
+      out[4 * n + 2] = w.kb1;
+      out[4 * n + 3] = w.piece;
+    }
+    ++n;
+  }
+  return n;
 }
 
 const char* iris_gemm_last_error() { return g_err; }

@@ -53,5 +53,64 @@ IRIS_SCHED_HD int rs_tile_of(int step, int rank, int world, int tiles_per_block)
   return ((rank + 1 + step) % world) * tiles_per_block + step / world;
 }
 
+// One piece of work of a scheduling unit: k-blocks [kb0, kb1) of `tile`.
+struct Work {
+  int tile, kb0, kb1;
+  int piece;  // K-split piece of the tile (0 when tiles are not K-split into slots)
+};
+
+// Persistent + stream-K schedule.  Tiles [0, dp_tiles) are taken whole, round-robin over the units (the reference's
+// `for tile_id in range(pid, total_tiles, NUM_SMS)`, examples/07_gemm_all_scatter/gemm_all_scatter.py:153).  The
+// remaining tiles form one long sequence of (tile, k-block) iterations that is cut into `sk_units` equal ranges —
+// the stream-K decomposition the reference only sketches (matmul_wrapper.py:73-103 computes its statistics, the
+// kernels never use them).  A unit's range may end in the middle of a tile; such a tile is finished by whichever
+// unit adds the last missing k-blocks (see the epilogue).  With `ksplit` > 1 every tile is instead cut into `ksplit`
+// fixed slices of its k-blocks and the (tile, piece) items go round-robin over the units.
+struct WorkIter {
+  int G, dp_tiles, kblocks, next_dp, ksplit, items;
+  long long it, end;
+  IRIS_SCHED_HD WorkIter(int unit, int G_, int total_tiles, int kblocks_, int dp_tiles_, int sk_units, int ksplit_)
+      : G(G_), dp_tiles(dp_tiles_), kblocks(kblocks_), next_dp(unit), ksplit(ksplit_ > 1 ? ksplit_ : 1),
+        items(total_tiles * (ksplit_ > 1 ? ksplit_ : 1)), it(0), end(0) {
+    const long long S = (long long)(total_tiles - dp_tiles_) * kblocks_;
+    if (S > 0 && unit < sk_units) {
+      it = S * unit / sk_units;
+      end = S * (unit + 1) / sk_units;
+    }
+  }
+  IRIS_SCHED_HD bool next(Work& w) {
+    w.piece = 0;
+    if (ksplit > 1) {
+      // K-split into inbox slots: item i = (tile i / ksplit, piece i % ksplit), each a fixed slice of the k-blocks
+      if (next_dp >= items) return false;
+      w.tile = next_dp / ksplit;
+      w.piece = next_dp - w.tile * ksplit;
+      w.kb0 = (int)((long long)kblocks * w.piece / ksplit);
+      w.kb1 = (int)((long long)kblocks * (w.piece + 1) / ksplit);
+      next_dp += G;
+      return true;
+    }
+    if (next_dp < dp_tiles) {
+      w.tile = next_dp;
+      w.kb0 = 0;
+      w.kb1 = kblocks;
+      next_dp += G;
+      return true;
+    }
+    if (it < end) {
+      const int t = (int)(it / kblocks);
+      const int kb0 = (int)(it - (long long)t * kblocks);
+      const long long left = end - it;
+      const int len = (int)((long long)(kblocks - kb0) < left ? (kblocks - kb0) : left);
+      w.tile = dp_tiles + t;
+      w.kb0 = kb0;
+      w.kb1 = kb0 + len;
+      it += len;
+      return true;
+    }
+    return false;
+  }
+};
+
 }  // namespace gemm
 }  // namespace iris

@@ -14,6 +14,8 @@ def lib():
     so = ctypes.CDLL(str(_build.build_all()["kernels"]))
     so.iris_sched_raster.argtypes = [ctypes.c_int] * 4 + [ctypes.POINTER(ctypes.c_int)] * 2
     so.iris_sched_raster.restype = None
+    so.iris_sched_work_list.argtypes = [ctypes.c_int] * 7 + [ctypes.POINTER(ctypes.c_int), ctypes.c_int]
+    so.iris_sched_work_list.restype = ctypes.c_int
     for f in (so.iris_sched_ag_actual_m, so.iris_sched_two_shot_owner, so.iris_sched_rs_tile_of):
         f.argtypes = [ctypes.c_int] * (3 if f is so.iris_sched_two_shot_owner else 4)
         f.restype = ctypes.c_int
@@ -79,3 +81,52 @@ def test_reduce_scatter_order(lib, world, tpb):
                 assert per_rank[r].index(b * tpb + j) < (j + 1) * world
     if world > 1:
         assert per_rank[0][0] // tpb == 1 and per_rank[0][world - 1] // tpb == 0   # next rank first, own block last
+
+
+def _work(lib, unit, units, tiles, kblocks, dp_tiles, sk_units, ksplit):
+    cap = 4096
+    buf = (ctypes.c_int * (4 * cap))()
+    n = lib.iris_sched_work_list(unit, units, tiles, kblocks, dp_tiles, sk_units, ksplit, buf, cap)
+    assert n <= cap
+    return [tuple(buf[4 * i:4 * i + 4]) for i in range(n)]
+
+
+@pytest.mark.parametrize("m,n,k,world,mode,kw", [
+    (8192, 1792, 4096, 8, "store", {}),                                  # whole tiles only
+    (8192, 1792, 4096, 8, "store", {"stream_k": True}),                  # ragged last wave split by k-blocks
+    (640, 768, 1376, 2, "one_shot", {"stream_k": True, "cta_group": 1}),
+    (300, 520, 200, 1, "store", {"stream_k": True}),
+    (128, 4096, 1376, 8, "one_shot", {}),                                # pushed, K split into pieces
+    (1, 1024, 5504, 2, "one_shot", {"ksplit": 3}),
+    (100, 4096, 64, 4, "one_shot", {}),                                  # one k-block: no split possible
+])
+def test_every_k_block_of_every_tile_is_computed_exactly_once(lib, m, n, k, world, mode, kw):
+    """Over all scheduling units: whole tiles, stream-K ranges and K-split pieces together cover each (tile, k-block)
+    once; a K-split tile has exactly `ksplit` pieces, which partition its k-blocks in order."""
+    from iris_b200.ops.gemm_plan import plan_gemm
+    p = plan_gemm(m, n, k, world, 1, mode, 148, **kw)
+    units = p.ctas_per_rank // p.cta_group
+    dp = p.dp_tiles if p.sk_units else p.total_tiles       # what FusedGemm hands to the kernel (-1 = all whole)
+    seen = {}
+    pieces = {}
+    for u in range(units):
+        for tile, kb0, kb1, piece in _work(lib, u, units, p.total_tiles, p.kblocks, dp, p.sk_units, p.ksplit):
+            assert 0 <= tile < p.total_tiles and 0 <= kb0 < kb1 <= p.kblocks
+            for kb in range(kb0, kb1):
+                assert (tile, kb) not in seen, f"k-block {kb} of tile {tile} computed by units {seen[(tile, kb)]} and {u}"
+                seen[(tile, kb)] = u
+            pieces.setdefault(tile, []).append((piece, kb0, kb1))
+    assert len(seen) == p.total_tiles * p.kblocks
+    if p.ksplit > 1:
+        for tile, ps in pieces.items():
+            ps.sort()
+            assert [q[0] for q in ps] == list(range(p.ksplit))
+            assert ps[0][1] == 0 and ps[-1][2] == p.kblocks and all(a[2] == b[1] for a, b in zip(ps, ps[1:]))
+    if kw.get("stream_k") and p.sk_units:
+        # stream-K: the units' shares of the split part differ by at most one k-block
+        share = [0] * units
+        for (tile, kb), u in seen.items():
+            if tile >= p.dp_tiles:
+                share[u] += 1
+        used = [x for x in share[:p.sk_units]]
+        assert max(used) - min(used) <= 1 and sum(share[p.sk_units:]) == 0

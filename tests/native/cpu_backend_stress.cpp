@@ -305,6 +305,78 @@ int main() {
     CHECK(failures.load() == 0, "all-scatter protocol: %d rank(s) saw a wrong block or a time-out", failures.load());
   }
 
+  // ---- 8. the two-shot protocol: partials stay home, one owner per tile pulls, sums and pushes the result ----
+  // Partial buffers alternate by call parity; outputs are single.  Per call: entry handshake; every rank stores its
+  // partial of every tile in its OWN memory and raises the tile's flag on the tile's owner; the owner waits for W
+  // arrivals, reads the partial of every rank (remote reads), and writes the sum into the output of EVERY rank; an
+  // arrival counter per rank tells it that all owners have delivered; then the rank consumes its output.  What must
+  // hold: no partial is overwritten while an owner still reads it (two calls later, same parity), and no output is
+  // overwritten while its rank still consumes the previous result.
+  {
+    constexpr int W = 4, kCalls = 30, kTiles = 8, kElems = 48;
+    // per rank: [done counter, entry flags (64 B) | tile flags (64 B) | partial[2][tiles][elems] | out[tiles][elems]]
+    constexpr uint64_t kPartial = 128, kOut = kPartial + 2ull * kTiles * kElems * 4;
+    constexpr uint64_t kRankBytes = kOut + (uint64_t)kTiles * kElems * 4;
+    static_assert(W * kRankBytes <= (64 << 10), "fits the data area B");
+    uint8_t* region = sym(0, kB);
+    memset(region, 0, W * kRankBytes);
+    uint64_t hbw[W];
+    for (int r = 0; r < W; ++r) hbw[r] = (uint64_t)(region + r * kRankBytes);
+    std::atomic<int> failures{0};
+    auto body = [&](int rank) {
+      unsigned seed = 4242u + 13u * rank;
+      auto nap = [&]() {
+        seed = seed * 1664525u + 1013904223u;
+        if ((seed >> 28) < 4) std::this_thread::sleep_for(std::chrono::microseconds((seed >> 20) & 63));
+      };
+      uint32_t* done = reinterpret_cast<uint32_t*>(hbw[rank]);
+      uint32_t* entry = done + 8;
+      uint32_t* tflag = reinterpret_cast<uint32_t*>(hbw[rank] + 64);
+      int32_t* partial = reinterpret_cast<int32_t*>(hbw[rank] + kPartial);
+      int32_t* out = reinterpret_cast<int32_t*>(hbw[rank] + kOut);
+      auto fail = [&]() { ++failures; };
+      for (int call = 1; call <= kCalls; ++call) {
+        const int par = call & 1;
+        for (int i = 0; i < W; ++i) signal_set(entry + rank, (uint32_t)call, rank, (rank + 1 + i) % W, hbw);
+        for (int q = 0; q < W; ++q) {
+          StatusBlock st{};
+          if (wait_until_ge(entry + q, (uint32_t)call, 1ull << 27, &st, 9, rank, q) != kOk) return fail();
+        }
+        for (int t = 0; t < kTiles; ++t) {  // "epilogue": partial tile into own memory, flag on the owner
+          int32_t* mine = partial + (par * kTiles + t) * kElems;
+          for (int e = 0; e < kElems; ++e) mine[e] = call * 1000 + t * 10 + rank;
+          signal_add(tflag + t, 1u, rank, t % W, hbw);
+          nap();
+        }
+        for (int t = rank; t < kTiles; t += W) {  // "reducer": the tiles this rank owns
+          StatusBlock st{};
+          if (wait_until_ge(tflag + t, (uint32_t)(W * call), 1ull << 27, &st, 10, rank, t) != kOk) return fail();
+          int32_t sum[kElems] = {0};
+          for (int q = 0; q < W; ++q) {
+            const int32_t* theirs = translate(partial, rank, q, hbw) + (par * kTiles + t) * kElems;
+            for (int e = 0; e < kElems; ++e) sum[e] += theirs[e];
+          }
+          nap();
+          for (int i = 0; i < W; ++i) {
+            int32_t* dst = translate(out, rank, (rank + 1 + i) % W, hbw) + t * kElems;
+            for (int e = 0; e < kElems; ++e) dst[e] = sum[e];
+          }
+        }
+        for (int i = 0; i < W; ++i) signal_add(done, 1u, rank, (rank + 1 + i) % W, hbw);
+        StatusBlock st{};
+        if (wait_until_ge(done, (uint32_t)(W * call), 1ull << 27, &st, 11, rank, call) != kOk) return fail();
+        nap();  // "kernel end"; the host consumes the output
+        for (int t = 0; t < kTiles; ++t)
+          for (int e = 0; e < kElems; ++e)
+            if (out[t * kElems + e] != W * (call * 1000 + t * 10) + W * (W - 1) / 2) return fail();
+      }
+    };
+    std::vector<std::thread> ranks;
+    for (int r = 0; r < W; ++r) ranks.emplace_back(body, r);
+    for (auto& t : ranks) t.join();
+    CHECK(failures.load() == 0, "two-shot protocol: %d rank(s) saw a wrong sum or a time-out", failures.load());
+  }
+
   for (int r = 0; r < kWorld; ++r) {
     CHECK(iris_cpu_heap_unmap(base[r], kHeap) == 0, "unmap");
     CHECK(iris_cpu_heap_unlink(name[r]) == 0, "unlink");

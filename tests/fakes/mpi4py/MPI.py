@@ -3,8 +3,9 @@ Ibarrier, Split_type} and COMM_TYPE_SHARED."""
 import datetime
 import os
 import pickle
+import tempfile
 
-from torch.distributed import TCPStore
+from torch.distributed import FileStore
 
 COMM_TYPE_SHARED = 1
 
@@ -21,9 +22,11 @@ class _Comm:
     def __init__(self):
         self._rank = int(os.environ.get("RANK", "0"))
         self._size = int(os.environ.get("WORLD_SIZE", "1"))
-        port = int(os.environ.get("MASTER_PORT", "29533")) + 17    # beside, not on, the launcher's rendezvous port
-        self._store = TCPStore(os.environ.get("MASTER_ADDR", "127.0.0.1"), port, self._size, self._rank == 0,
-                               timeout=datetime.timedelta(seconds=60))
+        # a file store named after the launcher (parent process) and its rendezvous port: no second port to collide on
+        path = os.path.join(tempfile.gettempdir(),
+                            f"iris_fake_mpi_{os.getppid()}_{os.environ.get('MASTER_PORT', '0')}")
+        self._store = FileStore(path, self._size)
+        self._store.set_timeout(datetime.timedelta(seconds=60))
         self._seq = 0
 
     def _next(self, what):

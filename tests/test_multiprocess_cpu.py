@@ -23,7 +23,7 @@ def test_cpu_plumbing_two_ranks():
 def test_cpu_plumbing_over_the_mpi_bootstrap(world):
     """``IRIS_BOOTSTRAP=mpi``: the same worker with the control plane on mpi4py's interface (the reference's only
     back end, iris/_mpi_helpers.py:8-51).  mpi4py is not installed here; tests/fakes/mpi4py implements the calls the
-    bootstrap makes over a TCP store, so that its MPI code path runs as real processes."""
+    bootstrap makes over a file store, so that its MPI code path runs as real processes."""
     fakes = os.path.join(os.path.dirname(__file__), "fakes")
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     code, outs = run_ranks(world, [os.path.join(W, "cpu_plumbing.py"), "--expect-bootstrap", "MpiBootstrap"],

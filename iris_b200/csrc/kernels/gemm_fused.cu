@@ -33,10 +33,12 @@
 // as rank rank0 + b / ctas_per_rank.  That is how the multi-rank protocols are tested on a single GPU.
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdio.h>
 #include <string.h>
 
+#include <atomic>
 #include <mutex>
 #include <new>
 
@@ -55,6 +57,7 @@ using namespace iris::ptx;
 enum Site : uint32_t {
   kSiteProducerEmpty = 10,
   kSiteProducerAgFlag = 11,
+  kSiteAgEntry = 12,
   kSiteMmaAccEmpty = 20,
   kSiteMmaFull = 21,
   kSiteEpiAccFull = 30,
@@ -80,14 +83,30 @@ __device__ __forceinline__ void trace(const FusedGemmParams& p, int rank, int re
   }
 }
 
-__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+// Two fp32 values -> one 32-bit word of the output type (round to nearest even).
+__device__ __forceinline__ uint32_t pack2(float lo, float hi, bool f16) {
+  if (f16) {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
-__device__ __forceinline__ void acc_bf16x8(float* acc, uint4 v) {
+// acc[0..8) += the eight 16-bit values of v (bf16 or fp16), in fp32.
+__device__ __forceinline__ void acc_x8(float* acc, uint4 v, bool f16) {
+  if (f16) {
+    const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 f = __half22float2(h[i]);
+      acc[2 * i] += f.x;
+      acc[2 * i + 1] += f.y;
+    }
+    return;
+  }
   const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
@@ -103,10 +122,10 @@ __device__ __forceinline__ void acc_bf16x8(float* acc, uint4 v) {
 // 16-byte load per lane), four rows of two slots in flight per thread.  Kept out of line so that its registers do
 // not add to those of the kernel's other roles.
 __device__ __noinline__ void rs_sum_part(const uint8_t* inbox, uint8_t* outp, uint64_t out_pitch, int N, int part_row0,
-                                         int slot_rows, int ns, int mo, int n0, int rt) {
+                                         int slot_rows, int ns, int mo, int n0, int rt, int bn, bool f16) {
   const int rw = rt >> 5, rl = rt & 31;
   const int col = n0 + rl * 8;
-  if (col >= N) return;
+  if (col >= N || rl * 8 >= bn) return;  // past the matrix edge / past this (narrower) tile
   const uint64_t row_bytes = (uint64_t)N * 2;
   const uint64_t slot_bytes = (uint64_t)slot_rows * row_bytes;
 #pragma unroll 1
@@ -132,17 +151,17 @@ __device__ __noinline__ void rs_sum_part(const uint8_t* inbox, uint8_t* outp, ui
       for (int q = 0; q < 2; ++q) {
         if (sl + q < ns) {
 #pragma unroll
-          for (int u = 0; u < 4; ++u) acc_bf16x8(a4[u], v[q][u]);
+          for (int u = 0; u < 4; ++u) acc_x8(a4[u], v[q][u], f16);
         }
       }
     }
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       uint4 o;
-      o.x = pack_bf16x2(a4[u][0], a4[u][1]);
-      o.y = pack_bf16x2(a4[u][2], a4[u][3]);
-      o.z = pack_bf16x2(a4[u][4], a4[u][5]);
-      o.w = pack_bf16x2(a4[u][6], a4[u][7]);
+      o.x = pack2(a4[u][0], a4[u][1], f16);
+      o.y = pack2(a4[u][2], a4[u][3], f16);
+      o.z = pack2(a4[u][4], a4[u][5], f16);
+      o.w = pack2(a4[u][6], a4[u][7], f16);
       st_v4(reinterpret_cast<uint4*>(outp + (uint64_t)(mo + r0 + u) * out_pitch + (uint64_t)col * 2), o);
     }
   }
@@ -172,7 +191,7 @@ struct Cfg {
   static_assert(kTilesBytes <= kSmemTiles, "shared-memory budget");
 };
 
-template <int CG, bool PULL>
+template <int CG, bool PULL, bool F16>
 __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
     fused_gemm_kernel(const __grid_constant__ FusedGemmParams p) {
   using C = Cfg<CG, PULL>;
@@ -196,6 +215,8 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
   volatile uint32_t* abort_flag = tmem_slot + 1;
   volatile uint32_t* epi_ok = tmem_slot + 2;
   volatile uint32_t* red_ok = tmem_slot + 3;
+  volatile uint32_t* ag_ok = tmem_slot + 4;
+  volatile uint32_t* never = tmem_slot + 5;  // stays 0: "abort" word for waits that must not be cut short
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -211,7 +232,9 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
 
   constexpr int TM = BM * CG;                     // rows of a scheduling unit's tile
   const int tiles_m = (p.M + TM - 1) / TM;
-  const int tiles_n = (p.N + BN - 1) / BN;
+  const int bn = p.bn;                            // tile width of this launch (64, 128 or 256)
+  constexpr bool f16 = F16;                       // element type of A, B, C: fp16, else bf16
+  const int tiles_n = (p.N + bn - 1) / bn;
   const int total_tiles = tiles_m * tiles_n;
   const int kblocks = (p.K + BK - 1) / BK;
   const int tiles_per_shard = p.ag ? (p.M / W) / TM : 0;
@@ -240,6 +263,8 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
     *abort_flag = 0;
     *epi_ok = 1;
     *red_ok = 1;
+    *ag_ok = 1;
+    *never = 0;
     mbar_fence_init();
     prefetch_tensormap(&p.tmA[lr]);
     prefetch_tensormap(&p.tmB[lr]);
@@ -275,14 +300,20 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
+      uint32_t fills = 0;  // ring slots filled so far
       bool ok = true;
-      WorkIter sched(unit, G, total_tiles, kblocks, p.dp_tiles, p.sk_units, p.ksplit);
+      WorkIter sched(unit, G, total_tiles, kblocks, p.dp_tiles, p.sk_units, p.ksplit, p.tail_tiles, p.tail_split);
       Work w;
       while (ok && sched.next(w)) {
         const int tile = tile_of(w.tile);
         TileCoord tc = raster(tile, tiles_m, tiles_n, p.group_m);
         if (p.ag) tc.m_idx = ag_actual_m(tc.m_idx, tiles_per_shard, rank, W);
         const int row0 = tc.m_idx * TM + pr * BM;
+        // Columns of this piece of work: the whole tile, or one of the column pieces of a tail tile.
+        const int wn = bn / w.nsub;                         // width of the piece
+        const int col0 = tc.n_idx * bn + w.sub * wn;        // its first column = first row of B^T
+        const int b_rows = wn / CG;                         // rows of B^T this CTA loads per k-block
+        const uint32_t stage_tx = (uint32_t)(kAStageBytes + b_rows * BK * 2);
         if (p.ag && row0 < p.M) {
           const int Ms = p.M / W;
           const int src = row0 / Ms;
@@ -306,21 +337,35 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
           }
           const uint32_t a_dst = smem_base + stage * C::kStage;
           const uint32_t b_dst = a_dst + kAStageBytes;
+          // B^T rows arrive as boxes of b_box_rows rows, stacked in shared memory (a box is a whole number of
+          // 8-row swizzle groups, so the stack has the layout of one tall box).
           if (CG == 1) {
-            mbar_expect_tx(full_bar(stage), C::kStage);
+            mbar_expect_tx(full_bar(stage), stage_tx);
             tma_load_2d(a_dst, &p.tmA[lr], kb * BK, row0, full_bar(stage));
-            tma_load_2d(b_dst, &p.tmB[lr], kb * BK, tc.n_idx * BN, full_bar(stage));
+            for (int r = 0; r < b_rows; r += p.b_box_rows)
+              tma_load_2d(b_dst + r * (BK * 2), &p.tmB[lr], kb * BK, col0 + r, full_bar(stage));
           } else {
             // Both CTAs' bytes are counted on the leader's barrier, which the leader arms for the pair.
             const uint32_t lead_full = mapa_shared(full_bar(stage), 0);
-            if (leader) mbar_expect_tx(full_bar(stage), 2 * C::kStage);
+            if (leader) mbar_expect_tx(full_bar(stage), 2 * stage_tx);
             tma_load_2d_pair(a_dst, &p.tmA[lr], kb * BK, row0, lead_full);
-            tma_load_2d_pair(b_dst, &p.tmB[lr], kb * BK, tc.n_idx * BN + pr * C::kBRows, lead_full);
+            for (int r = 0; r < b_rows; r += p.b_box_rows)
+              tma_load_2d_pair(b_dst + r * (BK * 2), &p.tmB[lr], kb * BK, col0 + pr * b_rows + r, lead_full);
           }
+          ++fills;
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1;
           }
+        }
+      }
+      if ((!ok || *abort_flag) && leader) {
+        // Leaving early: loads already issued still write into this CTA's (and, for a pair, the partner's) shared
+        // memory.  Wait, bounded, for the last fill of every ring slot; the pair's barriers live in the leader and
+        // count both CTAs' bytes, and the partner stays until the cluster barrier of the teardown.
+        for (int s2 = 0; s2 < kStages; ++s2) {
+          const uint32_t n = (fills + kStages - 1 - s2) / kStages;  // fills of slot s2
+          if (n > 0) mbar_wait(full_bar(s2), (n - 1) & 1, 200000, never);
         }
       }
     }
@@ -329,13 +374,15 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
     // MMA issuer (one thread; with CTA pairs only the leader's)
     // ------------------------------------------------------------------------------------------
     if (lane == 0 && leader) {
-      constexpr uint32_t idesc = umma_idesc_f16(TM, BN, true);
+      // instruction descriptors per piece width (bn, and bn / tail_split for the column pieces of tail tiles)
+      const uint32_t idesc_tile = umma_idesc_f16(TM, bn, !f16);
+      const uint32_t idesc_tail = umma_idesc_f16(TM, bn / (p.tail_split > 1 ? p.tail_split : 1), !f16);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      WorkIter sched(unit, G, total_tiles, kblocks, p.dp_tiles, p.sk_units, p.ksplit);
+      WorkIter sched(unit, G, total_tiles, kblocks, p.dp_tiles, p.sk_units, p.ksplit, p.tail_tiles, p.tail_split);
       Work w;
       while (ok && sched.next(w)) {
         const int tile = tile_of(w.tile);
@@ -347,6 +394,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
         tc_fence_after();
         trace(p, rank, tile * CG, kTrMmaBegin);
         const uint32_t d_tmem = tmem_base + acc * BN;
+        const uint32_t idesc = w.nsub > 1 ? idesc_tail : idesc_tile;
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!mbar_wait(full_bar(stage), phase, p.timeout_ns, abort_flag)) {
             record_status(status, kTimeout, kSiteMmaFull, rank, tile, kb);
@@ -410,6 +458,12 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
     // kernel start and the first publish comes a whole main loop later, so the wait is normally already satisfied.
     // Two-shot result pushes are made (and guarded the same way) by the reducer warps.
     const bool need_entry = W > 1 && (push_all || pulls);
+    // How finished sub-tiles leave (GEMM + all-scatter only; every other mode has one issuing thread and TMA):
+    const int push_kind = (!PULL && p.mode == kEpiStore && push_all) ? p.push_kind : (int)kPushTma;
+    const bool direct = push_kind >= kPushStores;                 // the 128 threads copy the staged sub-tile themselves
+    const int nlead = push_kind == kPushTmaSpread ? 4 : 1;        // threads that issue TMA stores (lane 0 of a warp)
+    const int lead_idx = warp - 2;
+    const bool lead = lane == 0 && lead_idx < nlead;              // lead 0 is `issuer`
     int acc = 0;
     uint32_t acc_phase = 0;
     int ebuf = 0;
@@ -430,7 +484,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
       }
     };
     bool ok_all = true;
-    WorkIter sched(unit, G, total_tiles, kblocks, p.dp_tiles, p.sk_units, p.ksplit);
+    WorkIter sched(unit, G, total_tiles, kblocks, p.dp_tiles, p.sk_units, p.ksplit, p.tail_tiles, p.tail_split);
     Work w;
     while (sched.next(w)) {
       const int tile = tile_of(w.tile);
@@ -460,7 +514,10 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
       tc_fence_after();
       if (issuer) trace(p, rank, tile * CG + pr, kTrEpiBegin);
 
-      const int x_base = (pulls ? 0 : rank * p.col_off_per_rank) + tc.n_idx * BN;
+      const int wn = bn / w.nsub;                    // width of this piece: the tile, or a column piece of a tail tile
+      const int ncol0 = tc.n_idx * bn + w.sub * wn;  // its first column inside this rank's N
+      const int nchunks = wn / kEpiCols;
+      const int x_base = (pulls ? 0 : rank * p.col_off_per_rank) + ncol0;
       const int y = tc.m_idx * TM + pr * BM;
       // row inside the tmC matrix: partial buffer of this call's parity, inbox slot of (rank, piece) when pushing
       const int slot = p.push_partials ? rank * (p.ksplit > 1 ? p.ksplit : 1) + w.piece : 0;
@@ -477,7 +534,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
         const size_t slot = (size_t)(tile - p.dp_tiles) * CG + pr;
         ws_row = reinterpret_cast<float*>(p.heap_base[rank] + p.ws_off) + (slot * BM + row) * BN;
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
+        for (int c = 0; c < bn / 32; ++c) {
           uint32_t v[32];
           tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN + c * 32, v);
           tmem_wait_ld();
@@ -512,8 +569,8 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
         if (!fin) continue;  // another unit completes this tile
       }
 #pragma unroll 1
-      for (int c = 0; c < BN / kEpiCols; ++c) {
-        const bool live = tc.n_idx * BN + c * kEpiCols < p.N && y < p.M;  // parts past the matrix edge are skipped
+      for (int c = 0; c < nchunks; ++c) {
+        const bool live = ncol0 + c * kEpiCols < p.N && y < p.M;  // parts past the matrix edge are skipped
         uint32_t v[kEpiCols];
         if (!whole) {
           // finishing a split tile: the sum of all pieces is in the workspace; read it and put zeros back
@@ -533,7 +590,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
         tmem_ld_32x32b_x32(taddr + 32, v + 32);
         tmem_wait_ld();
         }
-        if (whole && c == BN / kEpiCols - 1) {
+        if (whole && c == nchunks - 1) {
           // The accumulator has been read completely: hand it back to the MMA warp (of the leader CTA).
           tc_fence_before();
           __syncwarp();
@@ -543,25 +600,52 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
           }
         }
         if (!live) continue;  // uniform over the group
-        // The staging buffer was last used two sub-tiles ago: its TMA reads must have finished.
-        if (issuer) bulk_wait_read<kEpiBufs - 1>();
+        // The staging buffer was last used two sub-tiles ago: its TMA reads must have finished (every issuing thread
+        // waits for its own bulk groups; threads that copy the buffer themselves are past it at the barrier).
+        if (lead && !direct) bulk_wait_read<kEpiBufs - 1>();
         named_barrier_sync(1, 128);
         const uint32_t sbase = epi_base + ebuf * kEpiStageBytes + row * 128;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          const uint32_t a = pack_bf16x2(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]));
-          const uint32_t b = pack_bf16x2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
-          const uint32_t cc = pack_bf16x2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
-          const uint32_t d = pack_bf16x2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
+          const uint32_t a = pack2(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]), f16);
+          const uint32_t b = pack2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]), f16);
+          const uint32_t cc = pack2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]), f16);
+          const uint32_t d = pack2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]), f16);
           st_shared_v4(sbase + ((j ^ (row & 7)) << 4), a, b, cc, d);  // 128-byte swizzle, as the tensor map expects
         }
-        fence_proxy_async_smem();
+        if (!direct) fence_proxy_async_smem();
         named_barrier_sync(1, 128);
-        if (issuer) {
+        if (direct) {
+          // Copy the staged 128 x 64 sub-tile out with 16-byte stores: 8 lanes cover one 128-byte row segment, a warp
+          // four rows.  Element (r, j) of the buffer sits at the swizzled position the staging loop wrote it to.
+          const uint32_t src = epi_base + ebuf * kEpiStageBytes;
+          const int x = x_base + c * kEpiCols;
+          uint4 vv[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int idx = i * 128 + et, r = idx >> 3, j = idx & 7;
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(vv[i].x), "=r"(vv[i].y), "=r"(vv[i].z), "=r"(vv[i].w)
+                         : "r"(src + r * 128 + ((j ^ (r & 7)) << 4)));
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int idx = i * 128 + et, r = idx >> 3, j = idx & 7;
+            if (y + r < p.M) {
+              const uint64_t off = p.c_off + ((uint64_t)(y + r) * p.ldc + x + j * 8) * 2;
+              if (push_kind == kPushMultimem) {
+                nvls::st_v4(reinterpret_cast<void*>(p.mc_base + off), vv[i]);  // the switch delivers to every rank
+              } else {
+                for (int q = 0; q < W; ++q)  // peers first, starting with the next rank; own copy last
+                  st_v4(reinterpret_cast<uint4*>(p.heap_base[(rank + 1 + q) % W] + off), vv[i]);
+              }
+            }
+          }
+        } else if (lead) {
           const uint32_t src = epi_base + ebuf * kEpiStageBytes;
           const int x = x_base + c * kEpiCols;
           if (push_all) {
-            for (int i = 0; i < W; ++i) {  // peers first, starting with the next rank; own copy last
+            for (int i = lead_idx; i < W; i += nlead) {  // peers first, starting with the next rank; own copy last
               const int t = (rank + 1 + i) % W;
               if (keeper >= 0 && t != keeper) continue;
               if (p.mode == kEpiReduce) tma_reduce_add_2d(&p.tmC[t], x, y_st, src);
@@ -592,7 +676,11 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
         // groups just committed) and keep this one pending.  The reducer warps do the summing, concurrently.
         if (issuer) {
           if (pending_tile >= 0) {
-            if (groups_this_tile == BN / kEpiCols) bulk_wait<BN / kEpiCols>();
+            // at most the groups just committed may still be pending
+            if (groups_this_tile == 4) bulk_wait<4>();
+            else if (groups_this_tile == 3) bulk_wait<3>();
+            else if (groups_this_tile == 2) bulk_wait<2>();
+            else if (groups_this_tile == 1) bulk_wait<1>();
             else bulk_wait<0>();
             publish_tile(pending_tile);
           }
@@ -610,15 +698,20 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
     // every CTA of every rank has done the same, so that at kernel end all remote tiles are in local memory.
     const bool end_sync = push_all && !pulls;
     if (end_sync) {
-      named_barrier_sync(1, 128);
-      if (issuer) {
+      // Every thread that wrote to peers orders its own writes before the arrival the issuer announces below.
+      if (direct) {
+        fence_sys();
+      } else if (lead) {
         bulk_wait<0>();
         fence_proxy_async_all();
         fence_sys();
+      }
+      named_barrier_sync(1, 128);
+      if (issuer) {
         for (int i = 0; i < W; ++i) red_release_sys_add(flag_ptr(p, (rank + 1 + i) % W, 0), 1u);
         if (ok_all) wait_until_ge(flag_ptr(p, rank, 0), p.done_target, p.timeout_ns, status, kSiteDone, rank, cta);
       }
-    } else if (issuer) {
+    } else if (lead) {
       bulk_wait<0>();
     }
   } else {
@@ -644,7 +737,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
       const int ks = p.ksplit > 1 ? p.ksplit : 1;
       const int NS = p.push_partials ? W * ks : W;
       const bool by_chunk = p.ksplit > 1;
-      constexpr int kChunks = BN / kEpiCols;
+      const int kChunks = bn / kEpiCols;
       const int n_items = by_chunk ? total_tiles * kChunks : total_tiles;
       // reduce-scatter: only the tiles of this rank's row block, which are [rank * rs_tpc, (rank + 1) * rs_tpc)
       const int rs_base = p.rs_rows > 0 ? rank * p.rs_rows : 0;
@@ -656,7 +749,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
         const int c1 = by_chunk ? c0 + 1 : kChunks;
         if (two_shot && owner_of(t) != rank) continue;
         const TileCoord tc = raster(t, tiles_m, tiles_n, p.group_m);
-        const int m0 = tc.m_idx * TM + pr * BM, n0 = tc.n_idx * BN;
+        const int m0 = tc.m_idx * TM + pr * BM, n0 = tc.n_idx * bn;
         if (by_chunk && (n0 + c0 * kEpiCols >= p.N || m0 >= p.M)) continue;
         if (two_shot && p.mc_base != 0 && p.out_row0 >= 0 && W > 1) {
           // NVLS two-shot: the NVLink switch does the work.  One multimem.ld_reduce per 16 bytes returns the fp32-
@@ -677,13 +770,15 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
           }
           entered = true;
           named_barrier_sync(3, 128);
-          if (*red_ok == 0) {
+          const bool tile_ok = *red_ok != 0;
+          named_barrier_sync(3, 128);  // everybody has read the verdict before the issuer writes the next one
+          if (!tile_ok) {
             ok_all = false;
             break;
           }
           const int rw = rt >> 5, rl = rt & 31;
           const int col = n0 + rl * 8;
-          if (col < p.N) {
+          if (col < p.N && rl * 8 < bn) {
             const uint64_t mc = p.mc_base + p.partial_off;  // [partials | out] matrix of every rank at once
 #pragma unroll 1
             for (int r0 = rw * 32; r0 < rw * 32 + 32; r0 += 8) {
@@ -691,9 +786,10 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
 #pragma unroll
               for (int u = 0; u < 8; ++u) {
                 const int r = m0 + r0 + u;
-                if (r < p.M)
-                  v[u] = nvls::ld_reduce_add_bf16x8(
-                      reinterpret_cast<const void*>(mc + ((uint64_t)(p.part_row0 + r) * p.N + col) * 2));
+                if (r < p.M) {
+                  const void* src = reinterpret_cast<const void*>(mc + ((uint64_t)(p.part_row0 + r) * p.N + col) * 2);
+                  v[u] = f16 ? nvls::ld_reduce_add_f16x8(src) : nvls::ld_reduce_add_bf16x8(src);
+                }
               }
 #pragma unroll
               for (int u = 0; u < 8; ++u) {
@@ -728,7 +824,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
                                             (uint64_t)p.out_row0 * p.N * 2
                                       : reinterpret_cast<uint8_t*>(p.heap_base[rank] + p.out_off),
                       p.out_row0 >= 0 ? (uint64_t)p.N * 2 : (uint64_t)p.ldo * 2, p.N, p.part_row0, p.part_slot_rows, NS,
-                      m0 - rs_base, n0, rt);
+                      m0 - rs_base, n0, rt, bn, f16);
           if (rissuer) trace(p, rank, t * CG + pr, kTrPullEnd);
           continue;
         }
@@ -743,7 +839,9 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
             *red_ok = ok ? 1u : 0u;
           }
           named_barrier_sync(3, 128);
-          if (*red_ok == 0) {
+          const bool tile_ok = *red_ok != 0;
+          named_barrier_sync(3, 128);  // everybody has read the verdict before the issuer writes the next one
+          if (!tile_ok) {
             ok_all = false;
             break;
           }
@@ -766,14 +864,14 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
 #pragma unroll
                 for (int q = 0; q < 2; ++q)
 #pragma unroll
-                  for (int j = 0; j < 8; ++j) acc_bf16x8(accv + 8 * j, v[q][j]);
+                  for (int j = 0; j < 8; ++j) acc_x8(accv + 8 * j, v[q][j], f16);
               }
               for (; sl < NS; ++sl) {
                 uint4 v[8];
 #pragma unroll
                 for (int j = 0; j < 8; ++j) v[j] = ld_v4(reinterpret_cast<const uint4*>(src + sl * slot_bytes) + j);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) acc_bf16x8(accv + 8 * j, v[j]);
+                for (int j = 0; j < 8; ++j) acc_x8(accv + 8 * j, v[j], f16);
               }
             }
             if (p.out_row0 >= 0) {
@@ -782,9 +880,9 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
               const uint32_t sbase = redout_base + row * 128;
 #pragma unroll
               for (int j = 0; j < 8; ++j)
-                st_shared_v4(sbase + ((j ^ (row & 7)) << 4), pack_bf16x2(accv[8 * j + 0], accv[8 * j + 1]),
-                             pack_bf16x2(accv[8 * j + 2], accv[8 * j + 3]), pack_bf16x2(accv[8 * j + 4], accv[8 * j + 5]),
-                             pack_bf16x2(accv[8 * j + 6], accv[8 * j + 7]));
+                st_shared_v4(sbase + ((j ^ (row & 7)) << 4), pack2(accv[8 * j + 0], accv[8 * j + 1], f16),
+                             pack2(accv[8 * j + 2], accv[8 * j + 3], f16), pack2(accv[8 * j + 4], accv[8 * j + 5], f16),
+                             pack2(accv[8 * j + 6], accv[8 * j + 7], f16));
               fence_proxy_async_smem();
               named_barrier_sync(3, 128);
               if (rissuer) {
@@ -797,10 +895,10 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
                 const int col = n0 + c * kEpiCols + 8 * j;
                 if (col < p.N) {
                   uint4 o;
-                  o.x = pack_bf16x2(accv[8 * j + 0], accv[8 * j + 1]);
-                  o.y = pack_bf16x2(accv[8 * j + 2], accv[8 * j + 3]);
-                  o.z = pack_bf16x2(accv[8 * j + 4], accv[8 * j + 5]);
-                  o.w = pack_bf16x2(accv[8 * j + 6], accv[8 * j + 7]);
+                  o.x = pack2(accv[8 * j + 0], accv[8 * j + 1], f16);
+                  o.y = pack2(accv[8 * j + 2], accv[8 * j + 3], f16);
+                  o.z = pack2(accv[8 * j + 4], accv[8 * j + 5], f16);
+                  o.w = pack2(accv[8 * j + 6], accv[8 * j + 7], f16);
                   st_v4(reinterpret_cast<uint4*>(p.heap_base[rank] + p.out_off +
                                                  ((uint64_t)(m0 - rs_base + row) * p.ldo + col) * 2), o);
                 }
@@ -863,7 +961,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
             asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
                          : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                          : "r"(buf + ((j ^ (row & 7)) << 4)));
-            acc_bf16x8(accv + 8 * j, v);
+            acc_x8(accv + 8 * j, v, f16);
           }
           ++pull_done;
           if (sft == NS - 1 && p.out_row0 >= 0) {
@@ -886,9 +984,9 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
             const uint32_t sbase = redout_base + row * 128;
 #pragma unroll
             for (int j = 0; j < 8; ++j)
-              st_shared_v4(sbase + ((j ^ (row & 7)) << 4), pack_bf16x2(accv[8 * j + 0], accv[8 * j + 1]),
-                           pack_bf16x2(accv[8 * j + 2], accv[8 * j + 3]), pack_bf16x2(accv[8 * j + 4], accv[8 * j + 5]),
-                           pack_bf16x2(accv[8 * j + 6], accv[8 * j + 7]));
+              st_shared_v4(sbase + ((j ^ (row & 7)) << 4), pack2(accv[8 * j + 0], accv[8 * j + 1], f16),
+                           pack2(accv[8 * j + 2], accv[8 * j + 3], f16), pack2(accv[8 * j + 4], accv[8 * j + 5], f16),
+                           pack2(accv[8 * j + 6], accv[8 * j + 7], f16));
             fence_proxy_async_smem();
             named_barrier_sync(3, 128);
             if (rissuer) {
@@ -909,10 +1007,10 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
                 const int col = n0 + c * kEpiCols + 8 * j;
                 if (col < p.N) {
                   uint4 o;
-                  o.x = pack_bf16x2(accv[8 * j + 0], accv[8 * j + 1]);
-                  o.y = pack_bf16x2(accv[8 * j + 2], accv[8 * j + 3]);
-                  o.z = pack_bf16x2(accv[8 * j + 4], accv[8 * j + 5]);
-                  o.w = pack_bf16x2(accv[8 * j + 6], accv[8 * j + 7]);
+                  o.x = pack2(accv[8 * j + 0], accv[8 * j + 1], f16);
+                  o.y = pack2(accv[8 * j + 2], accv[8 * j + 3], f16);
+                  o.z = pack2(accv[8 * j + 4], accv[8 * j + 5], f16);
+                  o.w = pack2(accv[8 * j + 6], accv[8 * j + 7], f16);
                   const uint64_t ooff = p.out_off + ((uint64_t)r * p.ldo + col) * 2;
                   if (!two_shot) {
                     st_v4(reinterpret_cast<uint4*>(p.heap_base[rank] + ooff), o);
@@ -926,7 +1024,12 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
         }
         if (rissuer && ok_all) trace(p, rank, t * CG + pr, kTrPullEnd);
       }
-      if (!ok_all && rissuer) *abort_flag = 1;
+      if (!ok_all && rissuer) {
+        *abort_flag = 1;
+        // fetches already issued still write into the pull buffers: wait, bounded, for each of them
+        for (uint32_t i = pull_done; i < pull_issued; ++i)
+          mbar_wait(pull_full_bar(i % C::kPullBufs), (i / C::kPullBufs) & 1, 200000, never);
+      }
       // Two-shot: when this CTA's pushes have landed, bump every rank's arrival counter and wait (bounded) until
       // every CTA of every rank has done so: at kernel end all result tiles are in local memory.
       if (two_shot && W > 1) {
@@ -953,7 +1056,23 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
       const int slice_elems = p.K / S;             // multiple of 8 (checked on the host)
       const int vec_per_row = slice_elems / 8;     // 16-byte vectors per row of a slice
       const int items = (W - 1) * chunks_per_shard * S;
-      for (int item = cta; item < items; item += p.ctas_per_rank) {
+      // Nothing is written into a peer's gathered A before that peer has entered this call, i.e. finished the
+      // previous one: its producer may otherwise still be loading the rows of the previous call from that buffer.
+      if (cta < items) {
+        if (ct == 0) {
+          bool ok = true;
+          for (int i = 0; i + 1 < W && ok; ++i) {
+            const int q = (rank + 1 + i) % W;
+            ok = wait_until_ge(flag_ptr(p, rank, 8 + q), p.epoch, p.timeout_ns, status, kSiteAgEntry, rank, q) == kOk;
+          }
+          if (!ok) {
+            *ag_ok = 0;
+            *abort_flag = 1;
+          }
+        }
+        named_barrier_sync(2, 64);
+      }
+      for (int item = cta; item < items && *ag_ok; item += p.ctas_per_rank) {
         const int pi = item / (chunks_per_shard * S);          // peer-major: finish one peer's copy first
         const int rem = item - pi * (chunks_per_shard * S);
         const int chunk = rem / S;
@@ -992,12 +1111,9 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
   }
 
   // ---- teardown --------------------------------------------------------------------------------
+  // Every role that issued bulk copies has waited for them by now: stores with cp.async.bulk.wait_group 0, loads (on
+  // the error path) with a bounded wait for the barrier they complete on.
   __syncwarp();
-  if (*abort_flag) {
-    // Error path only: give copies in flight a bounded time to land before tensor memory is released.
-    const uint64_t t0 = timer_ns();
-    while (timer_ns() - t0 < 50000) __nanosleep(1000);
-  }
   tc_fence_before();
   __syncthreads();
   if (CG == 2) cluster_sync_all();  // neither CTA of a pair leaves while the other may still touch its memory
@@ -1034,9 +1150,10 @@ EncodeTiledFn encode_fn() {
   return g_encode;
 }
 
-// bf16 matrix [rows, cols] with `ld` elements between rows; box = box_cols x box_rows; 128-byte swizzle.
+// 16-bit matrix [rows, cols] (bf16, or fp16 with `f16`) with `ld` elements between rows; box = box_cols x box_rows;
+// 128-byte swizzle.
 int encode_2d(CUtensorMap* out, uint64_t ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_cols,
-              uint32_t box_rows, const char* what) {
+              uint32_t box_rows, const char* what, bool f16 = false) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) {
     snprintf(g_err, sizeof(g_err), "cuTensorMapEncodeTiled is not available");
@@ -1050,7 +1167,8 @@ int encode_2d(CUtensorMap* out, uint64_t ptr, uint64_t rows, uint64_t cols, uint
   cuuint64_t strides[1] = {ld * 2};
   cuuint32_t box[2] = {box_cols, box_rows};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, reinterpret_cast<void*>(ptr), dims, strides, box, estr,
+  CUresult r = fn(out, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                  reinterpret_cast<void*>(ptr), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
@@ -1068,9 +1186,13 @@ using namespace iris::gemm;
 
 namespace {
 using KernelFn = void (*)(const FusedGemmParams);
-KernelFn kernel_for(int cta_group, bool pull) {
-  if (cta_group == 2) return pull ? fused_gemm_kernel<2, true> : fused_gemm_kernel<2, false>;
-  return pull ? fused_gemm_kernel<1, true> : fused_gemm_kernel<1, false>;
+KernelFn kernel_for(int cta_group, bool pull, bool f16) {
+  if (f16) {
+    if (cta_group == 2) return pull ? fused_gemm_kernel<2, true, true> : fused_gemm_kernel<2, false, true>;
+    return pull ? fused_gemm_kernel<1, true, true> : fused_gemm_kernel<1, false, true>;
+  }
+  if (cta_group == 2) return pull ? fused_gemm_kernel<2, true, false> : fused_gemm_kernel<2, false, false>;
+  return pull ? fused_gemm_kernel<1, true, false> : fused_gemm_kernel<1, false, false>;
 }
 }  // namespace
 
@@ -1110,6 +1232,11 @@ struct IrisGemmDesc {
   int dp_tiles, sk_units, sk_flag_base;  // stream-K schedule (dp_tiles < 0: every tile whole)
   int push_partials, part_slot_rows, ksplit;
   int rs_rows;                 // reduce-scatter: rows kept per rank (0 = off); see FusedGemmParams::rs_rows
+  int bn;                      // tile width: 64, 128 or 256 (0 = 256)
+  int dtype;                   // ElemType: 0 = bf16, 1 = fp16
+  int push_kind;               // PushKind of the all-scatter epilogue
+  int tail_tiles, tail_split;  // column-split tail of the raster (see tail_split_plan); 0 / 1 = off
+  uint64_t c_off;              // symmetric offset of the C buffer (needed by push kinds 2 and 3)
 };
 
 struct IrisGemmPlan {
@@ -1120,6 +1247,7 @@ struct IrisGemmPlan {
   int cta_group;
   int ctas_per_rank;
   int pull;
+  int f16;
 };
 
 // The schedule arithmetic of the kernel, callable on the host (no device needed): see gemm_schedule.h.
@@ -1135,20 +1263,36 @@ int iris_sched_two_shot_owner(int tile, int units, int world) { return two_shot_
 int iris_sched_rs_tile_of(int step, int rank, int world, int tiles_per_block) {
   return rs_tile_of(step, rank, world, tiles_per_block);
 }
+void iris_sched_tail_split(int total_tiles, int units, int max_split, int* tail_tiles, int* split) {
+  tail_split_plan(total_tiles, units, max_split, tail_tiles, split);
+}
+
+int iris_sched_work_list_tail(int unit, int units, int total_tiles, int kblocks, int dp_tiles, int sk_units, int ksplit,
+                              int tail_tiles, int tail_split, int* out, int max_items, int stride);
 
 // The pieces of work scheduling unit `unit` of `units` goes through, as (tile, kb0, kb1, piece) quadruples; returns how
 // many there are (at most `max_items` are written).
 int iris_sched_work_list(int unit, int units, int total_tiles, int kblocks, int dp_tiles, int sk_units, int ksplit,
                          int* out, int max_items) {
-  WorkIter it(unit, units, total_tiles, kblocks, dp_tiles, sk_units, ksplit);
+  return iris_sched_work_list_tail(unit, units, total_tiles, kblocks, dp_tiles, sk_units, ksplit, 0, 1, out, max_items, 4);
+}
+
+// The same with a column-split tail; `stride` ints per item: (tile, kb0, kb1, piece[, sub, nsub]).
+int iris_sched_work_list_tail(int unit, int units, int total_tiles, int kblocks, int dp_tiles, int sk_units, int ksplit,
+                              int tail_tiles, int tail_split, int* out, int max_items, int stride) {
+  WorkIter it(unit, units, total_tiles, kblocks, dp_tiles, sk_units, ksplit, tail_tiles, tail_split);
   Work w;
   int n = 0;
   while (it.next(w)) {
     if (n < max_items) {
-      out[4 * n] = w.tile;
-      out[4 * n + 1] = w.kb0;
-      out[4 * n + 2] = w.kb1;
-      out[4 * n + 3] = w.piece;
+      out[stride * n] = w.tile;
+      out[stride * n + 1] = w.kb0;
+      out[stride * n + 2] = w.kb1;
+      out[stride * n + 3] = w.piece;
+      if (stride >= 6) {
+        out[stride * n + 4] = w.sub;
+        out[stride * n + 5] = w.nsub;
+      }
     }
     ++n;
   }
@@ -1178,6 +1322,34 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
     return nullptr;
   }
   const int cg = d->cta_group == 2 ? 2 : 1;
+  const int bn = d->bn > 0 ? d->bn : BN;
+  if (bn != 64 && bn != 128 && bn != 256) {
+    snprintf(g_err, sizeof(g_err), "tile width must be 64, 128 or 256 columns");
+    return nullptr;
+  }
+  if (d->dtype != kBf16 && d->dtype != kFp16) {
+    snprintf(g_err, sizeof(g_err), "element type must be bf16 (0) or fp16 (1)");
+    return nullptr;
+  }
+  const bool f16 = d->dtype == kFp16;
+  const int tail_split = d->tail_tiles > 0 && d->tail_split > 1 ? d->tail_split : 1;
+  const int tail_tiles = tail_split > 1 ? d->tail_tiles : 0;
+  if (tail_split > 1) {
+    const bool plain = (d->mode == kEpiStore || d->mode == kEpiReduce) && d->sk_units <= 0 && d->ksplit <= 1;
+    if (!plain || bn % tail_split != 0 || (bn / tail_split) % kEpiCols != 0 || ((bn / tail_split) / cg) % 8 != 0) {
+      snprintf(g_err, sizeof(g_err), "a column-split tail needs store / reduce mode, whole tiles and pieces of whole "
+                                     "%d-column sub-tiles", kEpiCols);
+      return nullptr;
+    }
+  }
+  if (d->push_kind < kPushTma || d->push_kind > kPushMultimem) {
+    snprintf(g_err, sizeof(g_err), "push_kind must be 0..3");
+    return nullptr;
+  }
+  if (d->push_kind == kPushMultimem && d->world > 1 && d->store_all && d->mode == kEpiStore && d->mc_base == 0) {
+    snprintf(g_err, sizeof(g_err), "push_kind 3 (multimem) needs a heap bound to an NVLS multicast object");
+    return nullptr;
+  }
   if (d->rs_rows > 0) {
     const int gm = d->group_m < 1 ? 1 : d->group_m;
     if (d->mode != kEpiOneShot || !d->push_partials || d->ksplit > 1 || d->sk_units > 0) {
@@ -1212,7 +1384,7 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
   const uint32_t c_box_rows = d->M >= BM ? BM : (uint32_t)((d->M + 7) / 8 * 8);
   int ctas_per_rank = d->ctas_per_rank - d->ctas_per_rank % cg;
   {
-    cudaError_t e = cudaFuncSetAttribute(kernel_for(cg, pull),
+    cudaError_t e = cudaFuncSetAttribute(kernel_for(cg, pull, f16),
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) {
       snprintf(g_err, sizeof(g_err), "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
@@ -1233,7 +1405,7 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     int max_clusters = 0;
-    cudaError_t e = cudaOccupancyMaxActiveClusters(&max_clusters, kernel_for(2, pull), &cfg);
+    cudaError_t e = cudaOccupancyMaxActiveClusters(&max_clusters, kernel_for(2, pull, f16), &cfg);
     if (e != cudaSuccess || max_clusters < d->num_local) {
       snprintf(g_err, sizeof(g_err), "CTA pairs cannot be scheduled (%s, %d clusters)", cudaGetErrorString(e),
                max_clusters);
@@ -1256,12 +1428,13 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
   plan->device = d->device;
   plan->cta_group = cg;
   plan->pull = pull ? 1 : 0;
+  plan->f16 = f16 ? 1 : 0;
   plan->ctas_per_rank = ctas_per_rank;
   for (int par = 0; par < 2; ++par) {
     FusedGemmParams& p = plan->params[par];
     for (int l = 0; l < d->num_local; ++l) {
-      if (encode_2d(&p.tmA[l], d->a_ptr[l], d->M, d->K, d->lda[l], BK, BM, "A") ||
-          encode_2d(&p.tmB[l], d->b_ptr[l], d->N, d->K, d->ldb[l], BK, BN / cg, "B")) {
+      if (encode_2d(&p.tmA[l], d->a_ptr[l], d->M, d->K, d->lda[l], BK, BM, "A", f16) ||
+          encode_2d(&p.tmB[l], d->b_ptr[l], d->N, d->K, d->ldb[l], BK, (bn / tail_split) / cg, "B", f16)) {
         delete plan;
         return nullptr;
       }
@@ -1269,7 +1442,8 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
     for (int t = 0; t < d->world; ++t) {
       const uint64_t cp = (par == 1 && d->c2_ptr[t]) ? d->c2_ptr[t] : d->c_ptr[t];
       if (!cp) continue;
-      if (encode_2d(&p.tmC[t], cp, d->c_rows > 0 ? d->c_rows : d->M, d->c_cols, d->ldc, kEpiCols, c_box_rows, "C")) {
+      if (encode_2d(&p.tmC[t], cp, d->c_rows > 0 ? d->c_rows : d->M, d->c_cols, d->ldc, kEpiCols, c_box_rows, "C",
+                    f16)) {
         delete plan;
         return nullptr;
       }
@@ -1285,7 +1459,7 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
     p.ws_off = d->ws_off;
     p.mc_base = d->mc_base;
     {
-      const int tiles = ((d->M + BM * cg - 1) / (BM * cg)) * ((d->N + BN - 1) / BN);
+      const int tiles = ((d->M + BM * cg - 1) / (BM * cg)) * ((d->N + bn - 1) / bn);
       p.dp_tiles = (d->dp_tiles < 0 || d->dp_tiles > tiles || d->sk_units <= 0) ? tiles : d->dp_tiles;
       p.sk_units = p.dp_tiles == tiles ? 0 : d->sk_units;
       if (p.sk_units > ctas_per_rank / cg) p.sk_units = ctas_per_rank / cg;  // only units that exist take a range
@@ -1315,6 +1489,14 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
     p.rs_rows = d->rs_rows > 0 ? d->rs_rows : 0;
     p.tile_flag_base = d->tile_flag_base;
     p.ag_flag_base = d->ag_flag_base;
+    p.bn = bn;
+    p.b_box_rows = (bn / tail_split) / cg;
+    p.dtype = d->dtype;
+    p.push_kind = d->push_kind;
+    p.tail_tiles = tail_tiles;
+    p.tail_split = tail_split;
+    p.ldc = (int)d->ldc;
+    p.c_off = d->c_off;
   }
   return plan;
 }
@@ -1353,21 +1535,21 @@ int iris_gemm_plan_launch(void* h, int parity, uint32_t epoch, uint32_t flag_tar
     // Ranks simulated on one GPU wait on one another: ask for a cooperative launch on top of the clusters.
     cfg.numAttrs = plan->cooperative ? 2 : 1;
     void* kargs[] = {&p};
-    e = cudaLaunchKernelExC(&cfg, reinterpret_cast<const void*>(kernel_for(2, plan->pull != 0)), kargs);
+    e = cudaLaunchKernelExC(&cfg, reinterpret_cast<const void*>(kernel_for(2, plan->pull != 0, plan->f16 != 0)), kargs);
     if (e != cudaSuccess && plan->cooperative) {
       // Cooperative + cluster launches are not accepted everywhere; the grid was sized by
       // cudaOccupancyMaxActiveClusters, so all pairs are resident on an otherwise idle GPU.
       (void)cudaGetLastError();
       cfg.numAttrs = 1;
-      e = cudaLaunchKernelExC(&cfg, reinterpret_cast<const void*>(kernel_for(2, plan->pull != 0)), kargs);
+      e = cudaLaunchKernelExC(&cfg, reinterpret_cast<const void*>(kernel_for(2, plan->pull != 0, plan->f16 != 0)), kargs);
     }
   } else if (plan->cooperative) {
     void* args[] = {&p};
-    e = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(kernel_for(1, plan->pull != 0)), dim3(plan->grid),
+    e = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(kernel_for(1, plan->pull != 0, plan->f16 != 0)), dim3(plan->grid),
                                     dim3(plan->pull ? kThreadsPull : kThreads), args, kSmemBytes, st);
   } else {
     void* args[] = {&p};
-    e = cudaLaunchKernel(reinterpret_cast<void*>(kernel_for(1, plan->pull != 0)), dim3(plan->grid),
+    e = cudaLaunchKernel(reinterpret_cast<void*>(kernel_for(1, plan->pull != 0, plan->f16 != 0)), dim3(plan->grid),
                          dim3(plan->pull ? kThreadsPull : kThreads), args, kSmemBytes, st);
   }
   if (e != cudaSuccess) {
@@ -1397,7 +1579,7 @@ constexpr uint64_t kNoAllocPartialOff = IRIS_GEMM_NOALLOC_HEADER_BYTES;  // bf16
 static_assert(IRIS_GEMM_NOALLOC_HEADER_BYTES % 256 == 0, "partial matrix must stay 256-byte aligned");
 
 struct NoAllocDevice {
-  bool ready = false;
+  std::atomic<bool> ready{false};    // set (release) after `scratch` and `sms`; read (acquire) without the mutex
   unsigned char* scratch = nullptr;  // device address of g_noalloc_scratch on this device
   int sms = 0;
 };
@@ -1408,7 +1590,7 @@ std::mutex g_noalloc_mutex;
 int noalloc_setup(int dev) {
   std::lock_guard<std::mutex> lock(g_noalloc_mutex);
   NoAllocDevice& d = g_noalloc_dev[dev];
-  if (d.ready) return 0;
+  if (d.ready.load(std::memory_order_acquire)) return 0;
   void* ptr = nullptr;
   cudaError_t e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
   if (e != cudaSuccess || ptr == nullptr) {
@@ -1417,13 +1599,13 @@ int noalloc_setup(int dev) {
   }
   e = cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev);
   if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(fused_gemm_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    e = cudaFuncSetAttribute(fused_gemm_kernel<1, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
   if (e != cudaSuccess) {
     snprintf(iris::gemm::g_err, sizeof(iris::gemm::g_err), "no-alloc set-up: %s", cudaGetErrorString(e));
     return -3;
   }
   d.scratch = static_cast<unsigned char*>(ptr);
-  d.ready = true;
+  d.ready.store(true, std::memory_order_release);
   return 0;
 }
 }  // namespace
@@ -1439,8 +1621,12 @@ int iris_gemm_noalloc(const void* a, int64_t lda, const void* bt, int64_t ldb, v
     snprintf(err, errn, "iris_gemm_noalloc: need non-null buffers, positive sizes, N and K multiples of 8");
     return -1;
   }
-  if (reinterpret_cast<uintptr_t>(out) % 16 != 0 || (ldo * 2) % 16 != 0 || ldo < N) {
-    snprintf(err, errn, "iris_gemm_noalloc: output must be 16-byte aligned with a pitch of at least N elements");
+  if (reinterpret_cast<uintptr_t>(out) % 16 != 0 || (ldo * 2) % 16 != 0 || ldo < N || ldo > 0x7fffffffLL) {
+    snprintf(err, errn, "iris_gemm_noalloc: output must be 16-byte aligned with a pitch of N .. 2^31 - 1 elements");
+    return -1;
+  }
+  if (lda < K || ldb < K) {
+    snprintf(err, errn, "iris_gemm_noalloc: the row pitches of a and bt must be at least K elements");
     return -1;
   }
   const long long tiles = (long long)((M + BM - 1) / BM) * ((N + BN - 1) / BN);
@@ -1457,7 +1643,7 @@ int iris_gemm_noalloc(const void* a, int64_t lda, const void* bt, int64_t ldb, v
     snprintf(err, errn, "iris_gemm_noalloc: no current CUDA device");
     return -3;
   }
-  if (!g_noalloc_dev[dev].ready) {
+  if (!g_noalloc_dev[dev].ready.load(std::memory_order_acquire)) {
     const int rc = noalloc_setup(dev);
     if (rc != 0) return rc;
   }
@@ -1467,9 +1653,11 @@ int iris_gemm_noalloc(const void* a, int64_t lda, const void* bt, int64_t ldb, v
   // Parameters live on the host stack; nothing is allocated.
   FusedGemmParams p;
   memset(&p, 0, sizeof(p));
+  // a short matrix moves short sub-tiles: the box of the scratch matrix is no taller than M needs (multiple of 8)
+  const uint32_t c_box_rows = M >= BM ? BM : (uint32_t)((M + 7) / 8 * 8);
   if (encode_2d(&p.tmA[0], reinterpret_cast<uint64_t>(a), M, K, lda, BK, BM, "A") ||
       encode_2d(&p.tmB[0], reinterpret_cast<uint64_t>(bt), N, K, ldb, BK, BN, "B") ||
-      encode_2d(&p.tmC[0], base + kNoAllocPartialOff, M, N, N, kEpiCols, BM, "scratch partial"))
+      encode_2d(&p.tmC[0], base + kNoAllocPartialOff, M, N, N, kEpiCols, c_box_rows, "scratch partial"))
     return -1;
   p.heap_base[0] = base;                // "heap" of the single rank = the scratch array
   p.flags_off = kNoAllocFlagsOff;
@@ -1481,7 +1669,7 @@ int iris_gemm_noalloc(const void* a, int64_t lda, const void* bt, int64_t ldb, v
   p.N = N;
   p.K = K;
   p.ldo = (int)ldo;
-  p.c_box_bytes = BM * 128u;
+  p.c_box_bytes = c_box_rows * 128u;
   p.part_row0 = 0;
   p.out_row0 = -1;  // the caller's output is a separate buffer: ordinary stores
   p.world = 1;
@@ -1495,15 +1683,21 @@ int iris_gemm_noalloc(const void* a, int64_t lda, const void* bt, int64_t ldb, v
   p.sk_units = 0;
   p.tile_flag_base = 16;
   p.ag_flag_base = 16;
+  p.bn = BN;
+  p.b_box_rows = BN;
+  p.dtype = kBf16;
+  p.tail_split = 1;
   p.epoch = 1;
   p.flag_target = 1;  // one rank raises each tile's flag once; the flags are cleared just below
   p.done_target = 0;
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // The scratch keeps the previous call's flags and status: clear what has to start at zero, in stream order.
-  cudaError_t e = cudaMemsetAsync(d.scratch, 0, kNoAllocPartialOff, st);
+  // The scratch keeps the previous call's contents.  The per-tile flags have to start at zero: clear them in stream
+  // order.  The status record is left alone, so that a time-out of an earlier call stays readable until
+  // iris_gemm_noalloc_status() has reported it.
+  cudaError_t e = cudaMemsetAsync(d.scratch + kNoAllocFlagsOff, 0, (size_t)(16 + tiles) * sizeof(uint32_t), st);
   if (e == cudaSuccess) {
-    fused_gemm_kernel<1, true><<<p.ctas_per_rank, kThreadsPull, kSmemBytes, st>>>(p);
+    fused_gemm_kernel<1, true, false><<<p.ctas_per_rank, kThreadsPull, kSmemBytes, st>>>(p);
     e = cudaGetLastError();
   }
   if (e != cudaSuccess) {
@@ -1515,12 +1709,15 @@ int iris_gemm_noalloc(const void* a, int64_t lda, const void* bt, int64_t ldb, v
 
 int iris_gemm_noalloc_status(void) {
   int dev = -1;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kNoAllocMaxDevices || !g_noalloc_dev[dev].ready) return 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kNoAllocMaxDevices ||
+      !g_noalloc_dev[dev].ready.load(std::memory_order_acquire))
+    return 0;
   if (cudaDeviceSynchronize() != cudaSuccess) return -3;
+  unsigned char* st = g_noalloc_dev[dev].scratch + kNoAllocStatusOff;
   uint32_t code = 0;
-  if (cudaMemcpy(&code, g_noalloc_dev[dev].scratch + kNoAllocStatusOff, sizeof(code), cudaMemcpyDeviceToHost) !=
-      cudaSuccess)
-    return -3;
+  if (cudaMemcpy(&code, st, sizeof(code), cudaMemcpyDeviceToHost) != cudaSuccess) return -3;
+  // reported once: the record is cleared so that it describes the calls made after this one
+  if (code != 0 && cudaMemset(st, 0, sizeof(iris::StatusBlock)) != cudaSuccess) return -3;
   return (int)code;
 }
 

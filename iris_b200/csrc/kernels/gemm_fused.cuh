@@ -16,7 +16,9 @@ namespace gemm {
 
 constexpr int kMaxRanks = 8;
 
-// Tile shape of one CTA: 128 x 256 output elements, 64-deep K slices (128 bytes of bf16: one swizzle row).
+// Tile shape of one CTA: 128 rows x up to 256 columns of output, 64-deep K slices (128 bytes of a 16-bit type: one
+// swizzle row).  The width actually used is a launch parameter (FusedGemmParams::bn: 64, 128 or 256); BN is the
+// widest, for which shared memory and tensor memory are laid out.
 constexpr int BM = 128;
 constexpr int BN = 256;
 constexpr int BK = 64;
@@ -41,6 +43,17 @@ enum TraceSlot : int { kTrMmaBegin = 0, kTrMmaEnd = 1, kTrEpiBegin = 2, kTrEpiEn
 constexpr int kThreads = 256;      // warp 0: TMA producer, warp 1: MMA issuer, warps 2-5: epilogue, warps 6-7: all-gather push
 constexpr int kThreadsPull = 320;  // one-/two-shot kernels: warps 6-9 are the reducer (pull, sum, write) instead
 
+// How a finished tile reaches the other ranks in store mode with store_all (GEMM + all-scatter).
+enum PushKind : int {
+  kPushTma = 0,       // one thread issues a TMA store per destination rank
+  kPushTmaSpread = 1, // the four epilogue warp leaders share the destination ranks
+  kPushStores = 2,    // all 128 epilogue threads copy the staged sub-tile with 16-byte stores, a row segment per 8 lanes
+  kPushMultimem = 3,  // as kPushStores, but ONE multimem.st per 16 bytes: the NVLink switch delivers it to every rank
+};
+
+// Element type of A, B and C (accumulation is always fp32).
+enum ElemType : int { kBf16 = 0, kFp16 = 1 };
+
 enum EpiMode : int {
   kEpiStore = 0,    // C tile -> TMA store into the C buffer of every rank (world 1: plain GEMM)
   kEpiReduce = 1,   // C tile -> TMA reduce-add into the C buffer of every rank (C must start at zero)
@@ -51,7 +64,7 @@ enum EpiMode : int {
 struct FusedGemmParams {
   // Tensor maps (host-encoded).  Index = local rank for A and B, target rank for C.
   CUtensorMap tmA[kMaxRanks];  // [rows M, cols K] bf16, K contiguous, box 64 x 128, 128-byte swizzle
-  CUtensorMap tmB[kMaxRanks];  // [rows N, cols K] bf16, K contiguous, box 64 x 256, 128-byte swizzle
+  CUtensorMap tmB[kMaxRanks];  // [rows N, cols K] bf16, K contiguous, box 64 x b_box_rows, 128-byte swizzle
   CUtensorMap tmC[kMaxRanks];  // [rows M, cols ldc] bf16, box 64 x 128, 128-byte swizzle
                                //   store/reduce: the output of rank t; one-/two-shot: the partial buffer of rank t
   uint64_t heap_base[kMaxRanks];  // base address of every rank's heap in this process
@@ -97,6 +110,14 @@ struct FusedGemmParams {
   int store_all;         // store/reduce modes: 1 = push the tile to every rank, 0 = own rank only
   int tile_flag_base;    // index (uint32 units from flags_off) of the per-tile flags
   int ag_flag_base;      // index of the all-gather chunk flags: [src rank][chunk]
+  int bn;                // tile width in columns: 64, 128 or 256 (multiple of 64)
+  int b_box_rows;        // rows of the B tensor map's box; a stage's B rows are fetched as (rows / b_box_rows) loads
+  int dtype;             // ElemType of A, B, C
+  int push_kind;         // PushKind (store mode with store_all)
+  int tail_tiles;        // the last `tail_tiles` tiles of the raster are cut into `tail_split` column pieces each
+  int tail_split;        //   (see tail_split_plan in gemm_schedule.h); 0 / 1 = no split
+  int ldc;               // row pitch (elements) of the C buffers, for the pushes made with ordinary / multimem stores
+  uint64_t c_off;        // symmetric offset of the C buffer (store / reduce with store_all)
   uint32_t c_box_bytes;  // bytes of one C / partial sub-tile transfer: rows of the tmC box (128, fewer when M < 128) x 128
   uint32_t epoch;        // call number (1, 2, ...): value of the entry flags in this call
   uint32_t flag_target;  // value per-tile / per-chunk flags reach in this call (cumulative over calls)

@@ -15,8 +15,9 @@
  * (about 8 MB) reserved until the process exits, whether or not this function is ever called.
  *
  * Limits: M * N <= IRIS_GEMM_NOALLOC_MAX_ELEMS and at most IRIS_GEMM_NOALLOC_MAX_TILES output tiles of
- * 128 x 256; N and K multiples of 8; all three base addresses and row pitches multiples of 16 bytes.  Larger
- * problems are rejected with a non-zero return code and a message (iris_gemm_last_error()).
+ * 128 x 256; N and K multiples of 8; all three base addresses and row pitches multiples of 16 bytes; lda and ldb
+ * at least K, ldo at least N and below 2^31.  Larger problems are rejected with a non-zero return code and a message
+ * (iris_gemm_last_error()).
  *
  * It calls no cudaMalloc, cudaFree or any other allocating routine, on the device or through a library.
  *
@@ -25,9 +26,9 @@
  * before starting any stream capture on that device.
  *
  * Sharing: every call on a device uses the same scratch, which still holds the previous call's contents; the
- * function clears the flags and the status record on `stream` before it launches.  Two calls whose kernels
- * may overlap on the GPU (different streams without an ordering between them) race on that scratch: order
- * them.
+ * function clears the per-tile flags on `stream` before it launches.  Two calls whose kernels may overlap on
+ * the GPU (different streams without an ordering between them) race on that scratch: order them.  The first
+ * call on a device may come from several host threads at once; the set-up is done once, under a lock.
  *
  * Returns 0 on success; -1 bad argument, -2 problem larger than the built-in scratch, -3 CUDA error.
  * After the stream has finished, iris_gemm_noalloc_status() reports whether a bounded wait inside the kernel
@@ -50,8 +51,8 @@ extern "C" {
 int iris_gemm_noalloc(const void* a, int64_t lda, const void* bt, int64_t ldb, void* out, int64_t ldo, int M, int N,
                       int K, void* stream);
 
-/* Synchronises the current device and returns the status code the last call(s) left in the scratch
- * (0 = none, 1 = a bounded wait expired).  Not needed on the fast path. */
+/* Synchronises the current device and returns the status code left in the scratch by the calls made since the
+ * previous query (0 = none, 1 = a bounded wait expired), then clears the record.  Not needed on the fast path. */
 int iris_gemm_noalloc_status(void);
 
 #ifdef __cplusplus

@@ -57,7 +57,30 @@ IRIS_SCHED_HD int rs_tile_of(int step, int rank, int world, int tiles_per_block)
 struct Work {
   int tile, kb0, kb1;
   int piece;  // K-split piece of the tile (0 when tiles are not K-split into slots)
+  int sub;    // column piece of a tail tile (0 .. tail_split - 1), 0 for a whole tile
+  int nsub;   // number of column pieces this tile is cut into (1: the piece is the whole tile)
 };
+
+// How many tiles at the end of the raster are cut into column pieces, and into how many, so that the last, ragged
+// wave of a persistent schedule keeps every unit busy: with T tiles on G units the last T % G tiles would occupy
+// only that many units for a whole tile time.  Cutting each of them into s column pieces (each piece a narrower MMA
+// on the same A rows, nothing to fix up afterwards, unlike a K split) turns the wave into (T % G) * s pieces of
+// 1 / s tile time.  s is the largest divisor of `max_split` with (T % G) * s <= G; 1 (no split) when the ragged
+// wave is more than half full or there is no full wave before it.
+IRIS_SCHED_HD void tail_split_plan(int total_tiles, int units, int max_split, int* tail_tiles, int* split) {
+  *tail_tiles = 0;
+  *split = 1;
+  if (units < 1 || total_tiles <= units) return;
+  const int r = total_tiles % units;
+  if (r == 0 || 2 * r > units) return;
+  int s = 1;
+  for (int c = 2; c <= max_split; c *= 2)
+    if (max_split % c == 0 && r * c <= units) s = c;
+  if (s > 1) {
+    *tail_tiles = r;
+    *split = s;
+  }
+}
 
 // Persistent + stream-K schedule.  Tiles [0, dp_tiles) are taken whole, round-robin over the units (the reference's
 // `for tile_id in range(pid, total_tiles, NUM_SMS)`, examples/07_gemm_all_scatter/gemm_all_scatter.py:153).  The
@@ -66,20 +89,33 @@ struct Work {
 // kernels never use them).  A unit's range may end in the middle of a tile; such a tile is finished by whichever
 // unit adds the last missing k-blocks (see the epilogue).  With `ksplit` > 1 every tile is instead cut into `ksplit`
 // fixed slices of its k-blocks and the (tile, piece) items go round-robin over the units.
+// With `tail_tiles` > 0 (whole-tile schedules only) the last `tail_tiles` tiles are not part of the round-robin: each
+// is cut into `tail_split` column pieces and the pieces go round-robin over the units after the whole tiles.
 struct WorkIter {
   int G, dp_tiles, kblocks, next_dp, ksplit, items;
+  int tail0, tail_split, tail_items, next_tail;
   long long it, end;
-  IRIS_SCHED_HD WorkIter(int unit, int G_, int total_tiles, int kblocks_, int dp_tiles_, int sk_units, int ksplit_)
+  IRIS_SCHED_HD WorkIter(int unit, int G_, int total_tiles, int kblocks_, int dp_tiles_, int sk_units, int ksplit_,
+                         int tail_tiles = 0, int tail_split_ = 1)
       : G(G_), dp_tiles(dp_tiles_), kblocks(kblocks_), next_dp(unit), ksplit(ksplit_ > 1 ? ksplit_ : 1),
-        items(total_tiles * (ksplit_ > 1 ? ksplit_ : 1)), it(0), end(0) {
+        items(total_tiles * (ksplit_ > 1 ? ksplit_ : 1)), tail0(total_tiles), tail_split(1), tail_items(0),
+        next_tail(unit), it(0), end(0) {
     const long long S = (long long)(total_tiles - dp_tiles_) * kblocks_;
     if (S > 0 && unit < sk_units) {
       it = S * unit / sk_units;
       end = S * (unit + 1) / sk_units;
     }
+    if (tail_tiles > 0 && tail_split_ > 1 && ksplit == 1 && dp_tiles_ == total_tiles) {
+      tail0 = total_tiles - tail_tiles;
+      dp_tiles = tail0;
+      tail_split = tail_split_;
+      tail_items = tail_tiles * tail_split_;
+    }
   }
   IRIS_SCHED_HD bool next(Work& w) {
     w.piece = 0;
+    w.sub = 0;
+    w.nsub = 1;
     if (ksplit > 1) {
       // K-split into inbox slots: item i = (tile i / ksplit, piece i % ksplit), each a fixed slice of the k-blocks
       if (next_dp >= items) return false;
@@ -106,6 +142,15 @@ struct WorkIter {
       w.kb0 = kb0;
       w.kb1 = kb0 + len;
       it += len;
+      return true;
+    }
+    if (next_tail < tail_items) {
+      w.tile = tail0 + next_tail / tail_split;
+      w.sub = next_tail % tail_split;
+      w.nsub = tail_split;
+      w.kb0 = 0;
+      w.kb1 = kblocks;
+      next_tail += G;
       return true;
     }
     return false;

@@ -43,6 +43,15 @@ __device__ __forceinline__ uint4 ld_reduce_add_bf16x8(const void* mc) {
                : "memory");
   return v;
 }
+// The same for 8 fp16 values.
+__device__ __forceinline__ uint4 ld_reduce_add_f16x8(const void* mc) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(mc)
+               : "memory");
+  return v;
+}
 __device__ __forceinline__ uint4 ld_reduce_add_f32x4(const void* mc) {
   uint4 v;
   asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"

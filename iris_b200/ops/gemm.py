@@ -1,4 +1,4 @@
-"""Fused bf16 GEMM + collective operators on the tcgen05 kernel of ``csrc/kernels/gemm_fused.cu``.
+"""Fused bf16 / fp16 GEMM + collective operators on the tcgen05 kernel of ``csrc/kernels/gemm_fused.cu``.
 
 Role in the reference: the ``matmul`` autograd-Function wrappers that launch the persistent Triton kernels
 (``examples/07_gemm_all_scatter/matmul_wrapper.py:19-219`` and its copies in 08/09) together with the buffer
@@ -23,9 +23,12 @@ import torch
 
 from .. import _native
 from ..context import Iris
-from .gemm_plan import BK, BM, BN, FLAG_HEADER, MODES, GemmPlan, plan_gemm  # noqa: F401  (re-exported)
+from .gemm_plan import (BK, BM, BN, DTYPES, FLAG_HEADER, MODES, PUSH_KINDS, TILE_WIDTHS, GemmPlan,  # noqa: F401
+                        plan_gemm)
 
 MAX_RANKS = 8
+# How GEMM + all-scatter tiles are pushed unless the caller says otherwise (see FusedGemm, ``push_kind``).
+DEFAULT_PUSH_KIND = "tma"
 
 
 class _Desc(ctypes.Structure):
@@ -49,6 +52,9 @@ class _Desc(ctypes.Structure):
         ("dp_tiles", ctypes.c_int), ("sk_units", ctypes.c_int), ("sk_flag_base", ctypes.c_int),
         ("push_partials", ctypes.c_int), ("part_slot_rows", ctypes.c_int), ("ksplit", ctypes.c_int),
         ("rs_rows", ctypes.c_int),
+        ("bn", ctypes.c_int), ("dtype", ctypes.c_int), ("push_kind", ctypes.c_int),
+        ("tail_tiles", ctypes.c_int), ("tail_split", ctypes.c_int),
+        ("c_off", ctypes.c_uint64),
     ]
 
 
@@ -70,9 +76,14 @@ def _lib():
     return lib
 
 
-def _check_operand(t: torch.Tensor, name: str):
-    if t.dtype != torch.bfloat16:
-        raise TypeError(f"{name} must be bfloat16, got {t.dtype}")
+_TORCH_DTYPES = {torch.bfloat16: "bf16", torch.float16: "fp16"}
+
+
+def _check_operand(t: torch.Tensor, name: str, dtype: Optional[torch.dtype] = None):
+    if t.dtype not in _TORCH_DTYPES:
+        raise TypeError(f"{name} must be bfloat16 or float16, got {t.dtype}")
+    if dtype is not None and t.dtype != dtype:
+        raise TypeError(f"{name} is {t.dtype}, the other operands are {dtype}")
     if t.dim() != 2 or t.stride(1) != 1:
         raise ValueError(f"{name} must be 2-D with a contiguous last dimension (K-major)")
     if t.data_ptr() % 16 or (t.stride(0) * 2) % 16:
@@ -109,6 +120,16 @@ class FusedGemm:
         push / ksplit: one-shot for short matrices: partials pushed into inbox slots of every rank, K cut into pieces.
         nvls: two-shot on a heap bound to an NVLS multicast object: ``None`` = use it when available.
         trace: record per-tile device timestamps (``trace_records()``).
+        bn: tile width in columns, 64 / 128 / 256 (default 256).  Together with ``cta_group`` (128 or 256 rows) this
+            gives the six tile shapes of the kernel (the reference's per-shape ``BLK_M`` / ``BLK_N``,
+            ``dataset/tiling.json``).
+        tail_split: cut the tiles of a ragged last wave into column pieces (default: on where it applies).
+        push_kind: how all-scatter tiles travel: ``"tma"`` (one thread issues a TMA store per rank), ``"tma_spread"``
+            (four issuing threads), ``"stores"`` (16-byte stores by all epilogue threads) or ``"multimem"`` (one
+            ``multimem.st`` per 16 bytes on a heap bound to an NVLS multicast object).  ``None``: ``DEFAULT_PUSH_KIND``.
+
+    The element type (bf16 or fp16, fp32 accumulation) is taken from ``bt``; the reference's drivers offer
+    ``--datatype fp16|bf16|...`` (``examples/07_gemm_all_scatter/benchmark.py:36-41``).
     """
 
     def __init__(self, ctxs: Union[Iris, Sequence[Iris]], a: Optional[Sequence[torch.Tensor]],
@@ -118,7 +139,8 @@ class FusedGemm:
                  ctas_per_rank: Optional[int] = None, group_m: int = 8, timeout_ms: float = 2000.0,
                  cta_group: Optional[int] = None, trace: bool = False, stream_k: Optional[bool] = None,
                  push: Optional[bool] = None, ksplit: Optional[int] = None, nvls: Optional[bool] = None,
-                 reduce_scatter: bool = False):
+                 reduce_scatter: bool = False, bn: Optional[int] = None, tail_split: Optional[bool] = None,
+                 push_kind: Optional[str] = None):
         self.ctxs: List[Iris] = [ctxs] if isinstance(ctxs, Iris) else list(ctxs)
         c0 = self.ctxs[0]
         if c0.backend != "cuda":
@@ -132,8 +154,9 @@ class FusedGemm:
         self.mode = mode
         self.rank0 = c0.get_rank()
         bt = [as_kmajor_bt(x) for x in bt]
+        self.dtype = bt[0].dtype
         for x in bt:
-            _check_operand(x, "B")
+            _check_operand(x, "B", self.dtype)
         self.N, self.K = bt[0].shape
         self.ag = bool(ag)
         if mode in ("one_shot", "two_shot") and ag:
@@ -143,12 +166,12 @@ class FusedGemm:
                 raise ValueError("ag=True needs M (rows of the gathered A)")
             self.M = int(M)
             # gathered A lives on the heap: peers write their rows into it
-            self.a_full = [c.zeros((self.M, self.K), dtype=torch.bfloat16) for c in self.ctxs]
+            self.a_full = [c.zeros((self.M, self.K), dtype=self.dtype) for c in self.ctxs]
             a_use = self.a_full
         else:
             a_use = list(a)
             for x in a_use:
-                _check_operand(x, "A")
+                _check_operand(x, "A", self.dtype)
             self.M = a_use[0].shape[0]
             if a_use[0].shape[1] != self.K:
                 raise ValueError(f"K mismatch: A has {a_use[0].shape[1]}, B has {self.K}")
@@ -158,7 +181,8 @@ class FusedGemm:
         # tile shape, persistent grid, schedule, flag count and buffer layout: a pure function of the problem
         pl = plan_gemm(self.M, self.N, self.K, self.world, self.num_local, mode, sms, ag=self.ag, cta_group=cta_group,
                        ctas_per_rank=ctas_per_rank, group_m=group_m, stream_k=stream_k, push=push, ksplit=ksplit,
-                       reduce_scatter=reduce_scatter, store_all=store_all, own_out=out is not None)
+                       reduce_scatter=reduce_scatter, store_all=store_all, own_out=out is not None, bn=bn,
+                       tail_split=tail_split)
         self.plan = pl
         cta_group, group_m = pl.cta_group, pl.group_m
         self.cta_group, self.rs_rows, self.ctas_per_rank = pl.cta_group, pl.rs_rows, pl.ctas_per_rank
@@ -177,7 +201,7 @@ class FusedGemm:
             # the output: [partial 0 | partial 1 | out], each padded to whole 256-row tiles, so that one tensor
             # map per rank serves partial stores, partial loads and output stores.
             rows, mp, slots, regions = pl.rows, pl.slot_rows, pl.slots, pl.regions
-            self._pull_buf = [c.zeros((regions * mp, self.N), dtype=torch.bfloat16) for c in self.ctxs]
+            self._pull_buf = [c.zeros((regions * mp, self.N), dtype=self.dtype) for c in self.ctxs]
             self.partial = [[b[q * slots * mp:q * slots * mp + rows] for b in self._pull_buf] for q in range(2)]
             self.out = list(out) if out is not None else [b[2 * slots * mp:2 * slots * mp + rows]
                                                           for b in self._pull_buf]
@@ -186,13 +210,13 @@ class FusedGemm:
             c_rows, part_row0, out_row0 = pl.c_rows, pl.part_row0, pl.out_row0
             self._slot_rows = mp
         else:
-            self.out = list(out) if out is not None else [c.zeros((self.M, self.c_cols), dtype=torch.bfloat16)
+            self.out = list(out) if out is not None else [c.zeros((self.M, self.c_cols), dtype=self.dtype)
                                                           for c in self.ctxs]
             c_bufs, c2_bufs = self.out, None
             ldc, c_cols_eff = self.out[0].stride(0), self.c_cols
             c_rows, part_row0, out_row0 = 0, (0, 0), -1
         for o in self.out:
-            _check_operand(o, "output")
+            _check_operand(o, "output", self.dtype)
         d = _Desc()
         for l, ctx in enumerate(self.ctxs):
             d.a_ptr[l], d.lda[l] = a_use[l].data_ptr(), a_use[l].stride(0)
@@ -238,12 +262,28 @@ class FusedGemm:
         d.sk_units = self.sk_units
         d.sk_flag_base = FLAG_HEADER + tile_flags + self.world * chunks_per_shard
         d.ws_off = c0.offset_of(self.workspace[0]) if self.workspace else 0
+        d.bn, d.dtype = pl.bn, DTYPES[_TORCH_DTYPES[self.dtype]]
+        d.tail_tiles, d.tail_split = pl.tail_tiles, pl.tail_split
+        self.bn, self.tail_tiles, self.tail_split = pl.bn, pl.tail_tiles, pl.tail_split
+        d.c_off = c_off if self.store_all else 0
         # two-shot on a heap bound to an NVLS multicast object: the switch sums and broadcasts
         mc = int(getattr(c0, "mc_base", 0) or 0)
         self.nvls = bool(mc) and mode == "two_shot" and self.num_local == 1 and out is None and nvls is not False
         if nvls and not self.nvls:
             raise RuntimeError("nvls=True needs heap_mode='vmm' with IRIS_NVLS=1, mode='two_shot', one process per GPU")
-        d.mc_base = mc if self.nvls else 0
+        # all-scatter pushes: which instructions carry a finished tile to the other ranks
+        pk = DEFAULT_PUSH_KIND if push_kind is None else push_kind
+        if pk not in PUSH_KINDS:
+            raise ValueError(f"push_kind must be one of {sorted(PUSH_KINDS)}")
+        if pk == "multimem" and not (mc and self.num_local == 1):
+            if push_kind is not None:
+                raise RuntimeError("push_kind='multimem' needs heap_mode='vmm' with IRIS_NVLS=1, one process per GPU")
+            pk = "tma"
+        if not (self.store_all and mode == "store"):
+            pk = "tma"
+        self.push_kind = pk
+        d.push_kind = PUSH_KINDS[pk]
+        d.mc_base = mc if (self.nvls or pk == "multimem") else 0
         self.ag_slices = int(ag_slices)
         lib = _lib()
         self._plan = lib.iris_gemm_plan_create(ctypes.byref(d))
@@ -305,7 +345,8 @@ class FusedGemm:
         ``examples/07_gemm_all_scatter/matmul_wrapper.py:152-155``).  Empty when the build record is missing."""
         from .. import _build
         pull = self.mode in ("one_shot", "two_shot")
-        want = f"fused_gemm_kernel<{self.cta_group}, {'true' if pull else 'false'}>"
+        want = (f"fused_gemm_kernel<{self.cta_group}, {'true' if pull else 'false'}, "
+                f"{'true' if self.dtype == torch.float16 else 'false'}>")
         for name, res in _build.kernel_resources().items():
             if want in name:
                 return dict(res, kernel=want)
@@ -375,8 +416,8 @@ _private_ctx = {}
 
 
 def gemm(a: torch.Tensor, bt: torch.Tensor, out: Optional[torch.Tensor] = None,
-         cta_group: Optional[int] = None) -> torch.Tensor:
-    """Single-GPU ``a @ bt.T`` on the tcgen05 kernel (world of one, no communication)."""
+         cta_group: Optional[int] = None, bn: Optional[int] = None, tail_split: Optional[bool] = None) -> torch.Tensor:
+    """Single-GPU ``a @ bt.T`` on the tcgen05 kernel (world of one, no communication); bf16 or fp16."""
     dev = a.device
     ctx = _private_ctx.get(dev)
     if ctx is None:
@@ -385,9 +426,9 @@ def gemm(a: torch.Tensor, bt: torch.Tensor, out: Optional[torch.Tensor] = None,
         _private_ctx[dev] = ctx
     n = as_kmajor_bt(bt).shape[0]
     if out is None:
-        out = torch.empty((a.shape[0], n), dtype=torch.bfloat16, device=dev)
+        out = torch.empty((a.shape[0], n), dtype=a.dtype, device=dev)
     mark = ctx.mark()
-    op = FusedGemm(ctx, [a], [bt], "store", out=[out], cta_group=cta_group)
+    op = FusedGemm(ctx, [a], [bt], "store", out=[out], cta_group=cta_group, bn=bn, tail_split=tail_split)
     op()
     op.close()
     torch.cuda.current_stream(dev).synchronize()  # the plan's flags and workspace are released just below
@@ -415,7 +456,8 @@ class matmul(torch.autograd.Function):
         if matmul._debug:
             print(f"[iris_b200.matmul] mode={op.mode} M={op.M} N={op.N} K={op.K} world={op.world} "
                   f"cta_group={op.cta_group} ctas/rank={op.ctas_per_rank} tiles={op.total_tiles} "
-                  f"whole_tiles={op.dp_tiles} stream_k_units={op.sk_units} ksplit={op.ksplit} push={op.push}")
+                  f"whole_tiles={op.dp_tiles} stream_k_units={op.sk_units} ksplit={op.ksplit} push={op.push} "
+                  f"tile={BM * op.cta_group}x{op.bn} tail={op.tail_tiles}x{op.tail_split} push_kind={op.push_kind}")
         out = op(stream)
         return out[0] if len(out) == 1 else tuple(out)
 

@@ -9,8 +9,11 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Optional, Tuple
 
-BM, BN, BK = 128, 256, 64   # the compiled tile of the kernel (rows per CTA, columns, k-block)
+BM, BN, BK = 128, 256, 64   # rows per CTA, widest tile in columns, k-block; the tile width is a launch parameter
+TILE_WIDTHS = (64, 128, 256)
 MODES = {"store": 0, "reduce": 1, "one_shot": 2, "two_shot": 3}
+PUSH_KINDS = {"tma": 0, "tma_spread": 1, "stores": 2, "multimem": 3}
+DTYPES = {"bf16": 0, "fp16": 1}
 FLAG_HEADER = 16            # flag words [0] arrival counter, [8 + r] entry flag of rank r; per-tile flags follow
 
 
@@ -48,6 +51,9 @@ class GemmPlan:
     c_rows: int
     part_row0: Tuple[int, int]
     out_row0: int
+    bn: int = BN            # tile width in columns
+    tail_tiles: int = 0     # tiles at the end of the raster that are cut into column pieces ...
+    tail_split: int = 1     # ... and into how many (1: none)
 
     @property
     def flags_per_call(self) -> int:
@@ -55,14 +61,38 @@ class GemmPlan:
         return self.world * self.ksplit
 
 
+def tail_split_plan(total_tiles: int, units: int, max_split: int) -> Tuple[int, int]:
+    """``(tail_tiles, split)``: the ragged last wave of ``total_tiles`` on ``units`` scheduling units is cut into
+    column pieces when it fills at most half of the units (the same rule as ``tail_split_plan`` in
+    ``csrc/kernels/gemm_schedule.h``; the reference's persistent loop has the ragged wave and nothing against it,
+    ``examples/07_gemm_all_scatter/gemm_all_scatter.py:153``)."""
+    if units < 1 or total_tiles <= units:
+        return 0, 1
+    r = total_tiles % units
+    if r == 0 or 2 * r > units:
+        return 0, 1
+    s, c = 1, 2
+    while c <= max_split:
+        if max_split % c == 0 and r * c <= units:
+            s = c
+        c *= 2
+    return (r, s) if s > 1 else (0, 1)
+
+
 def plan_gemm(M: int, N: int, K: int, world: int, num_local: int, mode: str, sms: int, *, ag: bool = False,
               cta_group: Optional[int] = None, ctas_per_rank: Optional[int] = None, group_m: int = 8,
               stream_k: Optional[bool] = None, push: Optional[bool] = None, ksplit: Optional[int] = None,
-              reduce_scatter: bool = False, store_all: bool = False, own_out: bool = False) -> GemmPlan:
+              reduce_scatter: bool = False, store_all: bool = False, own_out: bool = False,
+              bn: Optional[int] = None, tail_split: Optional[bool] = None) -> GemmPlan:
     """Decide tile shape, persistent grid, schedule, flag count and buffer layout.  ``sms``: SMs of the device;
-    ``own_out``: the caller brings the output buffer (the [partials | out] matrix then has no output region)."""
+    ``own_out``: the caller brings the output buffer (the [partials | out] matrix then has no output region);
+    ``bn``: tile width (64, 128 or 256; default 256); ``tail_split``: cut the tiles of a ragged last wave into column
+    pieces (default: on for the store / reduce modes with whole tiles)."""
     if mode not in MODES:
         raise ValueError(f"mode must be one of {sorted(MODES)}")
+    bn = BN if bn is None else int(bn)
+    if bn not in TILE_WIDTHS:
+        raise ValueError(f"tile width must be one of {TILE_WIDTHS}")
     if mode in ("one_shot", "two_shot") and ag:
         raise ValueError("the all-gather prologue is combined with mode='store' only")
     # CTA pairs (256 x 256 tiles, cta_group::2) for anything taller than one 128-row tile; single CTAs else
@@ -85,7 +115,7 @@ def plan_gemm(M: int, N: int, K: int, world: int, num_local: int, mode: str, sms
         group_m = max(g for g in range(1, max(1, int(group_m)) + 1) if mt % g == 0)
     ctas = int(ctas_per_rank) if ctas_per_rank else sms // num_local
     ctas -= ctas % cta_group
-    tiles_m, tiles_n = -(-M // (BM * cta_group)), -(-N // BN)
+    tiles_m, tiles_n = -(-M // (BM * cta_group)), -(-N // bn)
     T = tiles_m * tiles_n
     kblocks = -(-K // BK)
     # ---- schedule: whole tiles round-robin, plus (stream-K) a tail of tiles split by k-blocks ----
@@ -121,6 +151,13 @@ def plan_gemm(M: int, N: int, K: int, world: int, num_local: int, mode: str, sms
             dp_tiles, sk_units, sk_tiles = T, 0, 0
             ctas = min(max_units, T * ks) * cta_group
     pulls = mode in ("one_shot", "two_shot")
+    # ---- ragged last wave of a whole-tile schedule: cut its tiles into column pieces (nothing to fix up) ----
+    tail_tiles, tsplit = 0, 1
+    if (tail_split is None or tail_split) and not pulls and not sk_units and ks == 1:
+        max_split = min(4, bn // 64)                      # pieces are whole 64-column sub-tiles
+        while max_split > 1 and ((bn // max_split) // cta_group) % 8:
+            max_split //= 2
+        tail_tiles, tsplit = tail_split_plan(T, max(1, ctas // cta_group), max_split)
     chunks_per_shard = (M // world) // BM if ag else 0
     tile_flags = T * cta_group if pulls else 0
     sk_flags = sk_tiles * cta_group
@@ -142,4 +179,5 @@ def plan_gemm(M: int, N: int, K: int, world: int, num_local: int, mode: str, sms
                     dp_tiles=dp_tiles, sk_units=sk_units, sk_tiles=sk_tiles, push=do_push, ksplit=ks,
                     store_all=bool(store_all) and world > 1, pulls=pulls, chunks_per_shard=chunks_per_shard,
                     tile_flags=tile_flags, sk_flags=sk_flags, nflags=nflags, rows=rows, slot_rows=mp, slots=slots,
-                    regions=regions, c_rows=c_rows, part_row0=part_row0, out_row0=out_row0)
+                    regions=regions, c_rows=c_rows, part_row0=part_row0, out_row0=out_row0, bn=bn,
+                    tail_tiles=tail_tiles, tail_split=tsplit)

@@ -17,9 +17,9 @@ if not torch.cuda.is_available():
     pytest.skip("needs a CUDA device", allow_module_level=True)
 
 
-def _rand(shape, seed, scale=1.0):
+def _rand(shape, seed, scale=1.0, dtype=torch.bfloat16):
     g = torch.Generator(device="cuda").manual_seed(seed)
-    return (torch.randn(shape, generator=g, device="cuda", dtype=torch.float32) * scale).to(torch.bfloat16)
+    return (torch.randn(shape, generator=g, device="cuda", dtype=torch.float32) * scale).to(dtype)
 
 
 def _assert_close(got, ref_fp32, scale=None, ulps=2.0):
@@ -41,6 +41,43 @@ def test_plain_gemm(m, n, k, cta_group):
     out = G.gemm(a, bt, cta_group=cta_group)
     torch.cuda.synchronize()
     _assert_close(out, a.float() @ bt.float().t())
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("bn", [64, 128, 256])
+@pytest.mark.parametrize("m,n,k,cta_group", [(384, 832, 192, 1), (1000, 520, 1376, 2), (100, 1024, 512, 1)])
+def test_gemm_tile_widths_and_element_types(m, n, k, cta_group, bn, dtype):
+    """The six tile shapes (128 or 256 rows x 64 / 128 / 256 columns) in both 16-bit element types, ragged edges."""
+    a, bt = _rand((m, k), 1, dtype=dtype), _rand((n, k), 2, 0.05, dtype=dtype)
+    out = G.gemm(a, bt, cta_group=cta_group, bn=bn)
+    torch.cuda.synchronize()
+    assert out.dtype == dtype
+    _assert_close(out, a.float() @ bt.float().t())
+
+
+@pytest.mark.parametrize("bn", [128, 256])
+@pytest.mark.parametrize("m,n,k,cta_group", [(2560, 2048, 256, 2), (2560, 2048, 256, 1), (2816, 1800, 320, 2)])
+def test_column_split_tail(m, n, k, cta_group, bn):
+    """More tiles than scheduling units with a small ragged last wave: its tiles are cut into column pieces computed
+    by different units (narrower MMAs, B fetched in narrower boxes).  Same result as the unsplit schedule, bit for bit."""
+    a, bt = _rand((m, k), 3), _rand((n, k), 4, 0.05)
+    ctx = iris.Iris.local_world(1, heap_size=64 << 20)[0]
+    outs = []
+    for split in (True, False):
+        out = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
+        op = G.FusedGemm(ctx, [a], [bt], "store", out=[out], cta_group=cta_group, bn=bn, tail_split=split)
+        if split:
+            assert op.tail_tiles > 0 and op.tail_split > 1, "shape does not exercise the split tail on this device"
+        else:
+            assert op.tail_tiles == 0
+        for _ in range(2):
+            op()
+        op.check()
+        _assert_close(out, a.float() @ bt.float().t())
+        outs.append(out)
+        op.close()
+    assert torch.equal(outs[0], outs[1])
+    ctx.close()
 
 
 def test_many_tiles_per_cta_pair():
@@ -78,6 +115,29 @@ def test_gemm_strided_views():
     out = G.gemm(a, bt)
     torch.cuda.synchronize()
     _assert_close(out, a.float() @ bt.float().t())
+
+
+@pytest.mark.parametrize("push_kind", ["tma", "tma_spread", "stores"])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("world,m,n_local,bn", [(2, 2560, 1024, 256), (4, 1000, 320, 128), (8, 512, 192, 64)])
+def test_gemm_all_scatter_push_kinds(world, m, n_local, bn, dtype, push_kind):
+    """Every way a finished tile travels to the other ranks (TMA stores from one or four issuing threads, 16-byte
+    stores by all epilogue threads), with the column-split tail, narrower tiles, fp16 and a ragged M.  (The multimem
+    form needs an NVLS-bound heap across real GPUs: tests/workers/gpu_vmm_nvls.py.)"""
+    k = 384
+    ranks = iris.Iris.local_world(world, heap_size=64 << 20)
+    a = _rand((m, k), 5, dtype=dtype)
+    bts = [_rand((n_local, k), 10 + r, 0.05, dtype=dtype) for r in range(world)]
+    op = G.gemm_all_scatter(ranks, [a] * world, bts, bn=bn, push_kind=push_kind)
+    assert op.push_kind == push_kind
+    for _ in range(3):
+        outs = op()
+    op.check()
+    ref = torch.cat([a.float() @ b.float().t() for b in bts], dim=1)
+    for r in range(world):
+        _assert_close(outs[r], ref)
+    op.close()
+    ranks[0].close()
 
 
 @pytest.mark.parametrize("stream_k", [False, True])
@@ -119,6 +179,33 @@ def test_gemm_all_reduce_emulated(variant, world, cta_group, stream_k):
     scale = sum(p.abs() for p in parts)
     for r in range(world):
         _assert_close(outs[r], ref, scale=scale, ulps=2.0 + world)
+    op.close()
+    ranks[0].close()
+
+
+@pytest.mark.parametrize("variant", ["atomic", "one_shot", "two_shot", "reduce_scatter"])
+@pytest.mark.parametrize("bn,dtype", [(128, torch.float16), (64, torch.bfloat16), (256, torch.float16)])
+def test_collectives_in_fp16_and_narrow_tiles(variant, bn, dtype):
+    """The reductions with fp16 operands (fp32 accumulation and summing) and with 64- / 128-column tiles."""
+    world, m, n, k_full = 2, 1024, 832, 1408
+    ks = k_full // world
+    ranks = iris.Iris.local_world(world, heap_size=128 << 20)
+    a_full, b_full = _rand((m, k_full), 6, dtype=dtype), _rand((n, k_full), 7, 0.05, dtype=dtype)
+    a = [a_full[:, r * ks:(r + 1) * ks] for r in range(world)]
+    bt = [b_full[:, r * ks:(r + 1) * ks] for r in range(world)]
+    if variant == "reduce_scatter":
+        op = G.gemm_reduce_scatter(ranks, a, bt, bn=bn)
+    else:
+        op = G.gemm_all_reduce(ranks, a, bt, variant=variant, bn=bn)
+    for _ in range(3):
+        outs = op()
+    op.check()
+    parts = [a[r].float() @ bt[r].float().t() for r in range(world)]
+    ref, scale = sum(parts), sum(p.abs() for p in parts)
+    for r in range(world):
+        rows = slice(r * m // world, (r + 1) * m // world) if variant == "reduce_scatter" else slice(0, m)
+        assert outs[r].dtype == dtype
+        _assert_close(outs[r], ref[rows], scale=scale[rows], ulps=2.0 + world)
     op.close()
     ranks[0].close()
 
@@ -221,6 +308,31 @@ def test_all_gather_gemm_emulated(world, cta_group):
         for r in range(world):
             assert torch.equal(op.a_full[r], a_full), f"gathered A differs on rank {r}"
             _assert_close(outs[r], a_full.float() @ bts[r].float().t())
+    op.close()
+    ranks[0].close()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_all_gather_gemm_back_to_back_calls_with_new_rows(world):
+    """Calls follow one another on the stream with DIFFERENT rows and no host synchronisation in between: a rank
+    must not write call k + 1's rows into a peer's gathered A while that peer still loads call k's (the entry-flag
+    wait of the communication warps).  Every call's product is kept and checked at the end."""
+    m, n_local, k, calls = 1024, 256, 512, 4
+    ms = m // world
+    ranks = iris.Iris.local_world(world, heap_size=64 << 20)
+    bts = [_rand((n_local, k), 20 + r, 0.05) for r in range(world)]
+    a_calls = [_rand((m, k), 70 + c) for c in range(calls)]
+    op = G.all_gather_gemm(ranks, m, bts, ag_slices=4)
+    kept = []
+    for c in range(calls):
+        for r in range(world):
+            op.a_full[r][r * ms:(r + 1) * ms].copy_(a_calls[c][r * ms:(r + 1) * ms])
+        outs = op()
+        kept.append([o.clone() for o in outs])
+    op.check()
+    for c in range(calls):
+        for r in range(world):
+            _assert_close(kept[c][r], a_calls[c].float() @ bts[r].float().t())
     op.close()
     ranks[0].close()
 

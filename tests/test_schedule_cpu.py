@@ -130,3 +130,40 @@ def test_every_k_block_of_every_tile_is_computed_exactly_once(lib, m, n, k, worl
                 share[u] += 1
         used = [x for x in share[:p.sk_units]]
         assert max(used) - min(used) <= 1 and sum(share[p.sk_units:]) == 0
+
+
+@pytest.mark.parametrize("tiles,units,max_split", [(1792, 74, 4), (896, 74, 4), (448, 74, 4), (224, 74, 4), (300, 148, 2),
+                                                   (75, 74, 4), (74, 74, 4), (50, 74, 4), (200, 74, 1), (1776, 74, 4)])
+def test_column_split_tail_covers_every_piece_once_and_balances_the_last_wave(lib, tiles, units, max_split):
+    """The ragged last wave is cut into column pieces: the native rule and the Python planner agree, every whole tile
+    and every (tail tile, column piece) is visited exactly once, and no unit gets more than one piece of the tail."""
+    from iris_b200.ops.gemm_plan import tail_split_plan
+    lib.iris_sched_tail_split.argtypes = [ctypes.c_int] * 3 + [ctypes.POINTER(ctypes.c_int)] * 2
+    lib.iris_sched_tail_split.restype = None
+    lib.iris_sched_work_list_tail.argtypes = [ctypes.c_int] * 9 + [ctypes.POINTER(ctypes.c_int), ctypes.c_int, ctypes.c_int]
+    lib.iris_sched_work_list_tail.restype = ctypes.c_int
+    tt, sp = ctypes.c_int(), ctypes.c_int()
+    lib.iris_sched_tail_split(tiles, units, max_split, ctypes.byref(tt), ctypes.byref(sp))
+    assert (tt.value, sp.value) == tail_split_plan(tiles, units, max_split)
+    tail, split = tt.value, sp.value
+    if tiles % units and 2 * (tiles % units) <= units and tiles > units and max_split > 1:
+        assert tail == tiles % units and split > 1 and tail * split <= units
+    else:
+        assert (tail, split) == (0, 1)
+    kblocks, seen, per_unit_tail = 7, {}, []
+    for u in range(units):
+        buf = (ctypes.c_int * (6 * 64))()
+        n = lib.iris_sched_work_list_tail(u, units, tiles, kblocks, tiles, 0, 1, tail, split, buf, 64, 6)
+        assert n <= 64
+        items = [tuple(buf[6 * i:6 * i + 6]) for i in range(n)]
+        per_unit_tail.append(sum(1 for it in items if it[5] > 1))
+        for tile, kb0, kb1, piece, sub, nsub in items:
+            assert (kb0, kb1, piece) == (0, kblocks, 0)
+            assert (tile >= tiles - tail) == (nsub > 1) and 0 <= sub < nsub and nsub in (1, split)
+            seen[(tile, sub)] = seen.get((tile, sub), 0) + 1
+    want = {(t, 0) for t in range(tiles - tail)} | {(t, s) for t in range(tiles - tail, tiles) for s in range(split)}
+    assert set(seen) == want and set(seen.values()) == {1}
+    assert max(per_unit_tail) <= 1
+    # the whole tiles before the tail are whole waves: every unit has the same number of them
+    if tail:
+        assert (tiles - tail) % units == 0

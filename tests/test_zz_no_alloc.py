@@ -72,6 +72,38 @@ def test_noalloc_matches_plan_entry_twice_in_a_row():
     ctx.close()
 
 
+@pytest.mark.parametrize("m,n,k,pad,side_stream", [(100, 1024, 512, 0, False), (1000, 520, 320, 0, False),
+                                                    (384, 512, 256, 64, False), (512, 768, 448, 0, True)])
+def test_noalloc_shapes_pitches_streams_and_no_allocation(m, n, k, pad, side_stream):
+    """A matrix shorter than one tile, a width that ends inside a 64-column sub-tile, an output with padded rows and a
+    launch on a side stream; and the property in the name: the device's free memory is the same before and after the
+    first and the second call (nothing was allocated on the caller's behalf, by this library or by a library it uses)."""
+    lib, fn = _entry()
+    a, bt = _rand((m, k), 21), _rand((n, k), 22, 0.05)
+    out_full = torch.full((m, n + pad), float("nan"), dtype=torch.bfloat16, device="cuda")
+    out = out_full[:, :n]
+    st = torch.cuda.Stream() if side_stream else torch.cuda.current_stream()
+    ref = a.float() @ bt.float().t()
+    torch.cuda.synchronize()
+    rc = fn(a.data_ptr(), a.stride(0), bt.data_ptr(), bt.stride(0), out.data_ptr(), out.stride(0), m, n, k,
+            ctypes.c_void_p(st.cuda_stream))       # first use on this device may do the one-time set-up
+    assert rc == 0, lib.iris_gemm_last_error().decode()
+    torch.cuda.synchronize()
+    free0 = torch.cuda.mem_get_info()[0]
+    for call in range(2):
+        out_full.fill_(float("nan"))
+        torch.cuda.synchronize()
+        rc = fn(a.data_ptr(), a.stride(0), bt.data_ptr(), bt.stride(0), out.data_ptr(), out.stride(0), m, n, k,
+                ctypes.c_void_p(st.cuda_stream))
+        assert rc == 0, lib.iris_gemm_last_error().decode()
+        st.synchronize()
+        assert torch.cuda.mem_get_info()[0] == free0, f"call {call}: free device memory changed"
+        assert lib.iris_gemm_noalloc_status() == 0
+        _close(out, ref)
+        if pad:
+            assert bool(torch.isnan(out_full[:, n:].float()).all()), "wrote past the row's N columns"
+
+
 def test_noalloc_rejects_oversize_and_bad_arguments():
     lib, fn = _entry()
     a, bt = _rand((128, 64), 1), _rand((256, 64), 2)
@@ -83,4 +115,8 @@ def test_noalloc_rejects_oversize_and_bad_arguments():
     rc = fn(a.data_ptr(), 64, bt.data_ptr(), 64, out.data_ptr(), 256, 128, 252, 64, None)
     assert rc == -1
     rc = fn(None, 64, bt.data_ptr(), 64, out.data_ptr(), 256, 128, 256, 64, None)
+    assert rc == -1
+    rc = fn(a.data_ptr(), 56, bt.data_ptr(), 64, out.data_ptr(), 256, 128, 256, 64, None)      # lda < K
+    assert rc == -1 and b"row pitches" in lib.iris_gemm_last_error()
+    rc = fn(a.data_ptr(), 64, bt.data_ptr(), 64, out.data_ptr(), 1 << 31, 128, 256, 64, None)  # ldo does not fit
     assert rc == -1

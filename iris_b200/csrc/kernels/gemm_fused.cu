@@ -337,20 +337,19 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
           }
           const uint32_t a_dst = smem_base + stage * C::kStage;
           const uint32_t b_dst = a_dst + kAStageBytes;
-          // B^T rows arrive as boxes of b_box_rows rows, stacked in shared memory (a box is a whole number of
-          // 8-row swizzle groups, so the stack has the layout of one tall box).
+          // B^T rows of a whole tile come through tmB (box of bn / CG rows), those of a column piece of a tail tile
+          // through tmBt (a box as tall as the piece needs): one load either way.
+          const CUtensorMap* tm_b = w.nsub > 1 ? &p.tmBt[lr] : &p.tmB[lr];
           if (CG == 1) {
             mbar_expect_tx(full_bar(stage), stage_tx);
             tma_load_2d(a_dst, &p.tmA[lr], kb * BK, row0, full_bar(stage));
-            for (int r = 0; r < b_rows; r += p.b_box_rows)
-              tma_load_2d(b_dst + r * (BK * 2), &p.tmB[lr], kb * BK, col0 + r, full_bar(stage));
+            tma_load_2d(b_dst, tm_b, kb * BK, col0, full_bar(stage));
           } else {
             // Both CTAs' bytes are counted on the leader's barrier, which the leader arms for the pair.
             const uint32_t lead_full = mapa_shared(full_bar(stage), 0);
             if (leader) mbar_expect_tx(full_bar(stage), 2 * stage_tx);
             tma_load_2d_pair(a_dst, &p.tmA[lr], kb * BK, row0, lead_full);
-            for (int r = 0; r < b_rows; r += p.b_box_rows)
-              tma_load_2d_pair(b_dst + r * (BK * 2), &p.tmB[lr], kb * BK, col0 + pr * b_rows + r, lead_full);
+            tma_load_2d_pair(b_dst, tm_b, kb * BK, col0 + pr * b_rows, lead_full);
           }
           ++fills;
           if (++stage == kStages) {
@@ -1434,7 +1433,9 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
     FusedGemmParams& p = plan->params[par];
     for (int l = 0; l < d->num_local; ++l) {
       if (encode_2d(&p.tmA[l], d->a_ptr[l], d->M, d->K, d->lda[l], BK, BM, "A", f16) ||
-          encode_2d(&p.tmB[l], d->b_ptr[l], d->N, d->K, d->ldb[l], BK, (bn / tail_split) / cg, "B", f16)) {
+          encode_2d(&p.tmB[l], d->b_ptr[l], d->N, d->K, d->ldb[l], BK, bn / cg, "B", f16) ||
+          (tail_split > 1 &&
+           encode_2d(&p.tmBt[l], d->b_ptr[l], d->N, d->K, d->ldb[l], BK, (bn / tail_split) / cg, "B (tail)", f16))) {
         delete plan;
         return nullptr;
       }
@@ -1490,7 +1491,6 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
     p.tile_flag_base = d->tile_flag_base;
     p.ag_flag_base = d->ag_flag_base;
     p.bn = bn;
-    p.b_box_rows = (bn / tail_split) / cg;
     p.dtype = d->dtype;
     p.push_kind = d->push_kind;
     p.tail_tiles = tail_tiles;
@@ -1684,7 +1684,6 @@ int iris_gemm_noalloc(const void* a, int64_t lda, const void* bt, int64_t ldb, v
   p.tile_flag_base = 16;
   p.ag_flag_base = 16;
   p.bn = BN;
-  p.b_box_rows = BN;
   p.dtype = kBf16;
   p.tail_split = 1;
   p.epoch = 1;

@@ -64,7 +64,8 @@ enum EpiMode : int {
 struct FusedGemmParams {
   // Tensor maps (host-encoded).  Index = local rank for A and B, target rank for C.
   CUtensorMap tmA[kMaxRanks];  // [rows M, cols K] bf16, K contiguous, box 64 x 128, 128-byte swizzle
-  CUtensorMap tmB[kMaxRanks];  // [rows N, cols K] bf16, K contiguous, box 64 x b_box_rows, 128-byte swizzle
+  CUtensorMap tmB[kMaxRanks];  // [rows N, cols K] bf16, K contiguous, box 64 x (bn / cta group), 128-byte swizzle
+  CUtensorMap tmBt[kMaxRanks]; // the same matrix with the shorter box of a tail tile's column piece
   CUtensorMap tmC[kMaxRanks];  // [rows M, cols ldc] bf16, box 64 x 128, 128-byte swizzle
                                //   store/reduce: the output of rank t; one-/two-shot: the partial buffer of rank t
   uint64_t heap_base[kMaxRanks];  // base address of every rank's heap in this process
@@ -111,7 +112,6 @@ struct FusedGemmParams {
   int tile_flag_base;    // index (uint32 units from flags_off) of the per-tile flags
   int ag_flag_base;      // index of the all-gather chunk flags: [src rank][chunk]
   int bn;                // tile width in columns: 64, 128 or 256 (multiple of 64)
-  int b_box_rows;        // rows of the B tensor map's box; a stage's B rows are fetched as (rows / b_box_rows) loads
   int dtype;             // ElemType of A, B, C
   int push_kind;         // PushKind (store mode with store_all)
   int tail_tiles;        // the last `tail_tiles` tiles of the raster are cut into `tail_split` column pieces each

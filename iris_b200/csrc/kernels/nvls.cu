@@ -40,7 +40,12 @@ __global__ void nvls_all_reduce_bf16_kernel(uint64_t mc_buf, const uint64_t* hb,
                        (uint32_t)rank, 0) == kOk;
   }
   __syncthreads();
-  if (!ok) return;
+  if (!ok) {
+    // Phase 0 timed out: no data is touched, but the phase-1 arrival is still made, so that this rank keeps adding
+    // exactly two arrivals per block and call to every rank's counter (the invariant the host's targets rest on).
+    if (threadIdx.x == 0) nvls::red_release_add_u32(reinterpret_cast<void*>(mc_base + counter_off), 1u);
+    return;
+  }
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (size_t i = lo + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < hi; i += stride) {
     const uint4 v = nvls::ld_reduce_add_bf16x8(reinterpret_cast<const void*>(mc_buf + i * 16));

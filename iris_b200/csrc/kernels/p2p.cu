@@ -149,6 +149,15 @@ __global__ void p2p_atomic_add_f32_kernel(float* buf_sym, size_t n, int cur, int
   }
 }
 
+// The same for the other element types the device API adds in hardware (fp16, bf16, int32, int64): one relaxed,
+// system-scope reduction per element (examples/04_atomic_add/atomic_add_bench.py:20-41 of the reference).
+template <class T>
+__global__ void p2p_atomic_add_kernel(T* buf_sym, size_t n, int cur, int tgt, const uint64_t* hb, T one) {
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+    atomic_add<Sem::relaxed, Scope::sys>(buf_sym + i, one, cur, tgt, hb);
+}
+
 // out_local[i] = atomic_xchg(remote(buf)[i], 1), relaxed, system scope.
 __global__ void p2p_atomic_xchg_i32_kernel(int* buf_sym, int* out_local, size_t n, int cur, int tgt,
                                            const uint64_t* hb) {
@@ -182,48 +191,69 @@ struct MpArgs {
   int roles;            // bit 0: this launch runs the producer blocks, bit 1: the consumer blocks
   int use_put;          // 1: block-cooperative put; 0: per-thread load + store of floats
   uint32_t epoch;       // flag value that marks "chunk of this call has landed"
+  int parts;            // blocks per chunk: every chunk is cut into `parts` slices of whole 16-byte vectors
+  uint64_t arrive_off;  // uint32 per chunk, in the producer's heap: slices of the chunk copied so far (back at 0
+                        // when the chunk's flag has been raised)
 };
 
-// Blocks [0, nchunks) produce (when roles & 1); the following nchunks blocks consume (when roles & 2).
-// Producer: copy the chunk into the consumer's buffer, then raise the consumer's flag with release
-// semantics.  Consumer: bounded acquire-wait on its own flag, then out = 2 * landed.
+// Blocks [0, nchunks * parts) produce (when roles & 1); the following nchunks * parts blocks consume (when roles & 2).
+// Block (chunk c, slice q) handles slice q of chunk c, so that one chunk is moved by `parts` SMs at once and a
+// hand-off of a few large chunks still uses the whole GPU.
+// Producer: copy the slice into the consumer's buffer, make it visible (system-scope fence), then count the slice on
+// the chunk's arrival counter; the block that completes the count raises the CONSUMER's flag with release semantics
+// and puts the counter back to zero.  Consumer: every block of the chunk waits (bounded, acquire) on the chunk's flag
+// in its own memory, then writes out = 2 * landed for its slice.
 __global__ void mp_kernel(MpArgs a) {
   __shared__ uint32_t verdict;
   int b = blockIdx.x;
+  const int nblk = a.nchunks * a.parts;
   const bool has_prod = a.roles & 1;
-  if (has_prod && b < a.nchunks) {
+  // slice q of a chunk: whole 16-byte vectors, the last slice takes the remainder
+  const uint64_t vecs = a.chunk_bytes / 16;
+  const uint64_t per = (vecs + a.parts - 1) / a.parts;
+  if (has_prod && b < nblk) {
+    const int c = b / a.parts, q = b - c * a.parts;
+    const uint64_t v0 = per * q < vecs ? per * q : vecs, v1 = v0 + per < vecs ? v0 + per : vecs;
+    const uint64_t off = (uint64_t)c * a.chunk_bytes + v0 * 16, bytes = (v1 - v0) * 16;
     const uint64_t base = a.hb[a.producer];
-    const char* src = reinterpret_cast<const char*>(base + a.src_off) + (uint64_t)b * a.chunk_bytes;
-    char* dst_sym = reinterpret_cast<char*>(base + a.dst_off) + (uint64_t)b * a.chunk_bytes;
+    const char* src = reinterpret_cast<const char*>(base + a.src_off) + off;
+    char* dst_sym = reinterpret_cast<char*>(base + a.dst_off) + off;
     if (a.use_put) {
-      put_block(src, dst_sym, a.chunk_bytes, a.producer, a.consumer, a.hb);
+      put_block(src, dst_sym, bytes, a.producer, a.consumer, a.hb);
     } else {
       const float* s = reinterpret_cast<const float*>(src);
       float* d = reinterpret_cast<float*>(dst_sym);
-      for (size_t i = threadIdx.x; i < a.chunk_bytes / 4; i += blockDim.x)
+      for (size_t i = threadIdx.x; i < bytes / 4; i += blockDim.x)
         store(d + i, load(s + i, a.producer, a.producer, a.hb), a.producer, a.consumer, a.hb);
     }
     fence_sys();
     __syncthreads();
     if (threadIdx.x == 0) {
-      uint32_t* flag = reinterpret_cast<uint32_t*>(base + a.flags_off) + b;
-      signal_set(flag, a.epoch, a.producer, a.consumer, a.hb);
+      uint32_t* cnt = reinterpret_cast<uint32_t*>(base + a.arrive_off) + c;
+      const uint32_t old = atomic_add<Sem::acq_rel, Scope::gpu>(cnt, 1u, 0, 0, a.hb);
+      if (old + 1 == (uint32_t)a.parts) {
+        *cnt = 0;  // every slice has arrived: nobody touches the counter again in this call
+        uint32_t* flag = reinterpret_cast<uint32_t*>(base + a.flags_off) + c;
+        signal_set(flag, a.epoch, a.producer, a.consumer, a.hb);
+      }
     }
     return;
   }
-  if (has_prod) b -= a.nchunks;
-  if (!(a.roles & 2) || b >= a.nchunks) return;
+  if (has_prod) b -= nblk;
+  if (!(a.roles & 2) || b >= nblk) return;
+  const int c = b / a.parts, q = b - c * a.parts;
+  const uint64_t v0 = per * q < vecs ? per * q : vecs, v1 = v0 + per < vecs ? v0 + per : vecs;
   const uint64_t base = a.hb[a.consumer];
   if (threadIdx.x == 0) {
-    const uint32_t* flag = reinterpret_cast<const uint32_t*>(base + a.flags_off) + b;
+    const uint32_t* flag = reinterpret_cast<const uint32_t*>(base + a.flags_off) + c;
     verdict = wait_until_ge(flag, a.epoch, a.timeout_ns, reinterpret_cast<StatusBlock*>(base + a.status_off),
-                            /*where=*/60, (uint32_t)a.consumer, (uint32_t)b);
+                            /*where=*/60, (uint32_t)a.consumer, (uint32_t)c);
   }
   __syncthreads();
   if (verdict != kOk) return;
-  const float4* in = reinterpret_cast<const float4*>(base + a.dst_off + (uint64_t)b * a.chunk_bytes);
-  float4* out = reinterpret_cast<float4*>(base + a.out_off + (uint64_t)b * a.chunk_bytes);
-  for (size_t i = threadIdx.x; i < a.chunk_bytes / 16; i += blockDim.x) {
+  const float4* in = reinterpret_cast<const float4*>(base + a.dst_off + (uint64_t)c * a.chunk_bytes);
+  float4* out = reinterpret_cast<float4*>(base + a.out_off + (uint64_t)c * a.chunk_bytes);
+  for (size_t i = v0 + threadIdx.x; i < v1; i += blockDim.x) {
     float4 v = in[i];
     out[i] = make_float4(2.f * v.x, 2.f * v.y, 2.f * v.z, 2.f * v.w);
   }
@@ -286,6 +316,18 @@ int iris_k_p2p_atomic_add_f32(void* buf_sym, uint64_t n, int cur, int tgt, const
   p2p_atomic_add_f32_kernel<<<grid, block, 0, (cudaStream_t)stream>>>((float*)buf_sym, n, cur, tgt, hb, vec4);
   return check_launch();
 }
+// dtype: iris::ops::DType numbering (2 = int32, 3 = int64, 4 = fp16, 5 = bf16, 6 = fp32)
+int iris_k_p2p_atomic_add(void* buf_sym, uint64_t n, int dtype, int cur, int tgt, const uint64_t* hb, int grid,
+                          int block, void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == 6) p2p_atomic_add_f32_kernel<<<grid, block, 0, st>>>((float*)buf_sym, n, cur, tgt, hb, 0);
+  else if (dtype == 4) p2p_atomic_add_kernel<__half><<<grid, block, 0, st>>>((__half*)buf_sym, n, cur, tgt, hb, __float2half(1.f));
+  else if (dtype == 5) p2p_atomic_add_kernel<__nv_bfloat16><<<grid, block, 0, st>>>((__nv_bfloat16*)buf_sym, n, cur, tgt, hb, __float2bfloat16(1.f));
+  else if (dtype == 2) p2p_atomic_add_kernel<int><<<grid, block, 0, st>>>((int*)buf_sym, n, cur, tgt, hb, 1);
+  else if (dtype == 3) p2p_atomic_add_kernel<long long><<<grid, block, 0, st>>>((long long*)buf_sym, n, cur, tgt, hb, 1ll);
+  else return -2;
+  return check_launch();
+}
 int iris_k_p2p_atomic_xchg_i32(void* buf_sym, void* out_local, uint64_t n, int cur, int tgt, const uint64_t* hb,
                                int grid, int block, void* stream) {
   p2p_atomic_xchg_i32_kernel<<<grid, block, 0, (cudaStream_t)stream>>>((int*)buf_sym, (int*)out_local, n, cur, tgt, hb);
@@ -307,14 +349,27 @@ int iris_k_device_barrier(const uint64_t* hb, uint64_t counter_off, uint64_t sta
 }
 
 // roles: 1 producer side only, 2 consumer side only, 3 both in one (cooperative) launch on one GPU.
+// parts: blocks per chunk (>= 1); arrive_off: uint32[nchunks] in the producer's heap, zero before the first call.
 int iris_k_message_passing(const uint64_t* hb, uint64_t src_off, uint64_t dst_off, uint64_t out_off,
                            uint64_t flags_off, uint64_t status_off, uint64_t chunk_bytes, int nchunks, int producer,
                            int consumer, int roles, int use_put, uint32_t epoch, uint64_t timeout_ns, int block,
-                           void* stream) {
-  if (chunk_bytes % 16 != 0 || nchunks < 1) return -2;
+                           int parts, uint64_t arrive_off, void* stream) {
+  if (chunk_bytes % 16 != 0 || nchunks < 1 || parts < 1) return -2;
+  if (roles == 3) {
+    // Producer and consumer blocks wait on one another: all of them must be resident at once.  Lower `parts` to
+    // what the device holds (both sides of one launch use the same value, so the arrival counts stay consistent).
+    int dev = 0, sms = 0, per_sm = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, mp_kernel, block, 0) != cudaSuccess)
+      return -3;
+    const int fit = (sms * per_sm) / (2 * nchunks);
+    if (fit < 1) return -4;
+    if (parts > fit) parts = fit;
+  }
   MpArgs a{hb, src_off, dst_off, out_off, flags_off, status_off, chunk_bytes, timeout_ns, nchunks, producer, consumer,
-           roles, use_put, epoch};
-  const int grid = (roles == 3 ? 2 : 1) * nchunks;
+           roles, use_put, epoch, parts, arrive_off};
+  const int grid = (roles == 3 ? 2 : 1) * nchunks * parts;
   cudaError_t e;
   if (roles == 3) {
     // Producer and consumer blocks wait on one another: they must be co-resident.

@@ -3,8 +3,9 @@
 Role in the reference: ``mpirun -np N python script.py`` (``README.md:93-100``); neither ``mpirun`` nor
 ``mpi4py`` is needed here.  Each rank is a child process with ``RANK``, ``LOCAL_RANK``, ``WORLD_SIZE``,
 ``MASTER_ADDR=127.0.0.1`` and ``MASTER_PORT`` set — the same variables ``torchrun`` sets, so scripts work
-under either launcher.  If a rank fails or the time limit expires, the remaining ranks are terminated (by
-process id) and the launcher exits non-zero.
+under either launcher.  If a rank fails, the others get a grace period to leave on their own (their waits are
+bounded); ranks still running after it, or after the time limit, are terminated by process id, and the launcher exits
+non-zero.
 """
 from __future__ import annotations
 
@@ -13,6 +14,7 @@ import os
 import socket
 import subprocess
 import sys
+import threading
 import time
 from typing import List, Optional, Sequence
 
@@ -24,10 +26,19 @@ def free_port() -> int:
 
 
 def launch(nprocs: int, argv: Sequence[str], timeout_s: Optional[float] = None, env_extra: Optional[dict] = None,
-           module: bool = False, capture: bool = False):
-    """Run ``python argv...`` as ``nprocs`` ranks.  Returns (exit_code, [per-rank output or None])."""
+           module: bool = False, capture: bool = False, grace_s: float = 20.0):
+    """Run ``python argv...`` as ``nprocs`` ranks.  Returns (exit_code, [per-rank output or None]).
+
+    When a rank fails, the others are given ``grace_s`` seconds to end on their own: every device wait and every
+    ``barrier(timeout_s)`` of the package is bounded, so they notice the missing rank and leave with no kernel in
+    flight (a rank killed in the middle of a kernel, or while its heap is bound to an NVLink multicast object, can
+    disturb the GPUs of the others).  Only ranks still running after that, or after ``timeout_s``, are terminated, by
+    process id.  With ``capture`` the ranks' output is drained by reader threads while they run, so a talkative rank
+    never blocks on a full pipe."""
     port = free_port()
     procs: List[subprocess.Popen] = []
+    chunks: List[List[str]] = [[] for _ in range(nprocs)]
+    readers: List[threading.Thread] = []
     for r in range(nprocs):
         env = dict(os.environ)
         env.update(RANK=str(r), LOCAL_RANK=str(r), WORLD_SIZE=str(nprocs), LOCAL_WORLD_SIZE=str(nprocs),
@@ -35,10 +46,19 @@ def launch(nprocs: int, argv: Sequence[str], timeout_s: Optional[float] = None, 
         if env_extra:
             env.update({k: str(v) for k, v in env_extra.items()})
         cmd = [sys.executable] + (["-m"] if module else []) + list(argv)
-        procs.append(subprocess.Popen(cmd, env=env, stdout=subprocess.PIPE if capture else None,
-                                      stderr=subprocess.STDOUT if capture else None, text=capture))
+        p = subprocess.Popen(cmd, env=env, stdout=subprocess.PIPE if capture else None,
+                             stderr=subprocess.STDOUT if capture else None, text=capture)
+        procs.append(p)
+        if capture:
+            def pump(stream=p.stdout, sink=chunks[r]):
+                for line in stream:
+                    sink.append(line)
+            t = threading.Thread(target=pump, daemon=True)
+            t.start()
+            readers.append(t)
     deadline = None if timeout_s is None else time.monotonic() + timeout_s
     code = 0
+    grace_end = None
     pending = set(range(nprocs))
     while pending:
         for r in list(pending):
@@ -47,7 +67,10 @@ def launch(nprocs: int, argv: Sequence[str], timeout_s: Optional[float] = None, 
                 pending.discard(r)
                 if rc != 0 and code == 0:
                     code = rc
-        if code != 0 or (deadline is not None and time.monotonic() > deadline):
+                    grace_end = time.monotonic() + grace_s
+        now = time.monotonic()
+        timed_out = deadline is not None and now > deadline
+        if pending and (timed_out or (grace_end is not None and now > grace_end)):
             if code == 0:
                 code = 124  # time limit, as coreutils timeout
             for r in pending:
@@ -60,7 +83,14 @@ def launch(nprocs: int, argv: Sequence[str], timeout_s: Optional[float] = None, 
                     procs[r].kill()
             break
         time.sleep(0.02)
-    outs = [p.communicate()[0] if capture else None for p in procs]
+    for p in procs:
+        try:
+            p.wait(5)
+        except subprocess.TimeoutExpired:
+            pass
+    for t in readers:
+        t.join(5)
+    outs = ["".join(c) if capture else None for c in chunks]
     return code, outs
 
 

@@ -123,7 +123,8 @@ class FusedGemm:
         bn: tile width in columns, 64 / 128 / 256 (default 256).  Together with ``cta_group`` (128 or 256 rows) this
             gives the six tile shapes of the kernel (the reference's per-shape ``BLK_M`` / ``BLK_N``,
             ``dataset/tiling.json``).
-        tail_split: cut the tiles of a ragged last wave into column pieces (default: on where it applies).
+        tail_split: cut the tiles of a ragged last wave into column pieces: ``True`` = two, an integer = at most that
+            many (store / reduce modes, whole-tile schedule; default off).
         push_kind: how all-scatter tiles travel: ``"tma"`` (one thread issues a TMA store per rank), ``"tma_spread"``
             (four issuing threads), ``"stores"`` (16-byte stores by all epilogue threads) or ``"multimem"`` (one
             ``multimem.st`` per 16 bytes on a heap bound to an NVLS multicast object).  ``None``: ``DEFAULT_PUSH_KIND``.
@@ -292,6 +293,10 @@ class FusedGemm:
         self.ctas_per_rank = lib.iris_gemm_plan_ctas_per_rank(self._plan)  # what fits on the device
         self.calls = 0
         self.launches = 0
+        # Construction is collective.  The flags were zeroed on this rank's stream just now; a peer that is already
+        # past its own constructor must not launch (and bump this rank's counters) before that has happened.
+        if self.num_local == 1 and self.world > 1:
+            c0.barrier()
 
     # every rank of a real multi-process world must call this the same number of times
     def __call__(self, stream=None) -> List[torch.Tensor]:

@@ -87,7 +87,9 @@ def plan_gemm(M: int, N: int, K: int, world: int, num_local: int, mode: str, sms
     """Decide tile shape, persistent grid, schedule, flag count and buffer layout.  ``sms``: SMs of the device;
     ``own_out``: the caller brings the output buffer (the [partials | out] matrix then has no output region);
     ``bn``: tile width (64, 128 or 256; default 256); ``tail_split``: cut the tiles of a ragged last wave into column
-    pieces (default: on for the store / reduce modes with whole tiles)."""
+    pieces: ``True`` = into two, an integer = into at most that many (store / reduce modes with whole tiles; default
+    off: measured on the 8192 x 14336 x 4096 problem the narrower pieces re-read A and lose more than the ragged wave
+    costs)."""
     if mode not in MODES:
         raise ValueError(f"mode must be one of {sorted(MODES)}")
     bn = BN if bn is None else int(bn)
@@ -153,8 +155,8 @@ def plan_gemm(M: int, N: int, K: int, world: int, num_local: int, mode: str, sms
     pulls = mode in ("one_shot", "two_shot")
     # ---- ragged last wave of a whole-tile schedule: cut its tiles into column pieces (nothing to fix up) ----
     tail_tiles, tsplit = 0, 1
-    if (tail_split is None or tail_split) and not pulls and not sk_units and ks == 1:
-        max_split = min(4, bn // 64)                      # pieces are whole 64-column sub-tiles
+    if tail_split and not pulls and not sk_units and ks == 1:
+        max_split = min(int(tail_split) if tail_split > 1 else 2, bn // 64)   # pieces are whole 64-column sub-tiles
         while max_split > 1 and ((bn // max_split) // cta_group) % 8:
             max_split //= 2
         tail_tiles, tsplit = tail_split_plan(T, max(1, ctas // cta_group), max_split)

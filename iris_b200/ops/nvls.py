@@ -42,6 +42,16 @@ class AllReduce:
         self.counter = ctx.zeros(16, dtype=torch.int32)
         self.total = 0
         self.timeout_ns = int(timeout_ms * 1e6)
+        ctx.barrier()   # construction is collective: no rank arrives on a counter its owner has not zeroed yet
+
+    def reset(self) -> None:
+        """Collective recovery after ``ctx.check_status()`` reported a time-out of this op (sites 80 / 81): a rank whose
+        wait expired may have left a call half-way, so the cumulative counter no longer matches ``total`` everywhere.
+        Every rank calls ``reset()``: the counters are zeroed between two barriers and counting starts again."""
+        self.ctx.barrier()
+        self.counter.zero_()
+        self.total = 0
+        self.ctx.barrier()
 
     def __call__(self, buf: torch.Tensor, grid=None, block=512, stream=None) -> torch.Tensor:
         ctx = self.ctx

@@ -100,6 +100,22 @@ def atomic_add_f32(ctx, buf_sym, target: int, n=None, vec4=False, grid=None, blo
            "p2p_atomic_add")
 
 
+_ATOMIC_DT = {torch.int32: 2, torch.int64: 3, torch.float16: 4, torch.bfloat16: 5, torch.float32: 6}
+
+
+def atomic_add(ctx, buf_sym, target: int, n=None, grid=None, block=512, stream=None):
+    """``remote(target).buf[i] += 1`` for int32 / int64 / fp16 / bf16 / fp32 buffers, one relaxed system-scope
+    reduction per element (the ``--datatype`` choices of ``examples/04_atomic_add/atomic_add_bench.py:68`` of the
+    reference that the hardware adds natively; there is no 8-bit atomic on sm_100a)."""
+    lib = _native.kernels()
+    if buf_sym.dtype not in _ATOMIC_DT:
+        raise TypeError(f"atomic_add supports {list(_ATOMIC_DT)}")
+    n = buf_sym.numel() if n is None else int(n)
+    _check(lib.iris_k_p2p_atomic_add(_p(buf_sym), ctypes.c_uint64(n), _ATOMIC_DT[buf_sym.dtype], ctx.get_rank(),
+                                     int(target), _hb(ctx), grid or default_grid(ctx), block, _stream(ctx, stream)),
+           "p2p_atomic_add")
+
+
 def atomic_xchg_i32(ctx, buf_sym, out_local, target: int, n=None, grid=None, block=512, stream=None):
     """``out_local[i] = atomic_xchg(remote(target).buf[i], 1)`` (examples/05_atomic_xchg)."""
     lib = _native.kernels()
@@ -119,15 +135,25 @@ class MessagePassing:
     reference's example intends (``examples/06_message_passing/message_passing_put.py:16-78``), with the flag
     in the consumer's memory and real release/acquire ordering.
 
-    All three buffers and the flags are allocated on the heap here, in the same order on every rank.
+    Every chunk is moved by ``parts`` thread blocks at once (default: enough to put about two blocks on every SM, at
+    least 16 KB per block), so that a hand-off of a few large chunks runs at link rate instead of at the rate of one
+    SM per chunk; the block that finishes a chunk last raises its flag.
+
+    All three buffers, the flags and the arrival counters are allocated on the heap here, in the same order on every
+    rank.
     """
 
     def __init__(self, ctx, nchunks: int, chunk_bytes: int, producer: int = 0, consumer: int = 1,
-                 timeout_ms: float = 1000.0):
+                 timeout_ms: float = 1000.0, parts: Optional[int] = None):
         if chunk_bytes % 16:
             raise ValueError("chunk_bytes must be a multiple of 16")
         self.ctx, self.nchunks, self.chunk_bytes = ctx, nchunks, chunk_bytes
         self.producer, self.consumer = producer, consumer
+        sms = ctx.get_cu_count() if ctx.backend == "cuda" else 1
+        if parts is None:
+            parts = max(1, min((2 * sms) // max(1, nchunks), chunk_bytes // (16 << 10)))
+        self.parts = max(1, int(parts))
+        self.arrive = ctx.zeros(nchunks, dtype=torch.int32)
         n = nchunks * chunk_bytes // 4
         self.src = ctx.zeros(n, dtype=torch.float32)
         self.dst = ctx.zeros(n, dtype=torch.float32)
@@ -135,6 +161,7 @@ class MessagePassing:
         self.flags = ctx.zeros(nchunks, dtype=torch.int32)
         self.timeout_ns = int(timeout_ms * 1e6)
         self.epoch = 0
+        ctx.barrier()   # construction is collective: the producer must not raise a flag its owner has yet to zero
 
     def run(self, roles: Optional[int] = None, use_put: bool = True, block: int = 512, stream=None,
             advance: bool = True) -> None:
@@ -149,11 +176,13 @@ class MessagePassing:
             return
         lib = _native.kernels()
         lib.iris_k_message_passing.argtypes = [ctypes.c_void_p] + [ctypes.c_uint64] * 6 + [ctypes.c_int] * 5 + \
-            [ctypes.c_uint32, ctypes.c_uint64, ctypes.c_int, ctypes.c_void_p]
+            [ctypes.c_uint32, ctypes.c_uint64, ctypes.c_int, ctypes.c_int, ctypes.c_uint64, ctypes.c_void_p]
+        parts = self.parts   # with roles == 3 the launcher lowers it to what is resident at once
         rc = lib.iris_k_message_passing(
             _hb(ctx), ctx.offset_of(self.src), ctx.offset_of(self.dst), ctx.offset_of(self.out),
             ctx.offset_of(self.flags), ctx.offset_of(ctx.status), self.chunk_bytes, self.nchunks, self.producer,
-            self.consumer, roles, int(use_put), self.epoch, self.timeout_ns, block, _stream(ctx, stream))
+            self.consumer, roles, int(use_put), self.epoch, self.timeout_ns, block, parts,
+            ctx.offset_of(self.arrive), _stream(ctx, stream))
         _check(rc, "message_passing")
 
 
@@ -170,6 +199,7 @@ class DeviceBarrier:
         self.counter = ctx.zeros(16, dtype=torch.int32)
         self.calls = 0
         self.timeout_ns = int(timeout_ms * 1e6)
+        ctx.barrier()   # construction is collective: no rank bumps a counter its owner has not zeroed yet
 
     def __call__(self, stream=None) -> None:
         ctx = self.ctx

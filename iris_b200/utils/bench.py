@@ -140,6 +140,15 @@ class ClockSampler:
         self._thread.start()
         return self
 
+    def wait_first_sample(self, timeout_s: float = 10.0) -> bool:
+        """Block until the first sample has arrived (``nvidia-smi`` takes a second or more to start on a machine
+        with several GPUs): call it before the region of interest, so that the start-up neither falls into the timed
+        region nor leaves it without samples."""
+        t_end = time.monotonic() + timeout_s
+        while self.proc is not None and not self.lines and time.monotonic() < t_end and self.proc.poll() is None:
+            time.sleep(0.01)
+        return bool(self.lines)
+
     def stop(self) -> dict:
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"], "samples": 0}

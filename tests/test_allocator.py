@@ -35,11 +35,23 @@ def test_allocation_failure_returns_null_and_does_not_exit(capfd):
 
 
 CHILD = r"""
-import sys, torch
+import ctypes, os, sys, torch
 import iris_b200 as iris
+from iris_b200 import _native
 iris.install_allocator()
 x = torch.ones(1 << 20, device="cuda")            # 4 MB: one call of the plug-in (torch does not cache plug-in memory)
 assert float(x.sum()) == float(1 << 20)
+so = ctypes.CDLL(str(_native.lib_path("allocator")))     # the instance torch loaded
+so.iris_allocator_export_fd.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_size_t)]
+mode = os.environ.get("IRIS_ALLOCATOR_MODE", "vmm")
+nbytes = ctypes.c_size_t(0)
+fd = so.iris_allocator_export_fd(ctypes.c_void_p(x.data_ptr()), ctypes.byref(nbytes))
+if mode == "vmm":
+    # the tensor's memory is a shareable VMM object: it exports as a file descriptor another process could map
+    assert fd >= 0 and nbytes.value >= 4 << 20 and so.iris_allocator_vmm_live() >= 1, (fd, nbytes.value)
+    os.close(fd)
+else:
+    assert fd == -1 and so.iris_allocator_vmm_live() == 0
 ctx = iris.iris(1 << 24)
 t = ctx.arange(0, 1024, dtype=torch.int32)
 assert int(t.sum()) == 1023 * 1024 // 2
@@ -52,9 +64,11 @@ print("allocator OK")
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("mode", ["vmm", "cudamalloc"])
 @pytest.mark.parametrize("log", [False, True])
-def test_torch_allocates_through_the_plugin(log):
+def test_torch_allocates_through_the_plugin(log, mode):
     env = dict(os.environ, PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    env["IRIS_ALLOCATOR_MODE"] = mode
     env.pop("LOG_IRIS_ALLOCATOR", None)
     if log:
         env["LOG_IRIS_ALLOCATOR"] = "1"

@@ -63,7 +63,7 @@ def test_column_split_tail(m, n, k, cta_group, bn):
     a, bt = _rand((m, k), 3), _rand((n, k), 4, 0.05)
     ctx = iris.Iris.local_world(1, heap_size=64 << 20)[0]
     outs = []
-    for split in (True, False):
+    for split in (4, True, False):
         out = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
         op = G.FusedGemm(ctx, [a], [bt], "store", out=[out], cta_group=cta_group, bn=bn, tail_split=split)
         if split:
@@ -76,7 +76,7 @@ def test_column_split_tail(m, n, k, cta_group, bn):
         _assert_close(out, a.float() @ bt.float().t())
         outs.append(out)
         op.close()
-    assert torch.equal(outs[0], outs[1])
+    assert torch.equal(outs[0], outs[2]) and torch.equal(outs[1], outs[2])
     ctx.close()
 
 
@@ -128,7 +128,7 @@ def test_gemm_all_scatter_push_kinds(world, m, n_local, bn, dtype, push_kind):
     ranks = iris.Iris.local_world(world, heap_size=64 << 20)
     a = _rand((m, k), 5, dtype=dtype)
     bts = [_rand((n_local, k), 10 + r, 0.05, dtype=dtype) for r in range(world)]
-    op = G.gemm_all_scatter(ranks, [a] * world, bts, bn=bn, push_kind=push_kind)
+    op = G.gemm_all_scatter(ranks, [a] * world, bts, bn=bn, push_kind=push_kind, tail_split=4)
     assert op.push_kind == push_kind
     for _ in range(3):
         outs = op()

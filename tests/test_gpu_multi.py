@@ -45,6 +45,9 @@ EX = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "
     ("02_all_load/all_load_bench.py", ["-m", str(1 << 20), "-M", str(1 << 22), "-x", "2", "-d", "-p", str(1 << 28)]),
     ("03_all_store/all_store_bench.py", ["-m", str(1 << 20), "-M", str(1 << 22), "-x", "2", "-d", "-p", str(1 << 28)]),
     ("04_atomic_add/atomic_add_bench.py", ["-z", str(1 << 20), "-x", "2", "-w", "1", "-d"]),
+    ("04_atomic_add/atomic_add_bench.py", ["-t", "fp16", "-z", str(1 << 20), "-x", "2", "-w", "1", "-d"]),
+    ("04_atomic_add/atomic_add_bench.py", ["-t", "bf16", "-z", str(1 << 20), "-x", "2", "-w", "1", "-d"]),
+    ("04_atomic_add/atomic_add_bench.py", ["-t", "int32", "-z", str(1 << 20), "-x", "2", "-w", "1", "-d"]),
     ("05_atomic_xchg/atomic_xchg_bench.py", ["-z", str(1 << 20), "-x", "2", "-w", "1", "-d"]),
     ("06_message_passing/message_passing_put.py", ["-n", "3"]),
     ("06_message_passing/message_passing_load_store.py", ["-n", "3"]),

@@ -151,7 +151,28 @@ def main():
         ag.check()
         assert torch.equal(ag.a_full[0], a2), "gathered A differs"
         close(o, a2.float() @ bts[rank][:, :512].float().t())
+    # four calls back to back with new rows each time and no host barrier in between: a rank may be a whole call
+    # ahead of a peer; its pushes must wait until that peer has entered the same call
+    a_calls = [rand((m2, 512), 80 + c, dev=dev) for c in range(4)]
+    kept = []
+    ctx.barrier()
+    for c in range(4):
+        ag.a_full[0][rank * ms:(rank + 1) * ms].copy_(a_calls[c][rank * ms:(rank + 1) * ms])
+        kept.append(ag()[0].clone())
+    ctx.barrier()
+    ag.check()
+    for c in range(4):
+        close(kept[c], a_calls[c].float() @ bts[rank][:, :512].float().t())
     ag.close()
+    # every way an all-scatter tile can travel between real GPUs, fp16 and a narrow tile among them
+    for pk, dt, bn in (("tma_spread", torch.bfloat16, 256), ("stores", torch.float16, 128), ("stores", torch.bfloat16, 64)):
+        sc = G.gemm_all_scatter(ctx, [a.to(dt)], [bts[rank].to(dt)], push_kind=pk, bn=bn)
+        for _ in range(3):
+            c = sc()[0]
+        ctx.barrier()
+        sc.check()
+        close(c, torch.cat([a.to(dt).float() @ b.to(dt).float().t() for b in bts], dim=1))
+        sc.close()
     ctx.barrier()
     ctx.close()
     print(f"rank {rank}: OK", flush=True)

@@ -71,6 +71,22 @@ def main():
             tol = (2 + world) * 2.0 ** -8 * scale + 1e-3 * ref.abs().max().item()
             assert bool(((o.float() - ref).abs() <= tol).all()), "NVLS two-shot mismatch"
             op.close()
+            # fused GEMM + all-scatter whose tiles leave as multimem stores: one store per 16 bytes, the switch
+            # delivers it to every rank's C (this rank's own copy included)
+            n_local = 320
+            a = torch.randn((1000, 512), generator=g, device=dev).to(torch.bfloat16)
+            bts = [(torch.randn((n_local, 512), generator=g, device=dev) * 0.05).to(torch.bfloat16)
+                   for _ in range(world)]
+            sc = G.gemm_all_scatter(ctx, [a], [bts[rank]], push_kind="multimem")
+            assert sc.push_kind == "multimem"
+            for _ in range(3):
+                c = sc()[0]
+            ctx.barrier()
+            sc.check()
+            ref = torch.cat([a.float() @ b.float().t() for b in bts], dim=1)
+            assert bool(((c.float() - ref).abs() <= 2.0 ** -7 * ref.abs() + 1e-3 * ref.abs().max().item()).all()), \
+                "multimem all-scatter mismatch"
+            sc.close()
             msg += " + NVLS OK"
     ctx.barrier()
     ctx.close()

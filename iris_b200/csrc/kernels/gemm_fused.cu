@@ -458,7 +458,8 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
     // Two-shot result pushes are made (and guarded the same way) by the reducer warps.
     const bool need_entry = W > 1 && (push_all || pulls);
     // How finished sub-tiles leave (GEMM + all-scatter only; every other mode has one issuing thread and TMA):
-    const int push_kind = (!PULL && p.mode == kEpiStore && push_all) ? p.push_kind : (int)kPushTma;
+    const int push_kind =
+        (!PULL && (p.mode == kEpiStore || p.mode == kEpiReduce) && push_all) ? p.push_kind : (int)kPushTma;
     const bool direct = push_kind >= kPushStores;                 // the 128 threads copy the staged sub-tile themselves
     const int nlead = push_kind == kPushTmaSpread ? 4 : 1;        // threads that issue TMA stores (lane 0 of a warp)
     const int lead_idx = warp - 2;
@@ -633,7 +634,14 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
             if (y + r < p.M) {
               const uint64_t off = p.c_off + ((uint64_t)(y + r) * p.ldc + x + j * 8) * 2;
               if (push_kind == kPushMultimem) {
-                nvls::st_v4(reinterpret_cast<void*>(p.mc_base + off), vv[i]);  // the switch delivers to every rank
+                // one instruction, delivered (store) or added (reduce) by the switch on every rank's copy
+                void* mc = reinterpret_cast<void*>(p.mc_base + off);
+                if (p.mode == kEpiReduce) {
+                  if (f16) nvls::red_add_f16x8(mc, vv[i]);
+                  else nvls::red_add_bf16x8(mc, vv[i]);
+                } else {
+                  nvls::st_v4(mc, vv[i]);
+                }
               } else {
                 for (int q = 0; q < W; ++q)  // peers first, starting with the next rank; own copy last
                   st_v4(reinterpret_cast<uint4*>(p.heap_base[(rank + 1 + q) % W] + off), vv[i]);
@@ -1345,7 +1353,12 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
     snprintf(g_err, sizeof(g_err), "push_kind must be 0..3");
     return nullptr;
   }
-  if (d->push_kind == kPushMultimem && d->world > 1 && d->store_all && d->mode == kEpiStore && d->mc_base == 0) {
+  if (d->push_kind == kPushStores && d->mode == kEpiReduce) {
+    snprintf(g_err, sizeof(g_err), "push_kind 2 (plain stores) cannot add: use 0, 1 or 3 with mode reduce");
+    return nullptr;
+  }
+  if (d->push_kind == kPushMultimem && d->world > 1 && d->store_all &&
+      (d->mode == kEpiStore || d->mode == kEpiReduce) && d->mc_base == 0) {
     snprintf(g_err, sizeof(g_err), "push_kind 3 (multimem) needs a heap bound to an NVLS multicast object");
     return nullptr;
   }

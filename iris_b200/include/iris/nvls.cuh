@@ -62,7 +62,14 @@ __device__ __forceinline__ uint4 ld_reduce_add_f32x4(const void* mc) {
 }
 // Add 8 bf16 into every rank's copy.
 __device__ __forceinline__ void red_add_bf16x8(void* mc, uint4 v) {
-  asm volatile("multimem.red.relaxed.sys.global.add.noftz.v4.bf16x2 [%0], {%1,%2,%3,%4};" ::"l"(mc), "r"(v.x), "r"(v.y),
+  asm volatile("multimem.red.relaxed.sys.global.add.v4.bf16x2 [%0], {%1,%2,%3,%4};" ::"l"(mc), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+// The same for 8 fp16 values.
+__device__ __forceinline__ void red_add_f16x8(void* mc, uint4 v) {
+  asm volatile("multimem.red.relaxed.sys.global.add.v4.f16x2 [%0], {%1,%2,%3,%4};" ::"l"(mc), "r"(v.x), "r"(v.y),
                "r"(v.z), "r"(v.w)
                : "memory");
 }

@@ -118,6 +118,8 @@ class FusedGemm:
         reduce_scatter: with ``mode="one_shot"``: every rank keeps only its own ``M / world`` rows of the sum
             (``out[l]`` is that block); partial tiles are pushed to the keeper of their rows only.
         push / ksplit: one-shot for short matrices: partials pushed into inbox slots of every rank, K cut into pieces.
+            With ``mode="reduce"`` (atomic all-reduce) ``ksplit`` cuts K into pieces computed by different CTAs that
+            all add into the outputs, which spreads a short matrix over the whole GPU.
         nvls: two-shot on a heap bound to an NVLS multicast object: ``None`` = use it when available.
         trace: record per-tile device timestamps (``trace_records()``).
         bn: tile width in columns, 64 / 128 / 256 (default 256).  Together with ``cta_group`` (128 or 256 rows) this
@@ -125,9 +127,11 @@ class FusedGemm:
             ``dataset/tiling.json``).
         tail_split: cut the tiles of a ragged last wave into column pieces: ``True`` = two, an integer = at most that
             many (store / reduce modes, whole-tile schedule; default off).
-        push_kind: how all-scatter tiles travel: ``"tma"`` (one thread issues a TMA store per rank), ``"tma_spread"``
-            (four issuing threads), ``"stores"`` (16-byte stores by all epilogue threads) or ``"multimem"`` (one
-            ``multimem.st`` per 16 bytes on a heap bound to an NVLS multicast object).  ``None``: ``DEFAULT_PUSH_KIND``.
+        push_kind: how tiles travel in the all-scatter and atomic all-reduce forms: ``"tma"`` (one thread issues a TMA
+            store / reduce-add per rank), ``"tma_spread"`` (four issuing threads), ``"stores"`` (16-byte stores by all
+            epilogue threads; all-scatter only) or ``"multimem"`` (one ``multimem.st`` / ``multimem.red.add`` per 16
+            bytes on a heap bound to an NVLS multicast object: the switch delivers it to every rank).  ``None``:
+            ``DEFAULT_PUSH_KIND``.
 
     The element type (bf16 or fp16, fp32 accumulation) is taken from ``bt``; the reference's drivers offer
     ``--datatype fp16|bf16|...`` (``examples/07_gemm_all_scatter/benchmark.py:36-41``).
@@ -280,7 +284,9 @@ class FusedGemm:
             if push_kind is not None:
                 raise RuntimeError("push_kind='multimem' needs heap_mode='vmm' with IRIS_NVLS=1, one process per GPU")
             pk = "tma"
-        if not (self.store_all and mode == "store"):
+        if not (self.store_all and mode in ("store", "reduce")) or (mode == "reduce" and pk == "stores"):
+            if push_kind is not None and pk != "tma":
+                raise ValueError(f"push_kind={pk!r} does not apply to mode={mode!r}")
             pk = "tma"
         self.push_kind = pk
         d.push_kind = PUSH_KINDS[pk]

@@ -152,6 +152,13 @@ def plan_gemm(M: int, N: int, K: int, world: int, num_local: int, mode: str, sms
         if ks > 1:
             dp_tiles, sk_units, sk_tiles = T, 0, 0
             ctas = min(max_units, T * ks) * cta_group
+    # ---- atomic all-reduce of a short matrix: the K range of every tile is cut into pieces computed by different
+    # CTAs, each of which adds its partial tile straight into the outputs (no slots, no summing pass) ----
+    if mode == "reduce" and ksplit is not None and int(ksplit) > 1:
+        ks = max(1, min(int(ksplit), kblocks))
+        if ks > 1:
+            dp_tiles, sk_units, sk_tiles = T, 0, 0
+            ctas = min(max_units, T * ks) * cta_group
     pulls = mode in ("one_shot", "two_shot")
     # ---- ragged last wave of a whole-tile schedule: cut its tiles into column pieces (nothing to fix up) ----
     tail_tiles, tsplit = 0, 1

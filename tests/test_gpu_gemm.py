@@ -210,6 +210,34 @@ def test_collectives_in_fp16_and_narrow_tiles(variant, bn, dtype):
     ranks[0].close()
 
 
+@pytest.mark.parametrize("m,bn,ksplit", [(1, 64, 4), (128, 128, 8), (100, 256, 3), (256, 128, 2)])
+@pytest.mark.parametrize("world", [2, 4])
+def test_atomic_all_reduce_with_k_split(world, m, bn, ksplit):
+    """Atomic all-reduce of a short matrix: every (tile, K piece) is computed by its own CTA and added straight into
+    all ranks' outputs; called three times (the output is cleared before every call)."""
+    n, k_full = 1024, 5504
+    ks = k_full // world
+    ranks = iris.Iris.local_world(world, heap_size=96 << 20)
+    a_full, b_full = _rand((m, k_full), 16), _rand((n, k_full), 17, 0.05)
+    a = [a_full[:, r * ks:(r + 1) * ks] for r in range(world)]
+    bt = [b_full[:, r * ks:(r + 1) * ks] for r in range(world)]
+    op = G.gemm_all_reduce(ranks, a, bt, variant="atomic", bn=bn, ksplit=ksplit)
+    assert op.ksplit == ksplit
+    for _ in range(3):
+        outs = op()
+    op.check()
+    # the partial sums are added up in bf16, piece by piece, in memory: the rounding acts on the pieces' magnitudes
+    kb = -(-ks // 64)
+    cuts = [min(ks, 64 * (kb * q // ksplit)) for q in range(ksplit + 1)]
+    pieces = [a[r][:, cuts[q]:cuts[q + 1]].float() @ bt[r][:, cuts[q]:cuts[q + 1]].float().t()
+              for r in range(world) for q in range(ksplit)]
+    ref, scale = sum(pieces), sum(p.abs() for p in pieces)
+    for r in range(world):
+        _assert_close(outs[r], ref, scale=scale, ulps=2.0 + world * ksplit)
+    op.close()
+    ranks[0].close()
+
+
 @pytest.mark.parametrize("m,ksplit", [(1, None), (100, None), (128, 3), (256, None), (128, 1)])
 @pytest.mark.parametrize("world", [2, 4])
 def test_one_shot_push_short_matrices(world, m, ksplit):

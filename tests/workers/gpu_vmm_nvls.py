@@ -87,6 +87,22 @@ def main():
             assert bool(((c.float() - ref).abs() <= 2.0 ** -7 * ref.abs() + 1e-3 * ref.abs().max().item()).all()), \
                 "multimem all-scatter mismatch"
             sc.close()
+            # atomic all-reduce of a short matrix: every 64-column tile is added into all ranks' outputs by the
+            # switch (one multimem.red per 16 bytes)
+            ar = G.gemm_all_reduce(ctx, [a_full[:128, rank * ks:(rank + 1) * ks]],
+                                   [b_full[:, rank * ks:(rank + 1) * ks]], variant="atomic", bn=64,
+                                   push_kind="multimem")
+            assert ar.push_kind == "multimem" and ar.bn == 64
+            for _ in range(3):
+                o = ar()[0]
+            ctx.barrier()
+            ar.check()
+            parts = [a_full[:128, r * ks:(r + 1) * ks].float() @ b_full[:, r * ks:(r + 1) * ks].float().t()
+                     for r in range(world)]
+            ref, scale = sum(parts), sum(p.abs() for p in parts)
+            tol = (2 + 2 * world) * 2.0 ** -8 * scale + 1e-3 * ref.abs().max().item()
+            assert bool(((o.float() - ref).abs() <= tol).all()), "multimem atomic all-reduce mismatch"
+            ar.close()
             msg += " + NVLS OK"
     ctx.barrier()
     ctx.close()

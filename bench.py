@@ -117,7 +117,7 @@ def main() -> int:
     bt_peer = bt_full[peer * n_local:(peer + 1) * n_local].clone() if world > 1 else None
     del bt_full
     a_host = a_dev.cpu().pin_memory()
-    row_host = torch.empty((N,), dtype=torch.bfloat16).pin_memory()
+    rows_host = [torch.empty((N,), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
 
     def barrier():
         torch.cuda.synchronize()
@@ -196,13 +196,15 @@ def main() -> int:
         tflops = 2.0 * M * N * K / (ms_step * 1e-3) / 1e12
 
         # ---- end to end through the public API: H2D of this step's input, fused op, D2H of one row of C ----
-        # Two buffer sets (and a plan on each) let the copy of step i+1 run on a side stream while step i computes;
-        # the result row of step i is read back and the stream is synchronised before the next step, as a caller
-        # that consumes the result would do.
+        # Two buffer sets (and a plan on each) let the copy of step i+1 run on a side stream while step i computes.
+        # The result row of step i is copied back asynchronously; the host waits for the row of step i-1 after it has
+        # launched step i (a caller that consumes every result, one step behind, so that the device never idles
+        # waiting for the host to launch).
         copy_stream = torch.cuda.Stream(device=dev)
         main_stream = torch.cuda.current_stream()
         ready = [torch.cuda.Event(), torch.cuda.Event()]
         consumed = [torch.cuda.Event(), torch.cuda.Event()]
+        d2h_done = [torch.cuda.Event(), torch.cuda.Event()]
         if world == 1:
             a_bufs = [a_dev, torch.empty_like(a_dev)]
             ops = [op, G.gemm_all_scatter(ctx, [a_bufs[1]], [bt_local])]
@@ -233,8 +235,11 @@ def main() -> int:
                 main_stream.wait_event(ready[b])
                 row = run(b)
                 consumed[b].record(main_stream)
-                row_host.view(row.shape).copy_(row, non_blocking=True)
-                main_stream.synchronize()                    # the caller consumes the row before the next step
+                rows_host[b].view(row.shape).copy_(row, non_blocking=True)
+                d2h_done[b].record(main_stream)
+                if i >= 1:
+                    d2h_done[b ^ 1].synchronize()            # the row of step i-1 is on the host: the caller uses it
+            d2h_done[(n - 1) & 1].synchronize()
 
         def time_e2e(run, dst):
             e2e_steps(run, dst, 4)
@@ -296,7 +301,7 @@ def main() -> int:
                     "tflops": round(2.0 * M * N * K / (base_ms * 1e-3) / 1e12, 1), "per_step_ms": bst,
                     "e2e": {"ms_per_step": round(base_e2e_ms, 4),
                             "value": round(2.0 * M * N * K / (base_e2e_ms * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
-                            "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": row_host.numel() * 2}}
+                            "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": rows_host[0].numel() * 2}}
 
         out = {
             "metric": "fused GEMM+all-scatter TFLOPS (2MNK/time, device-timed, max over ranks)",
@@ -314,7 +319,7 @@ def main() -> int:
                                         "configuration"},
             "per_step_ms": dict(st, steps=[round(x, 4) for x in per_step]),
             "e2e": {"value": round(e2e_tflops, 2), "unit": "TFLOP/s", "ms_per_step": round(e2e_ms, 4),
-                    "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": row_host.numel() * 2,
+                    "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": rows_host[0].numel() * 2,
                     "input": "whole A per step" if world == 1 else
                              "M / N rows of A per rank per step; the kernel's all-gather prologue distributes them"},
             "gpu_launches": launches,
@@ -338,7 +343,7 @@ def main() -> int:
 
 
 def run_selfcheck(ctx, G, torch, dist, dev, rank, world, barrier):
-    """GEMM + all-reduce (atomic, one-shot, two-shot), GEMM + reduce-scatter and all-gather -> GEMM between the real
+    """GEMM + all-reduce (atomic, one-shot, two-shot, push two-shot), GEMM + reduce-scatter and all-gather -> GEMM between the real
     GPUs of this run, each called three times back to back without a host barrier, against an fp32 product of the
     unsharded operands.  Returns {name: worst error / tolerance over the ranks} (<= 1 passes)."""
     mark = ctx.mark()
@@ -357,7 +362,7 @@ def run_selfcheck(ctx, G, torch, dist, dev, rank, world, barrier):
     a_l, b_l = a_full[:, rank * ks:(rank + 1) * ks], b_full[:, rank * ks:(rank + 1) * ks]
     parts = [a_full[:, r * ks:(r + 1) * ks].float() @ b_full[:, r * ks:(r + 1) * ks].float().t() for r in range(world)]
     ref, scale = sum(parts), sum(p.abs() for p in parts)
-    for name in ("atomic", "one_shot", "two_shot", "reduce_scatter"):
+    for name in ("atomic", "one_shot", "two_shot", "two_shot_push", "reduce_scatter"):
         try:
             if name == "reduce_scatter":
                 op = G.gemm_reduce_scatter(ctx, [a_l], [b_l])

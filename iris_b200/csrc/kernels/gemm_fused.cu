@@ -121,8 +121,13 @@ __device__ __forceinline__ void acc_x8(float* acc, uint4 v, bool f16) {
 // `out_pitch` bytes).  Called by the 128 reducer threads (`rt` = 0..127).  A warp reads whole 512-byte rows (one
 // 16-byte load per lane), four rows of two slots in flight per thread.  Kept out of line so that its registers do
 // not add to those of the kernel's other roles.
+// With `bcast` (push two-shot all-reduce) every summed row is written to the outputs of all `W` ranks instead: `outp`
+// is then the offset of the output from the heap base and the row index is the global one (`mo + out_row_add`); on a
+// heap bound to an NVLS multicast object (`mc` != 0) that is one multimem.st per 16 bytes.
 __device__ __noinline__ void rs_sum_part(const uint8_t* inbox, uint8_t* outp, uint64_t out_pitch, int N, int part_row0,
-                                         int slot_rows, int ns, int mo, int n0, int rt, int bn, bool f16) {
+                                         int slot_rows, int ns, int mo, int n0, int rt, int bn, bool f16,
+                                         bool bcast = false, int out_row_add = 0, const uint64_t* heap_base = nullptr,
+                                         int rank = 0, int W = 1, uint64_t mc = 0) {
   const int rw = rt >> 5, rl = rt & 31;
   const int col = n0 + rl * 8;
   if (col >= N || rl * 8 >= bn) return;  // past the matrix edge / past this (narrower) tile
@@ -162,7 +167,17 @@ __device__ __noinline__ void rs_sum_part(const uint8_t* inbox, uint8_t* outp, ui
       o.y = pack2(a4[u][2], a4[u][3], f16);
       o.z = pack2(a4[u][4], a4[u][5], f16);
       o.w = pack2(a4[u][6], a4[u][7], f16);
-      st_v4(reinterpret_cast<uint4*>(outp + (uint64_t)(mo + r0 + u) * out_pitch + (uint64_t)col * 2), o);
+      if (!bcast) {
+        st_v4(reinterpret_cast<uint4*>(outp + (uint64_t)(mo + r0 + u) * out_pitch + (uint64_t)col * 2), o);
+      } else {
+        const uint64_t off = reinterpret_cast<uint64_t>(outp) + (uint64_t)(mo + out_row_add + r0 + u) * out_pitch +
+                             (uint64_t)col * 2;
+        if (mc) {
+          nvls::st_v4(reinterpret_cast<void*>(mc + off), o);
+        } else {
+          for (int q = 0; q < W; ++q) st_v4(reinterpret_cast<uint4*>(heap_base[(rank + 1 + q) % W] + off), o);
+        }
+      }
     }
   }
 }
@@ -286,10 +301,14 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
 
   // Entry flag: tell every rank that this rank has started call `epoch` (its output buffers are ready to be
   // written by peers).  One thread of one CTA per rank.
+  // The flag orders nothing written by this kernel (it has written nothing yet); what a peer relies on, the end of
+  // this rank's previous call, is ordered by the kernel boundary.  One fence, then relaxed stores: a release store
+  // per peer would wait for the previous peer's acknowledgement each time, a link round trip per rank.
   if (W > 1 && cta == 0 && threadIdx.x == 0) {
+    fence_sys();
     for (int i = 0; i < W; ++i) {
       const int t = (rank + 1 + i) % W;
-      st_release_sys(flag_ptr(p, t, 8 + rank), p.epoch);
+      st_relaxed_sys(flag_ptr(p, t, 8 + rank), p.epoch);
     }
   }
 
@@ -715,7 +734,10 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
       }
       named_barrier_sync(1, 128);
       if (issuer) {
-        for (int i = 0; i < W; ++i) red_release_sys_add(flag_ptr(p, (rank + 1 + i) % W, 0), 1u);
+        // every writer has fenced at system scope and met this thread at the barrier: one more fence makes that
+        // cumulative, and the arrivals themselves can be relaxed (a release per rank would cost a round trip each)
+        fence_sys();
+        for (int i = 0; i < W; ++i) red_relaxed_sys_add(flag_ptr(p, (rank + 1 + i) % W, 0), 1u);
         if (ok_all) wait_until_ge(flag_ptr(p, rank, 0), p.done_target, p.timeout_ns, status, kSiteDone, rank, cta);
       }
     } else if (lead) {
@@ -826,12 +848,20 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
             ok_all = false;
             break;
           }
+          if (p.rs_bcast) {
+            // push two-shot: the summed rows go to every rank's output (offset of the output from the heap base)
+            rs_sum_part(reinterpret_cast<const uint8_t*>(p.heap_base[rank] + p.partial_off),
+                        reinterpret_cast<uint8_t*>(p.partial_off + (uint64_t)p.out_row0 * p.N * 2), (uint64_t)p.N * 2,
+                        p.N, p.part_row0, p.part_slot_rows, NS, m0 - rs_base, n0, rt, bn, f16, true, rs_base,
+                        p.heap_base, rank, W, p.mc_base);
+          } else {
           rs_sum_part(reinterpret_cast<const uint8_t*>(p.heap_base[rank] + p.partial_off),
                       p.out_row0 >= 0 ? reinterpret_cast<uint8_t*>(p.heap_base[rank] + p.partial_off) +
                                             (uint64_t)p.out_row0 * p.N * 2
                                       : reinterpret_cast<uint8_t*>(p.heap_base[rank] + p.out_off),
                       p.out_row0 >= 0 ? (uint64_t)p.N * 2 : (uint64_t)p.ldo * 2, p.N, p.part_row0, p.part_slot_rows, NS,
                       m0 - rs_base, n0, rt, bn, f16);
+          }
           if (rissuer) trace(p, rank, t * CG + pr, kTrPullEnd);
           continue;
         }
@@ -1039,14 +1069,14 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
       }
       // Two-shot: when this CTA's pushes have landed, bump every rank's arrival counter and wait (bounded) until
       // every CTA of every rank has done so: at kernel end all result tiles are in local memory.
-      if (two_shot && W > 1) {
+      if ((two_shot || p.rs_bcast) && W > 1) {
         fence_sys();
         named_barrier_sync(3, 128);
         if (rissuer) {
           bulk_wait<0>();
           fence_proxy_async_all();
           fence_sys();
-          for (int i = 0; i < W; ++i) red_release_sys_add(flag_ptr(p, (rank + 1 + i) % W, 0), 1u);
+          for (int i = 0; i < W; ++i) red_relaxed_sys_add(flag_ptr(p, (rank + 1 + i) % W, 0), 1u);
           if (ok_all) wait_until_ge(flag_ptr(p, rank, 0), p.done_target, p.timeout_ns, status, kSiteDone, rank, cta);
         }
       } else if (rissuer) {
@@ -1239,6 +1269,7 @@ struct IrisGemmDesc {
   int dp_tiles, sk_units, sk_flag_base;  // stream-K schedule (dp_tiles < 0: every tile whole)
   int push_partials, part_slot_rows, ksplit;
   int rs_rows;                 // reduce-scatter: rows kept per rank (0 = off); see FusedGemmParams::rs_rows
+  int rs_bcast;                // with rs_rows: the keeper writes the summed rows to every rank's output (all-reduce)
   int bn;                      // tile width: 64, 128 or 256 (0 = 256)
   int dtype;                   // ElemType: 0 = bf16, 1 = fp16
   int push_kind;               // PushKind of the all-scatter epilogue
@@ -1377,6 +1408,10 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
       snprintf(g_err, sizeof(g_err), "reduce-scatter: inbox slots must hold rs_rows rows");
       return nullptr;
     }
+    if (d->rs_bcast && d->out_row0 < 0) {
+      snprintf(g_err, sizeof(g_err), "push two-shot: the output must be the symmetric one inside the partial matrix");
+      return nullptr;
+    }
   }
   if (d->ag) {
     if (d->M % d->world != 0 || (d->M / d->world) % (BM * cg) != 0) {
@@ -1501,6 +1536,7 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
     p.part_slot_rows = d->part_slot_rows;
     p.ksplit = d->ksplit > 1 ? d->ksplit : 1;
     p.rs_rows = d->rs_rows > 0 ? d->rs_rows : 0;
+    p.rs_bcast = (p.rs_rows > 0 && d->rs_bcast) ? 1 : 0;
     p.tile_flag_base = d->tile_flag_base;
     p.ag_flag_base = d->ag_flag_base;
     p.bn = bn;

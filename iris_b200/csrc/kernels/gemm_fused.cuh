@@ -108,6 +108,8 @@ struct FusedGemmParams {
                          // of the sum.  A partial tile goes to the inbox of the rank that keeps its rows only (slot = source
                          // rank, rows relative to the keeper's first row); rank r takes successive tiles from the row blocks
                          // r + 1, r + 2, ..., r in turn, so that at any time every keeper is receiving from one source.  0 = off
+  int rs_bcast;          // with rs_rows: the keeper writes every summed row to the output of ALL ranks (the output then has
+                         // all M rows): GEMM + all-reduce as reduce-scatter by pushes + broadcast ("push two-shot")
   int store_all;         // store/reduce modes: 1 = push the tile to every rank, 0 = own rank only
   int tile_flag_base;    // index (uint32 units from flags_off) of the per-tile flags
   int ag_flag_base;      // index of the all-gather chunk flags: [src rank][chunk]

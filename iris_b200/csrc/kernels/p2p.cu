@@ -265,9 +265,10 @@ __global__ void mp_kernel(MpArgs a) {
 __global__ void device_barrier_kernel(const uint64_t* hb, uint64_t counter_off, uint64_t status_off, int rank,
                                       int world, uint32_t target, uint64_t timeout_ns) {
   if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  fence_sys();  // one fence, then relaxed arrivals: a release per rank would wait for the previous rank's answer
   for (int i = 0; i < world; ++i) {
     const int t = (rank + 1 + i) % world;
-    red_release_sys_add(reinterpret_cast<uint32_t*>(hb[t] + counter_off), 1u);
+    red_relaxed_sys_add(reinterpret_cast<uint32_t*>(hb[t] + counter_off), 1u);
   }
   wait_until_ge(reinterpret_cast<const uint32_t*>(hb[rank] + counter_off), target, timeout_ns,
                 reinterpret_cast<StatusBlock*>(hb[rank] + status_off), /*where=*/70, (uint32_t)rank, target);

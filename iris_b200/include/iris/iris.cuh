@@ -429,6 +429,13 @@ IRIS_HD void st_release_sys(uint32_t* p, uint32_t v) {
   __atomic_store_n(p, v, __ATOMIC_RELEASE);
 #endif
 }
+IRIS_HD void st_relaxed_sys(uint32_t* p, uint32_t v) {
+#if IRIS_ON_DEVICE
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+#else
+  __atomic_store_n(p, v, __ATOMIC_RELAXED);
+#endif
+}
 IRIS_HD void red_release_sys_add(uint32_t* p, uint32_t v) {
 #if IRIS_ON_DEVICE
   asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");

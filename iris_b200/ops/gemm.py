@@ -51,7 +51,7 @@ class _Desc(ctypes.Structure):
         ("device", ctypes.c_int), ("cta_group", ctypes.c_int),
         ("dp_tiles", ctypes.c_int), ("sk_units", ctypes.c_int), ("sk_flag_base", ctypes.c_int),
         ("push_partials", ctypes.c_int), ("part_slot_rows", ctypes.c_int), ("ksplit", ctypes.c_int),
-        ("rs_rows", ctypes.c_int),
+        ("rs_rows", ctypes.c_int), ("rs_bcast", ctypes.c_int),
         ("bn", ctypes.c_int), ("dtype", ctypes.c_int), ("push_kind", ctypes.c_int),
         ("tail_tiles", ctypes.c_int), ("tail_split", ctypes.c_int),
         ("c_off", ctypes.c_uint64),
@@ -117,6 +117,8 @@ class FusedGemm:
         ag: run the all-gather prologue (A rows sharded M / world per rank; see ``a_full``).
         reduce_scatter: with ``mode="one_shot"``: every rank keeps only its own ``M / world`` rows of the sum
             (``out[l]`` is that block); partial tiles are pushed to the keeper of their rows only.
+        bcast: with ``reduce_scatter``: the keeper writes its summed rows into every rank's output, which makes the
+            op an all-reduce whose traffic is all one-way pushes ("push two-shot"; ``out[l]`` has all ``M`` rows).
         push / ksplit: one-shot for short matrices: partials pushed into inbox slots of every rank, K cut into pieces.
             With ``mode="reduce"`` (atomic all-reduce) ``ksplit`` cuts K into pieces computed by different CTAs that
             all add into the outputs, which spreads a short matrix over the whole GPU.
@@ -145,7 +147,7 @@ class FusedGemm:
                  cta_group: Optional[int] = None, trace: bool = False, stream_k: Optional[bool] = None,
                  push: Optional[bool] = None, ksplit: Optional[int] = None, nvls: Optional[bool] = None,
                  reduce_scatter: bool = False, bn: Optional[int] = None, tail_split: Optional[bool] = None,
-                 push_kind: Optional[str] = None):
+                 push_kind: Optional[str] = None, bcast: bool = False):
         self.ctxs: List[Iris] = [ctxs] if isinstance(ctxs, Iris) else list(ctxs)
         c0 = self.ctxs[0]
         if c0.backend != "cuda":
@@ -187,7 +189,7 @@ class FusedGemm:
         pl = plan_gemm(self.M, self.N, self.K, self.world, self.num_local, mode, sms, ag=self.ag, cta_group=cta_group,
                        ctas_per_rank=ctas_per_rank, group_m=group_m, stream_k=stream_k, push=push, ksplit=ksplit,
                        reduce_scatter=reduce_scatter, store_all=store_all, own_out=out is not None, bn=bn,
-                       tail_split=tail_split)
+                       tail_split=tail_split, bcast=bcast)
         self.plan = pl
         cta_group, group_m = pl.cta_group, pl.group_m
         self.cta_group, self.rs_rows, self.ctas_per_rank = pl.cta_group, pl.rs_rows, pl.ctas_per_rank
@@ -208,7 +210,7 @@ class FusedGemm:
             rows, mp, slots, regions = pl.rows, pl.slot_rows, pl.slots, pl.regions
             self._pull_buf = [c.zeros((regions * mp, self.N), dtype=self.dtype) for c in self.ctxs]
             self.partial = [[b[q * slots * mp:q * slots * mp + rows] for b in self._pull_buf] for q in range(2)]
-            self.out = list(out) if out is not None else [b[2 * slots * mp:2 * slots * mp + rows]
+            self.out = list(out) if out is not None else [b[2 * slots * mp:2 * slots * mp + pl.out_rows]
                                                           for b in self._pull_buf]
             c_bufs, c2_bufs = self._pull_buf, None
             ldc, c_cols_eff = self.N, self.N
@@ -263,6 +265,8 @@ class FusedGemm:
         d.part_slot_rows = getattr(self, "_slot_rows", 0)
         d.ksplit = self.ksplit
         d.rs_rows = self.rs_rows
+        d.rs_bcast = int(pl.bcast)
+        self.bcast = pl.bcast
         d.dp_tiles = self.dp_tiles if self.sk_units else -1
         d.sk_units = self.sk_units
         d.sk_flag_base = FLAG_HEADER + tile_flags + self.world * chunks_per_shard
@@ -273,9 +277,10 @@ class FusedGemm:
         d.c_off = c_off if self.store_all else 0
         # two-shot on a heap bound to an NVLS multicast object: the switch sums and broadcasts
         mc = int(getattr(c0, "mc_base", 0) or 0)
-        self.nvls = bool(mc) and mode == "two_shot" and self.num_local == 1 and out is None and nvls is not False
+        self.nvls = (bool(mc) and (mode == "two_shot" or pl.bcast) and self.num_local == 1 and out is None
+                     and nvls is not False)
         if nvls and not self.nvls:
-            raise RuntimeError("nvls=True needs heap_mode='vmm' with IRIS_NVLS=1, mode='two_shot', one process per GPU")
+            raise RuntimeError("nvls=True needs heap_mode='vmm' with IRIS_NVLS=1, a two-shot variant, one process per GPU")
         # all-scatter pushes: which instructions carry a finished tile to the other ranks
         pk = DEFAULT_PUSH_KIND if push_kind is None else push_kind
         if pk not in PUSH_KINDS:
@@ -395,8 +400,11 @@ def gemm_all_scatter(ctxs, a, bt, **kw) -> FusedGemm:
 
 def gemm_all_reduce(ctxs, a, bt, variant: str = "one_shot", **kw) -> FusedGemm:
     """``C[M, N] = sum over ranks of A_r @ B_r`` (K sharded).  ``variant``: ``"atomic"``
-    (``examples/08_gemm_atomics_all_reduce``), ``"one_shot"`` (``examples/09_gemm_one_shot_all_reduce``) or
-    ``"two_shot"`` (each tile summed by one owner rank and pushed: the bandwidth-optimal extra)."""
+    (``examples/08_gemm_atomics_all_reduce``), ``"one_shot"`` (``examples/09_gemm_one_shot_all_reduce``),
+    ``"two_shot"`` (each tile summed by one owner rank, which fetches the partials and pushes the result: the traffic
+    of a library all-reduce) or ``"two_shot_push"`` (the same traffic made of one-way pushes only: partial tiles are
+    pushed to the rank that keeps their rows, as in :func:`gemm_reduce_scatter`, and the keeper writes the summed rows
+    to every rank; needs ``M`` to be a multiple of ``world x 128``)."""
     if variant == "auto":
         # short matrices are latency-bound: one-shot with pushed partials; tall ones are bandwidth-bound: two-shot
         variant = "one_shot" if a[0].shape[0] <= 2 * BM else "two_shot"
@@ -404,7 +412,9 @@ def gemm_all_reduce(ctxs, a, bt, variant: str = "one_shot", **kw) -> FusedGemm:
         return FusedGemm(ctxs, a, bt, "reduce", store_all=True, **kw)
     if variant in ("one_shot", "two_shot"):
         return FusedGemm(ctxs, a, bt, variant, **kw)
-    raise ValueError("variant must be 'auto', 'atomic', 'one_shot' or 'two_shot'")
+    if variant == "two_shot_push":
+        return FusedGemm(ctxs, a, bt, "one_shot", reduce_scatter=True, bcast=True, **kw)
+    raise ValueError("variant must be 'auto', 'atomic', 'one_shot', 'two_shot' or 'two_shot_push'")
 
 
 def gemm_reduce_scatter(ctxs, a, bt, **kw) -> FusedGemm:

@@ -51,6 +51,8 @@ class GemmPlan:
     c_rows: int
     part_row0: Tuple[int, int]
     out_row0: int
+    out_rows: int = 0       # rows of the output region (M for the push two-shot, else `rows`)
+    bcast: bool = False     # reduce-scatter whose keeper broadcasts the summed rows (push two-shot all-reduce)
     bn: int = BN            # tile width in columns
     tail_tiles: int = 0     # tiles at the end of the raster that are cut into column pieces ...
     tail_split: int = 1     # ... and into how many (1: none)
@@ -83,7 +85,7 @@ def plan_gemm(M: int, N: int, K: int, world: int, num_local: int, mode: str, sms
               cta_group: Optional[int] = None, ctas_per_rank: Optional[int] = None, group_m: int = 8,
               stream_k: Optional[bool] = None, push: Optional[bool] = None, ksplit: Optional[int] = None,
               reduce_scatter: bool = False, store_all: bool = False, own_out: bool = False,
-              bn: Optional[int] = None, tail_split: Optional[bool] = None) -> GemmPlan:
+              bn: Optional[int] = None, tail_split: Optional[bool] = None, bcast: bool = False) -> GemmPlan:
     """Decide tile shape, persistent grid, schedule, flag count and buffer layout.  ``sms``: SMs of the device;
     ``own_out``: the caller brings the output buffer (the [partials | out] matrix then has no output region);
     ``bn``: tile width (64, 128 or 256; default 256); ``tail_split``: cut the tiles of a ragged last wave into column
@@ -178,15 +180,24 @@ def plan_gemm(M: int, N: int, K: int, world: int, num_local: int, mode: str, sms
         rows = rs_rows if rs_rows else M
         mp = -(-rows // (2 * BM)) * (2 * BM)
         slots = world * ks if do_push else 1
-        regions = 2 * slots + (0 if own_out else 1)
+        if bcast:
+            # push two-shot: the keeper of a row block writes its summed rows into every rank's output, which therefore
+            # holds all M rows (world blocks) and has to be the symmetric one
+            if not rs_rows or own_out:
+                raise ValueError("bcast=True goes with reduce_scatter=True and the op's own output buffer")
+            out_rows, out_regions = M, world
+        else:
+            out_rows, out_regions = rows, (0 if own_out else 1)
+        regions = 2 * slots + out_regions
         c_rows, part_row0 = regions * mp, (0, slots * mp)
         out_row0 = -1 if own_out else 2 * slots * mp
     else:
-        rows, mp, slots, regions, c_rows, part_row0, out_row0 = M, 0, 0, 0, 0, (0, 0), -1
+        rows, mp, slots, regions, c_rows, part_row0, out_row0, out_rows = M, 0, 0, 0, 0, (0, 0), -1, M
     return GemmPlan(M=M, N=N, K=K, world=world, num_local=num_local, mode=mode, ag=bool(ag), cta_group=cta_group,
                     group_m=int(group_m), rs_rows=rs_rows, ctas_per_rank=ctas, total_tiles=T, kblocks=kblocks,
                     dp_tiles=dp_tiles, sk_units=sk_units, sk_tiles=sk_tiles, push=do_push, ksplit=ks,
                     store_all=bool(store_all) and world > 1, pulls=pulls, chunks_per_shard=chunks_per_shard,
                     tile_flags=tile_flags, sk_flags=sk_flags, nflags=nflags, rows=rows, slot_rows=mp, slots=slots,
-                    regions=regions, c_rows=c_rows, part_row0=part_row0, out_row0=out_row0, bn=bn,
+                    regions=regions, c_rows=c_rows, part_row0=part_row0, out_row0=out_row0, out_rows=out_rows,
+                    bcast=bool(bcast) and bool(rs_rows), bn=bn,
                     tail_tiles=tail_tiles, tail_split=tsplit)

@@ -288,6 +288,32 @@ def test_gemm_reduce_scatter_emulated(world, m, cta_group):
     ranks[0].close()
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("world,m,cta_group,bn", [(2, 1024, 2, 256), (4, 2048, 2, 128), (4, 1536, 1, 256), (8, 2048, 2, 256),
+                                                  (8, 1024, 1, 64)])
+def test_push_two_shot_all_reduce_emulated(world, m, cta_group, bn, dtype):
+    """GEMM + all-reduce as pushes only: partial tiles go to the keeper of their rows, the keeper sums them from local
+    memory and writes the result rows into every rank's output."""
+    n, k_full = 768, 2048
+    ks = k_full // world
+    ranks = iris.Iris.local_world(world, heap_size=128 << 20)
+    a_full, b_full = _rand((m, k_full), 26, dtype=dtype), _rand((n, k_full), 27, 0.05, dtype=dtype)
+    a = [a_full[:, r * ks:(r + 1) * ks] for r in range(world)]
+    bt = [b_full[:, r * ks:(r + 1) * ks] for r in range(world)]
+    op = G.gemm_all_reduce(ranks, a, bt, variant="two_shot_push", cta_group=cta_group, bn=bn)
+    assert op.bcast and op.rs_rows == m // world
+    for _ in range(3):
+        outs = op()
+    op.check()
+    parts = [a[r].float() @ bt[r].float().t() for r in range(world)]
+    ref, scale = sum(parts), sum(p.abs() for p in parts)
+    for r in range(world):
+        assert outs[r].shape == (m, n)
+        _assert_close(outs[r], ref, scale=scale, ulps=2.0 + world)
+    op.close()
+    ranks[0].close()
+
+
 def test_no_kernel_writes_outside_its_buffers():
     """Every fused variant on a debug heap (guard bytes behind each allocation), shapes with ragged edges: after the
     calls the guards are intact and all ranks made the same allocations."""
@@ -302,6 +328,7 @@ def test_no_kernel_writes_outside_its_buffers():
     ops.append(G.gemm_all_reduce(ranks, [x[:100] for x in a], bt, variant="one_shot"))            # pushed, K-split
     ops.append(G.gemm_all_scatter(ranks, [a_full] * world, [_rand((320, k_full), 43 + r, 0.05) for r in range(world)]))
     ops.append(G.gemm_reduce_scatter(ranks, [x[:512] for x in a], bt))
+    ops.append(G.gemm_all_reduce(ranks, [x[:512] for x in a], bt, variant="two_shot_push"))
     ag = G.all_gather_gemm(ranks, 512, [_rand((320, 512), 50 + r, 0.05) for r in range(world)], ag_slices=4)
     for r in range(world):
         ag.a_full[r][r * 256:(r + 1) * 256].copy_(_rand((256, 512), 60 + r))

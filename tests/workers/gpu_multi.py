@@ -137,6 +137,15 @@ def main():
     rows = slice(rank * 512, (rank + 1) * 512)
     close(o, ref[rows], scale=scale[rows], ulps=2.0 + world)
     rs.close()
+    # the same partial pushes, but the keeper writes the summed rows to every rank: all-reduce made of pushes only
+    tp = G.gemm_all_reduce(ctx, [a_rs[:, rank * ks:(rank + 1) * ks]], [b_full[:, rank * ks:(rank + 1) * ks]],
+                           variant="two_shot_push")
+    for _ in range(4):
+        o = tp()[0]
+    ctx.barrier()
+    tp.check()
+    close(o, ref, scale=scale, ulps=2.0 + world)
+    tp.close()
 
     m2 = 256 * world
     ms = m2 // world

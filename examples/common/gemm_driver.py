@@ -27,20 +27,30 @@ def parse_args(kind: str):
     ap.add_argument("-v", "--validate", action="store_true")
     ap.add_argument("-t", "--trace_tiles", action="store_true", help="record per-tile device timestamps to trace_rank<r>.json")
     ap.add_argument("-b", "--benchmark", action="store_true")
-    ap.add_argument("--datatype", default="bf16", choices=["bf16"])
+    ap.add_argument("--datatype", default="bf16", choices=["fp16", "bf16"],
+                    help="element type of A, B and C (fp32 accumulation); the reference's fp32 / int8 are not offered")
     ap.add_argument("--output_file", default="")
     ap.add_argument("--gsize_m", type=int, default=8, help="m-tiles per raster group")
     ap.add_argument("--heap_size", type=int, default=1 << 31)
     ap.add_argument("--gemm_sms", type=int, default=0, help="CTAs of the persistent grid (0: one per SM)")
-    ap.add_argument("--variant", default=None, help="all-reduce only: atomic | one_shot | two_shot")
+    ap.add_argument("--variant", default=None,
+                    help="all-reduce only: atomic | one_shot | two_shot | two_shot_push | auto")
+    ap.add_argument("--BLK_M", type=int, default=None, choices=[128, 256],
+                    help="tile rows: 128 (one CTA per tile) or 256 (a CTA pair per tile); default: chosen from M")
+    ap.add_argument("--BLK_N", type=int, default=None, choices=[64, 128, 256], help="tile columns (default 256)")
+    ap.add_argument("--tail_split", type=int, default=0,
+                    help="cut the tiles of a ragged last wave into up to this many column pieces (0: off)")
+    ap.add_argument("--push_kind", default=None, choices=["tma", "tma_spread", "stores", "multimem"],
+                    help="all-scatter / atomic: how tiles travel to the other ranks")
+    ap.add_argument("--ksplit", type=int, default=None, help="atomic / one-shot on short matrices: K pieces per tile")
     ap.add_argument("--num_experiments", type=int, default=50)
     ap.add_argument("--num_warmup", type=int, default=10)
     ap.add_argument("--no_baseline", action="store_true")
     ap.add_argument("--heap_mode", default=None, choices=["ipc", "vmm"],
                     help="vmm + IRIS_NVLS=1 in the environment binds the heap to an NVLS multicast object")
     # knobs of the reference that have no meaning on this hardware are accepted and ignored
-    for flag in ("--BLK_M", "--BLK_N", "--BLK_K", "--num_stages", "--num_warps", "--waves_per_eu", "--mfmaInstrSize",
-                 "--kpack", "--total_sms"):
+    for flag in ("--BLK_K", "--num_stages", "--num_warps", "--waves_per_eu", "--mfmaInstrSize", "--kpack",
+                 "--total_sms"):
         ap.add_argument(flag, type=int, default=None, help=argparse.SUPPRESS)
     ap.add_argument("--two_tiles", default="True", help=argparse.SUPPRESS)
     ap.add_argument("--algorithm", default=None, help=argparse.SUPPRESS)
@@ -54,9 +64,14 @@ def run(kind: str, seed: int):
     dev = ctx.get_device()
     m, n, k = args["m"], args["n"], args["k"]
     gen = torch.Generator(device=dev).manual_seed(seed)  # same seed everywhere -> identical A and B
-    A = (torch.randn((m, k), generator=gen, device=dev) * 0.02).to(torch.bfloat16)
-    Bt = (torch.randn((n, k), generator=gen, device=dev) * 0.02).to(torch.bfloat16)  # B = Bt.T, K-major
+    dtype = {"bf16": torch.bfloat16, "fp16": torch.float16}[args["datatype"]]
+    A = (torch.randn((m, k), generator=gen, device=dev) * 0.02).to(dtype)
+    Bt = (torch.randn((n, k), generator=gen, device=dev) * 0.02).to(dtype)  # B = Bt.T, K-major
     ctas = args["gemm_sms"] or None
+    # tile shape and schedule knobs (the reference's BLK_M / BLK_N, examples/07_gemm_all_scatter/benchmark.py:53-60)
+    tile_kw = dict(bn=args["BLK_N"], cta_group={None: None, 128: 1, 256: 2}[args["BLK_M"]])
+    if args["tail_split"] > 1:
+        tile_kw["tail_split"] = args["tail_split"]
     peaks = roofline.load_peaks()
     import torch.distributed as dist
     if kind == "all_scatter":
@@ -65,10 +80,10 @@ def run(kind: str, seed: int):
         nl = n // world
         bt_local = Bt[rank * nl:(rank + 1) * nl].contiguous()
         op = G.gemm_all_scatter(ctx, [A], [bt_local], ctas_per_rank=ctas, group_m=args["gsize_m"],
-                                trace=args["trace_tiles"])
+                                trace=args["trace_tiles"], push_kind=args["push_kind"], **tile_kw)
         roof = roofline.all_scatter_roofline_us(m, n, k, world, peaks)
-        c_part = torch.empty((m, nl), dtype=torch.bfloat16, device=dev)
-        gathered = torch.empty((world, m, nl), dtype=torch.bfloat16, device=dev)
+        c_part = torch.empty((m, nl), dtype=dtype, device=dev)
+        gathered = torch.empty((world, m, nl), dtype=dtype, device=dev)
 
         def unfused():
             torch.cuda.nvtx.range_push("GEMM")
@@ -85,11 +100,12 @@ def run(kind: str, seed: int):
             raise SystemExit("K / ranks must be a multiple of 8")
         ks = k // world
         a_local, b_local = A[:, rank * ks:(rank + 1) * ks], Bt[:, rank * ks:(rank + 1) * ks]
+        tile_kw.pop("tail_split", None)
         op = G.gemm_reduce_scatter(ctx, [a_local], [b_local], ctas_per_rank=ctas, group_m=args["gsize_m"],
-                                   trace=args["trace_tiles"])
+                                   trace=args["trace_tiles"], **tile_kw)
         roof = roofline.all_reduce_roofline_us(m, n, k, world, peaks, "reduce_scatter")
-        c_part = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
-        c_kept = torch.empty((m // world, n), dtype=torch.bfloat16, device=dev)
+        c_part = torch.empty((m, n), dtype=dtype, device=dev)
+        c_kept = torch.empty((m // world, n), dtype=dtype, device=dev)
 
         def unfused():
             torch.matmul(a_local, b_local.t(), out=c_part)
@@ -102,11 +118,19 @@ def run(kind: str, seed: int):
             raise SystemExit("K / ranks must be a multiple of 8")
         ks = k // world
         a_local, b_local = A[:, rank * ks:(rank + 1) * ks], Bt[:, rank * ks:(rank + 1) * ks]  # views, pitch k
+        extra = {k_: v for k_, v in tile_kw.items() if v is not None}
+        if args["ksplit"]:
+            extra["ksplit"] = args["ksplit"]
+        if args["push_kind"] and variant == "atomic":
+            extra["push_kind"] = args["push_kind"]
+        if variant != "atomic":
+            extra.pop("tail_split", None)
         op = G.gemm_all_reduce(ctx, [a_local], [b_local], variant=variant, ctas_per_rank=ctas, group_m=args["gsize_m"],
-                               trace=args["trace_tiles"])
+                               trace=args["trace_tiles"], **extra)
+        variant = {"store": "?", "reduce": "atomic"}.get(op.mode, "two_shot_push" if op.bcast else op.mode)
         roof = roofline.all_reduce_roofline_us(m, n, k, world, peaks,
-                                               "two_shot" if variant == "two_shot" else "one_shot")
-        c_part = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+                                               "two_shot" if variant.startswith("two_shot") else "one_shot")
+        c_part = torch.empty((m, n), dtype=dtype, device=dev)
 
         def unfused():
             torch.matmul(a_local, b_local.t(), out=c_part)
@@ -114,7 +138,9 @@ def run(kind: str, seed: int):
                 dist.all_reduce(c_part)
     js = JSONWriter(args["output_file"] if rank == 0 else "")
     fields = {k_: v for k_, v in args.items() if v is not None}
-    fields.update(world_size=world, variant=variant, gemm_sms=op.ctas_per_rank, tile="128x256x64")
+    fields.update(world_size=world, variant=variant, gemm_sms=op.ctas_per_rank,
+                  tile=f"{128 * op.cta_group}x{op.bn}x64", ksplit=op.ksplit, push_kind=op.push_kind,
+                  tail=[op.tail_tiles, op.tail_split])
     res = op.resources()
     if res:  # the reference's gemm_registers / gemm_spills (examples/07_gemm_all_scatter/benchmark.py:237-242)
         fields.update(gemm_registers=res["registers"], gemm_spills=res["spill_store_bytes"] + res["spill_load_bytes"])

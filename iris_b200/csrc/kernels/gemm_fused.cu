@@ -124,10 +124,21 @@ __device__ __forceinline__ void acc_x8(float* acc, uint4 v, bool f16) {
 // With `bcast` (push two-shot all-reduce) every summed row is written to the outputs of all `W` ranks instead: `outp`
 // is then the offset of the output from the heap base and the row index is the global one (`mo + out_row_add`); on a
 // heap bound to an NVLS multicast object (`mc` != 0) that is one multimem.st per 16 bytes.
-__device__ __noinline__ void rs_sum_part(const uint8_t* inbox, uint8_t* outp, uint64_t out_pitch, int N, int part_row0,
-                                         int slot_rows, int ns, int mo, int n0, int rt, int bn, bool f16,
-                                         bool bcast = false, int out_row_add = 0, const uint64_t* heap_base = nullptr,
-                                         int rank = 0, int W = 1, uint64_t mc = 0) {
+// Few arguments on purpose (everything else is read from the launch parameters): the call sits in a role whose
+// registers are already scarce.
+__device__ __noinline__ void rs_sum_part(const FusedGemmParams& p, int rank, int ns, int mo, int n0, int rt, bool f16) {
+  const int W = p.world, N = p.N, bn = p.bn, part_row0 = p.part_row0, slot_rows = p.part_slot_rows;
+  const bool bcast = p.rs_bcast != 0;
+  const int out_row_add = bcast ? rank * p.rs_rows : 0;
+  const uint64_t mc = bcast ? p.mc_base : 0;
+  const uint64_t* heap_base = p.heap_base;
+  const uint8_t* inbox = reinterpret_cast<const uint8_t*>(p.heap_base[rank] + p.partial_off);
+  // plain reduce-scatter: address of the kept block; broadcast: offset of the output from the heap base
+  uint8_t* outp = bcast ? reinterpret_cast<uint8_t*>(p.partial_off + (uint64_t)p.out_row0 * p.N * 2)
+                  : p.out_row0 >= 0
+                      ? reinterpret_cast<uint8_t*>(p.heap_base[rank] + p.partial_off) + (uint64_t)p.out_row0 * p.N * 2
+                      : reinterpret_cast<uint8_t*>(p.heap_base[rank] + p.out_off);
+  const uint64_t out_pitch = (bcast || p.out_row0 >= 0) ? (uint64_t)p.N * 2 : (uint64_t)p.ldo * 2;
   const int rw = rt >> 5, rl = rt & 31;
   const int col = n0 + rl * 8;
   if (col >= N || rl * 8 >= bn) return;  // past the matrix edge / past this (narrower) tile
@@ -298,6 +309,8 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
   if (CG == 2) cluster_sync_all();  // the partner's barriers exist before anything arrives on them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // trace: when this CTA was ready to work / left (slots of the record of the first tile it handles)
+  if (p.trace_off && threadIdx.x == 0 && unit < total_tiles) trace(p, rank, tile_of(unit) * CG + pr, kTrCtaBegin);
 
   // Entry flag: tell every rank that this rank has started call `epoch` (its output buffers are ready to be
   // written by peers).  One thread of one CTA per rank.
@@ -848,20 +861,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
             ok_all = false;
             break;
           }
-          if (p.rs_bcast) {
-            // push two-shot: the summed rows go to every rank's output (offset of the output from the heap base)
-            rs_sum_part(reinterpret_cast<const uint8_t*>(p.heap_base[rank] + p.partial_off),
-                        reinterpret_cast<uint8_t*>(p.partial_off + (uint64_t)p.out_row0 * p.N * 2), (uint64_t)p.N * 2,
-                        p.N, p.part_row0, p.part_slot_rows, NS, m0 - rs_base, n0, rt, bn, f16, true, rs_base,
-                        p.heap_base, rank, W, p.mc_base);
-          } else {
-          rs_sum_part(reinterpret_cast<const uint8_t*>(p.heap_base[rank] + p.partial_off),
-                      p.out_row0 >= 0 ? reinterpret_cast<uint8_t*>(p.heap_base[rank] + p.partial_off) +
-                                            (uint64_t)p.out_row0 * p.N * 2
-                                      : reinterpret_cast<uint8_t*>(p.heap_base[rank] + p.out_off),
-                      p.out_row0 >= 0 ? (uint64_t)p.N * 2 : (uint64_t)p.ldo * 2, p.N, p.part_row0, p.part_slot_rows, NS,
-                      m0 - rs_base, n0, rt, bn, f16);
-          }
+          rs_sum_part(p, rank, NS, m0 - rs_base, n0, rt, f16);
           if (rissuer) trace(p, rank, t * CG + pr, kTrPullEnd);
           continue;
         }
@@ -1120,10 +1120,11 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
         const uint8_t* src = reinterpret_cast<const uint8_t*>(p.heap_base[rank] + base_off);
         uint8_t* dst = reinterpret_cast<uint8_t*>(p.heap_base[peer] + base_off);
         const int nvec = BM * vec_per_row;
-        for (int i0 = ct; i0 < nvec; i0 += 64 * 8) {
-          uint4 v[8];
+        constexpr int kInFlight = 16;  // 16-byte vectors in flight per thread: 16 KB per CTA, enough for link latency
+        for (int i0 = ct; i0 < nvec; i0 += 64 * kInFlight) {
+          uint4 v[kInFlight];
 #pragma unroll
-          for (int u = 0; u < 8; ++u) {
+          for (int u = 0; u < kInFlight; ++u) {
             const int i = i0 + u * 64;
             if (i < nvec) {
               const int r = i / vec_per_row, cv = i - r * vec_per_row;
@@ -1131,7 +1132,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
             }
           }
 #pragma unroll
-          for (int u = 0; u < 8; ++u) {
+          for (int u = 0; u < kInFlight; ++u) {
             const int i = i0 + u * 64;
             if (i < nvec) {
               const int r = i / vec_per_row, cv = i - r * vec_per_row;
@@ -1153,6 +1154,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
   __syncwarp();
   tc_fence_before();
   __syncthreads();
+  if (p.trace_off && threadIdx.x == 0 && unit < total_tiles) trace(p, rank, tile_of(unit) * CG + pr, kTrCtaEnd);
   if (CG == 2) cluster_sync_all();  // neither CTA of a pair leaves while the other may still touch its memory
   if (warp == 1) {
     __syncwarp();

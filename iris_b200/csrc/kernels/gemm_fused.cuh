@@ -38,7 +38,7 @@ constexpr int kSmemBytes = kSmemTiles + kSmemBarriers + 1024;  // + slack to ali
 
 // Slots of one per-tile trace record (nanoseconds of the global timer).
 enum TraceSlot : int { kTrMmaBegin = 0, kTrMmaEnd = 1, kTrEpiBegin = 2, kTrEpiEnd = 3, kTrWaitBegin = 4, kTrWaitEnd = 5,
-                       kTrPullEnd = 6, kTrSlots = 8 };
+                       kTrPullEnd = 6, kTrCtaBegin = 7, kTrCtaEnd = 8, kTrSlots = 10 };
 
 constexpr int kThreads = 256;      // warp 0: TMA producer, warp 1: MMA issuer, warps 2-5: epilogue, warps 6-7: all-gather push
 constexpr int kThreadsPull = 320;  // one-/two-shot kernels: warps 6-9 are the reducer (pull, sum, write) instead

@@ -199,7 +199,7 @@ class FusedGemm:
                                                                  pl.tile_flags, pl.nflags)
         # ---- symmetric allocations (identical sequence on every rank) ----
         self.flags = [c.zeros(nflags, dtype=torch.int32) for c in self.ctxs]
-        self.trace = [c.zeros((self.total_tiles * cta_group, 8), dtype=torch.int64) for c in self.ctxs] if trace else None
+        self.trace = [c.zeros((self.total_tiles * cta_group, 10), dtype=torch.int64) for c in self.ctxs] if trace else None
         self.workspace = [c.zeros((max(sk_tiles, 1) * cta_group * BM, BN), dtype=torch.float32)
                           for c in self.ctxs] if sk_tiles else None
         self.c_cols = int(c_cols) if c_cols else self.N
@@ -330,13 +330,15 @@ class FusedGemm:
 
     def trace_records(self, local: int = 0):
         """Per-tile timestamps of the last call in microseconds relative to the earliest one: a list of dicts with
-        ``mma_begin, mma_end, epi_begin, epi_end, wait_begin, wait_end, pull_end`` (the reference's per-tile trace
+        ``mma_begin, mma_end, epi_begin, epi_end, wait_begin, wait_end, pull_end`` and, in the record of the first
+        tile a CTA handles, ``cta_begin, cta_end`` (set-up done / leaving) (the reference's per-tile trace
         JSON, ``examples/common/utils.py:66-128``).  Needs ``trace=True`` at construction."""
         if self.trace is None:
             raise RuntimeError("construct the op with trace=True")
         torch.cuda.synchronize(self.ctxs[0].device)
         t = self.trace[local].cpu()
-        names = ["mma_begin", "mma_end", "epi_begin", "epi_end", "wait_begin", "wait_end", "pull_end"]
+        names = ["mma_begin", "mma_end", "epi_begin", "epi_end", "wait_begin", "wait_end", "pull_end", "cta_begin",
+                 "cta_end"]
         nz = t[t > 0]
         t0 = int(nz.min()) if nz.numel() else 0
         recs = []
@@ -398,6 +400,28 @@ def gemm_all_scatter(ctxs, a, bt, **kw) -> FusedGemm:
     return FusedGemm(ctxs, a, bt, "store", store_all=True, c_cols=world * n, col_off_per_rank=n, **kw)
 
 
+def world_of(ctxs) -> int:
+    return (ctxs if isinstance(ctxs, Iris) else list(ctxs)[0]).get_num_ranks()
+
+
+def auto_all_reduce_variant(m: int, world: int):
+    """``(variant, keyword arguments)`` that was fastest for a GEMM + all-reduce with ``m`` rows on ``world`` B200s
+    (N = 4096, K = 11008 sharded; 2 and 8 GPUs measured, 4 interpolated):
+
+    * up to 256 rows the time is fixed latencies (launch, one link round trip for the data, one for the arrival
+      count): the atomic form has the fewest steps.  A single row block leaves most SMs idle, so narrow tiles
+      (``bn``) or, while the tile is only a few rows, K pieces (``ksplit``: every piece adds a full tile into every
+      rank, so it multiplies the traffic by ``ksplit`` and only pays for the shortest matrices);
+    * taller matrices are bound by the link: on 2 GPUs all forms move the same bytes and one-shot has the fewest
+      steps; on more GPUs only the two-shot form has the traffic of a library all-reduce, 2 (W - 1) / W partials.
+    """
+    if m <= 256:
+        if world <= 2:
+            return "atomic", dict(bn=256, ksplit=8 if m <= 64 else 4)
+        return ("atomic", dict(bn=128, ksplit=4)) if m <= 64 else ("atomic", dict(bn=64))
+    return ("one_shot", {}) if world <= 2 else ("two_shot", {})
+
+
 def gemm_all_reduce(ctxs, a, bt, variant: str = "one_shot", **kw) -> FusedGemm:
     """``C[M, N] = sum over ranks of A_r @ B_r`` (K sharded).  ``variant``: ``"atomic"``
     (``examples/08_gemm_atomics_all_reduce``), ``"one_shot"`` (``examples/09_gemm_one_shot_all_reduce``),
@@ -406,8 +430,8 @@ def gemm_all_reduce(ctxs, a, bt, variant: str = "one_shot", **kw) -> FusedGemm:
     pushed to the rank that keeps their rows, as in :func:`gemm_reduce_scatter`, and the keeper writes the summed rows
     to every rank; needs ``M`` to be a multiple of ``world x 128``)."""
     if variant == "auto":
-        # short matrices are latency-bound: one-shot with pushed partials; tall ones are bandwidth-bound: two-shot
-        variant = "one_shot" if a[0].shape[0] <= 2 * BM else "two_shot"
+        variant, auto_kw = auto_all_reduce_variant(a[0].shape[0], world_of(ctxs))
+        kw = dict(auto_kw, **kw)
     if variant == "atomic":
         return FusedGemm(ctxs, a, bt, "reduce", store_all=True, **kw)
     if variant in ("one_shot", "two_shot"):

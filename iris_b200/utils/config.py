@@ -23,13 +23,27 @@ WORKLOADS: Dict[str, Tuple[str, Optional[str]]] = {
 
 @dataclass(frozen=True)
 class TileConfig:
-    """What can vary per shape on this kernel: the raster group and the size of the persistent grid (0 = all SMs).
-    The tile itself is fixed at compile time."""
-    BLK_M: int = 128
+    """What can vary per shape on this kernel: the tile (``BLK_M`` 128 = one CTA per tile, 256 = a CTA pair per tile,
+    0 = chosen from M; ``BLK_N`` 64 / 128 / 256 columns; the k-block is fixed at 64), the raster group, the size of
+    the persistent grid (0 = all SMs), the K pieces per tile of the short-matrix forms (0 = chosen by the planner)
+    and the column split of a ragged last wave (0 = off)."""
+    BLK_M: int = 0
     BLK_N: int = 256
     BLK_K: int = 64
     gsize_m: int = 8
     gemm_sms: int = 0
+    ksplit: int = 0
+    tail_split: int = 0
+
+    def problems(self) -> List[str]:
+        out = []
+        if self.BLK_M not in (0, 128, 256):
+            out.append("BLK_M must be 128 or 256 (0: chosen from M)")
+        if self.BLK_N not in (64, 128, 256):
+            out.append("BLK_N must be 64, 128 or 256")
+        if self.BLK_K != 64:
+            out.append("BLK_K is fixed at 64")
+        return out
 
 
 @dataclass(frozen=True)
@@ -52,8 +66,8 @@ class GemmPoint:
         w, out = self.world, []
         if self.workload not in WORKLOADS:
             return [f"unknown workload {self.workload!r}"]
-        if self.dtype != "bf16":
-            out.append("only bf16 is implemented")
+        if self.dtype not in ("bf16", "fp16"):
+            out.append("the element type must be bf16 or fp16")
         if min(self.m, self.n, self.k, w) < 1 or w > 8:
             out.append("m, n, k must be positive and 1 <= world <= 8")
             return out
@@ -96,7 +110,14 @@ class GemmPoint:
         cmd = [python, "-m", "iris_b200.launch", "-np", str(self.world), "--timeout", str(timeout_s),
                f"{root.rstrip('/')}/{script}", "-m", str(self.m), "-n", str(self.n), "-k", str(self.k), "-v", "-b",
                "--gsize_m", str(t.gsize_m), "--gemm_sms", str(t.gemm_sms), "--num_experiments",
-               str(self.num_experiments), "--num_warmup", str(self.num_warmup)]
+               str(self.num_experiments), "--num_warmup", str(self.num_warmup), "--datatype", self.dtype,
+               "--BLK_N", str(t.BLK_N)]
+        if t.BLK_M:
+            cmd += ["--BLK_M", str(t.BLK_M)]
+        if t.ksplit:
+            cmd += ["--ksplit", str(t.ksplit)]
+        if t.tail_split:
+            cmd += ["--tail_split", str(t.tail_split)]
         if variant:
             cmd += ["--variant", variant]
         if output_file:

@@ -377,6 +377,67 @@ int main() {
     CHECK(failures.load() == 0, "two-shot protocol: %d rank(s) saw a wrong sum or a time-out", failures.load());
   }
 
+  // ---- 9. the all-gather prologue: every rank pushes its own rows into every peer's gathered buffer ----
+  // The gathered buffer is single (not alternated by call parity) and the kernel has no end-of-call handshake: a rank
+  // may start call c + 1 while a peer still reads the rows of call c.  What keeps that peer's rows intact is the wait
+  // of the pushing side for the PEER's entry flag of call c + 1 (written when the peer starts that call, i.e. after it
+  // has read everything of call c) before the first remote store.  Chunk flags are cumulative arrival counters.
+  {
+    constexpr int W = 4, kCalls = 40, kElems = 96;
+    // per rank: [entry flags (64 B) | chunk flags (64 B) | gathered[W][kElems]]
+    constexpr uint64_t kGath = 128;
+    constexpr uint64_t kRankBytes = kGath + (uint64_t)W * kElems * 4;
+    static_assert(W * kRankBytes <= (64 << 10), "fits the data area B");
+    uint8_t* region = sym(0, kB);
+    memset(region, 0, W * kRankBytes);
+    uint64_t hbw[W];
+    for (int r = 0; r < W; ++r) hbw[r] = (uint64_t)(region + r * kRankBytes);
+    std::atomic<int> failures{0};
+    auto body = [&](int rank) {
+      unsigned seed = 777u + 17u * rank;
+      auto nap = [&]() {
+        seed = seed * 1664525u + 1013904223u;
+        if ((seed >> 28) < 5) std::this_thread::sleep_for(std::chrono::microseconds((seed >> 20) & 63));
+      };
+      uint32_t* entry = reinterpret_cast<uint32_t*>(hbw[rank]);
+      uint32_t* cflag = reinterpret_cast<uint32_t*>(hbw[rank] + 64);
+      int32_t* gathered = reinterpret_cast<int32_t*>(hbw[rank] + kGath);
+      auto fail = [&]() { ++failures; };
+      for (int call = 1; call <= kCalls; ++call) {
+        // "host": this call's own rows (stream-ordered after the previous call of this rank)
+        for (int e = 0; e < kElems; ++e) gathered[rank * kElems + e] = call * 1000 + rank * 10 + (e & 3);
+        // kernel start: entry flag to every rank
+        for (int i = 0; i < W; ++i) signal_set(entry + rank, (uint32_t)call, rank, (rank + 1 + i) % W, hbw);
+        nap();
+        // communication warps: wait for the peer's entry, then push own rows and count the chunk on the peer
+        for (int i = 0; i + 1 < W; ++i) {
+          const int peer = (rank - 1 - i + 2 * W) % W;
+          StatusBlock st{};
+          if (wait_until_ge(entry + peer, (uint32_t)call, 1ull << 27, &st, 12, rank, peer) != kOk) return fail();
+          int32_t* dst = translate(gathered, rank, peer, hbw) + rank * kElems;
+          for (int e = 0; e < kElems; ++e) dst[e] = gathered[rank * kElems + e];
+          signal_add(cflag + rank, 1u, rank, peer, hbw);
+          nap();
+        }
+        // producer: rows of every source, own first; peers' rows after their chunk flag
+        for (int sp = 0; sp < W; ++sp) {
+          const int src = (rank + sp) % W;
+          if (src != rank) {
+            StatusBlock st{};
+            if (wait_until_ge(cflag + src, (uint32_t)call, 1ull << 27, &st, 13, rank, src) != kOk) return fail();
+          }
+          nap();
+          for (int e = 0; e < kElems; ++e)
+            if (gathered[src * kElems + e] != call * 1000 + src * 10 + (e & 3)) return fail();
+        }
+      }
+    };
+    std::vector<std::thread> ranks;
+    for (int r = 0; r < W; ++r) ranks.emplace_back(body, r);
+    for (auto& t : ranks) t.join();
+    CHECK(failures.load() == 0, "all-gather protocol: %d rank(s) read rows of another call or timed out", failures.load());
+  }
+
   for (int r = 0; r < kWorld; ++r) {
     CHECK(iris_cpu_heap_unmap(base[r], kHeap) == 0, "unmap");
     CHECK(iris_cpu_heap_unlink(name[r]) == 0, "unlink");

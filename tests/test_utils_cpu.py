@@ -84,7 +84,15 @@ def test_config_files_and_sweep_dry_run():
     assert any(s["name"] == "config3_all_scatter" and (s["m"], s["n"], s["k"]) == (8192, 14336, 4096) for s in shapes)
     assert {1, 128, 1024, 8192} <= {s["m"] for s in shapes if "config4" in s["name"]}
     tiling = json.load(open(os.path.join(ROOT, "configs", "tiling_b200.json")))
-    assert tiling["default"]["BLK_M"] == 128 and tiling["default"]["BLK_N"] == 256
+    assert tiling["default"]["BLK_M"] in (0, 128, 256) and tiling["default"]["BLK_N"] == 256
+    # more than one tile shape in the table, every entry a shape the kernel has
+    from iris_b200.utils.config import TileConfig
+    shapes_used = set()
+    for o in tiling["overrides"]:
+        t = TileConfig(**{k: v for k, v in dict(tiling["default"], **o).items() if k not in ("m", "n", "k")})
+        assert not t.problems(), (o, t.problems())
+        shapes_used.add((t.BLK_M, t.BLK_N))
+    assert len(shapes_used) >= 4
     out = subprocess.run([sys.executable, os.path.join(ROOT, "examples", "benchmark", "bench_all_shapes.py"), "-n",
                           "--gpus", "8", "--only", "config3_all_scatter", "config4_all_reduce_m128"],
                          capture_output=True, text=True, check=True).stdout
@@ -166,7 +174,9 @@ def test_benchmark_points_validate_and_build_their_command():
     table = json.load(open(os.path.join(ROOT, "configs", "tiling_b200.json")))
     ok = GemmPoint("all_scatter", 8192, 14336, 4096, 8, name="c3")
     assert ok.problems() == [] and ok.per_rank_shape() == (8192, 1792, 4096)
-    assert ok.tile(table) == TileConfig(gsize_m=8)
+    assert ok.tile(table) == TileConfig(BLK_M=256, BLK_N=256, gsize_m=8)        # the table's entry for 8192x1792x4096
+    short = GemmPoint("atomic", 128, 4096, 11008, 8).tile(table)
+    assert (short.BLK_M, short.BLK_N, short.ksplit) == (128, 64, 1)                # another tile shape for a short matrix
     cmd = ok.command("/r", table, output_file="o.json")
     assert cmd[:5] == ["python", "-m", "iris_b200.launch", "-np", "8"] and "/r/examples/07_gemm_all_scatter/benchmark.py" in cmd
     assert cmd[cmd.index("--output_file") + 1] == "o.json"

@@ -71,6 +71,18 @@ def main():
             tol = (2 + world) * 2.0 ** -8 * scale + 1e-3 * ref.abs().max().item()
             assert bool(((o.float() - ref).abs() <= tol).all()), "NVLS two-shot mismatch"
             op.close()
+            # push two-shot: partial tiles pushed to the keeper of their rows, summed there, result rows delivered to
+            # every rank with multimem stores
+            if 512 % (world * 128) == 0:
+                tp = G.gemm_all_reduce(ctx, [a_full[:, rank * ks:(rank + 1) * ks]],
+                                       [b_full[:, rank * ks:(rank + 1) * ks]], variant="two_shot_push")
+                assert tp.nvls and tp.bcast
+                for _ in range(3):
+                    o = tp()[0]
+                ctx.barrier()
+                tp.check()
+                assert bool(((o.float() - ref).abs() <= tol).all()), "NVLS push two-shot mismatch"
+                tp.close()
             # fused GEMM + all-scatter whose tiles leave as multimem stores: one store per 16 bytes, the switch
             # delivers it to every rank's C (this rank's own copy included)
             n_local = 320

@@ -4,7 +4,8 @@
 * P2P RMA: remote load / store between rank 0 and rank 1 from 4 KB to 1 GB, all-load / all-store plateaus,
   remote atomic add (fp32) and exchange (int32);
 * GEMM + all-scatter on A[8192, 4096] x B[4096, 14336];
-* GEMM + all-reduce (atomic, one-shot, two-shot) on K = 11008, N = 4096 for M in {1, 128, 1024, 8192};
+* GEMM + all-reduce (atomic, one-shot, two-shot, push two-shot, and the automatic choice) on K = 11008, N = 4096 for
+  M in {1, 128, 1024, 8192};
 * GEMM + reduce-scatter on M = 16384, N = 4096, K in {4096, 11008} (the decoder's row-parallel projections);
 
 each fused kernel next to cuBLAS + NCCL on the same operands, device-timed, maximum over ranks, with the roofline
@@ -85,6 +86,15 @@ def main():
             bw = ctx.broadcast(na * 4 / (ms * 1e-3) / 1e9 if rank == 0 and ms > 0 else 0.0, 0)
             res["p2p"][name] = {"elements": na, "gbs": bw}
             log(f"{name} 0->1: {bw:.1f} GB/s")
+        # producer / consumer hand-off of 1 MB chunks guarded by release / acquire flags (rank 0 -> rank 1)
+        for nchunks in (8, 64):
+            mp = p2p.MessagePassing(ctx, nchunks=nchunks, chunk_bytes=1 << 20, producer=0, consumer=1, timeout_ms=5000)
+            ms = time_kernel_ms(ctx, lambda: mp.run(), 2, 10, active=(rank == 1), busy=True)
+            us = ctx.broadcast(ms * 1e3 if rank == 1 else 0.0, 1)
+            gbs = nchunks * (1 << 20) / (us * 1e-6) / 1e9 if us > 0 else 0.0
+            ctx.check_status()
+            res["p2p"][f"message_passing_{nchunks}x1MB"] = {"us_per_handoff": us, "gbs": gbs, "blocks_per_chunk": mp.parts}
+            log(f"message passing {nchunks} x 1 MB, {mp.parts} blocks per chunk: {us:.1f} us per hand-off ({gbs:.0f} GB/s)")
         ctx.reset(base)
 
     # ------------------------------------------------------------------ fused GEMMs
@@ -145,13 +155,21 @@ def main():
                     if world > 1:
                         dist.all_reduce(c_part)
                 ref = A[:128].float() @ Bt.float().t()
-                for variant in ("atomic", "one_shot", "two_shot"):
+                for variant in ("atomic", "one_shot", "two_shot", "two_shot_push", "auto"):
+                    if variant == "two_shot_push" and m % (world * 128):
+                        continue
                     op = G.gemm_all_reduce(ctx, [al], [bl], variant=variant)
-                    bench_pair({"workload": variant, "m": m, "n": n, "k": k}, op, unfused, 2.0 * m * n * k,
+                    chosen = "atomic" if op.mode == "reduce" else ("two_shot_push" if op.bcast else op.mode)
+                    label = {"workload": variant, "m": m, "n": n, "k": k, "tile": f"{128 * op.cta_group}x{op.bn}",
+                             "ksplit": op.ksplit}
+                    if variant == "auto":
+                        label["chosen"] = chosen
+                    bench_pair(label, op, unfused, 2.0 * m * n * k,
                                roofline.all_reduce_roofline_us(m, n, k, world, peaks,
-                                                               "two_shot" if variant == "two_shot" else "one_shot"))
+                                                               "two_shot" if chosen.startswith("two_shot") else "one_shot"))
                     err = (op.out[0][:128].float() - ref).abs().max().item()
-                    assert err <= (2 + world) * 2 ** -8 * ref.abs().max().item() + 1e-3, f"{variant} m={m}: err {err}"
+                    tol = (2 + world * op.ksplit) * 2 ** -8 * ref.abs().max().item() + 1e-3
+                    assert err <= tol, f"{variant} m={m}: err {err}"
                     op.close()
                     ctx.reset(base)
                 del A, c_part

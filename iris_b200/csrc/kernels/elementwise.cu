@@ -1,5 +1,6 @@
-// elementwise.cu — the memory-bound pieces of the tensor-parallel decoder block: RMSNorm, SwiGLU and the
-// residual add, bf16 in / bf16 out with fp32 arithmetic, 16-byte vector accesses.
+// elementwise.cu — the memory-bound pieces of the tensor-parallel decoder block: RMSNorm, residual add fused with
+// the RMSNorm that follows it, SwiGLU and the plain residual add, bf16 in / bf16 out with fp32 arithmetic, 16-byte
+// vector accesses.
 //
 // No counterpart in the reference (it has no model code); they exist for the tensor-parallel block built on
 // the fused GEMM + collective kernels.  RMSNorm writes straight into the row block that the all-gather -> GEMM
@@ -118,6 +119,72 @@ __global__ void __launch_bounds__(kThreads) rmsnorm_reg_kernel(const __nv_bfloat
   }
 }
 
+// Residual add fused with the norm that follows it: x[r, :] += y[r, :] (stored back, the residual stream), then
+// out[r, :] = x[r, :] * rsqrt(mean(x^2) + eps) * w.  The row stays in registers: x and y are read once, x and out
+// written once, instead of the three reads and two writes of the two separate kernels.  Rows of at most
+// kThreads * VPT vectors.
+template <int kThreads, int VPT>
+__global__ void __launch_bounds__(kThreads) add_rmsnorm_reg_kernel(__nv_bfloat16* __restrict__ x, int64_t ldx,
+                                                                   const __nv_bfloat16* __restrict__ y, int64_t ldy,
+                                                                   const __nv_bfloat16* __restrict__ w,
+                                                                   __nv_bfloat16* __restrict__ out, int64_t ldo,
+                                                                   int cols, float eps) {
+  __shared__ float red[kThreads / 32];
+  const int r = blockIdx.x;
+  uint4* xr = reinterpret_cast<uint4*>(x + (int64_t)r * ldx);
+  const uint4* yr = reinterpret_cast<const uint4*>(y + (int64_t)r * ldy);
+  const uint4* wv = reinterpret_cast<const uint4*>(w);
+  uint4* orow = reinterpret_cast<uint4*>(out + (int64_t)r * ldo);
+  const int nv = cols / 8;
+  uint4 xv[VPT], yv[VPT], wr[VPT];
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) {
+    const int i = threadIdx.x + v * kThreads;
+    if (i < nv) {
+      xv[v] = xr[i];
+      yv[v] = yr[i];
+      wr[v] = wv[i];
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) {
+    const int i = threadIdx.x + v * kThreads;
+    if (i < nv) {
+      float f[8], g[8];
+      unpack8(xv[v], f);
+      unpack8(yv[v], g);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] += g[j];
+      xv[v] = pack8(f);        // the residual stream is bf16: the norm sees the rounded sum, as the unfused pair does
+      xr[i] = xv[v];
+      unpack8(xv[v], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += f[j] * f[j];
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < kThreads / 32; ++i) tot += red[i];
+  const float scale = rsqrtf(tot / (float)cols + eps);
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) {
+    const int i = threadIdx.x + v * kThreads;
+    if (i < nv) {
+      float f[8], g[8];
+      unpack8(xv[v], f);
+      unpack8(wr[v], g);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = f[j] * scale * g[j];
+      orow[i] = pack8(f);
+    }
+  }
+}
+
 // silu(a) * b with two special-function operations per element (ex2 and rcp) and no IEEE division: the kernel has
 // to stay below about 25 instructions per element to be bound by memory rather than by instruction issue.
 __device__ __forceinline__ float silu_mul(float a, float b) {
@@ -200,6 +267,23 @@ int iris_k_rmsnorm_bf16(const void* x, int64_t ldx, const void* w, void* out, in
   else if (nv <= 512) rmsnorm_reg_kernel<256, 2><<<rows, 256, 0, st>>>(xp, ldx, wp, op, ldo, cols, eps);
   else if (nv <= 1024) rmsnorm_reg_kernel<256, 4><<<rows, 256, 0, st>>>(xp, ldx, wp, op, ldo, cols, eps);
   else rmsnorm_kernel<256><<<rows, 256, 0, st>>>(xp, ldx, wp, op, ldo, cols, eps);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+// x += y; out = rmsnorm(x) * w.  Returns -3 when the row is too long for the register-resident kernel (the caller
+// then runs the two separate kernels).
+int iris_k_add_rmsnorm_bf16(void* x, int64_t ldx, const void* y, int64_t ldy, const void* w, void* out, int64_t ldo,
+                            int rows, int cols, float eps, void* stream) {
+  if (cols % 8 != 0 || rows < 1) return -2;
+  __nv_bfloat16* xp = (__nv_bfloat16*)x;
+  const __nv_bfloat16* yp = (const __nv_bfloat16*)y;
+  const __nv_bfloat16* wp = (const __nv_bfloat16*)w;
+  __nv_bfloat16* op = (__nv_bfloat16*)out;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int nv = cols / 8;
+  if (nv <= 256) add_rmsnorm_reg_kernel<256, 1><<<rows, 256, 0, st>>>(xp, ldx, yp, ldy, wp, op, ldo, cols, eps);
+  else if (nv <= 512) add_rmsnorm_reg_kernel<256, 2><<<rows, 256, 0, st>>>(xp, ldx, yp, ldy, wp, op, ldo, cols, eps);
+  else if (nv <= 1024) add_rmsnorm_reg_kernel<256, 4><<<rows, 256, 0, st>>>(xp, ldx, yp, ldy, wp, op, ldo, cols, eps);
+  else return -3;
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 int iris_k_swiglu_bf16(const void* gu, int64_t ldg, void* out, int64_t ldo, int rows, int inter, void* stream) {

@@ -134,10 +134,15 @@ class TPDecoder:
         cfg, nl = self.cfg, len(self.ctxs)
         n = 0
         tick = timers if timers is not None else (lambda name: None)
+        pending = None   # output of the previous layer's down projection, not yet added to the residual stream
         for ops in self.layers:
             tick("norm")
             for l in range(nl):
-                E.rmsnorm(x_shards[l], ops["w"][l]["norm1"], ops["qkv"].a_full[l][self.rows(l)], cfg.eps)
+                dst = ops["qkv"].a_full[l][self.rows(l)]
+                if pending is None:
+                    E.rmsnorm(x_shards[l], ops["w"][l]["norm1"], dst, cfg.eps)
+                else:   # the previous layer's residual add rides along with this layer's first norm
+                    E.add_rmsnorm(x_shards[l], pending[l], ops["w"][l]["norm1"], dst, cfg.eps)
             tick("qkv_ag_gemm")
             qkv = ops["qkv"]()
             tick("attention")
@@ -146,9 +151,9 @@ class TPDecoder:
             tick("o_gemm_ar")
             o = ops["o"]()
             tick("norm")
-            for l in range(nl):
-                E.residual_add(x_shards[l], o[l] if self.scatter else o[l][self.rows(l)])
-                E.rmsnorm(x_shards[l], ops["w"][l]["norm2"], ops["gu"].a_full[l][self.rows(l)], cfg.eps)
+            for l in range(nl):   # residual add and the next norm in one pass, written into the gathered matrix
+                E.add_rmsnorm(x_shards[l], o[l] if self.scatter else o[l][self.rows(l)], ops["w"][l]["norm2"],
+                              ops["gu"].a_full[l][self.rows(l)], cfg.eps)
             tick("gu_ag_gemm")
             gu = ops["gu"]()
             tick("swiglu")
@@ -156,10 +161,12 @@ class TPDecoder:
                 E.swiglu(gu[l], self.h[l])
             tick("down_gemm_ar")
             d = ops["down"]()
-            tick("norm")
-            for l in range(nl):
-                E.residual_add(x_shards[l], d[l] if self.scatter else d[l][self.rows(l)])
-            n += 4 + 5 * nl
+            pending = [d[l] if self.scatter else d[l][self.rows(l)] for l in range(nl)]
+            n += 4 + 4 * nl     # 4 fused GEMMs; per rank: norm, attention, add+norm, SwiGLU
+        tick("norm")
+        for l in range(nl):
+            E.residual_add(x_shards[l], pending[l])
+        n += nl
         tick("end")
         self.kernel_launches += n
         return x_shards

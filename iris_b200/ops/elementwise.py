@@ -1,4 +1,4 @@
-"""RMSNorm, SwiGLU and residual add (``csrc/kernels/elementwise.cu``): bf16 tensors with a contiguous last
+"""RMSNorm, residual add + RMSNorm in one pass, SwiGLU and residual add (``csrc/kernels/elementwise.cu``): bf16 tensors with a contiguous last
 dimension, arbitrary row pitch, fp32 arithmetic.  Used by the tensor-parallel decoder block; no counterpart in the
 reference."""
 from __future__ import annotations
@@ -59,3 +59,22 @@ def residual_add(x: torch.Tensor, y: torch.Tensor, stream=None) -> torch.Tensor:
     if rc:
         raise RuntimeError(f"residual_add launch failed ({rc})")
     return x
+
+
+def add_rmsnorm(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float = 1e-6,
+                stream=None) -> torch.Tensor:
+    """``x += y`` (in place) and ``out = rmsnorm(x) * weight`` in one pass over the rows: the residual add at the end
+    of one sub-block fused with the norm that opens the next.  ``out`` may be a row block of a larger matrix."""
+    _check2d(x, "x"), _check2d(y, "y"), _check2d(out, "out")
+    lib = _native.kernels()
+    lib.iris_k_add_rmsnorm_bf16.argtypes = [ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p, ctypes.c_int64,
+                                            ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int,
+                                            ctypes.c_int, ctypes.c_float, ctypes.c_void_p]
+    rc = lib.iris_k_add_rmsnorm_bf16(x.data_ptr(), x.stride(0), y.data_ptr(), y.stride(0), weight.data_ptr(),
+                                     out.data_ptr(), out.stride(0), x.shape[0], x.shape[1], eps, _st(x, stream))
+    if rc == -3:     # row too long for the register-resident kernel
+        residual_add(x, y, stream)
+        return rmsnorm(x, weight, out, eps, stream)
+    if rc:
+        raise RuntimeError(f"add_rmsnorm launch failed ({rc})")
+    return out

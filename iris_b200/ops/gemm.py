@@ -148,6 +148,11 @@ class FusedGemm:
                  push: Optional[bool] = None, ksplit: Optional[int] = None, nvls: Optional[bool] = None,
                  reduce_scatter: bool = False, bn: Optional[int] = None, tail_split: Optional[bool] = None,
                  push_kind: Optional[str] = None, bcast: bool = False):
+        self._ctor = (ctxs, a, bt, mode, dict(
+            M=M, store_all=store_all, c_cols=c_cols, col_off_per_rank=col_off_per_rank, out=out, ag=ag,
+            ag_slices=ag_slices, ctas_per_rank=ctas_per_rank, group_m=group_m, timeout_ms=timeout_ms,
+            cta_group=cta_group, trace=trace, stream_k=stream_k, push=push, ksplit=ksplit, nvls=nvls,
+            reduce_scatter=reduce_scatter, bn=bn, tail_split=tail_split, push_kind=push_kind, bcast=bcast))
         self.ctxs: List[Iris] = [ctxs] if isinstance(ctxs, Iris) else list(ctxs)
         c0 = self.ctxs[0]
         if c0.backend != "cuda":
@@ -380,6 +385,19 @@ class FusedGemm:
         if getattr(self, "_plan", None):
             _lib().iris_gemm_plan_destroy(self._plan)
             self._plan = None
+
+    def rebuild(self) -> "FusedGemm":
+        """Recovery after :class:`~iris_b200.context.IrisTimeoutError`.  The flags of an op are cumulative counters
+        driven to per-call targets that every rank computes from its own call count; when a bounded wait expired on
+        some rank, that rank's kernel left the call half-way and the counters of the ranks no longer agree, so the op
+        must not be called again.  Every rank (collectively, like construction) calls ``rebuild()``: the old plan is
+        closed and a new op with the same arguments is returned, with fresh, zeroed flags and buffers and a call count
+        of zero; its constructor ends in a barrier, after which all ranks may call it.  With ``ag=True`` the rows in
+        ``a_full`` have to be written again.  The heap space of the old op is not reused (reset the heap to a mark
+        taken before the first construction to get it back)."""
+        ctxs, a, bt, mode, kw = self._ctor
+        self.close()
+        return FusedGemm(ctxs, a, bt, mode, **kw)
 
     def __del__(self):
         try:

@@ -392,6 +392,36 @@ def test_all_gather_gemm_back_to_back_calls_with_new_rows(world):
     ranks[0].close()
 
 
+def test_rebuild_after_a_reported_timeout_gives_a_working_op():
+    """Recovery path on the host: a time-out record in a rank's status block (written here by the host, as a bounded
+    wait of a kernel would) makes check() raise; rebuild() returns a fresh op that computes correctly.  (The device
+    side of a time-out, a wait that runs out and returns, is exercised in test_gpu_rma.py.)"""
+    world, m, n, k_full = 2, 640, 512, 1024
+    ks = k_full // world
+    ranks = iris.Iris.local_world(world, heap_size=128 << 20)
+    a_full, b_full = _rand((m, k_full), 6), _rand((n, k_full), 7, 0.05)
+    a = [a_full[:, r * ks:(r + 1) * ks] for r in range(world)]
+    bt = [b_full[:, r * ks:(r + 1) * ks] for r in range(world)]
+    parts = [a[r].float() @ bt[r].float().t() for r in range(world)]
+    ref, scale = sum(parts), sum(p.abs() for p in parts)
+    for variant in ("two_shot", "atomic"):
+        op = G.gemm_all_reduce(ranks, a, bt, variant=variant)
+        op()
+        op.check()
+        ranks[1].status[:4].copy_(torch.tensor([1, 32, 1, 7], dtype=torch.int32))   # code 1 = time-out, site, rank, tile
+        with pytest.raises(iris.IrisTimeoutError):
+            op.check()
+        op2 = op.rebuild()
+        assert op._plan is None and op2.calls == 0
+        for _ in range(2):
+            outs = op2()
+        op2.check()
+        for r in range(world):
+            _assert_close(outs[r], ref, scale=scale, ulps=2.0 + world)
+        op2.close()
+    ranks[0].close()
+
+
 def test_plan_rejects_bad_shapes():
     a, bt = _rand((128, 60), 1), _rand((256, 60), 2)
     with pytest.raises((RuntimeError, ValueError)):

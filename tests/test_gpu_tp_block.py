@@ -50,6 +50,28 @@ def test_rmsnorm_every_row_length(cols):
     assert float(out[:, cols:].abs().sum()) == 0
 
 
+@pytest.mark.parametrize("cols", [8, 1024, 4096, 8192, 16384])
+def test_add_rmsnorm_matches_the_two_kernels(cols):
+    """Residual add fused with the following norm: the residual stream gets the bf16-rounded sum and the norm is
+    taken of that rounded value, exactly what residual_add followed by rmsnorm produce (16384 columns: the fall-back
+    to the two kernels)."""
+    g = torch.Generator(device="cuda").manual_seed(cols + 1)
+    x = torch.randn((70, cols), generator=g, device="cuda").to(torch.bfloat16)
+    y = torch.randn((90, cols + 16), generator=g, device="cuda").to(torch.bfloat16)[10:80, 8:8 + cols]
+    w = (1 + 0.1 * torch.randn(cols, generator=g, device="cuda")).to(torch.bfloat16)
+    x_two, out_two = x.clone(), torch.zeros((70, cols), dtype=torch.bfloat16, device="cuda")
+    E.residual_add(x_two, y)
+    E.rmsnorm(x_two, w, out_two, 1e-6)
+    x_one, big = x.clone(), torch.zeros((100, cols + 8), dtype=torch.bfloat16, device="cuda")
+    out_one = E.add_rmsnorm(x_one, y, w, big[20:90, :cols], 1e-6)
+    assert torch.equal(x_one, x_two)
+    sf = x_two.float()
+    ref = sf * torch.rsqrt(sf.pow(2).mean(-1, keepdim=True) + 1e-6) * w.float()
+    assert (out_one.float() - ref).abs().max().item() <= 2 ** -7 * ref.abs().max().item()
+    assert (out_one.float() - out_two.float()).abs().max().item() <= 2 ** -7 * ref.abs().max().item()
+    assert float(big[:20].abs().sum()) == 0 and float(big[90:].abs().sum()) == 0 and float(big[:, cols:].abs().sum()) == 0
+
+
 def test_swiglu_extreme_inputs():
     """The sigmoid is computed with ex2 / rcp approximations: large negative gates give 0, large positive ones the
     gate itself, and nothing turns into NaN."""

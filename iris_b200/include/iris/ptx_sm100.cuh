@@ -179,6 +179,24 @@ __host__ __device__ constexpr uint32_t umma_idesc_f16(int m, int n, bool bf16) {
   return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | ((uint32_t)(n >> 3) << 17) |
          ((uint32_t)(m >> 4) << 24);
 }
+// Shared-memory matrix descriptor of an MN-major operand tile (the MN dimension contiguous, e.g. V[key][d] used as
+// the B operand of P * V with N = d) stored by TMA with the 128-byte swizzle: a row of the K dimension holds 64
+// 16-bit MN elements (128 bytes), rows are 128 bytes apart, groups of 8 K rows are `sbo_bytes` apart (1024 when the
+// rows are dense) and the next 64 MN elements start `lbo_bytes` further on.
+__device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+// Instruction descriptor as umma_idesc_f16 with the operand majors spelled out: bit 15 / 16 set = A / B is MN-major.
+__host__ __device__ constexpr uint32_t umma_idesc_f16_major(int m, int n, bool bf16, bool a_mn_major, bool b_mn_major) {
+  return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | ((a_mn_major ? 1u : 0u) << 15) |
+         ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
 // D[tmem] (+)= A[smem] * B[smem]; issued by ONE thread.
 __device__ __forceinline__ void umma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                             uint32_t accumulate) {

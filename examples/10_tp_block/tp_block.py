@@ -27,7 +27,10 @@ def main():
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--seq", type=int, default=2048)
-    ap.add_argument("--variant", default="two_shot", choices=["two_shot", "one_shot", "atomic", "reduce_scatter"],
+    ap.add_argument("--attention", default="iris", choices=["iris", "sdpa"],
+                    help="attention core of the fused stack: this repository's tcgen05 kernel or the library call")
+    ap.add_argument("--variant", default="two_shot",
+                    choices=["two_shot", "two_shot_push", "one_shot", "atomic", "auto", "reduce_scatter"],
                     help="row-parallel projections: an all-reduce variant, or reduce_scatter (every rank receives only its "
                          "own token rows; the baseline then uses NCCL reduce_scatter_tensor)")
     ap.add_argument("-v", "--validate", action="store_true", help="compare with the unsharded fp32 oracle (1 layer subset)")
@@ -46,13 +49,14 @@ def main():
     rank, world = ctx.get_rank(), ctx.get_num_ranks()
     dev = ctx.get_device()
     device_barrier(ctx)
-    model = TPDecoder(ctx, cfg, variant=args.variant)
+    model = TPDecoder(ctx, cfg, variant=args.variant, attention=args.attention)
     base = TPDecoderBaseline(cfg, rank, world, dev, scatter=args.variant == "reduce_scatter")
     g = torch.Generator(device=dev).manual_seed(cfg.seed)
     x = torch.randn((cfg.tokens, cfg.hidden), generator=g, device=dev).to(torch.bfloat16)
     ts = cfg.tokens // world
     mine = x[rank * ts:(rank + 1) * ts]
-    res = {"world": world, "variant": args.variant, "config": cfg.__dict__, "nvls": bool(ctx.mc_base)}
+    res = {"world": world, "variant": args.variant, "config": cfg.__dict__, "nvls": bool(ctx.mc_base),
+           "attention": "iris" if model.own_attention else "sdpa"}
     ok = True
     if args.validate:
         a, b = mine.clone(), mine.clone()

@@ -12,9 +12,8 @@
 //   warp 1      one thread issues tcgen05.mma:  S_j = Q K_j^T (128 x 128 x 128, both operands K-major) into one of
 //               two S accumulators in tensor memory, and O_j = P_j V_j (P from shared memory, V as an MN-major
 //               operand: V[key][d] is read as stored) into one of two O accumulators
-//   warps 2-3   idle (they complete the warp group whose registers are handed to the softmax warps: setmaxnreg)
-//   warps 4-11  softmax, two threads per query row (64 keys / 64 output columns each): tcgen05.ld of S_j, running
-//               maximum (halves combined through shared memory), exp2, row sum, P_j as 16-bit values into shared
+//   warps 2-9   softmax, two threads per query row (64 keys / 64 output columns each): tcgen05.ld of S_j, running
+//               maximum (over the whole row, read by both), exp2, row sum, P_j as 16-bit values into shared
 //               memory in the swizzled layout the MMA expects; then O_{j-1} is read from tensor memory and folded
 //               into the fp32 output row kept in registers (rescaled by exp2(m_old - m_new)).
 // While the softmax warps work on S_j the tensor cores already compute S_{j+1}.
@@ -45,12 +44,10 @@ constexpr int BQ = 128;           // queries per CTA
 constexpr int BKV = 128;          // keys per tile
 constexpr int kTileBytes = 128 * 128 * 2;   // one 128 x 128 tile of 16-bit elements (two 64-column swizzle blocks)
 constexpr int kHalfBytes = kTileBytes / 2;  // one 64-column block: 128 rows x 128 bytes
-constexpr int kThreads = 384;          // warp group 0: TMA warp, MMA warp, two idle warps; warp groups 1-2: softmax
-constexpr int kRegsLight = 88;         // registers per thread kept by warp group 0 ...
-constexpr int kRegsSoftmax = 208;      // ... so that the softmax warps can hold S, the output row and the exponentials
+constexpr int kThreads = 320;          // TMA warp, MMA warp, eight softmax warps
 // shared memory: Q | K[2] | V[2] | P, then barriers
 constexpr int kSmemTiles = 6 * kTileBytes;
-constexpr int kXchgBytes = 3 * 256 * 4;     // row maxima (two buffers) and row sums exchanged between the two halves
+constexpr int kXchgBytes = 256 * 4;         // row sums exchanged between the two halves at the end
 constexpr int kSmemBytes = kSmemTiles + 256 + kXchgBytes + 1024;
 
 enum Site : uint32_t { kSiteLoad = 90, kSiteMma = 91, kSiteSoftmax = 92 };
@@ -73,10 +70,9 @@ struct Params {
   float scale_log2;      // log2(e) / sqrt(128)
 };
 
-// REBAL: 12 warps, the first warp group gives registers to the softmax warps (setmaxnreg); else 10 warps, no exchange.
-template <bool F16, bool REBAL>
-__global__ void __launch_bounds__(REBAL ? kThreads : 320, 1) attention_fwd_kernel(const __grid_constant__ Params p) {
-  constexpr int kFirstSoftmaxWarp = REBAL ? 4 : 2;
+template <bool F16>
+__global__ void __launch_bounds__(kThreads, 1) attention_fwd_kernel(const __grid_constant__ Params p) {
+  constexpr int kFirstSoftmaxWarp = 2;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t q_s = smem_u32(smem);
@@ -118,10 +114,6 @@ __global__ void __launch_bounds__(REBAL ? kThreads : 320, 1) attention_fwd_kerne
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
-  if constexpr (REBAL) {
-    if (warp < 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsLight));
-    else asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
-  }
   if (warp == 0) {
     if (lane == 0) {
       mbar_expect_tx(bar(0), kTileBytes);
@@ -190,8 +182,8 @@ __global__ void __launch_bounds__(REBAL ? kThreads : 320, 1) attention_fwd_kerne
     }
   } else if (warp >= kFirstSoftmaxWarp) {
     // ---- softmax + output: two threads per query row, one for keys / output columns 0..63, one for 64..127 ----
-    // (a warp may only read the 32 tensor-memory lanes of its quadrant, warp id % 4; warps 4-7 take the first half of
-    // the columns, warps 8-11 the second, so that every scheduler of the SM has two softmax warps to switch between)
+    // (a warp may only read the 32 tensor-memory lanes of its quadrant, warp id % 4; warps 2-5 take the first half of
+    // the columns, warps 6-9 the second, so that every scheduler of the SM has two softmax warps to switch between)
     const int quad = warp & 3;
     const int half = (warp - kFirstSoftmaxWarp) >> 2;
     const int row = quad * 32 + lane;
@@ -211,93 +203,103 @@ __global__ void __launch_bounds__(REBAL ? kThreads : 320, 1) attention_fwd_kerne
       const int st = j & 1;
       if (!mbar_wait(bar(12 + st), (j >> 1) & 1, p.timeout_ns, abort_flag)) return fail(j, 2);
       tc_fence_after();
-      uint32_t v[64];
-      tmem_ld_32x32b_x32(tmem + lane_addr + 256 + st * 128 + half * 64, v);
-      tmem_ld_32x32b_x32(tmem + lane_addr + 256 + st * 128 + half * 64 + 32, v + 32);
-      tmem_wait_ld();
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {   // 32 columns at a time: the row of S or O is never whole in registers
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tmem + lane_addr + 256 + st * 128 + half * 64 + c * 32, v);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) acc[c * 32 + i] = acc[c * 32 + i] * alpha + __uint_as_float(v[i]);
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(14 + st));
-#pragma unroll
-      for (int i = 0; i < 64; ++i) acc[i] = acc[i] * alpha + __uint_as_float(v[i]);
     };
     for (int j = 0; j < nkv; ++j) {
       const int st = j & 1;
-      if (ok && !mbar_wait(bar(7 + st), (j >> 1) & 1, p.timeout_ns, abort_flag)) fail(j, 1);
+      if (!mbar_wait(bar(7 + st), (j >> 1) & 1, p.timeout_ns, abort_flag)) fail(j, 1);
       const bool diag = p.causal && j == qt;
-      uint32_t v[64];
+      if (!ok) break;
+      // pass 1: maximum of the WHOLE row of scores (both halves: two more tensor-memory loads are cheaper than an
+      // exchange through shared memory and a barrier of all softmax warps in every tile)
       float mx = -INFINITY;
-      if (ok) {
-        tc_fence_after();
-        tmem_ld_32x32b_x32(tmem + lane_addr + st * 128 + half * 64, v);
-        tmem_ld_32x32b_x32(tmem + lane_addr + st * 128 + half * 64 + 32, v + 32);
-        tmem_wait_ld();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(9 + st));    // S accumulator free: its values are in registers
+      tc_fence_after();
 #pragma unroll
-        for (int i = 0; i < 64; ++i)
-          if (!diag || half * 64 + i <= row) mx = fmaxf(mx, __uint_as_float(v[i]));
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tmem + lane_addr + st * 128 + c * 32, v);
+        tmem_wait_ld();
+        if (diag) {   // keys after the query: minus infinity (ignored by the maximum, 0 after the exponential)
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (c * 32 + i > row) v[i] = 0xff800000u;
+        }
+        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains instead of one long one
+#pragma unroll
+        for (int i = 0; i < 32; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(v[i]));
+        mx = fmaxf(mx, fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])));
       }
-      // the row maximum needs the other half: exchange through shared memory (buffer j & 1, so that the write of the
-      // next tile cannot overtake a slow reader of this one).  Every softmax thread takes part, failed or not.
-      xchg[(j & 1) * 256 + half * 128 + row] = ok ? mx : NAN;
-      named_barrier_sync(1, 256);
-      const float other = xchg[(j & 1) * 256 + (half ^ 1) * 128 + row];
-      if (!ok || other != other) {   // this half or the other one gave up: leave together
-        ok = false;
-        break;
-      }
-      const float m_new = fmaxf(m_run, fmaxf(mx, other) * p.scale_log2);
+      const float m_new = fmaxf(m_run, mx * p.scale_log2);
       const float alpha = fast_exp2(m_run - m_new);       // 0 for the first tile (m_run = -inf)
       // P overwrites the buffer the previous P V product reads: that product must have completed
       if (j >= 1 && !mbar_wait(bar(12 + ((j - 1) & 1)), ((j - 1) >> 1) & 1, p.timeout_ns, abort_flag)) fail(j, 3);
       float sum = 0.f;
+      float s4[4] = {0.f, 0.f, 0.f, 0.f};
       if (ok) {
         // keys half*64 .. +63 of this row = 64-key block `half`, eight 16-byte pieces, swizzled by the row
         const uint32_t base = p_s + half * kHalfBytes + row * 128;
 #pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          uint32_t pk[4];
+        for (int c2 = 0; c2 < 2; ++c2) {   // pass 2, 32 scores at a time
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(tmem + lane_addr + st * 128 + half * 64 + c2 * 32, v);
+          tmem_wait_ld();
+          if (diag) {
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int c = q * 8 + 2 * i;
-            float e0 = fast_exp2(__uint_as_float(v[c]) * p.scale_log2 - m_new);
-            float e1 = fast_exp2(__uint_as_float(v[c + 1]) * p.scale_log2 - m_new);
-            if (diag) {
-              if (half * 64 + c > row) e0 = 0.f;
-              if (half * 64 + c + 1 > row) e1 = 0.f;
-            }
-            if (F16) {
-              __half2 hh = __floats2half2_rn(e0, e1);
-              pk[i] = *reinterpret_cast<uint32_t*>(&hh);
-              const float2 r = __half22float2(hh);
-              sum += r.x + r.y;
-            } else {
-              __nv_bfloat162 bb = __floats2bfloat162_rn(e0, e1);
-              pk[i] = *reinterpret_cast<uint32_t*>(&bb);
-              const float2 r = __bfloat1622float2(bb);   // the sum of what the MMA will actually multiply
-              sum += r.x + r.y;
-            }
+            for (int i = 0; i < 32; ++i)
+              if (half * 64 + c2 * 32 + i > row) v[i] = 0xff800000u;
           }
-          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(base + ((q ^ (row & 7)) << 4)), "r"(pk[0]),
-                       "r"(pk[1]), "r"(pk[2]), "r"(pk[3])
-                       : "memory");
+#pragma unroll
+          for (int qq = 0; qq < 4; ++qq) {
+            const int q = c2 * 4 + qq;       // 16-byte piece (8 keys) of this thread's 64 keys
+            uint32_t pk[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int c = qq * 8 + 2 * i;  // index inside v
+              float e0 = fast_exp2(__uint_as_float(v[c]) * p.scale_log2 - m_new);
+              float e1 = fast_exp2(__uint_as_float(v[c + 1]) * p.scale_log2 - m_new);
+              s4[i] += e0 + e1;
+              if (F16) {
+                __half2 hh = __floats2half2_rn(e0, e1);
+                pk[i] = *reinterpret_cast<uint32_t*>(&hh);
+              } else {
+                __nv_bfloat162 bb = __floats2bfloat162_rn(e0, e1);
+                pk[i] = *reinterpret_cast<uint32_t*>(&bb);
+              }
+            }
+            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(base + ((q ^ (row & 7)) << 4)), "r"(pk[0]),
+                         "r"(pk[1]), "r"(pk[2]), "r"(pk[3])
+                         : "memory");
+          }
         }
+        sum = (s4[0] + s4[1]) + (s4[2] + s4[3]);
         l_run = l_run * alpha + sum;
         m_run = m_new;
         fence_proxy_async_smem();   // P is read by the tensor core through the async proxy
+        tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar(11));        // this warp's part of P_j is in shared memory
+        if (lane == 0) {
+          mbar_arrive(bar(11));        // this warp's part of P_j is in shared memory
+          mbar_arrive(bar(9 + st));    // and it has finished reading the S accumulator
+        }
         if (j >= 1) fold_o(j - 1, alpha_prev);
         alpha_prev = alpha;
       }
     }
     if (ok) fold_o(nkv - 1, alpha_prev);
     // total row sum = the two halves' sums
-    xchg[512 + half * 128 + row] = ok ? l_run : NAN;
+    xchg[half * 128 + row] = ok ? l_run : NAN;
     named_barrier_sync(1, 256);
-    const float l_other = xchg[512 + (half ^ 1) * 128 + row];
+    const float l_other = xchg[(half ^ 1) * 128 + row];
     if (ok && l_other == l_other) {
       const float inv = 1.f / (l_run + l_other);
       uint8_t* orow = reinterpret_cast<uint8_t*>(p.out) +
@@ -416,12 +418,10 @@ int iris_k_attention_fwd(const void* qkv, int64_t ld_qkv, void* out, int64_t ldo
   p.heads = heads;
   p.causal = causal ? 1 : 0;
   p.scale_log2 = 1.4426950408889634f / 11.313708498984761f;   // log2(e) / sqrt(128)
-  static const bool rebal = getenv("IRIS_ATTN_REBAL") ? atoi(getenv("IRIS_ATTN_REBAL")) != 0 : true;
-  auto kern = rebal ? (dtype ? attention_fwd_kernel<true, true> : attention_fwd_kernel<false, true>)
-                    : (dtype ? attention_fwd_kernel<true, false> : attention_fwd_kernel<false, false>);
-  static std::once_flag attr_once[4];
+  auto kern = dtype ? attention_fwd_kernel<true> : attention_fwd_kernel<false>;
+  static std::once_flag attr_once[2];
   cudaError_t e = cudaSuccess;
-  std::call_once(attr_once[dtype * 2 + (rebal ? 1 : 0)], [&]() {
+  std::call_once(attr_once[dtype], [&]() {
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
   });
   if (e != cudaSuccess) {
@@ -429,7 +429,7 @@ int iris_k_attention_fwd(const void* qkv, int64_t ld_qkv, void* out, int64_t ldo
     return -3;
   }
   const int grid = batch * heads * (seq / BQ);
-  kern<<<grid, rebal ? kThreads : 320, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(p);
+  kern<<<grid, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(p);
   e = cudaGetLastError();
   if (e != cudaSuccess) {
     snprintf(g_attn_err, sizeof(g_attn_err), "attention: launch: %s", cudaGetErrorString(e));

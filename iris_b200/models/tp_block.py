@@ -14,7 +14,9 @@ Per layer, on every rank (W ranks, tokens T = batch x seq, hidden H, SwiGLU widt
 The reference has no model code; its fused kernels are the ingredients (``docs/FINEGRAINED_OVERLAP.md:23-31``
 describes the row-parallel and column-parallel splits).  ``TPDecoderBaseline`` is the same network with cuBLAS GEMMs
 and NCCL ``all_gather_into_tensor`` / ``all_reduce``; ``reference_forward`` is the unsharded fp32 oracle.
-The attention core is ``torch.nn.functional.scaled_dot_product_attention`` (a library kernel) in both.
+The attention core of the fused stack is this repository's tcgen05 kernel (``iris_b200/ops/attention.py``) whenever
+the head dimension is 128 and the sequence length a multiple of 128; the baseline stack (and the fused one for other
+shapes, or with ``attention="sdpa"``) calls ``torch.nn.functional.scaled_dot_product_attention``.
 """
 from __future__ import annotations
 
@@ -25,6 +27,7 @@ import torch
 import torch.nn.functional as F
 
 from ..context import Iris
+from ..ops import attention as A
 from ..ops import elementwise as E
 from ..ops import gemm as G
 
@@ -84,10 +87,19 @@ def attention(qkv: torch.Tensor, cfg: TPConfig, heads_local: int, out: torch.Ten
     return out
 
 
-class TPDecoder:
-    """Fused implementation.  ``ctxs``: one ``Iris`` (one process per GPU) or all members of ``Iris.local_world``."""
+def attention_iris(qkv: torch.Tensor, cfg: TPConfig, heads_local: int, out: torch.Tensor, status=None) -> torch.Tensor:
+    """The same on the tcgen05 kernel: reads Q, K, V straight out of the projection's output, writes ``out`` in place
+    (no transposes, no copies)."""
+    return A.attention_fwd(qkv, out, cfg.batch, cfg.seq, heads_local, causal=True, status=status)
 
-    def __init__(self, ctxs: Union[Iris, Sequence[Iris]], cfg: TPConfig, variant: str = "two_shot", ag_slices: int = 8):
+
+class TPDecoder:
+    """Fused implementation.  ``ctxs``: one ``Iris`` (one process per GPU) or all members of ``Iris.local_world``.
+    ``variant``: how the row-parallel projections reduce (an all-reduce variant of ``gemm_all_reduce``, ``"auto"``, or
+    ``"reduce_scatter"``); ``attention``: ``"iris"`` (own kernel, when the shape allows) or ``"sdpa"``."""
+
+    def __init__(self, ctxs: Union[Iris, Sequence[Iris]], cfg: TPConfig, variant: str = "two_shot", ag_slices: int = 8,
+                 attention: str = "iris"):
         self.ctxs: List[Iris] = [ctxs] if isinstance(ctxs, Iris) else list(ctxs)
         self.cfg = cfg
         c0 = self.ctxs[0]
@@ -105,6 +117,7 @@ class TPDecoder:
                 return G.gemm_reduce_scatter(self.ctxs, a, bt)
             return G.gemm_all_reduce(self.ctxs, a, bt, variant=variant)
         self.heads_local = cfg.n_heads // W
+        self.own_attention = attention == "iris" and cfg.head_dim == A.HEAD_DIM and cfg.seq % 128 == 0
         self.ts = T // W
         nl = len(self.ctxs)
         self.attn = [torch.empty((T, H // W), dtype=torch.bfloat16, device=dev) for _ in range(nl)]
@@ -147,7 +160,10 @@ class TPDecoder:
             qkv = ops["qkv"]()
             tick("attention")
             for l in range(nl):
-                attention(qkv[l], cfg, self.heads_local, self.attn[l])
+                if self.own_attention:
+                    attention_iris(qkv[l], cfg, self.heads_local, self.attn[l], status=self.ctxs[l].status)
+                else:
+                    attention(qkv[l], cfg, self.heads_local, self.attn[l])
             tick("o_gemm_ar")
             o = ops["o"]()
             tick("norm")

@@ -173,3 +173,44 @@ def test_planner_named_configurations():
         plan_gemm(1024, 256, 256, 2, 1, "two_shot", 148, reduce_scatter=True)
     with pytest.raises(ValueError):
         plan_gemm(1024, 256, 256, 2, 1, "one_shot", 148, ag=True)
+
+
+def test_new_plan_knobs_reach_the_descriptor(world2):
+    """Tile width, element type, push kind, column-split tail, K pieces of the atomic form and the push two-shot
+    layout, as the native library receives them."""
+    ranks, fake = world2
+    a = [torch.zeros((2560, 256), dtype=torch.float16) for _ in range(2)]
+    bt = [torch.zeros((1024, 256), dtype=torch.float16) for _ in range(2)]
+    op = G.gemm_all_scatter(ranks, a, bt, bn=128, push_kind="stores", tail_split=2)
+    d, c0 = fake.descs[-1], ranks[0]
+    assert (d.bn, d.dtype, d.push_kind) == (128, G.DTYPES["fp16"], G.PUSH_KINDS["stores"])
+    assert d.c_off == c0.offset_of(op.out[0]) and op.out[0].dtype == torch.float16
+    # 10 x 8 = 80 pair-tiles on 37 units: 2 full waves, 6 tiles left -> cut in two column pieces each
+    assert (d.tail_tiles, d.tail_split) == (6, 2) == (op.tail_tiles, op.tail_split)
+    op.close()
+    with pytest.raises(RuntimeError, match="multimem"):
+        G.gemm_all_scatter(ranks, a, bt, push_kind="multimem")     # no NVLS-bound heap on this machine
+    with pytest.raises(TypeError):
+        G.gemm_all_scatter(ranks, a, [b.to(torch.bfloat16) for b in bt])   # mixed element types
+    a, bt = _ab(128, 1024, 2048, 2)
+    at = G.gemm_all_reduce(ranks, a, bt, variant="atomic", bn=64, ksplit=4)
+    d = fake.descs[-1]
+    assert (d.mode, d.ksplit, d.bn, d.store_all) == (G.MODES["reduce"], 4, 64, 1) and at.ctas_per_rank == 64
+    at.close()
+    a, bt = _ab(1024, 512, 256, 2)
+    tp = G.gemm_all_reduce(ranks, a, bt, variant="two_shot_push")
+    d = fake.descs[-1]
+    assert d.rs_rows == 512 and d.rs_bcast == 1 and d.push_partials == 1
+    # inbox: 2 parities x 2 slots of 512 rows; output: all 1024 rows on every rank
+    assert d.c_rows == (2 * 2 + 2) * 512 and d.out_row0 == 4 * 512 and tp.out[0].shape == (1024, 512)
+    tp2 = tp.rebuild()
+    assert tp._plan is None and fake.descs[-1].rs_bcast == 1 and tp2.calls == 0
+    tp2.close()
+
+
+def test_auto_variant_table():
+    assert G.auto_all_reduce_variant(1, 8) == ("atomic", dict(bn=128, ksplit=4))
+    assert G.auto_all_reduce_variant(128, 8) == ("atomic", dict(bn=64))
+    assert G.auto_all_reduce_variant(1, 2)[0] == "atomic" and G.auto_all_reduce_variant(1, 2)[1]["ksplit"] == 8
+    assert G.auto_all_reduce_variant(1024, 2)[0] == "one_shot"
+    assert G.auto_all_reduce_variant(8192, 8)[0] == "two_shot" and G.auto_all_reduce_variant(1024, 4)[0] == "two_shot"

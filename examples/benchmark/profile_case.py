@@ -52,40 +52,62 @@ def run_elementwise(args):
         E.rmsnorm(x, w, out, 1e-6)
         E.swiglu(gu, h)
         E.residual_add(x, y)
+        E.add_rmsnorm(x, y, w, out, 1e-6)
     torch.cuda.synchronize()
-    print(f"elementwise kernels: {args.launches} rounds of rmsnorm / swiglu / residual_add")
+    print(f"elementwise kernels: {args.launches} rounds of rmsnorm / swiglu / residual_add / add_rmsnorm")
+
+
+def run_attention(args):
+    """The tcgen05 attention kernel on batch 8 x seq 2048 x 4 heads of 128 (48 MB of qkv), causal."""
+    from iris_b200.ops.attention import attention_fwd
+    batch, seq, heads = 8, 2048, 4
+    g = torch.Generator(device="cuda").manual_seed(1)
+    dt = torch.float16 if args.dtype == "fp16" else torch.bfloat16
+    qkv = torch.randn((batch * seq, 3 * heads * 128), generator=g, device="cuda").to(dt)
+    out = torch.empty((batch * seq, heads * 128), dtype=dt, device="cuda")
+    for _ in range(args.launches):
+        attention_fwd(qkv, out, batch, seq, heads)
+    torch.cuda.synchronize()
+    print(f"attention: {args.launches} launches, batch {batch} x seq {seq} x {heads} heads, {args.dtype}")
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--workload", default="gemm", choices=["gemm", "all_scatter", "atomic", "one_shot", "two_shot", "reduce_scatter", "ag", "p2p",
-                             "elementwise"])
+                             "elementwise", "attention"])
     ap.add_argument("--world", type=int, default=1)
     ap.add_argument("-m", type=int, default=8192)
     ap.add_argument("-n", type=int, default=3584)
     ap.add_argument("-k", type=int, default=4096)
     ap.add_argument("--launches", type=int, default=3)
     ap.add_argument("--cta_group", type=int, default=0)
+    ap.add_argument("--bn", type=int, default=0, help="tile width: 64, 128 or 256 (0: the default, 256)")
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16"])
     args = ap.parse_args()
     W = args.world
     if args.workload == "p2p":
         return run_p2p(args)
     if args.workload == "elementwise":
         return run_elementwise(args)
+    if args.workload == "attention":
+        return run_attention(args)
     ranks = iris.Iris.local_world(W, heap_size=(1 << 30) // max(1, W // 2))
     g = torch.Generator(device="cuda").manual_seed(0)
 
+    dt = torch.float16 if args.dtype == "fp16" else torch.bfloat16
+
     def rand(r, c):
-        return (torch.randn((r, c), generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+        return (torch.randn((r, c), generator=g, device="cuda") * 0.02).to(dt)
     cg = args.cta_group or None
+    bn = args.bn or None
     m, n, k = args.m, args.n, args.k
     if args.workload in ("gemm", "all_scatter"):
         a = rand(m, k)
         bts = [rand(n // W, k) for _ in range(W)]
-        op = G.gemm_all_scatter(ranks, [a] * W, bts, cta_group=cg)
+        op = G.gemm_all_scatter(ranks, [a] * W, bts, cta_group=cg, bn=bn)
     elif args.workload == "ag":
         bts = [rand(n // W, k) for _ in range(W)]
-        op = G.all_gather_gemm(ranks, m, bts, cta_group=cg)
+        op = G.all_gather_gemm(ranks, m, bts, cta_group=cg, bn=bn)
         for r in range(W):
             op.a_full[r][r * (m // W):(r + 1) * (m // W)].copy_(rand(m // W, k))
     else:
@@ -94,13 +116,13 @@ def main():
         a_sh = [a_full[:, r * ks:(r + 1) * ks] for r in range(W)]
         b_sh = [b_full[:, r * ks:(r + 1) * ks] for r in range(W)]
         if args.workload == "reduce_scatter":
-            op = G.gemm_reduce_scatter(ranks, a_sh, b_sh, cta_group=cg)
+            op = G.gemm_reduce_scatter(ranks, a_sh, b_sh, cta_group=cg, bn=bn)
         else:
-            op = G.gemm_all_reduce(ranks, a_sh, b_sh, variant=args.workload, cta_group=cg)
+            op = G.gemm_all_reduce(ranks, a_sh, b_sh, variant=args.workload, cta_group=cg, bn=bn)
     for _ in range(args.launches):
         op()
     op.check()
-    print(f"{args.workload} W={W} {m}x{n}x{k}: {args.launches} launches, cta_group={op.cta_group}, "
+    print(f"{args.workload} W={W} {m}x{n}x{k} {args.dtype}: {args.launches} launches, tile {128 * op.cta_group}x{op.bn}, "
           f"ctas/rank={op.ctas_per_rank}")
     op.close()
     ranks[0].close()

@@ -143,7 +143,7 @@ class FusedGemm:
                  bt: Sequence[torch.Tensor], mode: str = "store", *, M: Optional[int] = None,
                  store_all: bool = False, c_cols: Optional[int] = None, col_off_per_rank: int = 0,
                  out: Optional[Sequence[torch.Tensor]] = None, ag: bool = False, ag_slices: int = 8,
-                 ctas_per_rank: Optional[int] = None, group_m: int = 8, timeout_ms: float = 2000.0,
+                 ctas_per_rank: Optional[int] = None, group_m: Optional[int] = None, timeout_ms: float = 2000.0,
                  cta_group: Optional[int] = None, trace: bool = False, stream_k: Optional[bool] = None,
                  push: Optional[bool] = None, ksplit: Optional[int] = None, nvls: Optional[bool] = None,
                  reduce_scatter: bool = False, bn: Optional[int] = None, tail_split: Optional[bool] = None,
@@ -261,6 +261,7 @@ class FusedGemm:
         d.col_off_per_rank = int(col_off_per_rank)
         d.world, d.num_local, d.rank0, d.ctas_per_rank = self.world, self.num_local, self.rank0, self.ctas_per_rank
         d.mode, d.group_m, d.ag, d.ag_slices = MODES[mode], int(group_m), int(self.ag), int(ag_slices)
+        self.group_m = int(group_m)
         d.store_all = int(self.store_all)
         d.tile_flag_base = FLAG_HEADER
         d.ag_flag_base = FLAG_HEADER + tile_flags

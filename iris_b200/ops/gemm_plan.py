@@ -82,7 +82,7 @@ def tail_split_plan(total_tiles: int, units: int, max_split: int) -> Tuple[int, 
 
 
 def plan_gemm(M: int, N: int, K: int, world: int, num_local: int, mode: str, sms: int, *, ag: bool = False,
-              cta_group: Optional[int] = None, ctas_per_rank: Optional[int] = None, group_m: int = 8,
+              cta_group: Optional[int] = None, ctas_per_rank: Optional[int] = None, group_m: Optional[int] = 8,
               stream_k: Optional[bool] = None, push: Optional[bool] = None, ksplit: Optional[int] = None,
               reduce_scatter: bool = False, store_all: bool = False, own_out: bool = False,
               bn: Optional[int] = None, tail_split: Optional[bool] = None, bcast: bool = False) -> GemmPlan:
@@ -99,11 +99,18 @@ def plan_gemm(M: int, N: int, K: int, world: int, num_local: int, mode: str, sms
         raise ValueError(f"tile width must be one of {TILE_WIDTHS}")
     if mode in ("one_shot", "two_shot") and ag:
         raise ValueError("the all-gather prologue is combined with mode='store' only")
-    # CTA pairs (256 x 256 tiles, cta_group::2) for anything taller than one 128-row tile; single CTAs else
+    # CTA pairs (256-row tiles, cta_group::2) or single CTAs (128-row tiles).  Measured on 8192 x N x 4096: the pair
+    # wins only when there are many column tiles (N = 14336: 658 us against 675 us); at N = 7168 / 3584 / 1792 single
+    # CTAs are 3 to 7 % faster (343 / 185 / 107 us against 358 / 196 / 115 us), so the kernels without reducer warps
+    # use pairs only above 8192 columns.  The one- / two-shot family keeps pairs (half as many per-tile flags).
     if cta_group is None:
         cta_group = 2 if M > BM and (not ag or (M // world) % (2 * BM) == 0) else 1
+        if mode in ("store", "reduce") and N <= 8192:
+            cta_group = 1
         if reduce_scatter and M % (world * 2 * BM) != 0:
             cta_group = 1
+    if group_m is None:   # m-tiles per raster group: wider groups pay once a row of tiles no longer fits a wave
+        group_m = 16 if N >= 12288 else 8
     if cta_group not in (1, 2):
         raise ValueError("cta_group must be 1 or 2")
     # reduce-scatter: rank r keeps rows [r * M / world, (r + 1) * M / world) of the sum

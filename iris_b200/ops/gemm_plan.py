@@ -101,12 +101,13 @@ def plan_gemm(M: int, N: int, K: int, world: int, num_local: int, mode: str, sms
         raise ValueError("the all-gather prologue is combined with mode='store' only")
     # CTA pairs (256-row tiles, cta_group::2) or single CTAs (128-row tiles).  Measured on 8192 x N x 4096: the pair
     # wins only when there are many column tiles (N = 14336: 658 us against 675 us); at N = 7168 / 3584 / 1792 single
-    # CTAs are 3 to 7 % faster (343 / 185 / 107 us against 358 / 196 / 115 us), so the kernels without reducer warps
-    # use pairs only above 8192 columns.  The one- / two-shot family keeps pairs (half as many per-tile flags).
+    # CTAs are 3 to 7 % faster (343 / 185 / 107 us against 358 / 196 / 115 us), so the kernels that keep their tiles
+    # (plain GEMM, all-gather -> GEMM) use pairs only above 8192 columns.  The one- / two-shot family keeps pairs (half
+    # as many per-tile flags).
     if cta_group is None:
         cta_group = 2 if M > BM and (not ag or (M // world) % (2 * BM) == 0) else 1
-        if mode in ("store", "reduce") and N <= 8192:
-            cta_group = 1
+        if mode in ("store", "reduce") and N <= 8192 and not (store_all and world > 1):
+            cta_group = 1   # (with tiles pushed to peers the pair stays ahead: 380 us against 392 us on 2 GPUs)
         if reduce_scatter and M % (world * 2 * BM) != 0:
             cta_group = 1
     if group_m is None:   # m-tiles per raster group: wider groups pay once a row of tiles no longer fits a wave

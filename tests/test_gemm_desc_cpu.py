@@ -62,7 +62,7 @@ def test_all_scatter_descriptor(world2):
     d = fake.descs[-1]
     c0 = ranks[0]
     assert (d.M, d.N, d.K, d.world, d.num_local, d.rank0) == (512, 320, 256, 2, 2, 0)
-    assert d.mode == G.MODES["store"] and d.store_all == 1 and d.cta_group == 1   # few column tiles: single CTAs
+    assert d.mode == G.MODES["store"] and d.store_all == 1 and d.cta_group == 2
     assert d.c_cols == 640 and d.col_off_per_rank == 320 and d.ldc == 640
     assert [d.c_ptr[t] for t in range(2)] == [c0.heap_base(t) + c0.offset_of(op.out[0]) for t in range(2)]
     assert d.flags_off == c0.offset_of(op.flags[0]) and d.status_off == c0.offset_of(c0.status)
@@ -162,7 +162,9 @@ def test_planner_invariants(world):
 
 def test_planner_named_configurations():
     p = plan_gemm(8192, 1792, 4096, 8, 1, "store", 148, store_all=True)          # GEMM + all-scatter, 8 ranks
-    assert (p.cta_group, p.ctas_per_rank, p.total_tiles, p.kblocks) == (1, 148, 448, 64)
+    assert (p.cta_group, p.ctas_per_rank, p.total_tiles, p.kblocks) == (2, 148, 224, 64)
+    p = plan_gemm(8192, 1792, 4096, 1, 1, "store", 148)                          # the same shape kept local: single CTAs
+    assert (p.cta_group, p.total_tiles) == (1, 448)
     p = plan_gemm(8192, 14336, 4096, 1, 1, "store", 148, group_m=None)           # the whole product on one GPU
     assert (p.cta_group, p.ctas_per_rank, p.total_tiles, p.group_m) == (2, 148, 1792, 16)
     p = plan_gemm(8192, 4096, 1376, 8, 1, "two_shot", 148)                       # GEMM + all-reduce, 8 ranks
@@ -187,8 +189,8 @@ def test_new_plan_knobs_reach_the_descriptor(world2):
     d, c0 = fake.descs[-1], ranks[0]
     assert (d.bn, d.dtype, d.push_kind) == (128, G.DTYPES["fp16"], G.PUSH_KINDS["stores"])
     assert d.c_off == c0.offset_of(op.out[0]) and op.out[0].dtype == torch.float16
-    # 20 x 8 = 160 tiles on 74 CTAs: 2 full waves, 12 tiles left -> cut in two column pieces each
-    assert (d.tail_tiles, d.tail_split) == (12, 2) == (op.tail_tiles, op.tail_split)
+    # 10 x 8 = 80 pair-tiles on 37 units: 2 full waves, 6 tiles left -> cut in two column pieces each
+    assert (d.tail_tiles, d.tail_split) == (6, 2) == (op.tail_tiles, op.tail_split)
     op.close()
     with pytest.raises(RuntimeError, match="multimem"):
         G.gemm_all_scatter(ranks, a, bt, push_kind="multimem")     # no NVLS-bound heap on this machine

@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import argparse
 
-from .harness import iris, reduce_ranks, time_kernel_ms, torch
+from .harness import device_barrier, iris, reduce_ranks, time_kernel_ms, torch
 from iris_b200.ops import gemm as G
 from iris_b200.utils import roofline
 from iris_b200.utils.results import JSONWriter
@@ -42,6 +42,9 @@ def parse_args(kind: str):
                     help="cut the tiles of a ragged last wave into up to this many column pieces (0: off)")
     ap.add_argument("--push_kind", default=None, choices=["tma", "tma_spread", "stores", "multimem"],
                     help="all-scatter / atomic: how tiles travel to the other ranks")
+    ap.add_argument("--all_gather", action="store_true",
+                    help="all-scatter only: A arrives row-sharded (M / ranks rows per rank) and the kernel's all-gather "
+                         "prologue distributes it while the tiles of rows already present are computed")
     ap.add_argument("--ksplit", type=int, default=None, help="atomic / one-shot on short matrices: K pieces per tile")
     ap.add_argument("--num_experiments", type=int, default=50)
     ap.add_argument("--num_warmup", type=int, default=10)
@@ -62,6 +65,7 @@ def run(kind: str, seed: int):
     ctx = iris.iris(args["heap_size"], heap_mode=args["heap_mode"])
     rank, world = ctx.get_rank(), ctx.get_num_ranks()
     dev = ctx.get_device()
+    dbar = device_barrier(ctx)   # allocated first, in the same order on every rank
     m, n, k = args["m"], args["n"], args["k"]
     gen = torch.Generator(device=dev).manual_seed(seed)  # same seed everywhere -> identical A and B
     dtype = {"bf16": torch.bfloat16, "fp16": torch.float16}[args["datatype"]]
@@ -79,8 +83,17 @@ def run(kind: str, seed: int):
             raise SystemExit("N must be divisible by the number of ranks")
         nl = n // world
         bt_local = Bt[rank * nl:(rank + 1) * nl].contiguous()
-        op = G.gemm_all_scatter(ctx, [A], [bt_local], ctas_per_rank=ctas, group_m=args["gsize_m"],
-                                trace=args["trace_tiles"], push_kind=args["push_kind"], **tile_kw)
+        if args["all_gather"]:
+            if m % world:
+                raise SystemExit("M must be divisible by the number of ranks")
+            op = G.FusedGemm(ctx, None, [bt_local], "store", M=m, ag=True, store_all=True, c_cols=n,
+                             col_off_per_rank=nl, ctas_per_rank=ctas, group_m=args["gsize_m"],
+                             trace=args["trace_tiles"], push_kind=args["push_kind"], **tile_kw)
+            rows = slice(rank * (m // world), (rank + 1) * (m // world))
+            op.a_full[0][rows].copy_(A[rows])       # this rank's rows only; the kernel fetches the rest
+        else:
+            op = G.gemm_all_scatter(ctx, [A], [bt_local], ctas_per_rank=ctas, group_m=args["gsize_m"],
+                                    trace=args["trace_tiles"], push_kind=args["push_kind"], **tile_kw)
         roof = roofline.all_scatter_roofline_us(m, n, k, world, peaks)
         c_part = torch.empty((m, nl), dtype=dtype, device=dev)
         gathered = torch.empty((world, m, nl), dtype=dtype, device=dev)
@@ -148,6 +161,9 @@ def run(kind: str, seed: int):
     js.add_environment(dev)
     G.matmul.set_debug(args["debug"])
     ctx.barrier()
+    if dbar is not None:   # the ranks' streams start the validated / traced call together
+        torch.cuda._sleep(1000000)
+        dbar()
     out = G.matmul.apply(op)
     ctx.barrier()
     op.check()

@@ -58,6 +58,7 @@ enum Site : uint32_t {
   kSiteProducerEmpty = 10,
   kSiteProducerAgFlag = 11,
   kSiteAgEntry = 12,
+  kSiteZero = 13,
   kSiteMmaAccEmpty = 20,
   kSiteMmaFull = 21,
   kSiteEpiAccFull = 30,
@@ -193,6 +194,9 @@ __device__ __noinline__ void rs_sum_part(const FusedGemmParams& p, int rank, int
   }
 }
 
+__device__ __forceinline__ void red_relaxed_gpu_add(uint32_t* p, uint32_t v) {
+  asm volatile("red.relaxed.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 __device__ __forceinline__ void red_add_v4_f32_gpu(float* p, float a, float b, float c, float d) {
   asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d)
                : "memory");
@@ -317,6 +321,24 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
   // The flag orders nothing written by this kernel (it has written nothing yet); what a peer relies on, the end of
   // this rank's previous call, is ordered by the kernel boundary.  One fence, then relaxed stores: a release store
   // per peer would wait for the previous peer's acknowledgement each time, a link round trip per rank.
+  if (p.zero_bytes) {
+    // Atomic all-reduce of a short matrix: the output, which every rank adds into, is cleared here instead of by a
+    // launch of its own.  Every CTA clears its share, counts itself on a local counter, and the entry flags (which
+    // tell the peers that this rank's output may be added into) go out only when all CTAs of the rank have done so.
+    uint8_t* outp = reinterpret_cast<uint8_t*>(p.heap_base[rank] + p.c_off);
+    const uint64_t n16 = p.zero_bytes / 16;
+    for (uint64_t i = (uint64_t)cta * blockDim.x + threadIdx.x; i < n16; i += (uint64_t)p.ctas_per_rank * blockDim.x)
+      st_v4(reinterpret_cast<uint4*>(outp) + i, make_uint4(0u, 0u, 0u, 0u));
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      red_relaxed_gpu_add(flag_ptr(p, rank, 1), 1u);
+      if (cta == 0 &&
+          wait_until_ge(flag_ptr(p, rank, 1), p.epoch * (uint32_t)p.ctas_per_rank, p.timeout_ns, status, kSiteZero, rank,
+                        0) != kOk)
+        *abort_flag = 1;
+    }
+  }
   if (W > 1 && cta == 0 && threadIdx.x == 0) {
     fence_sys();
     for (int i = 0; i < W; ++i) {
@@ -1277,6 +1299,7 @@ struct IrisGemmDesc {
   int push_kind;               // PushKind of the all-scatter epilogue
   int tail_tiles, tail_split;  // column-split tail of the raster (see tail_split_plan); 0 / 1 = off
   uint64_t c_off;              // symmetric offset of the C buffer (needed by push kinds 2 and 3)
+  uint64_t zero_bytes;         // atomic all-reduce: bytes of the output (from c_off) the kernel clears itself; 0 = none
 };
 
 struct IrisGemmPlan {
@@ -1548,6 +1571,7 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
     p.tail_split = tail_split;
     p.ldc = (int)d->ldc;
     p.c_off = d->c_off;
+    p.zero_bytes = (d->mode == kEpiReduce && d->store_all && d->c_off) ? (d->zero_bytes / 16) * 16 : 0;
   }
   return plan;
 }

@@ -120,6 +120,8 @@ struct FusedGemmParams {
   int tail_split;        //   (see tail_split_plan in gemm_schedule.h); 0 / 1 = no split
   int ldc;               // row pitch (elements) of the C buffers, for the pushes made with ordinary / multimem stores
   uint64_t c_off;        // symmetric offset of the C buffer (store / reduce with store_all)
+  uint64_t zero_bytes;   // reduce mode: bytes of this rank's output, from c_off, that the kernel clears before it
+                         // raises its entry flags (multiple of 16; 0 = the caller clears the output)
   uint32_t c_box_bytes;  // bytes of one C / partial sub-tile transfer: rows of the tmC box (128, fewer when M < 128) x 128
   uint32_t epoch;        // call number (1, 2, ...): value of the entry flags in this call
   uint32_t flag_target;  // value per-tile / per-chunk flags reach in this call (cumulative over calls)

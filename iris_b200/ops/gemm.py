@@ -29,6 +29,8 @@ from .gemm_plan import (BK, BM, BN, DTYPES, FLAG_HEADER, MODES, PUSH_KINDS, TILE
 MAX_RANKS = 8
 # How GEMM + all-scatter tiles are pushed unless the caller says otherwise (see FusedGemm, ``push_kind``).
 DEFAULT_PUSH_KIND = "tma"
+# Atomic all-reduce: outputs up to this size are cleared by the kernel itself instead of by a launch before it.
+ZERO_IN_KERNEL_MAX_BYTES = 8 << 20
 
 
 class _Desc(ctypes.Structure):
@@ -54,7 +56,7 @@ class _Desc(ctypes.Structure):
         ("rs_rows", ctypes.c_int), ("rs_bcast", ctypes.c_int),
         ("bn", ctypes.c_int), ("dtype", ctypes.c_int), ("push_kind", ctypes.c_int),
         ("tail_tiles", ctypes.c_int), ("tail_split", ctypes.c_int),
-        ("c_off", ctypes.c_uint64),
+        ("c_off", ctypes.c_uint64), ("zero_bytes", ctypes.c_uint64),
     ]
 
 
@@ -281,6 +283,12 @@ class FusedGemm:
         d.tail_tiles, d.tail_split = pl.tail_tiles, pl.tail_split
         self.bn, self.tail_tiles, self.tail_split = pl.bn, pl.tail_tiles, pl.tail_split
         d.c_off = c_off if self.store_all else 0
+        # atomic all-reduce of a short matrix: the kernel clears the output itself (one launch less); a large output
+        # is cleared faster by a launch of its own than by CTAs that should already be loading operands
+        out_bytes = self.out[0].shape[0] * self.out[0].stride(0) * 2
+        self._zero_in_kernel = (mode == "reduce" and self.store_all and out is None
+                                and self.out[0].is_contiguous() and out_bytes <= ZERO_IN_KERNEL_MAX_BYTES)
+        d.zero_bytes = out_bytes if self._zero_in_kernel else 0
         # two-shot on a heap bound to an NVLS multicast object: the switch sums and broadcasts
         mc = int(getattr(c0, "mc_base", 0) or 0)
         self.nvls = (bool(mc) and (mode == "two_shot" or pl.bcast) and self.num_local == 1 and out is None
@@ -319,7 +327,7 @@ class FusedGemm:
     def __call__(self, stream=None) -> List[torch.Tensor]:
         c0 = self.ctxs[0]
         st = torch.cuda.current_stream(c0.device).cuda_stream if stream is None else stream
-        if self.mode == "reduce":
+        if self.mode == "reduce" and not self._zero_in_kernel:
             for o in self.out[:self.num_local]:
                 o.zero_()  # partial sums are added into the output: it has to start at zero
             self.launches += self.num_local

@@ -53,7 +53,17 @@ EX = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "
     ("06_message_passing/message_passing_load_store.py", ["-n", "3"]),
     ("07_gemm_all_scatter/benchmark.py", ["-m", "1024", "-n", "2048", "-k", "512", "-v", "-b", "--num_experiments", "3",
                                           "--num_warmup", "1", "--heap_size", str(1 << 28)]),
+    ("07_gemm_all_scatter/benchmark.py", ["-m", "1024", "-n", "2048", "-k", "512", "-v", "-b", "--num_experiments", "3",
+                                          "--num_warmup", "1", "--heap_size", str(1 << 28), "--datatype", "fp16",
+                                          "--BLK_M", "128", "--BLK_N", "128", "--push_kind", "stores", "--all_gather"]),
     ("08_gemm_atomics_all_reduce/benchmark.py", ["-m", "1024", "-n", "1024", "-k", "1024", "-v", "--heap_size", str(1 << 28)]),
+    ("08_gemm_atomics_all_reduce/benchmark.py", ["-m", "128", "-n", "1024", "-k", "2048", "-v", "-b", "--num_experiments", "3",
+                                                 "--num_warmup", "1", "--BLK_N", "64", "--ksplit", "2",
+                                                 "--heap_size", str(1 << 28)]),
+    ("09_gemm_one_shot_all_reduce/benchmark.py", ["-m", "1024", "-n", "1024", "-k", "1024", "-v", "--variant", "two_shot_push",
+                                                  "--heap_size", str(1 << 28)]),
+    ("09_gemm_one_shot_all_reduce/benchmark.py", ["-m", "64", "-n", "1024", "-k", "1024", "-v", "--variant", "auto",
+                                                  "--heap_size", str(1 << 28)]),
     ("09_gemm_one_shot_all_reduce/benchmark.py", ["-m", "128", "-n", "1024", "-k", "1024", "-v", "--heap_size", str(1 << 28)]),
     ("10_tp_block/tp_block.py", ["-v", "--hidden", "512", "--heads", "4", "--intermediate", "1024", "--batch", "2",
                                  "--seq", "512", "--layers", "1", "--heap_size", str(1 << 29)]),

@@ -27,8 +27,9 @@ def parse_args(kind: str):
     ap.add_argument("-v", "--validate", action="store_true")
     ap.add_argument("-t", "--trace_tiles", action="store_true", help="record per-tile device timestamps to trace_rank<r>.json")
     ap.add_argument("-b", "--benchmark", action="store_true")
-    ap.add_argument("--datatype", default="bf16", choices=["fp16", "bf16"],
-                    help="element type of A, B and C (fp32 accumulation); the reference's fp32 / int8 are not offered")
+    ap.add_argument("--datatype", default="bf16", choices=["fp16", "fp32", "int8", "bf16"],
+                    help="element type of A, B and C: bf16 / fp16 (fp32 accumulation) for every kernel; fp32 (multiplied "
+                         "as tf32) and int8 (int32 accumulation, low 8 bits stored) for the all-scatter kernel")
     ap.add_argument("--output_file", default="")
     ap.add_argument("--gsize_m", type=int, default=8, help="m-tiles per raster group")
     ap.add_argument("--heap_size", type=int, default=1 << 31)
@@ -68,9 +69,17 @@ def run(kind: str, seed: int):
     dbar = device_barrier(ctx)   # allocated first, in the same order on every rank
     m, n, k = args["m"], args["n"], args["k"]
     gen = torch.Generator(device=dev).manual_seed(seed)  # same seed everywhere -> identical A and B
-    dtype = {"bf16": torch.bfloat16, "fp16": torch.float16}[args["datatype"]]
-    A = (torch.randn((m, k), generator=gen, device=dev) * 0.02).to(dtype)
-    Bt = (torch.randn((n, k), generator=gen, device=dev) * 0.02).to(dtype)  # B = Bt.T, K-major
+    dtype = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32, "int8": torch.int8}[args["datatype"]]
+    if dtype in (torch.float32, torch.int8) and kind != "all_scatter":
+        raise SystemExit("fp32 and int8 are offered by the all-scatter kernel only (the reductions are 16-bit)")
+    if dtype == torch.int8:
+        A = torch.randint(-128, 128, (m, k), generator=gen, device=dev, dtype=torch.int32).to(dtype)
+        Bt = torch.randint(-128, 128, (n, k), generator=gen, device=dev, dtype=torch.int32).to(dtype)
+    else:
+        A = (torch.randn((m, k), generator=gen, device=dev) * 0.02).to(dtype)
+        Bt = (torch.randn((n, k), generator=gen, device=dev) * 0.02).to(dtype)  # B = Bt.T, K-major
+    if dtype == torch.float32:
+        torch.backends.cuda.matmul.allow_tf32 = True   # the library arm multiplies as tf32 too
     ctas = args["gemm_sms"] or None
     # tile shape and schedule knobs (the reference's BLK_M / BLK_N, examples/07_gemm_all_scatter/benchmark.py:53-60)
     tile_kw = dict(bn=args["BLK_N"], cta_group={None: None, 128: 1, 256: 2}[args["BLK_M"]])
@@ -94,13 +103,16 @@ def run(kind: str, seed: int):
         else:
             op = G.gemm_all_scatter(ctx, [A], [bt_local], ctas_per_rank=ctas, group_m=args["gsize_m"],
                                     trace=args["trace_tiles"], push_kind=args["push_kind"], **tile_kw)
-        roof = roofline.all_scatter_roofline_us(m, n, k, world, peaks)
+        roof = roofline.all_scatter_roofline_us(m, n, k, world, peaks, args["datatype"])
         c_part = torch.empty((m, nl), dtype=dtype, device=dev)
         gathered = torch.empty((world, m, nl), dtype=dtype, device=dev)
 
         def unfused():
             torch.cuda.nvtx.range_push("GEMM")
-            torch.matmul(A, bt_local.t(), out=c_part)
+            if dtype == torch.int8:   # the library's int8 GEMM returns the int32 sums; the cast keeps their low 8 bits
+                c_part.copy_(torch._int_mm(A, bt_local.t()))
+            else:
+                torch.matmul(A, bt_local.t(), out=c_part)
             torch.cuda.nvtx.range_pop()
             if world > 1:
                 torch.cuda.nvtx.range_push("Communication")
@@ -152,7 +164,7 @@ def run(kind: str, seed: int):
     js = JSONWriter(args["output_file"] if rank == 0 else "")
     fields = {k_: v for k_, v in args.items() if v is not None}
     fields.update(world_size=world, variant=variant, gemm_sms=op.ctas_per_rank,
-                  tile=f"{128 * op.cta_group}x{op.bn}x64", ksplit=op.ksplit, push_kind=op.push_kind,
+                  tile=f"{128 * op.cta_group}x{op.bn}x{128 // A.element_size()}", ksplit=op.ksplit, push_kind=op.push_kind,
                   tail=[op.tail_tiles, op.tail_split])
     res = op.resources()
     if res:  # the reference's gemm_registers / gemm_spills (examples/07_gemm_all_scatter/benchmark.py:237-242)
@@ -180,10 +192,18 @@ def run(kind: str, seed: int):
         if kind == "reduce_scatter":  # this rank holds rows [rank * m / world, ...) only
             rows = slice(rank * (m // world), rank * (m // world) + min(m // world, 1024))
             got = out[:rows.stop - rows.start]
-        ref = A[rows].float() @ Bt.float().t()
-        # bf16 rounding of the result and (all-reduce) of the partials, relative to the largest entry
-        err = (got.float() - ref).abs().max().item()
-        ok = err <= (2.0 + world) * 2.0 ** -8 * ref.abs().max().item()
+        if dtype == torch.int8:   # exact: the low 8 bits of the integer sums
+            full = (A[rows].double() @ Bt.double().t()).to(torch.int64)
+            ok = torch.equal(got, (((full + 128) % 256) - 128).to(torch.int8))
+        elif dtype == torch.float32:   # two tf32 roundings (2^-11 each) per product
+            ref = A[rows].double() @ Bt.double().t()
+            tol = 2.0 ** -9 * (A[rows].double().abs() @ Bt.double().abs().t())
+            ok = bool(((got.double() - ref).abs() <= tol + 1e-9).all())
+        else:
+            ref = A[rows].float() @ Bt.float().t()
+            # bf16 rounding of the result and (all-reduce) of the partials, relative to the largest entry
+            err = (got.float() - ref).abs().max().item()
+            ok = err <= (2.0 + world) * 2.0 ** -8 * ref.abs().max().item()
         ctx.log(f"Validation {'successful' if ok else 'FAILED'}.")
         js.add_field("success", ok)
     if args["benchmark"]:

@@ -221,7 +221,7 @@ struct Cfg {
   static_assert(kTilesBytes <= kSmemTiles, "shared-memory budget");
 };
 
-template <int CG, bool PULL, bool F16>
+template <int CG, bool PULL, int ET>
 __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
     fused_gemm_kernel(const __grid_constant__ FusedGemmParams p) {
   using C = Cfg<CG, PULL>;
@@ -263,10 +263,14 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
   constexpr int TM = BM * CG;                     // rows of a scheduling unit's tile
   const int tiles_m = (p.M + TM - 1) / TM;
   const int bn = p.bn;                            // tile width of this launch (64, 128 or 256)
-  constexpr bool f16 = F16;                       // element type of A, B, C: fp16, else bf16
+  constexpr bool f16 = ET == kFp16;               // which 16-bit type, where the code below handles 16-bit values
+  constexpr int ES = elem_size(ET);               // bytes per element of A, B and C
+  constexpr int BKE = 128 / ES;                   // K elements per ring stage: one 128-byte swizzle row
+  constexpr int EC = 128 / ES;                    // output columns per epilogue sub-tile: 128-byte rows again
+  static_assert(!PULL || ES == 2, "the summing kernels exist for the 16-bit types only");
   const int tiles_n = (p.N + bn - 1) / bn;
   const int total_tiles = tiles_m * tiles_n;
-  const int kblocks = (p.K + BK - 1) / BK;
+  const int kblocks = (p.K + BKE - 1) / BKE;
   const int tiles_per_shard = p.ag ? (p.M / W) / TM : 0;
   const int chunks_per_shard = p.ag ? (p.M / W) / BM : 0;  // all-gather flags are per 128 rows
   // Two-shot: the rank that sums tile t.  A scheduling unit visits tiles u, u + G, u + 2G, ...; rotating the owner
@@ -367,7 +371,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
         const int wn = bn / w.nsub;                         // width of the piece
         const int col0 = tc.n_idx * bn + w.sub * wn;        // its first column = first row of B^T
         const int b_rows = wn / CG;                         // rows of B^T this CTA loads per k-block
-        const uint32_t stage_tx = (uint32_t)(kAStageBytes + b_rows * BK * 2);
+        const uint32_t stage_tx = (uint32_t)(kAStageBytes + b_rows * 128);  // 128-byte rows of K, whatever the type
         if (p.ag && row0 < p.M) {
           const int Ms = p.M / W;
           const int src = row0 / Ms;
@@ -396,14 +400,14 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
           const CUtensorMap* tm_b = w.nsub > 1 ? &p.tmBt[lr] : &p.tmB[lr];
           if (CG == 1) {
             mbar_expect_tx(full_bar(stage), stage_tx);
-            tma_load_2d(a_dst, &p.tmA[lr], kb * BK, row0, full_bar(stage));
-            tma_load_2d(b_dst, tm_b, kb * BK, col0, full_bar(stage));
+            tma_load_2d(a_dst, &p.tmA[lr], kb * BKE, row0, full_bar(stage));
+            tma_load_2d(b_dst, tm_b, kb * BKE, col0, full_bar(stage));
           } else {
             // Both CTAs' bytes are counted on the leader's barrier, which the leader arms for the pair.
             const uint32_t lead_full = mapa_shared(full_bar(stage), 0);
             if (leader) mbar_expect_tx(full_bar(stage), 2 * stage_tx);
-            tma_load_2d_pair(a_dst, &p.tmA[lr], kb * BK, row0, lead_full);
-            tma_load_2d_pair(b_dst, tm_b, kb * BK, col0 + pr * b_rows, lead_full);
+            tma_load_2d_pair(a_dst, &p.tmA[lr], kb * BKE, row0, lead_full);
+            tma_load_2d_pair(b_dst, tm_b, kb * BKE, col0 + pr * b_rows, lead_full);
           }
           ++fills;
           if (++stage == kStages) {
@@ -428,8 +432,11 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
     // ------------------------------------------------------------------------------------------
     if (lane == 0 && leader) {
       // instruction descriptors per piece width (bn, and bn / tail_split for the column pieces of tail tiles)
-      const uint32_t idesc_tile = umma_idesc_f16(TM, bn, !f16);
-      const uint32_t idesc_tail = umma_idesc_f16(TM, bn / (p.tail_split > 1 ? p.tail_split : 1), !f16);
+      auto idesc_for = [](int n) {
+        return ET == kTf32 ? umma_idesc_tf32(TM, n) : ET == kInt8 ? umma_idesc_s8(TM, n) : umma_idesc_f16(TM, n, !f16);
+      };
+      const uint32_t idesc_tile = idesc_for(bn);
+      const uint32_t idesc_tail = idesc_for(bn / (p.tail_split > 1 ? p.tail_split : 1));
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -463,8 +470,17 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
             const uint64_t a_desc = umma_desc_k_sw128(a_addr + k * UMMA_K * 2);
             const uint64_t b_desc = umma_desc_k_sw128(b_addr + k * UMMA_K * 2);
             const uint32_t accumulate = (kb > w.kb0 || k > 0) ? 1u : 0u;  // the first MMA of a piece overwrites
-            if (CG == 1) umma_f16_ss(d_tmem, a_desc, b_desc, idesc, accumulate);
-            else umma_f16_ss_pair(d_tmem, a_desc, b_desc, idesc, accumulate);
+            // every kind covers 32 bytes of K per instruction: 16 16-bit, 8 tf32 or 32 8-bit elements
+            if constexpr (ET == kTf32) {
+              if (CG == 1) umma_tf32_ss(d_tmem, a_desc, b_desc, idesc, accumulate);
+              else umma_tf32_ss_pair(d_tmem, a_desc, b_desc, idesc, accumulate);
+            } else if constexpr (ET == kInt8) {
+              if (CG == 1) umma_i8_ss(d_tmem, a_desc, b_desc, idesc, accumulate);
+              else umma_i8_ss_pair(d_tmem, a_desc, b_desc, idesc, accumulate);
+            } else {
+              if (CG == 1) umma_f16_ss(d_tmem, a_desc, b_desc, idesc, accumulate);
+              else umma_f16_ss_pair(d_tmem, a_desc, b_desc, idesc, accumulate);
+            }
           }
           // Free the ring slot (in both CTAs of a pair) once these MMAs have read it.
           if (CG == 1) {
@@ -570,7 +586,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
 
       const int wn = bn / w.nsub;                    // width of this piece: the tile, or a column piece of a tail tile
       const int ncol0 = tc.n_idx * bn + w.sub * wn;  // its first column inside this rank's N
-      const int nchunks = wn / kEpiCols;
+      const int nchunks = wn / EC;
       const int x_base = (pulls ? 0 : rank * p.col_off_per_rank) + ncol0;
       const int y = tc.m_idx * TM + pr * BM;
       // row inside the tmC matrix: partial buffer of this call's parity, inbox slot of (rank, piece) when pushing
@@ -624,7 +640,28 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
       }
 #pragma unroll 1
       for (int c = 0; c < nchunks; ++c) {
-        const bool live = ncol0 + c * kEpiCols < p.N && y < p.M;  // parts past the matrix edge are skipped
+        const bool live = ncol0 + c * EC < p.N && y < p.M;  // parts past the matrix edge are skipped
+        // o[0..32): this thread's 128 bytes of the sub-tile's row, as they go to shared memory
+        uint32_t o[32];
+        if constexpr (ES != 2) {
+          // 32-bit results are the accumulator's bits; 8-bit results are the low byte of each 32-bit sum, four to a word
+          const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN + c * EC;
+          if constexpr (ET == kTf32) {
+            tmem_ld_32x32b_x32(taddr, o);
+            tmem_wait_ld();
+          } else {
+#pragma unroll
+            for (int s4 = 0; s4 < 4; ++s4) {
+              uint32_t v[32];
+              tmem_ld_32x32b_x32(taddr + 32 * s4, v);
+              tmem_wait_ld();
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                o[8 * s4 + j] = (v[4 * j] & 0xffu) | ((v[4 * j + 1] & 0xffu) << 8) | ((v[4 * j + 2] & 0xffu) << 16) |
+                                (v[4 * j + 3] << 24);
+            }
+          }
+        } else {
         uint32_t v[kEpiCols];
         if (!whole) {
           // finishing a split tile: the sum of all pieces is in the workspace; read it and put zeros back
@@ -644,6 +681,9 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
         tmem_ld_32x32b_x32(taddr + 32, v + 32);
         tmem_wait_ld();
         }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) o[j] = pack2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]), f16);
+        }
         if (whole && c == nchunks - 1) {
           // The accumulator has been read completely: hand it back to the MMA warp (of the leader CTA).
           tc_fence_before();
@@ -660,20 +700,15 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
         named_barrier_sync(1, 128);
         const uint32_t sbase = epi_base + ebuf * kEpiStageBytes + row * 128;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const uint32_t a = pack2(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]), f16);
-          const uint32_t b = pack2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]), f16);
-          const uint32_t cc = pack2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]), f16);
-          const uint32_t d = pack2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]), f16);
-          st_shared_v4(sbase + ((j ^ (row & 7)) << 4), a, b, cc, d);  // 128-byte swizzle, as the tensor map expects
-        }
+        for (int j = 0; j < 8; ++j)  // 128-byte swizzle, as the tensor map expects
+          st_shared_v4(sbase + ((j ^ (row & 7)) << 4), o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
         if (!direct) fence_proxy_async_smem();
         named_barrier_sync(1, 128);
         if (direct) {
-          // Copy the staged 128 x 64 sub-tile out with 16-byte stores: 8 lanes cover one 128-byte row segment, a warp
+          // Copy the staged 128-row sub-tile (128 bytes per row) out with 16-byte stores: 8 lanes cover one 128-byte row segment, a warp
           // four rows.  Element (r, j) of the buffer sits at the swizzled position the staging loop wrote it to.
           const uint32_t src = epi_base + ebuf * kEpiStageBytes;
-          const int x = x_base + c * kEpiCols;
+          const int x = x_base + c * EC;
           uint4 vv[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
@@ -686,11 +721,11 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
           for (int i = 0; i < 8; ++i) {
             const int idx = i * 128 + et, r = idx >> 3, j = idx & 7;
             if (y + r < p.M) {
-              const uint64_t off = p.c_off + ((uint64_t)(y + r) * p.ldc + x + j * 8) * 2;
+              const uint64_t off = p.c_off + ((uint64_t)(y + r) * p.ldc + x) * ES + j * 16;
               if (push_kind == kPushMultimem) {
                 // one instruction, delivered (store) or added (reduce) by the switch on every rank's copy
                 void* mc = reinterpret_cast<void*>(p.mc_base + off);
-                if (p.mode == kEpiReduce) {
+                if (ES == 2 && p.mode == kEpiReduce) {
                   if (f16) nvls::red_add_f16x8(mc, vv[i]);
                   else nvls::red_add_bf16x8(mc, vv[i]);
                 } else {
@@ -704,7 +739,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
           }
         } else if (lead) {
           const uint32_t src = epi_base + ebuf * kEpiStageBytes;
-          const int x = x_base + c * kEpiCols;
+          const int x = x_base + c * EC;
           if (push_all) {
             for (int i = lead_idx; i < W; i += nlead) {  // peers first, starting with the next rank; own copy last
               const int t = (rank + 1 + i) % W;
@@ -1112,8 +1147,8 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
       const int ct = threadIdx.x - 192;
       const int Ms = p.M / W;
       const int S = p.ag_slices;
-      const int slice_elems = p.K / S;             // multiple of 8 (checked on the host)
-      const int vec_per_row = slice_elems / 8;     // 16-byte vectors per row of a slice
+      const int slice_elems = p.K / S;             // a multiple of 16 bytes (checked on the host)
+      const int vec_per_row = slice_elems * ES / 16;  // 16-byte vectors per row of a slice
       const int items = (W - 1) * chunks_per_shard * S;
       // Nothing is written into a peer's gathered A before that peer has entered this call, i.e. finished the
       // previous one: its producer may otherwise still be loading the rows of the previous call from that buffer.
@@ -1138,7 +1173,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
         const int slice = rem - chunk * S;
         const int peer = (rank - 1 - pi + 2 * W) % W;           // the peer that needs these rows earliest
         const int r0 = rank * Ms + chunk * BM;
-        const uint64_t base_off = p.agsrc_off + ((uint64_t)r0 * p.lda_full + (uint64_t)slice * slice_elems) * 2;
+        const uint64_t base_off = p.agsrc_off + ((uint64_t)r0 * p.lda_full + (uint64_t)slice * slice_elems) * ES;
         const uint8_t* src = reinterpret_cast<const uint8_t*>(p.heap_base[rank] + base_off);
         uint8_t* dst = reinterpret_cast<uint8_t*>(p.heap_base[peer] + base_off);
         const int nvec = BM * vec_per_row;
@@ -1150,7 +1185,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
             const int i = i0 + u * 64;
             if (i < nvec) {
               const int r = i / vec_per_row, cv = i - r * vec_per_row;
-              v[u] = ld_v4(reinterpret_cast<const uint4*>(src + ((uint64_t)r * p.lda_full) * 2 + cv * 16));
+              v[u] = ld_v4(reinterpret_cast<const uint4*>(src + ((uint64_t)r * p.lda_full) * ES + cv * 16));
             }
           }
 #pragma unroll
@@ -1158,7 +1193,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
             const int i = i0 + u * 64;
             if (i < nvec) {
               const int r = i / vec_per_row, cv = i - r * vec_per_row;
-              st_v4(reinterpret_cast<uint4*>(dst + ((uint64_t)r * p.lda_full) * 2 + cv * 16), v[u]);
+              st_v4(reinterpret_cast<uint4*>(dst + ((uint64_t)r * p.lda_full) * ES + cv * 16), v[u]);
             }
           }
         }
@@ -1211,25 +1246,29 @@ EncodeTiledFn encode_fn() {
   return g_encode;
 }
 
-// 16-bit matrix [rows, cols] (bf16, or fp16 with `f16`) with `ld` elements between rows; box = box_cols x box_rows;
+// Matrix [rows, cols] of element type `et` (an ElemType) with `ld` elements between rows; box = box_cols x box_rows;
 // 128-byte swizzle.
 int encode_2d(CUtensorMap* out, uint64_t ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_cols,
-              uint32_t box_rows, const char* what, bool f16 = false) {
+              uint32_t box_rows, const char* what, int et = kBf16) {
+  const uint64_t es = (uint64_t)elem_size(et);
+  const CUtensorMapDataType dt = et == kFp16   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                 : et == kTf32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                 : et == kInt8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                               : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   EncodeTiledFn fn = encode_fn();
   if (!fn) {
     snprintf(g_err, sizeof(g_err), "cuTensorMapEncodeTiled is not available");
     return -1;
   }
-  if (ptr % 16 != 0 || (ld * 2) % 16 != 0) {
+  if (ptr % 16 != 0 || (ld * es) % 16 != 0) {
     snprintf(g_err, sizeof(g_err), "%s: base address and row pitch must be multiples of 16 bytes", what);
     return -2;
   }
   cuuint64_t dims[2] = {cols, rows};
-  cuuint64_t strides[1] = {ld * 2};
+  cuuint64_t strides[1] = {ld * es};
   cuuint32_t box[2] = {box_cols, box_rows};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(out, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
-                  reinterpret_cast<void*>(ptr), dims, strides, box, estr,
+  CUresult r = fn(out, dt, 2, reinterpret_cast<void*>(ptr), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
@@ -1247,13 +1286,16 @@ using namespace iris::gemm;
 
 namespace {
 using KernelFn = void (*)(const FusedGemmParams);
-KernelFn kernel_for(int cta_group, bool pull, bool f16) {
-  if (f16) {
-    if (cta_group == 2) return pull ? fused_gemm_kernel<2, true, true> : fused_gemm_kernel<2, false, true>;
-    return pull ? fused_gemm_kernel<1, true, true> : fused_gemm_kernel<1, false, true>;
+// The summing (pull) kernels exist for the 16-bit types only; plan creation rejects the other combinations.
+KernelFn kernel_for(int cta_group, bool pull, int et) {
+  if (et == kTf32) return cta_group == 2 ? fused_gemm_kernel<2, false, kTf32> : fused_gemm_kernel<1, false, kTf32>;
+  if (et == kInt8) return cta_group == 2 ? fused_gemm_kernel<2, false, kInt8> : fused_gemm_kernel<1, false, kInt8>;
+  if (et == kFp16) {
+    if (cta_group == 2) return pull ? fused_gemm_kernel<2, true, kFp16> : fused_gemm_kernel<2, false, kFp16>;
+    return pull ? fused_gemm_kernel<1, true, kFp16> : fused_gemm_kernel<1, false, kFp16>;
   }
-  if (cta_group == 2) return pull ? fused_gemm_kernel<2, true, false> : fused_gemm_kernel<2, false, false>;
-  return pull ? fused_gemm_kernel<1, true, false> : fused_gemm_kernel<1, false, false>;
+  if (cta_group == 2) return pull ? fused_gemm_kernel<2, true, kBf16> : fused_gemm_kernel<2, false, kBf16>;
+  return pull ? fused_gemm_kernel<1, true, kBf16> : fused_gemm_kernel<1, false, kBf16>;
 }
 }  // namespace
 
@@ -1295,7 +1337,7 @@ struct IrisGemmDesc {
   int rs_rows;                 // reduce-scatter: rows kept per rank (0 = off); see FusedGemmParams::rs_rows
   int rs_bcast;                // with rs_rows: the keeper writes the summed rows to every rank's output (all-reduce)
   int bn;                      // tile width: 64, 128 or 256 (0 = 256)
-  int dtype;                   // ElemType: 0 = bf16, 1 = fp16
+  int dtype;                   // ElemType: 0 = bf16, 1 = fp16, 2 = fp32 as tf32, 3 = int8
   int push_kind;               // PushKind of the all-scatter epilogue
   int tail_tiles, tail_split;  // column-split tail of the raster (see tail_split_plan); 0 / 1 = off
   uint64_t c_off;              // symmetric offset of the C buffer (needed by push kinds 2 and 3)
@@ -1310,7 +1352,7 @@ struct IrisGemmPlan {
   int cta_group;
   int ctas_per_rank;
   int pull;
-  int f16;
+  int et;                      // ElemType of the launch
 };
 
 // The schedule arithmetic of the kernel, callable on the host (no device needed): see gemm_schedule.h.
@@ -1376,12 +1418,24 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
     snprintf(g_err, sizeof(g_err), "M, N, K must be positive");
     return nullptr;
   }
-  if (d->N % 8 != 0 || d->K % 8 != 0) {
-    snprintf(g_err, sizeof(g_err), "N and K must be multiples of 8 (16-byte rows)");
+  if (d->dtype < kBf16 || d->dtype > kInt8) {
+    snprintf(g_err, sizeof(g_err), "element type must be bf16 (0), fp16 (1), fp32 multiplied as tf32 (2) or int8 (3)");
     return nullptr;
   }
-  if (d->world > 1 && d->store_all && d->N % kEpiCols != 0) {
-    snprintf(g_err, sizeof(g_err), "N per rank must be a multiple of %d when tiles are pushed to peers", kEpiCols);
+  const int et = d->dtype;
+  const int es = elem_size(et);
+  const int epi_cols = 128 / es;  // columns of an epilogue sub-tile (128-byte rows)
+  if ((d->N * es) % 16 != 0 || (d->K * es) % 16 != 0) {
+    snprintf(g_err, sizeof(g_err), "rows of N and of K elements must be multiples of 16 bytes");
+    return nullptr;
+  }
+  if (d->world > 1 && d->store_all && d->N % epi_cols != 0) {
+    snprintf(g_err, sizeof(g_err), "N per rank must be a multiple of %d when tiles are pushed to peers", epi_cols);
+    return nullptr;
+  }
+  if (es != 2 && (d->mode != kEpiStore || d->sk_units > 0 || d->ksplit > 1)) {
+    snprintf(g_err, sizeof(g_err), "fp32 and int8 matrices: store mode with whole tiles only (plain GEMM, all-scatter, "
+                                   "all-gather prologue)");
     return nullptr;
   }
   const int cg = d->cta_group == 2 ? 2 : 1;
@@ -1390,18 +1444,17 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
     snprintf(g_err, sizeof(g_err), "tile width must be 64, 128 or 256 columns");
     return nullptr;
   }
-  if (d->dtype != kBf16 && d->dtype != kFp16) {
-    snprintf(g_err, sizeof(g_err), "element type must be bf16 (0) or fp16 (1)");
+  if (bn % epi_cols != 0) {
+    snprintf(g_err, sizeof(g_err), "tile width must be a multiple of %d columns for this element type", epi_cols);
     return nullptr;
   }
-  const bool f16 = d->dtype == kFp16;
   const int tail_split = d->tail_tiles > 0 && d->tail_split > 1 ? d->tail_split : 1;
   const int tail_tiles = tail_split > 1 ? d->tail_tiles : 0;
   if (tail_split > 1) {
     const bool plain = (d->mode == kEpiStore || d->mode == kEpiReduce) && d->sk_units <= 0 && d->ksplit <= 1;
-    if (!plain || bn % tail_split != 0 || (bn / tail_split) % kEpiCols != 0 || ((bn / tail_split) / cg) % 8 != 0) {
+    if (!plain || bn % tail_split != 0 || (bn / tail_split) % epi_cols != 0 || ((bn / tail_split) / cg) % 8 != 0) {
       snprintf(g_err, sizeof(g_err), "a column-split tail needs store / reduce mode, whole tiles and pieces of whole "
-                                     "%d-column sub-tiles", kEpiCols);
+                                     "%d-column sub-tiles", epi_cols);
       return nullptr;
     }
   }
@@ -1443,8 +1496,8 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
       snprintf(g_err, sizeof(g_err), "all-gather prologue needs M / world to be a multiple of %d", BM * cg);
       return nullptr;
     }
-    if (d->ag_slices < 1 || d->K % d->ag_slices != 0 || (d->K / d->ag_slices) % 8 != 0) {
-      snprintf(g_err, sizeof(g_err), "ag_slices must divide K into multiples of 8 elements");
+    if (d->ag_slices < 1 || d->K % d->ag_slices != 0 || (d->K / d->ag_slices * es) % 16 != 0) {
+      snprintf(g_err, sizeof(g_err), "ag_slices must divide the rows of K elements into multiples of 16 bytes");
       return nullptr;
     }
   }
@@ -1456,7 +1509,7 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
   const uint32_t c_box_rows = d->M >= BM ? BM : (uint32_t)((d->M + 7) / 8 * 8);
   int ctas_per_rank = d->ctas_per_rank - d->ctas_per_rank % cg;
   {
-    cudaError_t e = cudaFuncSetAttribute(kernel_for(cg, pull, f16),
+    cudaError_t e = cudaFuncSetAttribute(kernel_for(cg, pull, et),
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) {
       snprintf(g_err, sizeof(g_err), "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
@@ -1477,7 +1530,7 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     int max_clusters = 0;
-    cudaError_t e = cudaOccupancyMaxActiveClusters(&max_clusters, kernel_for(2, pull, f16), &cfg);
+    cudaError_t e = cudaOccupancyMaxActiveClusters(&max_clusters, kernel_for(2, pull, et), &cfg);
     if (e != cudaSuccess || max_clusters < d->num_local) {
       snprintf(g_err, sizeof(g_err), "CTA pairs cannot be scheduled (%s, %d clusters)", cudaGetErrorString(e),
                max_clusters);
@@ -1500,15 +1553,16 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
   plan->device = d->device;
   plan->cta_group = cg;
   plan->pull = pull ? 1 : 0;
-  plan->f16 = f16 ? 1 : 0;
+  plan->et = et;
   plan->ctas_per_rank = ctas_per_rank;
   for (int par = 0; par < 2; ++par) {
     FusedGemmParams& p = plan->params[par];
     for (int l = 0; l < d->num_local; ++l) {
-      if (encode_2d(&p.tmA[l], d->a_ptr[l], d->M, d->K, d->lda[l], BK, BM, "A", f16) ||
-          encode_2d(&p.tmB[l], d->b_ptr[l], d->N, d->K, d->ldb[l], BK, bn / cg, "B", f16) ||
+      const uint32_t bk = 128 / es;  // K elements of one ring stage: 128 bytes
+      if (encode_2d(&p.tmA[l], d->a_ptr[l], d->M, d->K, d->lda[l], bk, BM, "A", et) ||
+          encode_2d(&p.tmB[l], d->b_ptr[l], d->N, d->K, d->ldb[l], bk, bn / cg, "B", et) ||
           (tail_split > 1 &&
-           encode_2d(&p.tmBt[l], d->b_ptr[l], d->N, d->K, d->ldb[l], BK, (bn / tail_split) / cg, "B (tail)", f16))) {
+           encode_2d(&p.tmBt[l], d->b_ptr[l], d->N, d->K, d->ldb[l], bk, (bn / tail_split) / cg, "B (tail)", et))) {
         delete plan;
         return nullptr;
       }
@@ -1516,8 +1570,8 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
     for (int t = 0; t < d->world; ++t) {
       const uint64_t cp = (par == 1 && d->c2_ptr[t]) ? d->c2_ptr[t] : d->c_ptr[t];
       if (!cp) continue;
-      if (encode_2d(&p.tmC[t], cp, d->c_rows > 0 ? d->c_rows : d->M, d->c_cols, d->ldc, kEpiCols, c_box_rows, "C",
-                    f16)) {
+      if (encode_2d(&p.tmC[t], cp, d->c_rows > 0 ? d->c_rows : d->M, d->c_cols, d->ldc, epi_cols, c_box_rows, "C",
+                    et)) {
         delete plan;
         return nullptr;
       }
@@ -1610,21 +1664,21 @@ int iris_gemm_plan_launch(void* h, int parity, uint32_t epoch, uint32_t flag_tar
     // Ranks simulated on one GPU wait on one another: ask for a cooperative launch on top of the clusters.
     cfg.numAttrs = plan->cooperative ? 2 : 1;
     void* kargs[] = {&p};
-    e = cudaLaunchKernelExC(&cfg, reinterpret_cast<const void*>(kernel_for(2, plan->pull != 0, plan->f16 != 0)), kargs);
+    e = cudaLaunchKernelExC(&cfg, reinterpret_cast<const void*>(kernel_for(2, plan->pull != 0, plan->et)), kargs);
     if (e != cudaSuccess && plan->cooperative) {
       // Cooperative + cluster launches are not accepted everywhere; the grid was sized by
       // cudaOccupancyMaxActiveClusters, so all pairs are resident on an otherwise idle GPU.
       (void)cudaGetLastError();
       cfg.numAttrs = 1;
-      e = cudaLaunchKernelExC(&cfg, reinterpret_cast<const void*>(kernel_for(2, plan->pull != 0, plan->f16 != 0)), kargs);
+      e = cudaLaunchKernelExC(&cfg, reinterpret_cast<const void*>(kernel_for(2, plan->pull != 0, plan->et)), kargs);
     }
   } else if (plan->cooperative) {
     void* args[] = {&p};
-    e = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(kernel_for(1, plan->pull != 0, plan->f16 != 0)), dim3(plan->grid),
+    e = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(kernel_for(1, plan->pull != 0, plan->et)), dim3(plan->grid),
                                     dim3(plan->pull ? kThreadsPull : kThreads), args, kSmemBytes, st);
   } else {
     void* args[] = {&p};
-    e = cudaLaunchKernel(reinterpret_cast<void*>(kernel_for(1, plan->pull != 0, plan->f16 != 0)), dim3(plan->grid),
+    e = cudaLaunchKernel(reinterpret_cast<void*>(kernel_for(1, plan->pull != 0, plan->et)), dim3(plan->grid),
                          dim3(plan->pull ? kThreadsPull : kThreads), args, kSmemBytes, st);
   }
   if (e != cudaSuccess) {

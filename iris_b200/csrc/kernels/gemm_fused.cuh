@@ -51,8 +51,12 @@ enum PushKind : int {
   kPushMultimem = 3,  // as kPushStores, but ONE multimem.st per 16 bytes: the NVLink switch delivers it to every rank
 };
 
-// Element type of A, B and C (accumulation is always fp32).
-enum ElemType : int { kBf16 = 0, kFp16 = 1 };
+// Element type of A, B and C.  bf16 / fp16: fp32 accumulation.  kTf32: fp32 matrices, multiplied as tf32 (10-bit
+// mantissa) with fp32 accumulation.  kInt8: signed 8-bit matrices, 32-bit integer accumulation, and the low 8 bits
+// of the sum as the result (two's-complement wrap, what a cast of the accumulator to int8 gives).  The 32- and 8-bit
+// types exist for the store mode only (plain GEMM, GEMM + all-scatter, all-gather + GEMM).
+enum ElemType : int { kBf16 = 0, kFp16 = 1, kTf32 = 2, kInt8 = 3 };
+__host__ __device__ constexpr int elem_size(int et) { return et == kTf32 ? 4 : et == kInt8 ? 1 : 2; }
 
 enum EpiMode : int {
   kEpiStore = 0,    // C tile -> TMA store into the C buffer of every rank (world 1: plain GEMM)

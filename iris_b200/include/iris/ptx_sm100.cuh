@@ -179,6 +179,16 @@ __host__ __device__ constexpr uint32_t umma_idesc_f16(int m, int n, bool bf16) {
   return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | ((uint32_t)(n >> 3) << 17) |
          ((uint32_t)(m >> 4) << 24);
 }
+// Instruction descriptors of the other operand kinds (same field layout: accumulator format at bit 4, A format at
+// bit 7, B format at bit 10, N / 8 at bit 17, M / 16 at bit 24; both operands K-major).
+//   kind::tf32: fp32 operands read as tf32 (format 2), fp32 accumulator (1); one MMA covers K = 8.
+//   kind::i8:   signed 8-bit operands (format 1), 32-bit integer accumulator (2); one MMA covers K = 32.
+__host__ __device__ constexpr uint32_t umma_idesc_tf32(int m, int n) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+__host__ __device__ constexpr uint32_t umma_idesc_s8(int m, int n) {
+  return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
 // Shared-memory matrix descriptor of an MN-major operand tile (the MN dimension contiguous, e.g. V[key][d] used as
 // the B operand of P * V with N = d) stored by TMA with the 128-byte swizzle: a row of the K dimension holds 64
 // 16-bit MN elements (128 bytes), rows are 128 bytes apart, groups of 8 K rows are `sbo_bytes` apart (1024 when the
@@ -206,6 +216,17 @@ __device__ __forceinline__ void umma_f16_ss(uint32_t d_tmem, uint64_t a_desc, ui
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+#define IRIS_UMMA_SS(NAME, KIND)                                                                              \
+  __device__ __forceinline__ void NAME(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,        \
+                                       uint32_t accumulate) {                                                   \
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"                                             \
+                 "tcgen05.mma.cta_group::1.kind::" KIND " [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),              \
+                 "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)                                          \
+                 : "memory");                                                                                   \
+  }
+IRIS_UMMA_SS(umma_tf32_ss, "tf32")
+IRIS_UMMA_SS(umma_i8_ss, "i8")
+#undef IRIS_UMMA_SS
 // Arrive once on `bar` when every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -263,6 +284,18 @@ __device__ __forceinline__ void umma_f16_ss_pair(uint32_t d_tmem, uint64_t a_des
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
       : "memory");
 }
+#define IRIS_UMMA_SS_PAIR(NAME, KIND)                                                                         \
+  __device__ __forceinline__ void NAME(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,        \
+                                       uint32_t accumulate) {                                                   \
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"                                             \
+                 "tcgen05.mma.cta_group::2.kind::" KIND                                                         \
+                 " [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}" ::"r"(d_tmem),                   \
+                 "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)                                 \
+                 : "memory");                                                                                   \
+  }
+IRIS_UMMA_SS_PAIR(umma_tf32_ss_pair, "tf32")
+IRIS_UMMA_SS_PAIR(umma_i8_ss_pair, "i8")
+#undef IRIS_UMMA_SS_PAIR
 // Arrive once on the mbarrier at `bar_cluster_addr` (either CTA of the pair) when the pair's MMAs issued so
 // far have completed.
 __device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {

@@ -78,17 +78,17 @@ def _lib():
     return lib
 
 
-_TORCH_DTYPES = {torch.bfloat16: "bf16", torch.float16: "fp16"}
+_TORCH_DTYPES = {torch.bfloat16: "bf16", torch.float16: "fp16", torch.float32: "fp32", torch.int8: "int8"}
 
 
 def _check_operand(t: torch.Tensor, name: str, dtype: Optional[torch.dtype] = None):
     if t.dtype not in _TORCH_DTYPES:
-        raise TypeError(f"{name} must be bfloat16 or float16, got {t.dtype}")
+        raise TypeError(f"{name} must be bfloat16, float16, float32 or int8, got {t.dtype}")
     if dtype is not None and t.dtype != dtype:
         raise TypeError(f"{name} is {t.dtype}, the other operands are {dtype}")
     if t.dim() != 2 or t.stride(1) != 1:
         raise ValueError(f"{name} must be 2-D with a contiguous last dimension (K-major)")
-    if t.data_ptr() % 16 or (t.stride(0) * 2) % 16:
+    if t.data_ptr() % 16 or (t.stride(0) * t.element_size()) % 16:
         raise ValueError(f"{name}: base address and row pitch must be multiples of 16 bytes")
 
 
@@ -137,8 +137,11 @@ class FusedGemm:
             bytes on a heap bound to an NVLS multicast object: the switch delivers it to every rank).  ``None``:
             ``DEFAULT_PUSH_KIND``.
 
-    The element type (bf16 or fp16, fp32 accumulation) is taken from ``bt``; the reference's drivers offer
-    ``--datatype fp16|bf16|...`` (``examples/07_gemm_all_scatter/benchmark.py:36-41``).
+    The element type is taken from ``bt``: bf16 or fp16 (fp32 accumulation) for every mode; float32 (multiplied as
+    tf32, fp32 accumulation) and int8 (32-bit integer accumulation, the low 8 bits of the sum as the result, which is
+    what the reference's kernel stores when it casts its int32 accumulator to the output type) for mode ``"store"``:
+    plain GEMM, GEMM + all-scatter and all-gather + GEMM.  The reference's drivers offer
+    ``--datatype fp16|fp32|int8|bf16`` (``examples/07_gemm_all_scatter/benchmark.py:36-41``).
     """
 
     def __init__(self, ctxs: Union[Iris, Sequence[Iris]], a: Optional[Sequence[torch.Tensor]],
@@ -196,7 +199,7 @@ class FusedGemm:
         pl = plan_gemm(self.M, self.N, self.K, self.world, self.num_local, mode, sms, ag=self.ag, cta_group=cta_group,
                        ctas_per_rank=ctas_per_rank, group_m=group_m, stream_k=stream_k, push=push, ksplit=ksplit,
                        reduce_scatter=reduce_scatter, store_all=store_all, own_out=out is not None, bn=bn,
-                       tail_split=tail_split, bcast=bcast)
+                       tail_split=tail_split, bcast=bcast, dtype=_TORCH_DTYPES[self.dtype])
         self.plan = pl
         cta_group, group_m = pl.cta_group, pl.group_m
         self.cta_group, self.rs_rows, self.ctas_per_rank = pl.cta_group, pl.rs_rows, pl.ctas_per_rank
@@ -285,7 +288,7 @@ class FusedGemm:
         d.c_off = c_off if self.store_all else 0
         # atomic all-reduce of a short matrix: the kernel clears the output itself (one launch less); a large output
         # is cleared faster by a launch of its own than by CTAs that should already be loading operands
-        out_bytes = self.out[0].shape[0] * self.out[0].stride(0) * 2
+        out_bytes = self.out[0].shape[0] * self.out[0].stride(0) * self.out[0].element_size()
         self._zero_in_kernel = (mode == "reduce" and self.store_all and out is None
                                 and self.out[0].is_contiguous() and out_bytes <= ZERO_IN_KERNEL_MAX_BYTES)
         d.zero_bytes = out_bytes if self._zero_in_kernel else 0
@@ -378,7 +381,7 @@ class FusedGemm:
         from .. import _build
         pull = self.mode in ("one_shot", "two_shot")
         want = (f"fused_gemm_kernel<{self.cta_group}, {'true' if pull else 'false'}, "
-                f"{'true' if self.dtype == torch.float16 else 'false'}>")
+                f"{DTYPES[_TORCH_DTYPES[self.dtype]]}>")
         for name, res in _build.kernel_resources().items():
             if want in name:
                 return dict(res, kernel=want)
@@ -489,7 +492,8 @@ _private_ctx = {}
 
 def gemm(a: torch.Tensor, bt: torch.Tensor, out: Optional[torch.Tensor] = None,
          cta_group: Optional[int] = None, bn: Optional[int] = None, tail_split: Optional[bool] = None) -> torch.Tensor:
-    """Single-GPU ``a @ bt.T`` on the tcgen05 kernel (world of one, no communication); bf16 or fp16."""
+    """Single-GPU ``a @ bt.T`` on the tcgen05 kernel (world of one, no communication): bf16, fp16, float32 (as tf32)
+    or int8 (the low 8 bits of the integer sums)."""
     dev = a.device
     ctx = _private_ctx.get(dev)
     if ctx is None:

@@ -13,7 +13,8 @@ BM, BN, BK = 128, 256, 64   # rows per CTA, widest tile in columns, k-block; the
 TILE_WIDTHS = (64, 128, 256)
 MODES = {"store": 0, "reduce": 1, "one_shot": 2, "two_shot": 3}
 PUSH_KINDS = {"tma": 0, "tma_spread": 1, "stores": 2, "multimem": 3}
-DTYPES = {"bf16": 0, "fp16": 1}
+DTYPES = {"bf16": 0, "fp16": 1, "fp32": 2, "int8": 3}   # ElemType of the kernel; fp32 is multiplied as tf32
+ELEM_BYTES = {"bf16": 2, "fp16": 2, "fp32": 4, "int8": 1}
 FLAG_HEADER = 16            # flag words [0] arrival counter, [8 + r] entry flag of rank r; per-tile flags follow
 
 
@@ -85,18 +86,29 @@ def plan_gemm(M: int, N: int, K: int, world: int, num_local: int, mode: str, sms
               cta_group: Optional[int] = None, ctas_per_rank: Optional[int] = None, group_m: Optional[int] = 8,
               stream_k: Optional[bool] = None, push: Optional[bool] = None, ksplit: Optional[int] = None,
               reduce_scatter: bool = False, store_all: bool = False, own_out: bool = False,
-              bn: Optional[int] = None, tail_split: Optional[bool] = None, bcast: bool = False) -> GemmPlan:
+              bn: Optional[int] = None, tail_split: Optional[bool] = None, bcast: bool = False,
+              dtype: str = "bf16") -> GemmPlan:
     """Decide tile shape, persistent grid, schedule, flag count and buffer layout.  ``sms``: SMs of the device;
     ``own_out``: the caller brings the output buffer (the [partials | out] matrix then has no output region);
     ``bn``: tile width (64, 128 or 256; default 256); ``tail_split``: cut the tiles of a ragged last wave into column
     pieces: ``True`` = into two, an integer = into at most that many (store / reduce modes with whole tiles; default
     off: measured on the 8192 x 14336 x 4096 problem the narrower pieces re-read A and lose more than the ragged wave
-    costs)."""
+    costs); ``dtype``: element type of A, B and C (``DTYPES``); the 32- and 8-bit types exist for mode ``"store"``
+    with whole tiles, and their tiles are a multiple of 32 / 128 columns wide (one 128-byte row of output per
+    sub-tile)."""
     if mode not in MODES:
         raise ValueError(f"mode must be one of {sorted(MODES)}")
     bn = BN if bn is None else int(bn)
     if bn not in TILE_WIDTHS:
         raise ValueError(f"tile width must be one of {TILE_WIDTHS}")
+    if dtype not in DTYPES:
+        raise ValueError(f"dtype must be one of {sorted(DTYPES)}")
+    es = ELEM_BYTES[dtype]
+    sub_cols = 128 // es                     # output columns of one epilogue sub-tile; also K elements per ring stage
+    if bn % sub_cols:
+        raise ValueError(f"{dtype}: the tile width must be a multiple of {sub_cols} columns")
+    if es != 2 and (mode != "store" or stream_k or reduce_scatter or (ksplit or 1) > 1):
+        raise ValueError(f"{dtype} matrices: mode 'store' with whole tiles only (plain GEMM, all-scatter, all-gather)")
     if mode in ("one_shot", "two_shot") and ag:
         raise ValueError("the all-gather prologue is combined with mode='store' only")
     # CTA pairs (256-row tiles, cta_group::2) or single CTAs (128-row tiles).  Measured on 8192 x N x 4096: the pair
@@ -129,7 +141,7 @@ def plan_gemm(M: int, N: int, K: int, world: int, num_local: int, mode: str, sms
     ctas -= ctas % cta_group
     tiles_m, tiles_n = -(-M // (BM * cta_group)), -(-N // bn)
     T = tiles_m * tiles_n
-    kblocks = -(-K // BK)
+    kblocks = -(-K // sub_cols)
     # ---- schedule: whole tiles round-robin, plus (stream-K) a tail of tiles split by k-blocks ----
     units = max(1, ctas // cta_group)
     if stream_k is None:
@@ -173,7 +185,7 @@ def plan_gemm(M: int, N: int, K: int, world: int, num_local: int, mode: str, sms
     # ---- ragged last wave of a whole-tile schedule: cut its tiles into column pieces (nothing to fix up) ----
     tail_tiles, tsplit = 0, 1
     if tail_split and not pulls and not sk_units and ks == 1:
-        max_split = min(int(tail_split) if tail_split > 1 else 2, bn // 64)   # pieces are whole 64-column sub-tiles
+        max_split = min(int(tail_split) if tail_split > 1 else 2, bn // sub_cols)   # pieces are whole sub-tiles
         while max_split > 1 and ((bn // max_split) // cta_group) % 8:
             max_split //= 2
         tail_tiles, tsplit = tail_split_plan(T, max(1, ctas // cta_group), max_split)

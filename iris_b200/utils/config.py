@@ -66,18 +66,22 @@ class GemmPoint:
         w, out = self.world, []
         if self.workload not in WORKLOADS:
             return [f"unknown workload {self.workload!r}"]
-        if self.dtype not in ("bf16", "fp16"):
-            out.append("the element type must be bf16 or fp16")
+        if self.dtype not in ("bf16", "fp16", "fp32", "int8"):
+            out.append("the element type must be bf16, fp16, fp32 or int8")
+        elif self.dtype in ("fp32", "int8") and self.workload != "all_scatter":
+            out.append("fp32 and int8 are offered by the all-scatter kernel only")
         if min(self.m, self.n, self.k, w) < 1 or w > 8:
             out.append("m, n, k must be positive and 1 <= world <= 8")
             return out
+        es = {"fp32": 4, "int8": 1}.get(self.dtype, 2)
+        sub, vec = 128 // es, 16 // es      # columns of a 128-byte sub-tile row, elements of a 16-byte vector
         if self.workload == "all_scatter":
             if self.n % w:
                 out.append("N must divide by the number of ranks")
-            elif (self.n // w) % (64 if w > 1 else 8):
-                out.append("N per rank must be a multiple of 64 (8 on one rank)")
-            if self.k % 8:
-                out.append("K must be a multiple of 8")
+            elif (self.n // w) % (sub if w > 1 else vec):
+                out.append(f"N per rank must be a multiple of {sub} ({vec} on one rank)")
+            if self.k % vec:
+                out.append(f"K must be a multiple of {vec}")
         else:
             if self.k % w or (self.k // w) % 8:
                 out.append("K per rank must be a multiple of 8")

@@ -44,10 +44,16 @@ def gemm_flops(m: int, n: int, k: int) -> float:
     return 2.0 * m * n * k
 
 
-def all_scatter_roofline_us(m, n, k, world, peaks: Peaks) -> dict:
+# Tensor-core rate of an element type relative to bf16 (nominal ratios of the dense peaks: tf32 half, int8 twice), and
+# bytes per element.  Only the bf16 rate is measured on this hardware; the others are that figure scaled.
+DTYPE_RATE = {"bf16": 1.0, "fp16": 1.0, "fp32": 0.5, "int8": 2.0}
+DTYPE_BYTES = {"bf16": 2, "fp16": 2, "fp32": 4, "int8": 1}
+
+
+def all_scatter_roofline_us(m, n, k, world, peaks: Peaks, dtype: str = "bf16") -> dict:
     """C[m, n] = A[m, k] B[k, n], B column-sharded: each rank computes m*n/world outputs and receives the rest."""
-    compute = gemm_flops(m, n // world, k) / (peaks.bf16_tflops * 1e12) * 1e6
-    ingress = (world - 1) * m * (n // world) * 2
+    compute = gemm_flops(m, n // world, k) / (peaks.bf16_tflops * DTYPE_RATE[dtype] * 1e12) * 1e6
+    ingress = (world - 1) * m * (n // world) * DTYPE_BYTES[dtype]
     link = ingress / (peaks.nvlink_gbs * 1e9) * 1e6
     return {"compute_us": compute, "link_us": link, "bound": "compute" if compute >= link else "link",
             "target_us": max(compute, link)}

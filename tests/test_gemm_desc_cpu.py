@@ -218,3 +218,25 @@ def test_auto_variant_table():
     assert G.auto_all_reduce_variant(1, 2)[0] == "atomic" and G.auto_all_reduce_variant(1, 2)[1]["ksplit"] == 8
     assert G.auto_all_reduce_variant(1024, 2)[0] == "one_shot"
     assert G.auto_all_reduce_variant(8192, 8)[0] == "two_shot" and G.auto_all_reduce_variant(1024, 4)[0] == "two_shot"
+
+
+def test_planner_element_types():
+    """K slices and epilogue sub-tiles are 128 bytes whatever the element: 64 / 32 / 128 elements for 16- / 32- / 8-bit
+    types; the 32- and 8-bit types are store-mode only."""
+    kw = dict(world=1, num_local=1, mode="store", sms=148)
+    assert plan_gemm(1024, 1024, 4096, dtype="bf16", **kw).kblocks == 64
+    assert plan_gemm(1024, 1024, 4096, dtype="fp32", **kw).kblocks == 128
+    assert plan_gemm(1024, 1024, 4096, dtype="int8", **kw).kblocks == 32
+    assert plan_gemm(1024, 1024, 4096, dtype="fp32", bn=64, **kw).bn == 64
+    with pytest.raises(ValueError):
+        plan_gemm(1024, 1024, 4096, dtype="int8", bn=64, **kw)
+    for bad in (dict(mode="reduce"), dict(mode="one_shot"), dict(mode="two_shot"), dict(stream_k=True)):
+        args = dict(kw)
+        args.update(bad)
+        with pytest.raises(ValueError):
+            plan_gemm(1024, 1024, 4096, dtype="int8", **args)
+    with pytest.raises(ValueError):
+        plan_gemm(1024, 1024, 4096, dtype="fp64", **kw)
+    # a tail piece is a whole number of sub-tiles: int8 tiles of 256 columns split into two at most
+    p = plan_gemm(2560, 2048, 256, dtype="int8", tail_split=4, ctas_per_rank=148, cta_group=1, **kw)
+    assert p.tail_split in (1, 2)

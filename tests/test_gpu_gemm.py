@@ -55,6 +55,108 @@ def test_gemm_tile_widths_and_element_types(m, n, k, cta_group, bn, dtype):
     _assert_close(out, a.float() @ bt.float().t())
 
 
+def _int8_rand(shape, seed):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return torch.randint(-128, 128, shape, generator=g, device="cuda", dtype=torch.int32).to(torch.int8)
+
+
+def _int8_ref(a, bt):
+    """The low 8 bits of the exact integer product (int8 operands, sums far below 2^53: exact in float64)."""
+    full = (a.double() @ bt.double().t()).to(torch.int64)
+    return (((full + 128) % 256) - 128).to(torch.int8)
+
+
+@pytest.mark.parametrize("bn", [64, 128, 256])
+@pytest.mark.parametrize("m,n,k,cta_group", [(384, 832, 192, 1), (1000, 520, 1376, 2), (100, 1024, 516, 1),
+                                             (2048, 1792, 2048, 2)])
+def test_gemm_fp32_as_tf32(m, n, k, cta_group, bn):
+    """float32 matrices multiplied on the tensor cores as tf32 (10-bit mantissa, fp32 accumulation), fp32 result:
+    32-element K slices and 32-column epilogue sub-tiles.  Bound: two tf32 roundings per product (2^-10 relative)."""
+    a, bt = _rand((m, k), 1, dtype=torch.float32), _rand((n, k), 2, 0.05, dtype=torch.float32)
+    out = G.gemm(a, bt, cta_group=cta_group, bn=bn)
+    torch.cuda.synchronize()
+    assert out.dtype == torch.float32
+    ref = a.double() @ bt.double().t()
+    scale = a.double().abs() @ bt.double().abs().t()      # what the operand roundings act on
+    err = (out.double() - ref).abs()
+    bad = err > 2.0 ** -9 * scale + 1e-6
+    assert not bool(bad.any()), f"{int(bad.sum())} mismatches, max err {err.max().item():.4g}"
+    # and it is a tensor-core product, not an fp32 one: the error is visible at fp32 resolution for long K
+    if k >= 1024:
+        assert err.max().item() > 0
+
+
+@pytest.mark.parametrize("bn", [128, 256])
+@pytest.mark.parametrize("m,n,k,cta_group", [(384, 896, 192, 1), (1000, 528, 1376, 2), (100, 1024, 512, 1),
+                                             (2048, 1792, 4096, 2)])
+def test_gemm_int8(m, n, k, cta_group, bn):
+    """int8 matrices, 32-bit integer accumulation, int8 result = the low 8 bits of the sum: exact."""
+    a, bt = _int8_rand((m, k), 1), _int8_rand((n, k), 2)
+    out = G.gemm(a, bt, cta_group=cta_group, bn=bn)
+    torch.cuda.synchronize()
+    assert out.dtype == torch.int8
+    assert torch.equal(out, _int8_ref(a, bt))
+
+
+@pytest.mark.parametrize("push_kind", ["tma", "tma_spread", "stores"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.int8])
+def test_all_scatter_and_all_gather_fp32_int8(dtype, push_kind):
+    """GEMM + all-scatter and all-gather + GEMM with 32- and 8-bit elements (two ranks in one cooperative launch)."""
+    world, m, n_local, k = 2, 1024, 640, 512
+    ranks = iris.Iris.local_world(world, heap_size=128 << 20)
+    if dtype == torch.int8:
+        a = _int8_rand((m, k), 5)
+        bts = [_int8_rand((n_local, k), 10 + r) for r in range(world)]
+        refs = [_int8_ref(a, b) for b in bts]
+        same = [lambda got, want=want: torch.equal(got, want) for want in refs]
+    else:
+        a = _rand((m, k), 5, dtype=dtype)
+        bts = [_rand((n_local, k), 10 + r, 0.05, dtype=dtype) for r in range(world)]
+        refs = [a.double() @ b.double().t() for b in bts]
+        tols = [2.0 ** -9 * (a.double().abs() @ b.double().abs().t()) + 1e-6 for b in bts]
+        same = [lambda got, want=want, tol=tol: bool(((got.double() - want).abs() <= tol).all())
+                for want, tol in zip(refs, tols)]
+    op = G.gemm_all_scatter(ranks, [a] * world, bts, push_kind=push_kind)
+    for _ in range(3):
+        outs = op()
+    op.check()
+    for r in range(world):
+        assert outs[r].dtype == dtype
+        for q in range(world):       # rank q's column block, as it arrived on rank r
+            assert same[q](outs[r][:, q * n_local:(q + 1) * n_local]), (r, q)
+    op.close()
+    # all-gather prologue: every rank brings m / world rows of A, multiplies all m rows with its own B
+    ag = G.all_gather_gemm(ranks, m, bts)
+    ms = m // world
+    for r in range(world):
+        ag.a_full[r][r * ms:(r + 1) * ms].copy_(a[r * ms:(r + 1) * ms])
+    for _ in range(2):
+        outs = ag()
+    ag.check()
+    for r in range(world):
+        assert same[r](outs[r]), r
+    ag.close()
+    ranks[0].close()
+
+
+def test_fp32_int8_rejections():
+    """The 32- and 8-bit types exist for the store mode with whole tiles; int8 tiles are 128 or 256 columns wide."""
+    ctx = iris.Iris.local_world(1, heap_size=32 << 20)[0]
+    a8, b8 = _int8_rand((256, 256), 1), _int8_rand((256, 256), 2)
+    with pytest.raises(ValueError):
+        G.FusedGemm(ctx, [a8], [b8], "store", bn=64)
+    with pytest.raises(ValueError):
+        G.FusedGemm(ctx, [a8], [b8], "reduce")
+    af, bf = _rand((256, 256), 1, dtype=torch.float32), _rand((256, 256), 2, dtype=torch.float32)
+    with pytest.raises(ValueError):
+        G.FusedGemm(ctx, [af], [bf], "one_shot")
+    with pytest.raises(ValueError):
+        G.FusedGemm(ctx, [af], [bf], "store", stream_k=True)
+    with pytest.raises(TypeError):
+        G.FusedGemm(ctx, [af], [b8], "store")
+    ctx.close()
+
+
 @pytest.mark.parametrize("bn", [128, 256])
 @pytest.mark.parametrize("m,n,k,cta_group", [(2560, 2048, 256, 2), (2560, 2048, 256, 1), (2816, 1800, 320, 2)])
 def test_column_split_tail(m, n, k, cta_group, bn):

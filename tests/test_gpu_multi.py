@@ -56,6 +56,11 @@ EX = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "
     ("07_gemm_all_scatter/benchmark.py", ["-m", "1024", "-n", "2048", "-k", "512", "-v", "-b", "--num_experiments", "3",
                                           "--num_warmup", "1", "--heap_size", str(1 << 28), "--datatype", "fp16",
                                           "--BLK_M", "128", "--BLK_N", "128", "--push_kind", "stores", "--all_gather"]),
+    ("07_gemm_all_scatter/benchmark.py", ["-m", "1024", "-n", "2048", "-k", "512", "-v", "-b", "--num_experiments", "3",
+                                          "--num_warmup", "1", "--heap_size", str(1 << 28), "--datatype", "fp32"]),
+    ("07_gemm_all_scatter/benchmark.py", ["-m", "1024", "-n", "2048", "-k", "512", "-v", "-b", "--num_experiments", "3",
+                                          "--num_warmup", "1", "--heap_size", str(1 << 28), "--datatype", "int8",
+                                          "--all_gather"]),
     ("08_gemm_atomics_all_reduce/benchmark.py", ["-m", "1024", "-n", "1024", "-k", "1024", "-v", "--heap_size", str(1 << 28)]),
     ("08_gemm_atomics_all_reduce/benchmark.py", ["-m", "128", "-n", "1024", "-k", "2048", "-v", "-b", "--num_experiments", "3",
                                                  "--num_warmup", "1", "--BLK_N", "64", "--ksplit", "2",

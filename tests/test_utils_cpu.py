@@ -131,10 +131,10 @@ ptxas info    : Used 32 registers, used 1 barriers
     _build.build_all()
     res = _build.kernel_resources()
     gemm = {k: v for k, v in res.items() if "fused_gemm_kernel<" in k}
-    assert len(gemm) == 8   # cta_group x pull x element type
+    assert len(gemm) == 12   # cta_group x pull x 16-bit type, plus cta_group x (fp32, int8) without reducer warps
     for name, v in gemm.items():
         # 8 warps: at most 255; 10 warps (reducer kernels): 168 per thread, or the CTA would not fit the register file
-        pull = ", true, " in name       # fused_gemm_kernel<cta_group, pull, fp16>
+        pull = ", true, " in name       # fused_gemm_kernel<cta_group, pull, element type>
         assert 0 < v["registers"] <= (168 if pull else 255), (name, v)
     # the main-loop kernels without reducer warps must not spill
     assert all(v["spill_store_bytes"] == 0 for k, v in gemm.items() if ", false, " in k)

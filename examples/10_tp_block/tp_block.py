@@ -39,6 +39,8 @@ def main():
     ap.add_argument("--num_warmup", type=int, default=3)
     ap.add_argument("--heap_size", type=int, default=12 << 30)
     ap.add_argument("--output_file", default="")
+    ap.add_argument("--cuda_graph", action="store_true",
+                    help="benchmark: also time the fused forward pass replayed from a CUDA graph")
     ap.add_argument("--breakdown", action="store_true", help="per-phase device times (max over ranks) of one forward")
     ap.add_argument("--heap_mode", default=None, choices=["ipc", "vmm"],
                     help="vmm + IRIS_NVLS=1 in the environment binds the heap to an NVLS multicast object")
@@ -83,6 +85,15 @@ def main():
         b_ms = reduce_ranks(ctx, time_kernel_ms(ctx, lambda: base.forward(b), args.num_warmup,
                                                 args.num_experiments, align=True), "max")
         res.update(fused_us=f_ms * 1e3, baseline_us=b_ms * 1e3, speedup=b_ms / f_ms)
+        if args.cuda_graph:
+            graph = model.capture([a])
+            ctx.barrier()
+            g_ms = reduce_ranks(ctx, time_kernel_ms(ctx, graph.replay, args.num_warmup, args.num_experiments,
+                                                    align=True), "max")
+            model.check()
+            res.update(fused_graph_us=g_ms * 1e3, speedup_graph=b_ms / g_ms)
+            if rank == 0:
+                print(f"  fused, replayed from a CUDA graph: {g_ms * 1e3:.0f} us | x{b_ms / g_ms:.2f}", flush=True)
         if rank == 0:
             print(f"TP decoder x{cfg.n_layers} layers, W={world}, {cfg.tokens} tokens: fused {f_ms * 1e3:.0f} us | "
                   f"cuBLAS+NCCL {b_ms * 1e3:.0f} us | x{b_ms / f_ms:.2f}", flush=True)

@@ -127,8 +127,9 @@ __device__ __forceinline__ void acc_x8(float* acc, uint4 v, bool f16) {
 // heap bound to an NVLS multicast object (`mc` != 0) that is one multimem.st per 16 bytes.
 // Few arguments on purpose (everything else is read from the launch parameters): the call sits in a role whose
 // registers are already scarce.
-__device__ __noinline__ void rs_sum_part(const FusedGemmParams& p, int rank, int ns, int mo, int n0, int rt, bool f16) {
-  const int W = p.world, N = p.N, bn = p.bn, part_row0 = p.part_row0, slot_rows = p.part_slot_rows;
+__device__ __noinline__ void rs_sum_part(const FusedGemmParams& p, int rank, int ns, int mo, int n0, int rt, bool f16,
+                                         int part_row0) {
+  const int W = p.world, N = p.N, bn = p.bn, slot_rows = p.part_slot_rows;
   const bool bcast = p.rs_bcast != 0;
   const int out_row_add = bcast ? rank * p.rs_rows : 0;
   const uint64_t mc = bcast ? p.mc_base : 0;
@@ -247,6 +248,9 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
   volatile uint32_t* red_ok = tmem_slot + 3;
   volatile uint32_t* ag_ok = tmem_slot + 4;
   volatile uint32_t* never = tmem_slot + 5;  // stays 0: "abort" word for waits that must not be cut short
+  // this call, derived from the call counter in device memory: [0] call number = value of the entry flags, [1] value
+  // the per-tile / per-chunk flags reach, [2] value the arrival counter reaches, [3] first row of the partial buffer
+  volatile uint32_t* callv = tmem_slot + 6;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -299,6 +303,13 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
     *red_ok = 1;
     *ag_ok = 1;
     *never = 0;
+    {
+      const uint32_t call = *reinterpret_cast<volatile uint32_t*>(flag_ptr(p, p.rank0 + blockIdx.x / p.ctas_per_rank, 2)) + 1u;
+      callv[0] = call;
+      callv[1] = p.per_flag * call;
+      callv[2] = call * (uint32_t)p.world * (uint32_t)p.ctas_per_rank;
+      callv[3] = (uint32_t)((call & 1u) ? p.part_row0_odd : p.part_row0);
+    }
     mbar_fence_init();
     prefetch_tensormap(&p.tmA[lr]);
     prefetch_tensormap(&p.tmB[lr]);
@@ -338,7 +349,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
     if (threadIdx.x == 0) {
       red_relaxed_gpu_add(flag_ptr(p, rank, 1), 1u);
       if (cta == 0 &&
-          wait_until_ge(flag_ptr(p, rank, 1), p.epoch * (uint32_t)p.ctas_per_rank, p.timeout_ns, status, kSiteZero, rank,
+          wait_until_ge(flag_ptr(p, rank, 1), callv[0] * (uint32_t)p.ctas_per_rank, p.timeout_ns, status, kSiteZero, rank,
                         0) != kOk)
         *abort_flag = 1;
     }
@@ -347,7 +358,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
     fence_sys();
     for (int i = 0; i < W; ++i) {
       const int t = (rank + 1 + i) % W;
-      st_relaxed_sys(flag_ptr(p, t, 8 + rank), p.epoch);
+      st_relaxed_sys(flag_ptr(p, t, 8 + rank), callv[0]);
     }
   }
 
@@ -378,7 +389,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
           if (src != rank) {
             const int chunk = (row0 - src * Ms) / BM;
             const uint32_t* f = flag_ptr(p, rank, p.ag_flag_base + src * chunks_per_shard + chunk);
-            if (wait_until_ge(f, p.flag_target, p.timeout_ns, status, kSiteProducerAgFlag, rank, tile) != kOk) {
+            if (wait_until_ge(f, callv[1], p.timeout_ns, status, kSiteProducerAgFlag, rank, tile) != kOk) {
               *abort_flag = 1;
               ok = false;
               break;
@@ -568,7 +579,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
           // Before the first push of this call: every peer must have entered the call.
           for (int i = 0; i < W && ok; ++i) {
             const int t = (rank + 1 + i) % W;
-            ok = wait_until_ge(flag_ptr(p, rank, 8 + t), p.epoch, p.timeout_ns, status, kSiteEpiEntry, rank, t) == kOk;
+            ok = wait_until_ge(flag_ptr(p, rank, 8 + t), callv[0], p.timeout_ns, status, kSiteEpiEntry, rank, t) == kOk;
           }
         }
         *epi_ok = ok ? 1u : 0u;
@@ -592,7 +603,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
       // row inside the tmC matrix: partial buffer of this call's parity, inbox slot of (rank, piece) when pushing
       const int slot = p.push_partials ? rank * (p.ksplit > 1 ? p.ksplit : 1) + w.piece : 0;
       const int keeper = p.rs_rows > 0 ? tile / rs_tpc : -1;  // reduce-scatter: the rank that keeps these rows
-      const int y_st = (pulls ? p.part_row0 + slot * p.part_slot_rows : 0) + y - (keeper > 0 ? keeper * p.rs_rows : 0);
+      const int y_st = (pulls ? (int)callv[3] + slot * p.part_slot_rows : 0) + y - (keeper > 0 ? keeper * p.rs_rows : 0);
 
       // Stream-K: a piece that covers only part of the tile's k-blocks adds its fp32 accumulator into the tile's
       // workspace and bumps the tile's k-block counter; the unit whose addition completes the count finishes the
@@ -808,7 +819,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
         // cumulative, and the arrivals themselves can be relaxed (a release per rank would cost a round trip each)
         fence_sys();
         for (int i = 0; i < W; ++i) red_relaxed_sys_add(flag_ptr(p, (rank + 1 + i) % W, 0), 1u);
-        if (ok_all) wait_until_ge(flag_ptr(p, rank, 0), p.done_target, p.timeout_ns, status, kSiteDone, rank, cta);
+        if (ok_all) wait_until_ge(flag_ptr(p, rank, 0), callv[2], p.timeout_ns, status, kSiteDone, rank, cta);
       }
     } else if (lead) {
       bulk_wait<0>();
@@ -857,11 +868,11 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
           if (rissuer) {
             const uint32_t* f = flag_ptr(p, rank, p.tile_flag_base + t * CG + pr);
             trace(p, rank, t * CG + pr, kTrWaitBegin);
-            bool ok = wait_until_ge(f, p.flag_target, p.timeout_ns, status, kSiteEpiTileFlag, rank, t) == kOk;
+            bool ok = wait_until_ge(f, callv[1], p.timeout_ns, status, kSiteEpiTileFlag, rank, t) == kOk;
             if (ok && !entered) {
               for (int i = 0; i < W && ok; ++i) {
                 const int q = (rank + 1 + i) % W;
-                ok = wait_until_ge(flag_ptr(p, rank, 8 + q), p.epoch, p.timeout_ns, status, kSiteEpiEntry, rank, q) == kOk;
+                ok = wait_until_ge(flag_ptr(p, rank, 8 + q), callv[0], p.timeout_ns, status, kSiteEpiEntry, rank, q) == kOk;
               }
             }
             trace(p, rank, t * CG + pr, kTrWaitEnd);
@@ -886,7 +897,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
               for (int u = 0; u < 8; ++u) {
                 const int r = m0 + r0 + u;
                 if (r < p.M) {
-                  const void* src = reinterpret_cast<const void*>(mc + ((uint64_t)(p.part_row0 + r) * p.N + col) * 2);
+                  const void* src = reinterpret_cast<const void*>(mc + ((uint64_t)((int)callv[3] + r) * p.N + col) * 2);
                   v[u] = f16 ? nvls::ld_reduce_add_f16x8(src) : nvls::ld_reduce_add_bf16x8(src);
                 }
               }
@@ -907,7 +918,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
           if (rissuer) {
             const uint32_t* f = flag_ptr(p, rank, p.tile_flag_base + t * CG + pr);
             trace(p, rank, t * CG + pr, kTrWaitBegin);
-            const bool ok = wait_until_ge(f, p.flag_target, p.timeout_ns, status, kSiteEpiTileFlag, rank, t) == kOk;
+            const bool ok = wait_until_ge(f, callv[1], p.timeout_ns, status, kSiteEpiTileFlag, rank, t) == kOk;
             trace(p, rank, t * CG + pr, kTrWaitEnd);
             *red_ok = ok ? 1u : 0u;
           }
@@ -918,7 +929,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
             ok_all = false;
             break;
           }
-          rs_sum_part(p, rank, NS, m0 - rs_base, n0, rt, f16);
+          rs_sum_part(p, rank, NS, m0 - rs_base, n0, rt, f16, (int)callv[3]);
           if (rissuer) trace(p, rank, t * CG + pr, kTrPullEnd);
           continue;
         }
@@ -928,7 +939,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
           if (rissuer) {
             const uint32_t* f = flag_ptr(p, rank, p.tile_flag_base + t * CG + pr);
             trace(p, rank, t * CG + pr, kTrWaitBegin);
-            const bool ok = wait_until_ge(f, p.flag_target, p.timeout_ns, status, kSiteEpiTileFlag, rank, t) == kOk;
+            const bool ok = wait_until_ge(f, callv[1], p.timeout_ns, status, kSiteEpiTileFlag, rank, t) == kOk;
             trace(p, rank, t * CG + pr, kTrWaitEnd);
             *red_ok = ok ? 1u : 0u;
           }
@@ -946,7 +957,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
             for (int j = 0; j < kEpiCols; ++j) accv[j] = 0.f;
             if (row_live) {
               const uint8_t* src = reinterpret_cast<const uint8_t*>(p.heap_base[rank] + p.partial_off) +
-                                   ((uint64_t)(p.part_row0 + m0 - rs_base + row) * p.N + n0 + c * kEpiCols) * 2;
+                                   ((uint64_t)((int)callv[3] + m0 - rs_base + row) * p.N + n0 + c * kEpiCols) * 2;
               const uint64_t slot_bytes = (uint64_t)p.part_slot_rows * p.N * 2;
               int sl = 0;
               for (; sl + 1 < NS; sl += 2) {
@@ -1009,21 +1020,21 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
           mbar_expect_tx(pull_full_bar(b), p.c_box_bytes);
           if (p.push_partials)
             tma_load_2d(pull_base + b * kEpiStageBytes, &p.tmC[rank], n0 + c * kEpiCols,
-                        p.part_row0 + sft * p.part_slot_rows + m0, pull_full_bar(b));
+                        (int)callv[3] + sft * p.part_slot_rows + m0, pull_full_bar(b));
           else
-            tma_load_2d(pull_base + b * kEpiStageBytes, &p.tmC[(rank + sft) % W], n0 + c * kEpiCols, p.part_row0 + m0,
+            tma_load_2d(pull_base + b * kEpiStageBytes, &p.tmC[(rank + sft) % W], n0 + c * kEpiCols, (int)callv[3] + m0,
                         pull_full_bar(b));
           ++pull_issued;
         };
         if (rissuer) {
           const uint32_t* f = flag_ptr(p, rank, p.tile_flag_base + t * CG + pr);
           trace(p, rank, t * CG + pr, kTrWaitBegin);
-          bool ok = wait_until_ge(f, p.flag_target, p.timeout_ns, status, kSiteEpiTileFlag, rank, t) == kOk;
+          bool ok = wait_until_ge(f, callv[1], p.timeout_ns, status, kSiteEpiTileFlag, rank, t) == kOk;
           if (ok && !entered) {
             // before the first push of this call: every peer must have entered the call
             for (int i = 0; i < W && ok; ++i) {
               const int q = (rank + 1 + i) % W;
-              ok = wait_until_ge(flag_ptr(p, rank, 8 + q), p.epoch, p.timeout_ns, status, kSiteEpiEntry, rank, q) == kOk;
+              ok = wait_until_ge(flag_ptr(p, rank, 8 + q), callv[0], p.timeout_ns, status, kSiteEpiEntry, rank, q) == kOk;
             }
           }
           trace(p, rank, t * CG + pr, kTrWaitEnd);
@@ -1134,7 +1145,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
           fence_proxy_async_all();
           fence_sys();
           for (int i = 0; i < W; ++i) red_relaxed_sys_add(flag_ptr(p, (rank + 1 + i) % W, 0), 1u);
-          if (ok_all) wait_until_ge(flag_ptr(p, rank, 0), p.done_target, p.timeout_ns, status, kSiteDone, rank, cta);
+          if (ok_all) wait_until_ge(flag_ptr(p, rank, 0), callv[2], p.timeout_ns, status, kSiteDone, rank, cta);
         }
       } else if (rissuer) {
         bulk_wait<0>();
@@ -1157,7 +1168,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
           bool ok = true;
           for (int i = 0; i + 1 < W && ok; ++i) {
             const int q = (rank + 1 + i) % W;
-            ok = wait_until_ge(flag_ptr(p, rank, 8 + q), p.epoch, p.timeout_ns, status, kSiteAgEntry, rank, q) == kOk;
+            ok = wait_until_ge(flag_ptr(p, rank, 8 + q), callv[0], p.timeout_ns, status, kSiteAgEntry, rank, q) == kOk;
           }
           if (!ok) {
             *ag_ok = 0;
@@ -1212,6 +1223,13 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
   tc_fence_before();
   __syncthreads();
   if (p.trace_off && threadIdx.x == 0 && unit < total_tiles) trace(p, rank, tile_of(unit) * CG + pr, kTrCtaEnd);
+  if (threadIdx.x == 0) {
+    // Call counter: every CTA read it at the start and counts itself here; the last CTA of this rank to arrive makes
+    // the call number the new count.  The next launch of this op follows in stream order.
+    const uint32_t call = callv[0];
+    if (atomicAdd(flag_ptr(p, rank, 3), 1u) + 1u == call * (uint32_t)p.ctas_per_rank)
+      *reinterpret_cast<volatile uint32_t*>(flag_ptr(p, rank, 2)) = call;
+  }
   if (CG == 2) cluster_sync_all();  // neither CTA of a pair leaves while the other may still touch its memory
   if (warp == 1) {
     __syncwarp();
@@ -1306,7 +1324,7 @@ struct IrisGemmDesc {
   uint64_t a_ptr[kMaxRanks];   // per local rank (with ag = 1: the gathered A buffer)
   uint64_t b_ptr[kMaxRanks];   // per local rank
   uint64_t c_ptr[kMaxRanks];   // per target rank: output (store/reduce) or partial buffer parity 0 (one-/two-shot)
-  uint64_t c2_ptr[kMaxRanks];  // partial buffer parity 1, else 0
+  uint64_t c2_ptr[kMaxRanks];  // unused (must be 0): both partial buffers are row ranges of the matrix at c_ptr
   uint64_t heap_base[kMaxRanks];
   int64_t lda[kMaxRanks];      // elements
   int64_t ldb[kMaxRanks];
@@ -1345,7 +1363,7 @@ struct IrisGemmDesc {
 };
 
 struct IrisGemmPlan {
-  FusedGemmParams params[2];  // one per parity of the partial buffers
+  FusedGemmParams params;      // the same for every call: what changes per call is derived in the kernel
   int grid;
   int cooperative;
   int device;
@@ -1505,6 +1523,12 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
   int sms = 0;
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, d->device);
   const bool pull = d->mode == kEpiOneShot || d->mode == kEpiTwoShot;
+  for (int t = 0; t < kMaxRanks; ++t) {
+    if (d->c2_ptr[t] != 0 || d->partial_off[0] != d->partial_off[1]) {
+      snprintf(g_err, sizeof(g_err), "the two partial buffers are row ranges (part_row0) of one matrix per rank");
+      return nullptr;
+    }
+  }
   // Short matrices move short sub-tiles: the C / partial box has only as many rows as M needs (multiple of 8).
   const uint32_t c_box_rows = d->M >= BM ? BM : (uint32_t)((d->M + 7) / 8 * 8);
   int ctas_per_rank = d->ctas_per_rank - d->ctas_per_rank % cg;
@@ -1555,8 +1579,8 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
   plan->pull = pull ? 1 : 0;
   plan->et = et;
   plan->ctas_per_rank = ctas_per_rank;
-  for (int par = 0; par < 2; ++par) {
-    FusedGemmParams& p = plan->params[par];
+  {
+    FusedGemmParams& p = plan->params;
     for (int l = 0; l < d->num_local; ++l) {
       const uint32_t bk = 128 / es;  // K elements of one ring stage: 128 bytes
       if (encode_2d(&p.tmA[l], d->a_ptr[l], d->M, d->K, d->lda[l], bk, BM, "A", et) ||
@@ -1568,7 +1592,7 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
       }
     }
     for (int t = 0; t < d->world; ++t) {
-      const uint64_t cp = (par == 1 && d->c2_ptr[t]) ? d->c2_ptr[t] : d->c_ptr[t];
+      const uint64_t cp = d->c_ptr[t];
       if (!cp) continue;
       if (encode_2d(&p.tmC[t], cp, d->c_rows > 0 ? d->c_rows : d->M, d->c_cols, d->ldc, epi_cols, c_box_rows, "C",
                     et)) {
@@ -1578,7 +1602,7 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
     }
     for (int t = 0; t < kMaxRanks; ++t) p.heap_base[t] = d->heap_base[t];
     p.flags_off = d->flags_off;
-    p.partial_off = d->partial_off[par];
+    p.partial_off = d->partial_off[0];
     p.out_off = d->out_off;
     p.status_off = d->status_off;
     p.agsrc_off = d->agsrc_off;
@@ -1598,7 +1622,9 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
     p.N = d->N;
     p.K = d->K;
     p.ldo = d->ldo;
-    p.part_row0 = d->part_row0[par];
+    p.part_row0 = d->part_row0[0];
+    p.part_row0_odd = d->part_row0[1];
+    p.per_flag = (uint32_t)(pull ? d->world * (d->ksplit > 1 ? d->ksplit : 1) : d->ag_slices);
     p.out_row0 = d->out_row0;
     p.lda_full = (int)d->lda[0];
     p.col_off_per_rank = d->col_off_per_rank;
@@ -1638,13 +1664,11 @@ int iris_gemm_plan_cta_group(void* h) { return static_cast<IrisGemmPlan*>(h)->ct
 
 // Launch one call.  `parity` selects the partial-buffer set; epoch / flag_target / done_target are the
 // cumulative values this call drives the flags to (kept by the caller).
-int iris_gemm_plan_launch(void* h, int parity, uint32_t epoch, uint32_t flag_target, uint32_t done_target,
-                          void* stream) {
+// The launch carries no per-call argument (the kernel keeps the call number in device memory), so it may be recorded
+// by a stream capture and replayed as part of a CUDA graph.
+int iris_gemm_plan_launch(void* h, void* stream) {
   IrisGemmPlan* plan = static_cast<IrisGemmPlan*>(h);
-  FusedGemmParams& p = plan->params[parity & 1];
-  p.epoch = epoch;
-  p.flag_target = flag_target;
-  p.done_target = done_target;
+  FusedGemmParams& p = plan->params;
   cudaError_t e;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (plan->cta_group == 2) {
@@ -1799,7 +1823,8 @@ int iris_gemm_noalloc(const void* a, int64_t lda, const void* bt, int64_t ldb, v
   p.K = K;
   p.ldo = (int)ldo;
   p.c_box_bytes = c_box_rows * 128u;
-  p.part_row0 = 0;
+  p.part_row0 = p.part_row0_odd = 0;
+  p.per_flag = 1;  // one rank raises each tile's flag once; the flags (call counter included) are cleared just below
   p.out_row0 = -1;  // the caller's output is a separate buffer: ordinary stores
   p.world = 1;
   p.num_local = 1;
@@ -1815,9 +1840,6 @@ int iris_gemm_noalloc(const void* a, int64_t lda, const void* bt, int64_t ldb, v
   p.bn = BN;
   p.dtype = kBf16;
   p.tail_split = 1;
-  p.epoch = 1;
-  p.flag_target = 1;  // one rank raises each tile's flag once; the flags are cleared just below
-  p.done_target = 0;
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // The scratch keeps the previous call's contents.  The per-tile flags have to start at zero: clear them in stream
@@ -1825,7 +1847,7 @@ int iris_gemm_noalloc(const void* a, int64_t lda, const void* bt, int64_t ldb, v
   // iris_gemm_noalloc_status() has reported it.
   cudaError_t e = cudaMemsetAsync(d.scratch + kNoAllocFlagsOff, 0, (size_t)(16 + tiles) * sizeof(uint32_t), st);
   if (e == cudaSuccess) {
-    fused_gemm_kernel<1, true, false><<<p.ctas_per_rank, kThreadsPull, kSmemBytes, st>>>(p);
+    fused_gemm_kernel<1, true, kBf16><<<p.ctas_per_rank, kThreadsPull, kSmemBytes, st>>>(p);
     e = cudaGetLastError();
   }
   if (e != cudaSuccess) {

@@ -127,9 +127,14 @@ struct FusedGemmParams {
   uint64_t zero_bytes;   // reduce mode: bytes of this rank's output, from c_off, that the kernel clears before it
                          // raises its entry flags (multiple of 16; 0 = the caller clears the output)
   uint32_t c_box_bytes;  // bytes of one C / partial sub-tile transfer: rows of the tmC box (128, fewer when M < 128) x 128
-  uint32_t epoch;        // call number (1, 2, ...): value of the entry flags in this call
-  uint32_t flag_target;  // value per-tile / per-chunk flags reach in this call (cumulative over calls)
-  uint32_t done_target;  // value the arrival counter reaches when every CTA of every rank has finished
+  // Nothing in the launch arguments changes from call to call: the call number is kept in device memory (flag
+  // word [2]: calls completed, written by the last CTA of a launch to leave, counted on word [3]) and everything
+  // that depends on it is derived in the kernel: the value of the entry flags (the call number), what the
+  // cumulative per-tile / per-chunk flags reach in this call (per_flag x call), what the arrival counter reaches
+  // (call x world x CTAs per rank), and which of the two partial buffers is written (call parity).  A launch can
+  // therefore be recorded in a CUDA graph and replayed.
+  uint32_t per_flag;     // what one call adds to a per-tile flag (ranks x K pieces) or to a per-chunk flag (slices)
+  int part_row0_odd;     // part_row0 of odd-numbered calls (part_row0 above: even-numbered calls)
 };
 
 }  // namespace gemm

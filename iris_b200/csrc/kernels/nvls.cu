@@ -23,16 +23,30 @@ __global__ void nvls_all_store_kernel(uint64_t mc_ptr, size_t n16) {
   }
 }
 
-// counter: uint32 at symmetric offset counter_off (cumulative); two barrier phases per call.
+// counter: uint32[3] at symmetric offset counter_off.  [0]: arrivals, cumulative over calls, written by every rank
+// through the multicast address; two barrier phases per call, every block of every rank arrives once per phase.
+// [1] (local): arrivals counted up to the end of the previous call; [2] (local): blocks of this launch that have left.
+// The last block to leave advances [1] and clears [2], so a launch has no per-call argument and can be replayed from
+// a CUDA graph, with any grid size (the same on every rank) from call to call.
+__device__ __forceinline__ void all_reduce_leave(uint32_t* my_counter, uint32_t base, int world) {
+  if (atomicAdd(my_counter + 2, 1u) + 1u == gridDim.x) {
+    *reinterpret_cast<volatile uint32_t*>(my_counter + 2) = 0u;
+    *reinterpret_cast<volatile uint32_t*>(my_counter + 1) = base + 2u * gridDim.x * (uint32_t)world;
+  }
+}
+
 __global__ void nvls_all_reduce_bf16_kernel(uint64_t mc_buf, const uint64_t* hb, uint64_t counter_off,
-                                            uint64_t status_off, size_t n16, int rank, int world, uint32_t target0,
+                                            uint64_t status_off, size_t n16, int rank, int world,
                                             uint64_t timeout_ns, uint64_t mc_base) {
-  __shared__ uint32_t ok;
+  __shared__ uint32_t ok, base_s;
   const size_t per = (n16 + world - 1) / world;
   const size_t lo = per * rank, hi = lo + per < n16 ? lo + per : n16;
   uint32_t* my_counter = reinterpret_cast<uint32_t*>(hb[rank] + counter_off);
+  if (threadIdx.x == 0) base_s = *reinterpret_cast<volatile uint32_t*>(my_counter + 1);
   // Phase 0: every rank's input is complete (kernel ordering on its own stream) -> all blocks of all ranks arrive.
   __syncthreads();
+  const uint32_t base = base_s;
+  const uint32_t target0 = base + (uint32_t)(gridDim.x * world);
   if (threadIdx.x == 0) {
     fence_sys();
     nvls::red_release_add_u32(reinterpret_cast<void*>(mc_base + counter_off), 1u);
@@ -43,7 +57,10 @@ __global__ void nvls_all_reduce_bf16_kernel(uint64_t mc_buf, const uint64_t* hb,
   if (!ok) {
     // Phase 0 timed out: no data is touched, but the phase-1 arrival is still made, so that this rank keeps adding
     // exactly two arrivals per block and call to every rank's counter (the invariant the host's targets rest on).
-    if (threadIdx.x == 0) nvls::red_release_add_u32(reinterpret_cast<void*>(mc_base + counter_off), 1u);
+    if (threadIdx.x == 0) {
+      nvls::red_release_add_u32(reinterpret_cast<void*>(mc_base + counter_off), 1u);
+      all_reduce_leave(my_counter, base, world);
+    }
     return;
   }
   const size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -58,6 +75,7 @@ __global__ void nvls_all_reduce_bf16_kernel(uint64_t mc_buf, const uint64_t* hb,
     nvls::red_release_add_u32(reinterpret_cast<void*>(mc_base + counter_off), 1u);
     wait_until_ge(my_counter, target0 + (uint32_t)(gridDim.x * world), timeout_ns,
                   reinterpret_cast<StatusBlock*>(hb[rank] + status_off), 81, (uint32_t)rank, 1);
+    all_reduce_leave(my_counter, base, world);
   }
 }
 
@@ -70,12 +88,11 @@ int iris_k_nvls_all_store(uint64_t mc_ptr, uint64_t bytes, int grid, int block, 
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
-// target0 = (counter value before this call) + grid * world: every block of every rank arrives once per phase.
 int iris_k_nvls_all_reduce_bf16(uint64_t mc_buf, const uint64_t* hb, uint64_t counter_off, uint64_t status_off,
-                                uint64_t bytes, int rank, int world, uint32_t target0, uint64_t timeout_ns,
-                                uint64_t mc_base, int grid, int block, void* stream) {
+                                uint64_t bytes, int rank, int world, uint64_t timeout_ns, uint64_t mc_base, int grid,
+                                int block, void* stream) {
   nvls_all_reduce_bf16_kernel<<<grid, block, 0, (cudaStream_t)stream>>>(mc_buf, hb, counter_off, status_off, bytes / 16,
-                                                                        rank, world, target0, timeout_ns, mc_base);
+                                                                        rank, world, timeout_ns, mc_base);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 

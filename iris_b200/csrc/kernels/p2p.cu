@@ -260,11 +260,16 @@ __global__ void mp_kernel(MpArgs a) {
 }
 
 // Device-side barrier across ranks: one thread adds 1 to counter[0] of every rank (release, system scope),
-// then waits (bounded) until its own counter reaches `target` = calls * world.  Streams of different GPUs are
-// aligned to within a few microseconds when this kernel completes.
+// then waits (bounded) until its own counter reaches calls * world.  Streams of different GPUs are
+// aligned to within a few microseconds when this kernel completes.  The number of calls so far is kept in
+// counter[1] of the rank's own heap and advanced by the kernel, so that a launch has no per-call argument and can
+// be replayed from a CUDA graph.
 __global__ void device_barrier_kernel(const uint64_t* hb, uint64_t counter_off, uint64_t status_off, int rank,
-                                      int world, uint32_t target, uint64_t timeout_ns) {
+                                      int world, uint64_t timeout_ns) {
   if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  volatile uint32_t* calls = reinterpret_cast<volatile uint32_t*>(hb[rank] + counter_off) + 1;
+  const uint32_t call = *calls + 1u;
+  const uint32_t target = call * (uint32_t)world;
   fence_sys();  // one fence, then relaxed arrivals: a release per rank would wait for the previous rank's answer
   for (int i = 0; i < world; ++i) {
     const int t = (rank + 1 + i) % world;
@@ -272,6 +277,7 @@ __global__ void device_barrier_kernel(const uint64_t* hb, uint64_t counter_off, 
   }
   wait_until_ge(reinterpret_cast<const uint32_t*>(hb[rank] + counter_off), target, timeout_ns,
                 reinterpret_cast<StatusBlock*>(hb[rank] + status_off), /*where=*/70, (uint32_t)rank, target);
+  *calls = call;
 }
 
 int check_launch() { return cudaGetLastError() == cudaSuccess ? 0 : -1; }
@@ -343,9 +349,8 @@ int iris_k_memset_i32(void* p, int value, uint64_t n, void* stream) {
 }
 
 int iris_k_device_barrier(const uint64_t* hb, uint64_t counter_off, uint64_t status_off, int rank, int world,
-                          uint32_t target, uint64_t timeout_ns, void* stream) {
-  device_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(hb, counter_off, status_off, rank, world, target,
-                                                            timeout_ns);
+                          uint64_t timeout_ns, void* stream) {
+  device_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(hb, counter_off, status_off, rank, world, timeout_ns);
   return check_launch();
 }
 

@@ -187,6 +187,18 @@ class TPDecoder:
         self.kernel_launches += n
         return x_shards
 
+    def capture(self, x_shards: Sequence[torch.Tensor]) -> "torch.cuda.CUDAGraph":
+        """Record one forward pass over ``x_shards`` (updated in place, as ``forward`` does) into a CUDA graph and
+        return it; ``graph.replay()`` then runs the whole pass, all ranks' collectives included, with one submission
+        instead of one launch per kernel.  Every rank captures and replays the same number of times.  The fused
+        kernels keep their call numbers (flag targets, buffer parity) in device memory, so a recorded launch is
+        valid for every replay and may be mixed with ordinary ``forward`` calls."""
+        torch.cuda.synchronize(self.ctxs[0].device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self.forward(x_shards)
+        return graph
+
     def check(self) -> None:
         torch.cuda.synchronize(self.ctxs[0].device)
         for c in self.ctxs:

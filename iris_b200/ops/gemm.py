@@ -70,8 +70,7 @@ def _lib():
         lib.iris_gemm_plan_ctas_per_rank.argtypes = [ctypes.c_void_p]
         lib.iris_gemm_plan_cta_group.argtypes = [ctypes.c_void_p]
         lib.iris_gemm_plan_launch.restype = ctypes.c_int
-        lib.iris_gemm_plan_launch.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_uint32, ctypes.c_uint32,
-                                              ctypes.c_uint32, ctypes.c_void_p]
+        lib.iris_gemm_plan_launch.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
         if lib.iris_gemm_desc_size() != ctypes.sizeof(_Desc):
             raise RuntimeError("IrisGemmDesc layout mismatch between Python and the native library")
         lib._gemm_typed = True
@@ -334,12 +333,10 @@ class FusedGemm:
             for o in self.out[:self.num_local]:
                 o.zero_()  # partial sums are added into the output: it has to start at zero
             self.launches += self.num_local
+        # No per-call argument: the kernel keeps the call number (entry-flag value, flag targets, partial-buffer parity)
+        # in device memory, so this launch may be recorded by a stream capture and replayed from a CUDA graph.
         self.calls += 1
-        per_flag = self.world * self.ksplit if self.mode in ("one_shot", "two_shot") else self.ag_slices
-        rc = _lib().iris_gemm_plan_launch(self._plan, self.calls & 1, self.calls & 0xFFFFFFFF,
-                                          (per_flag * self.calls) & 0xFFFFFFFF,
-                                          (self.calls * self.world * self.ctas_per_rank) & 0xFFFFFFFF,
-                                          ctypes.c_void_p(st))
+        rc = _lib().iris_gemm_plan_launch(self._plan, ctypes.c_void_p(st))
         if rc != 0:
             raise RuntimeError("fused GEMM launch: " + _lib().iris_gemm_last_error().decode())
         self.launches += 1

@@ -58,17 +58,16 @@ class AllReduce:
         assert buf.dtype == torch.bfloat16 and (buf.numel() * 2) % 16 == 0
         grid = min(grid or ctx.get_cu_count(), ctx.get_cu_count())  # all blocks wait on one another: co-resident
         world = ctx.get_num_ranks()
-        target0 = self.total + grid * world
-        self.total += 2 * grid * world
+        self.total += 2 * grid * world   # arrivals so far; the kernel keeps its own count in device memory
         lib = _native.kernels()
         lib.iris_k_nvls_all_reduce_bf16.argtypes = [ctypes.c_uint64, ctypes.c_void_p, ctypes.c_uint64, ctypes.c_uint64,
-                                                    ctypes.c_uint64, ctypes.c_int, ctypes.c_int, ctypes.c_uint32,
+                                                    ctypes.c_uint64, ctypes.c_int, ctypes.c_int,
                                                     ctypes.c_uint64, ctypes.c_uint64, ctypes.c_int, ctypes.c_int,
                                                     ctypes.c_void_p]
         st = torch.cuda.current_stream(ctx.device).cuda_stream if stream is None else stream
         rc = lib.iris_k_nvls_all_reduce_bf16(
             _mc(ctx, buf), ctypes.c_void_p(ctx.get_heap_bases().data_ptr()), ctx.offset_of(self.counter),
-            ctx.offset_of(ctx.status), buf.numel() * 2, ctx.get_rank(), world, target0 & 0xFFFFFFFF, self.timeout_ns,
+            ctx.offset_of(ctx.status), buf.numel() * 2, ctx.get_rank(), world, self.timeout_ns,
             ctx.mc_base, grid, block, ctypes.c_void_p(st))
         if rc:
             raise RuntimeError("nvls_all_reduce launch failed")

@@ -208,9 +208,8 @@ class DeviceBarrier:
             return
         lib = _native.kernels()
         lib.iris_k_device_barrier.argtypes = [ctypes.c_void_p, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_int,
-                                              ctypes.c_int, ctypes.c_uint32, ctypes.c_uint64, ctypes.c_void_p]
+                                              ctypes.c_int, ctypes.c_uint64, ctypes.c_void_p]
+        # no per-call argument (the kernel counts its calls in counter[1]): the launch can be replayed from a CUDA graph
         rc = lib.iris_k_device_barrier(_hb(ctx), ctx.offset_of(self.counter), ctx.offset_of(ctx.status),
-                                       ctx.get_rank(), ctx.get_num_ranks(),
-                                       (self.calls * ctx.get_num_ranks()) & 0xFFFFFFFF, self.timeout_ns,
-                                       _stream(ctx, stream))
+                                       ctx.get_rank(), ctx.get_num_ranks(), self.timeout_ns, _stream(ctx, stream))
         _check(rc, "device_barrier")

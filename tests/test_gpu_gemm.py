@@ -528,3 +528,68 @@ def test_plan_rejects_bad_shapes():
     a, bt = _rand((128, 60), 1), _rand((256, 60), 2)
     with pytest.raises((RuntimeError, ValueError)):
         G.gemm(a, bt)
+
+
+def test_fused_ops_replay_from_a_cuda_graph():
+    """Launches carry no per-call argument (call number, flag targets and buffer parity live in device memory), so a
+    stream capture records them once and the graph replays them: all-scatter, pulled and pushed all-reduce,
+    reduce-scatter and the all-gather prologue, two ranks in one launch, with new inputs before every replay and
+    ordinary calls mixed in."""
+    world, m, n, k = 2, 512, 512, 512
+    ranks = iris.Iris.local_world(world, heap_size=128 << 20)
+    a = _rand((m, k), 1)
+    bts = [_rand((n, k), 10 + r, 0.05) for r in range(world)]
+    ks = k // world
+    a_sh = [a[:, r * ks:(r + 1) * ks] for r in range(world)]
+    b_sh = [bts[0][:, r * ks:(r + 1) * ks] for r in range(world)]
+    ops = {
+        "all_scatter": G.gemm_all_scatter(ranks, [a] * world, bts),
+        "two_shot": G.gemm_all_reduce(ranks, a_sh, b_sh, variant="two_shot"),
+        "one_shot": G.gemm_all_reduce(ranks, a_sh, b_sh, variant="one_shot"),
+        "atomic": G.gemm_all_reduce(ranks, a_sh, b_sh, variant="atomic"),
+        "reduce_scatter": G.gemm_reduce_scatter(ranks, a_sh, b_sh),
+        "all_gather": G.all_gather_gemm(ranks, m, bts),
+    }
+    ms = m // world
+
+    def fill_gathered():
+        for r in range(world):
+            ops["all_gather"].a_full[r][r * ms:(r + 1) * ms].copy_(a[r * ms:(r + 1) * ms])
+
+    def run_all():
+        fill_gathered()
+        for op in ops.values():
+            op()
+
+    def verify():
+        torch.cuda.synchronize()
+        for op in ops.values():
+            op.check()
+        full = [a.float() @ b.float().t() for b in bts]
+        parts = [a_sh[r].float() @ b_sh[r].float().t() for r in range(world)]
+        red, scale = sum(parts), sum(p.abs() for p in parts)
+        for r in range(world):
+            _assert_close(ops["all_scatter"].out[r], torch.cat(full, dim=1))
+            _assert_close(ops["all_gather"].out[r], full[r])
+            for name in ("two_shot", "one_shot", "atomic"):
+                _assert_close(ops[name].out[r], red, scale=scale, ulps=2.0 + world)
+            _assert_close(ops["reduce_scatter"].out[r], red[r * ms:(r + 1) * ms], scale=scale[r * ms:(r + 1) * ms],
+                          ulps=2.0 + world)
+
+    run_all()                # an ordinary call first (odd call number)
+    verify()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        run_all()
+    for i in range(3):       # replays see even and odd call numbers, with new operands every time
+        a.copy_(_rand((m, k), 100 + i))
+        graph.replay()
+        verify()
+    a.copy_(_rand((m, k), 200))
+    run_all()                # and ordinary calls keep working after replays
+    verify()
+    graph.replay()
+    verify()
+    for op in ops.values():
+        op.close()
+    ranks[0].close()

@@ -182,6 +182,39 @@ def main():
         sc.check()
         close(c, torch.cat([a.to(dt).float() @ b.to(dt).float().t() for b in bts], dim=1))
         sc.close()
+    # CUDA graph over real GPUs: all-scatter, two-shot all-reduce and the device barrier recorded once and replayed
+    # with new operands (nothing in a launch changes from call to call: the call numbers are kept in device memory)
+    from iris_b200.ops.p2p import DeviceBarrier
+    ks2 = 1024 // world
+    ag_in = a.clone()
+    sc = G.gemm_all_scatter(ctx, [ag_in], [bts[rank]])
+    ar = G.gemm_all_reduce(ctx, [ag_in[:, rank * ks2:(rank + 1) * ks2]], [bts[0][:, rank * ks2:(rank + 1) * ks2]],
+                           variant="two_shot")
+    db = DeviceBarrier(ctx)
+    sc(), ar(), db()            # ordinary calls first
+    torch.cuda.synchronize()
+    ctx.barrier()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        db()
+        sc()
+        ar()
+    for i in range(3):
+        ag_in.copy_(rand(tuple(a.shape), 300 + i, dev=dev))
+        ctx.barrier()
+        graph.replay()
+        torch.cuda.synchronize()
+        ctx.barrier()
+        sc.check(), ar.check()
+        close(sc.out[0], torch.cat([ag_in.float() @ b.float().t() for b in bts], dim=1))
+        parts = [ag_in[:, r * ks2:(r + 1) * ks2].float() @ bts[0][:, r * ks2:(r + 1) * ks2].float().t()
+                 for r in range(world)]
+        close(ar.out[0], sum(parts), scale=sum(p.abs() for p in parts), ulps=2.0 + world)
+    sc(), ar(), db()            # and after the replays
+    torch.cuda.synchronize()
+    ctx.barrier()
+    sc.check(), ar.check()
+    sc.close(), ar.close()
     ctx.barrier()
     ctx.close()
     print(f"rank {rank}: OK", flush=True)

@@ -24,6 +24,10 @@ def parse_args(default_variant="put"):
     ap.add_argument("-p", "--heap_size", type=int, default=1 << 30)
     ap.add_argument("-n", "--num_experiments", type=int, default=20)
     ap.add_argument("--variant", default=default_variant, choices=["put", "load_store"])
+    ap.add_argument("--parts", type=int, default=None, help="slices (thread blocks at work) per chunk; default: from the sizes")
+    ap.add_argument("--blocks", type=int, default=None,
+                    help="thread blocks per side; fewer than chunks x parts makes the chunks land in order, so that "
+                         "the consumer works on early chunks while later ones are on the link")
     return vars(ap.parse_args())
 
 
@@ -34,7 +38,8 @@ def main(default_variant="put"):
     if world != 2:
         raise SystemExit("This example requires exactly two processes.")
     nchunks = max(1, args["buffer_size"] * 4 // args["chunk_bytes"])
-    mp = p2p.MessagePassing(ctx, nchunks, args["chunk_bytes"], producer=0, consumer=1, timeout_ms=5000)
+    mp = p2p.MessagePassing(ctx, nchunks, args["chunk_bytes"], producer=0, consumer=1, timeout_ms=5000,
+                            parts=args["parts"], blocks=args["blocks"])
     if rank == 0:
         mp.src.copy_(torch.arange(mp.src.numel(), device=mp.src.device, dtype=torch.float32) % 4096)
     use_put = args["variant"] == "put"

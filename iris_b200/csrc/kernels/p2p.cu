@@ -194,12 +194,15 @@ struct MpArgs {
   int parts;            // blocks per chunk: every chunk is cut into `parts` slices of whole 16-byte vectors
   uint64_t arrive_off;  // uint32 per chunk, in the producer's heap: slices of the chunk copied so far (back at 0
                         // when the chunk's flag has been raised)
+  int blocks;           // blocks per role: block b handles the (chunk, slice) pairs b, b + blocks, ... in that order
 };
 
-// Blocks [0, nchunks * parts) produce (when roles & 1); the following nchunks * parts blocks consume (when roles & 2).
-// Block (chunk c, slice q) handles slice q of chunk c, so that one chunk is moved by `parts` SMs at once and a
-// hand-off of a few large chunks still uses the whole GPU.
-// Producer: copy the slice into the consumer's buffer, make it visible (system-scope fence), then count the slice on
+// Blocks [0, blocks) produce (when roles & 1); the following `blocks` blocks consume (when roles & 2).
+// A chunk is cut into `parts` slices, so that one chunk is moved by `parts` SMs at once and a hand-off of a few large
+// chunks still uses the whole GPU.  Block b of a role handles the (chunk, slice) pairs b, b + blocks, ... in order:
+// with blocks = nchunks * parts all chunks travel at once and land together at the end; with fewer blocks the chunks
+// complete one group after the other, and the consumer works on the early ones while the later ones are on the link.
+// Producer: copy the slice into the consumer's buffer, make it visible (barrier + one system-scope fence), count the slice on
 // the chunk's arrival counter; the block that completes the count raises the CONSUMER's flag with release semantics
 // and puts the counter back to zero.  Consumer: every block of the chunk waits (bounded, acquire) on the chunk's flag
 // in its own memory, then writes out = 2 * landed for its slice.
@@ -207,12 +210,14 @@ __global__ void mp_kernel(MpArgs a) {
   __shared__ uint32_t verdict;
   int b = blockIdx.x;
   const int nblk = a.nchunks * a.parts;
+  const int R = a.blocks;
   const bool has_prod = a.roles & 1;
   // slice q of a chunk: whole 16-byte vectors, the last slice takes the remainder
   const uint64_t vecs = a.chunk_bytes / 16;
   const uint64_t per = (vecs + a.parts - 1) / a.parts;
-  if (has_prod && b < nblk) {
-    const int c = b / a.parts, q = b - c * a.parts;
+  if (has_prod && b < R) {
+   for (int w = b; w < nblk; w += R) {
+    const int c = w / a.parts, q = w - c * a.parts;
     const uint64_t v0 = per * q < vecs ? per * q : vecs, v1 = v0 + per < vecs ? v0 + per : vecs;
     const uint64_t off = (uint64_t)c * a.chunk_bytes + v0 * 16, bytes = (v1 - v0) * 16;
     const uint64_t base = a.hb[a.producer];
@@ -226,9 +231,11 @@ __global__ void mp_kernel(MpArgs a) {
       for (size_t i = threadIdx.x; i < bytes / 4; i += blockDim.x)
         store(d + i, load(s + i, a.producer, a.producer, a.hb), a.producer, a.consumer, a.hb);
     }
-    fence_sys();
+    // One thread publishes for the block: the barrier orders every thread's stores before its system-scope fence
+    // (fences are cumulative), and only its warp waits for the link round trip; the others start the next slice.
     __syncthreads();
     if (threadIdx.x == 0) {
+      fence_sys();
       uint32_t* cnt = reinterpret_cast<uint32_t*>(base + a.arrive_off) + c;
       const uint32_t old = atomic_add<Sem::acq_rel, Scope::gpu>(cnt, 1u, 0, 0, a.hb);
       if (old + 1 == (uint32_t)a.parts) {
@@ -237,11 +244,13 @@ __global__ void mp_kernel(MpArgs a) {
         signal_set(flag, a.epoch, a.producer, a.consumer, a.hb);
       }
     }
+   }
     return;
   }
-  if (has_prod) b -= nblk;
-  if (!(a.roles & 2) || b >= nblk) return;
-  const int c = b / a.parts, q = b - c * a.parts;
+  if (has_prod) b -= R;
+  if (!(a.roles & 2) || b >= R) return;
+  for (int w = b; w < nblk; w += R) {
+  const int c = w / a.parts, q = w - c * a.parts;
   const uint64_t v0 = per * q < vecs ? per * q : vecs, v1 = v0 + per < vecs ? v0 + per : vecs;
   const uint64_t base = a.hb[a.consumer];
   if (threadIdx.x == 0) {
@@ -250,12 +259,14 @@ __global__ void mp_kernel(MpArgs a) {
                             /*where=*/60, (uint32_t)a.consumer, (uint32_t)c);
   }
   __syncthreads();
-  if (verdict != kOk) return;
+  if (verdict != kOk) return;  // uniform over the block
   const float4* in = reinterpret_cast<const float4*>(base + a.dst_off + (uint64_t)c * a.chunk_bytes);
   float4* out = reinterpret_cast<float4*>(base + a.out_off + (uint64_t)c * a.chunk_bytes);
   for (size_t i = v0 + threadIdx.x; i < v1; i += blockDim.x) {
     float4 v = in[i];
     out[i] = make_float4(2.f * v.x, 2.f * v.y, 2.f * v.z, 2.f * v.w);
+  }
+  __syncthreads();  // everybody has read `verdict` before thread 0 writes the next one
   }
 }
 
@@ -355,11 +366,12 @@ int iris_k_device_barrier(const uint64_t* hb, uint64_t counter_off, uint64_t sta
 }
 
 // roles: 1 producer side only, 2 consumer side only, 3 both in one (cooperative) launch on one GPU.
-// parts: blocks per chunk (>= 1); arrive_off: uint32[nchunks] in the producer's heap, zero before the first call.
+// parts: slices per chunk (>= 1); blocks: thread blocks per role (0 or more than nchunks * parts: one per slice);
+// arrive_off: uint32[nchunks] in the producer's heap, zero before the first call.
 int iris_k_message_passing(const uint64_t* hb, uint64_t src_off, uint64_t dst_off, uint64_t out_off,
                            uint64_t flags_off, uint64_t status_off, uint64_t chunk_bytes, int nchunks, int producer,
                            int consumer, int roles, int use_put, uint32_t epoch, uint64_t timeout_ns, int block,
-                           int parts, uint64_t arrive_off, void* stream) {
+                           int parts, uint64_t arrive_off, int blocks, void* stream) {
   if (chunk_bytes % 16 != 0 || nchunks < 1 || parts < 1) return -2;
   if (roles == 3) {
     // Producer and consumer blocks wait on one another: all of them must be resident at once.  Lower `parts` to
@@ -369,13 +381,14 @@ int iris_k_message_passing(const uint64_t* hb, uint64_t src_off, uint64_t dst_of
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
         cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, mp_kernel, block, 0) != cudaSuccess)
       return -3;
-    const int fit = (sms * per_sm) / (2 * nchunks);
+    const int fit = (sms * per_sm) / 2;   // blocks per role that are resident together with the other role's
     if (fit < 1) return -4;
-    if (parts > fit) parts = fit;
+    if (blocks <= 0 || blocks > fit) blocks = fit;
   }
+  if (blocks <= 0 || blocks > nchunks * parts) blocks = nchunks * parts;
   MpArgs a{hb, src_off, dst_off, out_off, flags_off, status_off, chunk_bytes, timeout_ns, nchunks, producer, consumer,
-           roles, use_put, epoch, parts, arrive_off};
-  const int grid = (roles == 3 ? 2 : 1) * nchunks * parts;
+           roles, use_put, epoch, parts, arrive_off, blocks};
+  const int grid = (roles == 3 ? 2 : 1) * blocks;
   cudaError_t e;
   if (roles == 3) {
     // Producer and consumer blocks wait on one another: they must be co-resident.

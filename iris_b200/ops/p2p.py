@@ -144,7 +144,7 @@ class MessagePassing:
     """
 
     def __init__(self, ctx, nchunks: int, chunk_bytes: int, producer: int = 0, consumer: int = 1,
-                 timeout_ms: float = 1000.0, parts: Optional[int] = None):
+                 timeout_ms: float = 1000.0, parts: Optional[int] = None, blocks: Optional[int] = None):
         if chunk_bytes % 16:
             raise ValueError("chunk_bytes must be a multiple of 16")
         self.ctx, self.nchunks, self.chunk_bytes = ctx, nchunks, chunk_bytes
@@ -153,6 +153,8 @@ class MessagePassing:
         if parts is None:
             parts = max(1, min((2 * sms) // max(1, nchunks), chunk_bytes // (16 << 10)))
         self.parts = max(1, int(parts))
+        # thread blocks per role; fewer than one per slice makes the chunks complete in order (see mp_kernel)
+        self.blocks = 0 if blocks is None else int(blocks)
         self.arrive = ctx.zeros(nchunks, dtype=torch.int32)
         n = nchunks * chunk_bytes // 4
         self.src = ctx.zeros(n, dtype=torch.float32)
@@ -176,13 +178,13 @@ class MessagePassing:
             return
         lib = _native.kernels()
         lib.iris_k_message_passing.argtypes = [ctypes.c_void_p] + [ctypes.c_uint64] * 6 + [ctypes.c_int] * 5 + \
-            [ctypes.c_uint32, ctypes.c_uint64, ctypes.c_int, ctypes.c_int, ctypes.c_uint64, ctypes.c_void_p]
-        parts = self.parts   # with roles == 3 the launcher lowers it to what is resident at once
+            [ctypes.c_uint32, ctypes.c_uint64, ctypes.c_int, ctypes.c_int, ctypes.c_uint64, ctypes.c_int, ctypes.c_void_p]
+        parts = self.parts   # with roles == 3 the launcher lowers the block count to what is resident at once
         rc = lib.iris_k_message_passing(
             _hb(ctx), ctx.offset_of(self.src), ctx.offset_of(self.dst), ctx.offset_of(self.out),
             ctx.offset_of(self.flags), ctx.offset_of(ctx.status), self.chunk_bytes, self.nchunks, self.producer,
             self.consumer, roles, int(use_put), self.epoch, self.timeout_ns, block, parts,
-            ctx.offset_of(self.arrive), _stream(ctx, stream))
+            ctx.offset_of(self.arrive), self.blocks, _stream(ctx, stream))
         _check(rc, "message_passing")
 
 

@@ -120,7 +120,7 @@ __device__ __forceinline__ void acc_x8(float* acc, uint4 v, bool f16) {
 // Reduce-scatter reducer, one 128 x 256 part: sums `ns` inbox slots (local memory, `slot_rows` rows apart, first row
 // `part_row0`) over rows [mo, mo + 128) and columns [n0, n0 + 256) and writes the bf16 rows to `outp` (row pitch
 // `out_pitch` bytes).  Called by the 128 reducer threads (`rt` = 0..127).  A warp reads whole 512-byte rows (one
-// 16-byte load per lane), four rows of two slots in flight per thread.  Kept out of line so that its registers do
+// 16-byte load per lane), four rows of four slots in flight per thread.  Kept out of line so that its registers do
 // not add to those of the kernel's other roles.
 // With `bcast` (push two-shot all-reduce) every summed row is written to the outputs of all `W` ranks instead: `outp`
 // is then the offset of the output from the heap base and the row index is the global one (`mo + out_row_add`); on a
@@ -129,6 +129,7 @@ __device__ __forceinline__ void acc_x8(float* acc, uint4 v, bool f16) {
 // registers are already scarce.
 __device__ __noinline__ void rs_sum_part(const FusedGemmParams& p, int rank, int ns, int mo, int n0, int rt, bool f16,
                                          int part_row0) {
+  constexpr int kSlotsInFlight = 4;
   const int W = p.world, N = p.N, bn = p.bn, slot_rows = p.part_slot_rows;
   const bool bcast = p.rs_bcast != 0;
   const int out_row_add = bcast ? rank * p.rs_rows : 0;
@@ -155,10 +156,12 @@ __device__ __noinline__ void rs_sum_part(const FusedGemmParams& p, int rank, int
       for (int j = 0; j < 8; ++j) a4[u][j] = 0.f;
     const uint8_t* src = inbox + (uint64_t)(part_row0 + mo + r0) * row_bytes + (uint64_t)col * 2;
 #pragma unroll 1
-    for (int sl = 0; sl < ns; sl += 2) {
-      uint4 v[2][4];  // [slot][row]: eight 16-byte loads in flight
+    for (int sl = 0; sl < ns; sl += kSlotsInFlight) {
+      // [slot][row]: sixteen 16-byte loads in flight per thread, 32 KB per CTA: the loop is bound by the latency of
+      // local memory under load, and with 8 ranks a part is 512 KB
+      uint4 v[kSlotsInFlight][4];
 #pragma unroll
-      for (int q = 0; q < 2; ++q) {
+      for (int q = 0; q < kSlotsInFlight; ++q) {
         if (sl + q < ns) {
 #pragma unroll
           for (int u = 0; u < 4; ++u)
@@ -166,7 +169,7 @@ __device__ __noinline__ void rs_sum_part(const FusedGemmParams& p, int rank, int
         }
       }
 #pragma unroll
-      for (int q = 0; q < 2; ++q) {
+      for (int q = 0; q < kSlotsInFlight; ++q) {
         if (sl + q < ns) {
 #pragma unroll
           for (int u = 0; u < 4; ++u) acc_x8(a4[u], v[q][u], f16);

@@ -65,6 +65,7 @@ enum Site : uint32_t {
   kSiteEpiEntry = 31,
   kSiteEpiTileFlag = 32,
   kSitePullFull = 33,
+  kSiteEpiStreamK = 34,   // finisher of a split tile waiting for the other pieces (or a schedule out of bounds)
   kSiteDone = 40,
 };
 
@@ -574,10 +575,37 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
       const int tile = tile_of(w.tile);
       TileCoord tc = raster(tile, tiles_m, tiles_n, p.group_m);
       if (p.ag) tc.m_idx = ag_actual_m(tc.m_idx, tiles_per_shard, rank, W);
+      // Stream-K: a piece that covers only part of the tile's k-blocks.  The piece with the tile's first k-blocks (the
+      // last item of its unit's range) finishes the tile: it adds the other pieces, which their units parked as fp32 in
+      // workspace slots and counted on the tile's counter, to its own accumulator on the way out of tensor memory.
+      const bool whole = (w.kb0 == 0 && w.kb1 == kblocks) || p.ksplit > 1;  // a K-split piece is a slot of its own
+      int sk_add = 0;               // finisher: pieces to add from the workspace
+      int sk_slot = -1;             // other pieces: the slot to park the accumulator in
+      float4* sk_ws = nullptr;      // workspace of this CTA's part of the tile: [slot][group of 4 columns][row]
+      uint32_t* sk_cnt = nullptr;   // pieces of the tile parked so far
+      if (!whole) {
+        const int t_sk = tile - p.dp_tiles;
+        const long long S = (long long)(total_tiles - p.dp_tiles) * kblocks;
+        const int head = sk_unit_of((long long)t_sk * kblocks, S, p.sk_units);
+        const size_t part = (size_t)t_sk * CG + pr;
+        sk_ws = reinterpret_cast<float4*>(p.heap_base[rank] + p.ws_off) + part * kSkSlots * (size_t)(BM * BN / 4);
+        sk_cnt = flag_ptr(p, rank, p.sk_flag_base + (int)part);
+        if (w.kb0 > 0) sk_slot = unit - head - 1;
+        else sk_add = sk_unit_of((long long)(t_sk + 1) * kblocks - 1, S, p.sk_units) - head;
+      }
       // Uniform decision for the whole epilogue group: one thread waits, everybody reads the verdict.
       if (issuer) {
         bool ok = mbar_wait(acc_full_bar(acc), acc_phase, p.timeout_ns, abort_flag);
         if (!ok) record_status(status, kTimeout, kSiteEpiAccFull, rank, tile, acc);
+        if (ok && !whole && (sk_slot >= kSkSlots || sk_add > kSkSlots || (sk_slot < 0 && sk_add < 1))) {
+          record_status(status, kTimeout, kSiteEpiStreamK, rank, tile, sk_slot);  // a schedule the planner must not make
+          ok = false;
+        }
+        if (ok && sk_add > 0) {
+          // the other pieces were first in their units' ranges: normally this is already satisfied
+          ok = wait_until_ge(sk_cnt, (uint32_t)sk_add, p.timeout_ns, status, kSiteEpiStreamK, rank, tile) == kOk;
+          if (ok) *reinterpret_cast<volatile uint32_t*>(sk_cnt) = 0u;  // ready for the next call
+        }
         if (ok && !entered) {
           // Before the first push of this call: every peer must have entered the call.
           for (int i = 0; i < W && ok; ++i) {
@@ -608,15 +636,11 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
       const int keeper = p.rs_rows > 0 ? tile / rs_tpc : -1;  // reduce-scatter: the rank that keeps these rows
       const int y_st = (pulls ? (int)callv[3] + slot * p.part_slot_rows : 0) + y - (keeper > 0 ? keeper * p.rs_rows : 0);
 
-      // Stream-K: a piece that covers only part of the tile's k-blocks adds its fp32 accumulator into the tile's
-      // workspace and bumps the tile's k-block counter; the unit whose addition completes the count finishes the
-      // tile from the workspace (and leaves workspace and counter at zero for the next call).  Nobody waits.
       int groups_this_tile = 0;  // bulk groups the issuer committed for this tile
-      const bool whole = (w.kb0 == 0 && w.kb1 == kblocks) || p.ksplit > 1;  // a K-split piece is a slot of its own
-      float* ws_row = nullptr;
-      if (!whole) {
-        const size_t slot = (size_t)(tile - p.dp_tiles) * CG + pr;
-        ws_row = reinterpret_cast<float*>(p.heap_base[rank] + p.ws_off) + (slot * BM + row) * BN;
+      if (sk_slot >= 0) {
+        // Park this piece: 32 columns at a time out of tensor memory, four columns (16 bytes) per store, the 32 rows of
+        // a warp next to one another so that every store instruction writes one 512-byte run.
+        float4* dst = sk_ws + (size_t)sk_slot * (BM * BN / 4) + row;
 #pragma unroll 1
         for (int c = 0; c < bn / 32; ++c) {
           uint32_t v[32];
@@ -624,8 +648,8 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
           tmem_wait_ld();
 #pragma unroll
           for (int j = 0; j < 8; ++j)
-            red_add_v4_f32_gpu(ws_row + c * 32 + 4 * j, __uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
-                               __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+            __stcg(dst + (size_t)(c * 8 + j) * BM, make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                                              __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3])));
         }
         tc_fence_before();
         __syncwarp();
@@ -637,20 +661,10 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
           acc = 0;
           acc_phase ^= 1;
         }
-        __threadfence();  // this thread's additions are visible before the count says so
+        __threadfence();  // this thread's stores are visible before the count says so
         named_barrier_sync(1, 128);
-        if (issuer) {
-          uint32_t* cnt = flag_ptr(p, rank, p.sk_flag_base + (int)slot);
-          const uint32_t len = (uint32_t)(w.kb1 - w.kb0);
-          const uint32_t old = atomic_add<Sem::acq_rel, Scope::gpu>(cnt, len, 0, 0, p.heap_base);
-          const bool fin = old + len == (uint32_t)kblocks;
-          if (fin) *cnt = 0;
-          *epi_ok = fin ? 1u : 0u;
-        }
-        named_barrier_sync(1, 128);
-        const bool fin = *epi_ok != 0;
-        named_barrier_sync(1, 128);
-        if (!fin) continue;  // another unit completes this tile
+        if (issuer) atomic_add<Sem::release, Scope::gpu>(sk_cnt, 1u, 0, 0, p.heap_base);
+        continue;  // the unit with the tile's first k-blocks finishes it
       }
 #pragma unroll 1
       for (int c = 0; c < nchunks; ++c) {
@@ -677,28 +691,27 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
           }
         } else {
         uint32_t v[kEpiCols];
-        if (!whole) {
-          // finishing a split tile: the sum of all pieces is in the workspace; read it and put zeros back
-#pragma unroll
-          for (int j = 0; j < kEpiCols / 4; ++j) {
-            float4* q = reinterpret_cast<float4*>(ws_row + c * kEpiCols + 4 * j);
-            const float4 f = __ldcg(q);
-            __stcg(q, make_float4(0.f, 0.f, 0.f, 0.f));
-            v[4 * j] = __float_as_uint(f.x);
-            v[4 * j + 1] = __float_as_uint(f.y);
-            v[4 * j + 2] = __float_as_uint(f.z);
-            v[4 * j + 3] = __float_as_uint(f.w);
-          }
-        } else {
         const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN + c * kEpiCols;
         tmem_ld_32x32b_x32(taddr, v);
         tmem_ld_32x32b_x32(taddr + 32, v + 32);
         tmem_wait_ld();
+#pragma unroll 1
+        for (int s2 = 0; s2 < sk_add; ++s2) {
+          // finishing a split tile: add the pieces the other units parked (L2 reads, never through L1)
+          const float4* src = sk_ws + (size_t)s2 * (BM * BN / 4) + (size_t)(c * (kEpiCols / 4)) * BM + row;
+#pragma unroll
+          for (int j = 0; j < kEpiCols / 4; ++j) {
+            const float4 f = __ldcg(src + (size_t)j * BM);
+            v[4 * j] = __float_as_uint(__uint_as_float(v[4 * j]) + f.x);
+            v[4 * j + 1] = __float_as_uint(__uint_as_float(v[4 * j + 1]) + f.y);
+            v[4 * j + 2] = __float_as_uint(__uint_as_float(v[4 * j + 2]) + f.z);
+            v[4 * j + 3] = __float_as_uint(__uint_as_float(v[4 * j + 3]) + f.w);
+          }
         }
 #pragma unroll
         for (int j = 0; j < 32; ++j) o[j] = pack2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]), f16);
         }
-        if (whole && c == nchunks - 1) {
+        if (c == nchunks - 1) {
           // The accumulator has been read completely: hand it back to the MMA warp (of the leader CTA).
           tc_fence_before();
           __syncwarp();
@@ -774,7 +787,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
         }
         ebuf ^= 1;
       }
-      if (whole && ++acc == kAccBufs) {
+      if (++acc == kAccBufs) {
         acc = 0;
         acc_phase ^= 1;
       }
@@ -1386,6 +1399,8 @@ int iris_sched_ag_actual_m(int logical_m, int tiles_per_shard, int rank, int wor
   return ag_actual_m(logical_m, tiles_per_shard, rank, world);
 }
 int iris_sched_two_shot_owner(int tile, int units, int world) { return two_shot_owner(tile, units, world); }
+int iris_sched_sk_unit_of(long long x, long long S, int U) { return sk_unit_of(x, S, U); }
+int iris_sched_sk_slots() { return kSkSlots; }
 int iris_sched_rs_tile_of(int step, int rank, int world, int tiles_per_block) {
   return rs_tile_of(step, rank, world, tiles_per_block);
 }
@@ -1618,6 +1633,7 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
       p.dp_tiles = (d->dp_tiles < 0 || d->dp_tiles > tiles || d->sk_units <= 0) ? tiles : d->dp_tiles;
       p.sk_units = p.dp_tiles == tiles ? 0 : d->sk_units;
       if (p.sk_units > ctas_per_rank / cg) p.sk_units = ctas_per_rank / cg;  // only units that exist take a range
+      if (p.sk_units > 2 * (tiles - p.dp_tiles)) p.sk_units = 2 * (tiles - p.dp_tiles);  // ranges of half a tile or more
       p.sk_flag_base = d->sk_flag_base;
     }
     p.timeout_ns = d->timeout_ns;

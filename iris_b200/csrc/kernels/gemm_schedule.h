@@ -82,12 +82,22 @@ IRIS_SCHED_HD void tail_split_plan(int total_tiles, int units, int max_split, in
   }
 }
 
+// Stream-K bookkeeping.  The stream-K iterations [0, S) are cut into U ranges with boundaries floor(S * i / U)
+// (WorkIter below); the unit whose range holds iteration x is the largest i with floor(S * i / U) <= x.
+IRIS_SCHED_HD int sk_unit_of(long long x, long long S, int U) { return (int)(((x + 1) * U - 1) / S); }
+// A split tile is finished by the unit that computes its FIRST k-blocks: that piece is the last item of the unit's
+// range, while the tile's other pieces are the first items of the following units' ranges, so they are done (or
+// nearly) when the finisher asks for them.  Each of those other pieces is parked in a workspace slot of its own,
+// slot = (its unit) - (the finisher's unit) - 1.  kSkSlots bounds the slots a tile may need; the planner keeps the
+// ranges at least half a tile long, so a tile meets at most four ranges.
+constexpr int kSkSlots = 3;
+
 // Persistent + stream-K schedule.  Tiles [0, dp_tiles) are taken whole, round-robin over the units (the reference's
 // `for tile_id in range(pid, total_tiles, NUM_SMS)`, examples/07_gemm_all_scatter/gemm_all_scatter.py:153).  The
 // remaining tiles form one long sequence of (tile, k-block) iterations that is cut into `sk_units` equal ranges —
 // the stream-K decomposition the reference only sketches (matmul_wrapper.py:73-103 computes its statistics, the
-// kernels never use them).  A unit's range may end in the middle of a tile; such a tile is finished by whichever
-// unit adds the last missing k-blocks (see the epilogue).  With `ksplit` > 1 every tile is instead cut into `ksplit`
+// kernels never use them).  A unit's range may end in the middle of a tile; such a tile is finished by the unit that
+// holds its first k-blocks (see sk_unit_of above and the epilogue).  With `ksplit` > 1 every tile is instead cut into `ksplit`
 // fixed slices of its k-blocks and the (tile, piece) items go round-robin over the units.
 // With `tail_tiles` > 0 (whole-tile schedules only) the last `tail_tiles` tiles are not part of the round-robin: each
 // is cut into `tail_split` column pieces and the pieces go round-robin over the units after the whole tiles.

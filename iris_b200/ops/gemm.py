@@ -23,7 +23,7 @@ import torch
 
 from .. import _native
 from ..context import Iris
-from .gemm_plan import (BK, BM, BN, DTYPES, FLAG_HEADER, MODES, PUSH_KINDS, TILE_WIDTHS, GemmPlan,  # noqa: F401
+from .gemm_plan import (BK, BM, BN, DTYPES, FLAG_HEADER, MODES, PUSH_KINDS, SK_SLOTS, TILE_WIDTHS, GemmPlan,  # noqa: F401
                         plan_gemm)
 
 MAX_RANKS = 8
@@ -209,7 +209,8 @@ class FusedGemm:
         # ---- symmetric allocations (identical sequence on every rank) ----
         self.flags = [c.zeros(nflags, dtype=torch.int32) for c in self.ctxs]
         self.trace = [c.zeros((self.total_tiles * cta_group, 10), dtype=torch.int64) for c in self.ctxs] if trace else None
-        self.workspace = [c.zeros((max(sk_tiles, 1) * cta_group * BM, BN), dtype=torch.float32)
+        # stream-K: SK_SLOTS parked fp32 pieces per split tile part (never read before written: no clearing needed)
+        self.workspace = [c.empty((max(sk_tiles, 1) * cta_group * SK_SLOTS * BM, BN), dtype=torch.float32)
                           for c in self.ctxs] if sk_tiles else None
         self.c_cols = int(c_cols) if c_cols else self.N
         if pulls:

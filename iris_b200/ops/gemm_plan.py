@@ -15,6 +15,7 @@ MODES = {"store": 0, "reduce": 1, "one_shot": 2, "two_shot": 3}
 PUSH_KINDS = {"tma": 0, "tma_spread": 1, "stores": 2, "multimem": 3}
 DTYPES = {"bf16": 0, "fp16": 1, "fp32": 2, "int8": 3}   # ElemType of the kernel; fp32 is multiplied as tf32
 ELEM_BYTES = {"bf16": 2, "fp16": 2, "fp32": 4, "int8": 1}
+SK_SLOTS = 3                # workspace slots per split tile part (kSkSlots of gemm_schedule.h)
 FLAG_HEADER = 16            # flag words [0] arrival counter, [8 + r] entry flag of rank r; per-tile flags follow
 
 
@@ -154,7 +155,8 @@ def plan_gemm(M: int, N: int, K: int, world: int, num_local: int, mode: str, sms
         sk_tiles = T % units + (units if T >= units else 0)   # the ragged wave plus one full wave
         sk_tiles = min(sk_tiles, T)
         dp_tiles = T - sk_tiles
-        sk_units = max(1, min(units, (sk_tiles * kblocks) // 4))  # at least 4 k-blocks per unit
+        # ranges of at least half a tile: a split tile then meets at most four ranges, the finisher's and SK_SLOTS others
+        sk_units = max(1, min(units, 2 * sk_tiles))
     if dp_tiles == 0:
         units = sk_units if sk_units else min(units, max(T, 1 if not ag else 8))
     elif not sk_units:

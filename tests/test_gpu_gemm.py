@@ -193,8 +193,9 @@ def test_many_tiles_per_cta_pair():
 @pytest.mark.parametrize("m,n,k,cta_group", [(128, 4096, 1376, 1), (1, 4096, 1376, 1), (1024, 4096, 1376, 2),
                                                (2304, 2560, 2048, 2), (8192, 1792, 1024, 2), (640, 1280, 4160, 1)])
 def test_stream_k_schedule(m, n, k, cta_group):
-    """Tiles split by k-blocks across CTAs, fp32 fix-up through the workspace, last contributor finishes the tile;
-    called twice: the workspace and the counters must be back at zero after every call."""
+    """Tiles split by k-blocks across CTAs: the pieces that do not hold a tile's first k-blocks are parked as fp32 in
+    workspace slots, the unit with the first k-blocks adds them to its accumulator and finishes the tile; called
+    twice: the per-tile counters must be back at zero after every call."""
     a, bt = _rand((m, k), 1), _rand((n, k), 2, 0.05)
     ctx = iris.Iris.local_world(1, heap_size=256 << 20)[0]
     out = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
@@ -205,7 +206,8 @@ def test_stream_k_schedule(m, n, k, cta_group):
         op()
         op.check()
         _assert_close(out, a.float() @ bt.float().t())
-    assert float(op.workspace[0].abs().sum()) == 0.0
+    from iris_b200.ops.gemm_plan import FLAG_HEADER
+    assert int(op.flags[0][FLAG_HEADER:].abs().sum()) == 0
     op.close()
     ctx.close()
 

@@ -167,3 +167,43 @@ def test_column_split_tail_covers_every_piece_once_and_balances_the_last_wave(li
     # the whole tiles before the tail are whole waves: every unit has the same number of them
     if tail:
         assert (tiles - tail) % units == 0
+
+
+@pytest.mark.parametrize("m,n,k,cta_group", [(4096, 4096, 4096, 2), (4096, 4096, 4096, 1), (128, 4096, 1376, 1),
+                                             (1, 4096, 1376, 1), (1024, 8192, 8192, 2), (2304, 2560, 2048, 2),
+                                             (640, 1280, 4160, 1), (8192, 1792, 1024, 2), (300, 520, 200, 1)])
+def test_stream_k_pieces_know_their_slot_and_finisher(lib, m, n, k, cta_group):
+    """What the epilogue derives from `sk_unit_of`: the piece with a tile's first k-blocks is the last item of its unit's
+    range and expects exactly the tile's other pieces; those are computed by the following units, each the first item
+    of its range unless the range lies inside one tile, and their slots are 0 .. kSkSlots - 1 without repeats."""
+    from iris_b200.ops.gemm_plan import SK_SLOTS, plan_gemm
+    assert lib.iris_sched_sk_slots() == SK_SLOTS
+    lib.iris_sched_sk_unit_of.argtypes = [ctypes.c_longlong, ctypes.c_longlong, ctypes.c_int]
+    p = plan_gemm(m, n, k, 1, 1, "store", 148, stream_k=True, cta_group=cta_group)
+    if not p.sk_units:
+        pytest.skip("no ragged wave on this shape")
+    units = p.ctas_per_rank // p.cta_group
+    S = (p.total_tiles - p.dp_tiles) * p.kblocks
+    split = {}
+    for u in range(units):
+        items = _work(lib, u, units, p.total_tiles, p.kblocks, p.dp_tiles, p.sk_units, 1)
+        sk = [it for it in items if it[0] >= p.dp_tiles]
+        for i, (tile, kb0, kb1, _) in enumerate(sk):
+            if kb0 == 0 and kb1 == p.kblocks:
+                continue
+            t = tile - p.dp_tiles
+            head = lib.iris_sched_sk_unit_of(t * p.kblocks, S, p.sk_units)
+            last = lib.iris_sched_sk_unit_of((t + 1) * p.kblocks - 1, S, p.sk_units)
+            rec = split.setdefault(tile, dict(head=head, last=last, slots=[], finisher=None))
+            assert (rec["head"], rec["last"]) == (head, last)
+            if kb0 == 0:
+                assert u == head and i == len(sk) - 1, "the finisher's piece must close its unit's range"
+                rec["finisher"] = u
+            else:
+                assert head < u <= last
+                rec["slots"].append(u - head - 1)
+    assert split, "shape does not exercise split tiles"
+    for tile, rec in split.items():
+        assert rec["finisher"] == rec["head"]
+        assert sorted(rec["slots"]) == list(range(rec["last"] - rec["head"])), (tile, rec)
+        assert len(rec["slots"]) <= SK_SLOTS

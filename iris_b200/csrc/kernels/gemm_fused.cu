@@ -554,6 +554,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
     int ebuf = 0;
     const uint64_t evict_first = l2_policy_evict_first();
     int pending_tile = -1;  // one-/two-shot: tile whose partial is stored but not yet published
+    const bool publish_early = pulls && p.push_partials && W > 1;
     bool entered = !need_entry;
 
     // Make a stored partial tile known: one release fence, then a relaxed increment of the tile's flag on every rank
@@ -592,6 +593,14 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
         sk_cnt = flag_ptr(p, rank, p.sk_flag_base + (int)part);
         if (w.kb0 > 0) sk_slot = unit - head - 1;
         else sk_add = sk_unit_of((long long)(t_sk + 1) * kblocks - 1, S, p.sk_units) - head;
+      }
+      // Partials pushed into a peer's inbox: the previous tile is published here, before this tile's stores exist, so
+      // that the system-scope fence of the publish has no younger stores of this thread behind it (reduce-scatter on 4
+      // GPUs: 283 -> 278 us against publishing after the next tile's stores were issued).
+      if (publish_early && issuer && pending_tile >= 0) {
+        bulk_wait<0>();
+        publish_tile(pending_tile);
+        pending_tile = -1;
       }
       // Uniform decision for the whole epilogue group: one thread waits, everybody reads the verdict.
       if (issuer) {
@@ -797,7 +806,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
         // The partial tile is on its way into this rank's buffer.  Publishing needs its stores to be complete;
         // rather than wait for them now, publish the PREVIOUS tile (its stores are the ones before the up to four
         // groups just committed) and keep this one pending.  The reducer warps do the summing, concurrently.
-        if (issuer) {
+        if (issuer && !publish_early) {
           if (pending_tile >= 0) {
             // at most the groups just committed may still be pending
             if (groups_this_tile == 4) bulk_wait<4>();

@@ -82,7 +82,8 @@ def main():
     ap.add_argument("--launches", type=int, default=3)
     ap.add_argument("--cta_group", type=int, default=0)
     ap.add_argument("--bn", type=int, default=0, help="tile width: 64, 128 or 256 (0: the default, 256)")
-    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16"])
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16", "fp32", "int8"],
+                    help="fp32 (multiplied as tf32) and int8: workloads gemm, all_scatter and ag only")
     args = ap.parse_args()
     W = args.world
     if args.workload == "p2p":
@@ -94,9 +95,11 @@ def main():
     ranks = iris.Iris.local_world(W, heap_size=(1 << 30) // max(1, W // 2))
     g = torch.Generator(device="cuda").manual_seed(0)
 
-    dt = torch.float16 if args.dtype == "fp16" else torch.bfloat16
+    dt = {"fp16": torch.float16, "fp32": torch.float32, "int8": torch.int8}.get(args.dtype, torch.bfloat16)
 
     def rand(r, c):
+        if dt == torch.int8:
+            return torch.randint(-128, 128, (r, c), generator=g, device="cuda", dtype=torch.int32).to(dt)
         return (torch.randn((r, c), generator=g, device="cuda") * 0.02).to(dt)
     cg = args.cta_group or None
     bn = args.bn or None

@@ -146,10 +146,13 @@ def plan_gemm(M: int, N: int, K: int, world: int, num_local: int, mode: str, sms
     # ---- schedule: whole tiles round-robin, plus (stream-K) a tail of tiles split by k-blocks ----
     units = max(1, ctas // cta_group)
     if stream_k is None:
-        # Off unless asked for: on B200 the fix-up of a split tile (fp32 partials through L2 plus a second
-        # epilogue for the finishing unit) costs more than the ragged last wave it removes, for every shape
-        # measured so far (8192 x 1792 x 4096: 108 us against 101 us); the whole-tile schedule is the default.
-        stream_k = False
+        # On where it was measured to pay: kernels that keep or push whole tiles (store / reduce), 16-bit elements,
+        # at least one full wave of whole tiles before the split part, a ragged last wave.  One GPU, 8192 x N x 4096:
+        # N = 3584: 192 -> 181 us, N = 7168: 380 -> 364 us, N = 14336: 654 -> 650 us.  Off where every tile would be
+        # split (fewer tiles than units: 1024 x 8192 x 8192 loses 10 %), for the summing kernels (not measured) and with
+        # the all-gather prologue (tiles there wait for their rows; the combination is not tested).
+        stream_k = (mode in ("store", "reduce") and es == 2 and not ag and not tail_split and (ksplit or 1) == 1
+                    and T >= units and T % units != 0)
     dp_tiles, sk_units, sk_tiles = T, 0, 0
     if stream_k and T % units != 0:
         sk_tiles = T % units + (units if T >= units else 0)   # the ragged wave plus one full wave

@@ -589,7 +589,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
         const long long S = (long long)(total_tiles - p.dp_tiles) * kblocks;
         const int head = sk_unit_of((long long)t_sk * kblocks, S, p.sk_units);
         const size_t part = (size_t)t_sk * CG + pr;
-        sk_ws = reinterpret_cast<float4*>(p.heap_base[rank] + p.ws_off) + part * kSkSlots * (size_t)(BM * BN / 4);
+        sk_ws = reinterpret_cast<float4*>(p.heap_base[rank] + p.ws_off) + part * p.sk_slots * (size_t)(BM * BN / 4);
         sk_cnt = flag_ptr(p, rank, p.sk_flag_base + (int)part);
         if (w.kb0 > 0) sk_slot = unit - head - 1;
         else sk_add = sk_unit_of((long long)(t_sk + 1) * kblocks - 1, S, p.sk_units) - head;
@@ -606,7 +606,7 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
       if (issuer) {
         bool ok = mbar_wait(acc_full_bar(acc), acc_phase, p.timeout_ns, abort_flag);
         if (!ok) record_status(status, kTimeout, kSiteEpiAccFull, rank, tile, acc);
-        if (ok && !whole && (sk_slot >= kSkSlots || sk_add > kSkSlots || (sk_slot < 0 && sk_add < 1))) {
+        if (ok && !whole && (sk_slot >= p.sk_slots || sk_add > p.sk_slots || (sk_slot < 0 && sk_add < 1))) {
           record_status(status, kTimeout, kSiteEpiStreamK, rank, tile, sk_slot);  // a schedule the planner must not make
           ok = false;
         }
@@ -1383,6 +1383,7 @@ struct IrisGemmDesc {
   int dtype;                   // ElemType: 0 = bf16, 1 = fp16, 2 = fp32 as tf32, 3 = int8
   int push_kind;               // PushKind of the all-scatter epilogue
   int tail_tiles, tail_split;  // column-split tail of the raster (see tail_split_plan); 0 / 1 = off
+  int sk_slots;                // stream-K: workspace slots per split tile part (1 .. kSkSlots; 0 = kSkSlots)
   uint64_t c_off;              // symmetric offset of the C buffer (needed by push kinds 2 and 3)
   uint64_t zero_bytes;         // atomic all-reduce: bytes of the output (from c_off) the kernel clears itself; 0 = none
 };
@@ -1643,6 +1644,24 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
       p.sk_units = p.dp_tiles == tiles ? 0 : d->sk_units;
       if (p.sk_units > ctas_per_rank / cg) p.sk_units = ctas_per_rank / cg;  // only units that exist take a range
       if (p.sk_units > 2 * (tiles - p.dp_tiles)) p.sk_units = 2 * (tiles - p.dp_tiles);  // ranges of half a tile or more
+      // Slots a split tile needs: the units its k-blocks meet, less the finisher.  The caller sized the workspace for
+      // d->sk_slots of them (0: the maximum).
+      p.sk_slots = d->sk_slots > 0 ? d->sk_slots : kSkSlots;
+      if (p.sk_units > 0) {
+        const int kb = (d->K + 128 / es - 1) / (128 / es);
+        const long long S = (long long)(tiles - p.dp_tiles) * kb;
+        int need = 0;
+        for (int t = 0; t < tiles - p.dp_tiles; ++t) {
+          const int span = sk_unit_of((long long)(t + 1) * kb - 1, S, p.sk_units) - sk_unit_of((long long)t * kb, S, p.sk_units);
+          if (span > need) need = span;
+        }
+        if (need > p.sk_slots || p.sk_slots > kSkSlots) {
+          snprintf(g_err, sizeof(g_err), "stream-K: split tiles need %d workspace slots, %d given (at most %d)", need,
+                   p.sk_slots, kSkSlots);
+          delete plan;
+          return nullptr;
+        }
+      }
       p.sk_flag_base = d->sk_flag_base;
     }
     p.timeout_ns = d->timeout_ns;

@@ -102,7 +102,8 @@ struct FusedGemmParams {
   int dp_tiles;          // tiles [0, dp_tiles) are computed whole (tile = unit + i * units); the others are split
                          // by k-blocks over `sk_units` scheduling units (stream-K), 0 = no split tiles
   int sk_units;
-  int sk_flag_base;      // index of the per-(split tile, CTA of the group) k-block counters
+  int sk_flag_base;      // index of the per-(split tile, CTA of the group) counters of parked pieces
+  int sk_slots;          // workspace slots per split tile part (stride of the workspace; at most kSkSlots)
   int push_partials;     // one-shot: 1 = every rank's partial tile is pushed into a slot of every rank's inbox and summed
                          // from local memory; 0 = partials stay home and are fetched by the reducers
   int part_slot_rows;    // rows between consecutive inbox slots inside the tmC matrices

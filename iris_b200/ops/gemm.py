@@ -55,7 +55,7 @@ class _Desc(ctypes.Structure):
         ("push_partials", ctypes.c_int), ("part_slot_rows", ctypes.c_int), ("ksplit", ctypes.c_int),
         ("rs_rows", ctypes.c_int), ("rs_bcast", ctypes.c_int),
         ("bn", ctypes.c_int), ("dtype", ctypes.c_int), ("push_kind", ctypes.c_int),
-        ("tail_tiles", ctypes.c_int), ("tail_split", ctypes.c_int),
+        ("tail_tiles", ctypes.c_int), ("tail_split", ctypes.c_int), ("sk_slots", ctypes.c_int),
         ("c_off", ctypes.c_uint64), ("zero_bytes", ctypes.c_uint64),
     ]
 
@@ -210,7 +210,7 @@ class FusedGemm:
         self.flags = [c.zeros(nflags, dtype=torch.int32) for c in self.ctxs]
         self.trace = [c.zeros((self.total_tiles * cta_group, 10), dtype=torch.int64) for c in self.ctxs] if trace else None
         # stream-K: SK_SLOTS parked fp32 pieces per split tile part (never read before written: no clearing needed)
-        self.workspace = [c.empty((max(sk_tiles, 1) * cta_group * SK_SLOTS * BM, BN), dtype=torch.float32)
+        self.workspace = [c.empty((max(sk_tiles, 1) * cta_group * max(pl.sk_slots, 1) * BM, BN), dtype=torch.float32)
                           for c in self.ctxs] if sk_tiles else None
         self.c_cols = int(c_cols) if c_cols else self.N
         if pulls:
@@ -281,6 +281,7 @@ class FusedGemm:
         d.dp_tiles = self.dp_tiles if self.sk_units else -1
         d.sk_units = self.sk_units
         d.sk_flag_base = FLAG_HEADER + tile_flags + self.world * chunks_per_shard
+        d.sk_slots = pl.sk_slots
         d.ws_off = c0.offset_of(self.workspace[0]) if self.workspace else 0
         d.bn, d.dtype = pl.bn, DTYPES[_TORCH_DTYPES[self.dtype]]
         d.tail_tiles, d.tail_split = pl.tail_tiles, pl.tail_split

@@ -58,11 +58,18 @@ class GemmPlan:
     bn: int = BN            # tile width in columns
     tail_tiles: int = 0     # tiles at the end of the raster that are cut into column pieces ...
     tail_split: int = 1     # ... and into how many (1: none)
+    sk_slots: int = 0       # stream-K: workspace slots per split tile part (the units a tile meets, less the finisher)
 
     @property
     def flags_per_call(self) -> int:
         """What one call adds to a per-tile flag (arrivals from all ranks and pieces)."""
         return self.world * self.ksplit
+
+
+def sk_unit_of(x: int, S: int, U: int) -> int:
+    """The unit whose stream-K range holds iteration ``x`` when ``S`` iterations are cut into ``U`` ranges with
+    boundaries ``S * i // U`` (``sk_unit_of`` of ``csrc/kernels/gemm_schedule.h``)."""
+    return ((x + 1) * U - 1) // S
 
 
 def tail_split_plan(total_tiles: int, units: int, max_split: int) -> Tuple[int, int]:
@@ -197,6 +204,15 @@ def plan_gemm(M: int, N: int, K: int, world: int, num_local: int, mode: str, sms
     chunks_per_shard = (M // world) // BM if ag else 0
     tile_flags = T * cta_group if pulls else 0
     sk_flags = sk_tiles * cta_group
+    # workspace slots of a split tile: one per unit its k-blocks meet, less the unit that finishes it
+    sk_slots = 0
+    if sk_units:
+        S = sk_tiles * kblocks
+        sk_slots = max(sk_unit_of((t + 1) * kblocks - 1, S, sk_units) - sk_unit_of(t * kblocks, S, sk_units)
+                       for t in range(sk_tiles))
+        sk_slots = max(1, sk_slots)
+        if sk_slots > SK_SLOTS:
+            raise ValueError("stream-K schedule needs more workspace slots per tile than the kernel addresses")
     nflags = FLAG_HEADER + tile_flags + world * chunks_per_shard + sk_flags
     if pulls:
         # One matrix per rank holds both partial buffers (call parity) and, unless the caller brings its own, the
@@ -225,4 +241,4 @@ def plan_gemm(M: int, N: int, K: int, world: int, num_local: int, mode: str, sms
                     tile_flags=tile_flags, sk_flags=sk_flags, nflags=nflags, rows=rows, slot_rows=mp, slots=slots,
                     regions=regions, c_rows=c_rows, part_row0=part_row0, out_row0=out_row0, out_rows=out_rows,
                     bcast=bool(bcast) and bool(rs_rows), bn=bn,
-                    tail_tiles=tail_tiles, tail_split=tsplit)
+                    tail_tiles=tail_tiles, tail_split=tsplit, sk_slots=sk_slots)

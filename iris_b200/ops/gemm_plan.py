@@ -6,6 +6,7 @@ full waves, split tiles) and the buffer set-up of ``examples/09_gemm_one_shot_al
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Optional, Tuple
 
@@ -156,10 +157,16 @@ def plan_gemm(M: int, N: int, K: int, world: int, num_local: int, mode: str, sms
         # On where it was measured to pay: kernels that keep or push whole tiles (store / reduce), 16-bit elements,
         # at least one full wave of whole tiles before the split part, a ragged last wave.  One GPU, 8192 x N x 4096:
         # N = 3584: 192 -> 181 us, N = 7168: 380 -> 364 us, N = 14336: 654 -> 650 us.  Off where every tile would be
-        # split (fewer tiles than units: 1024 x 8192 x 8192 loses 10 %), for the summing kernels (not measured) and with
-        # the all-gather prologue (tiles there wait for their rows; the combination is not tested).
-        stream_k = (mode in ("store", "reduce") and es == 2 and not ag and not tail_split and (ksplit or 1) == 1
-                    and T >= units and T % units != 0)
+        # split (fewer tiles than units: 1024 x 8192 x 8192 loses 10 %) and for the summing kernels (not measured).
+        # The environment variable IRIS_STREAM_K overrides this default for A/B runs of whole programs: 0 = never,
+        # 1 = wherever the kernel can (also with fewer tiles than units).
+        eligible = mode in ("store", "reduce") and es == 2 and not tail_split and (ksplit or 1) == 1
+        stream_k = eligible and T >= units and T % units != 0
+        env = os.environ.get("IRIS_STREAM_K")
+        if env == "0":
+            stream_k = False
+        elif env == "1":
+            stream_k = eligible
     dp_tiles, sk_units, sk_tiles = T, 0, 0
     if stream_k and T % units != 0:
         sk_tiles = T % units + (units if T >= units else 0)   # the ragged wave plus one full wave

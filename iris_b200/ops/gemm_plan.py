@@ -162,6 +162,11 @@ def plan_gemm(M: int, N: int, K: int, world: int, num_local: int, mode: str, sms
         # 1 = wherever the kernel can (also with fewer tiles than units).
         eligible = mode in ("store", "reduce") and es == 2 and not tail_split and (ksplit or 1) == 1
         stream_k = eligible and T >= units and T % units != 0
+        if stream_k and store_all and world > 1:
+            # Tiles pushed to every peer: where the pushes, not the MMAs, set the time, the units' ranges ending together
+            # only bunches the last pushes (4 GPUs, 8192 x 3584 x 4096 per rank: 320 -> 332 us with stream-K; 2 GPUs,
+            # compute-bound: 393 -> 381 us).  Rough rates: 1.4 PFLOP/s, 700 GB/s out of every GPU.
+            stream_k = 2.0 * M * N * K / 1.4e15 > (world - 1) * M * N * es / 700e9
         env = os.environ.get("IRIS_STREAM_K")
         if env == "0":
             stream_k = False

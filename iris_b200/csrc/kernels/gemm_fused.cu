@@ -1,6 +1,12 @@
-// gemm_fused.cu — persistent, warp-specialised bf16 GEMM for sm_100a with the collective fused into it.
+// gemm_fused.cu — persistent, warp-specialised GEMM for sm_100a with the collective fused into it.
 //
-//   C[M, N] = A[M, K] * B[N, K]^T        (both operands K-contiguous, fp32 accumulation, bf16 output)
+//   C[M, N] = A[M, K] * B[N, K]^T        (both operands K-contiguous; C has the operands' element type)
+//
+// Element types (template parameter ET): bf16 and fp16 with fp32 accumulation for every mode; float32 multiplied as
+// tf32 and int8 with 32-bit integer accumulation (low 8 bits stored) for the store mode.  A ring stage and an
+// epilogue sub-tile row are 128 bytes for every type, so "128 x 64" below reads 128 x 32 for float32 and 128 x 128 for
+// int8.  Nothing in the launch arguments changes from call to call (the call number lives in device memory), so a
+// launch can be captured into a CUDA graph.
 //
 // Data path per CTA (one CTA per SM; 128 x 256 output tile per CTA, or 256 x 256 per pair of CTAs):
 //   warp 0      TMA producer: cp.async.bulk.tensor loads of the A (128 x 64) and B slices into a shared-memory ring,
@@ -8,7 +14,7 @@
 //   warp 1      one thread issues tcgen05.mma (M128 N256 K16 with cta_group::1, M256 N256 K16 with cta_group::2);
 //               accumulators live in tensor memory, two of them, so the epilogue of tile i overlaps the main loop
 //               of tile i+1.
-//   warps 2-5   epilogue: tcgen05.ld -> bf16 -> swizzled shared memory -> the collective:
+//   warps 2-5   epilogue: tcgen05.ld -> output type -> swizzled shared memory -> the collective:
 //                 store     TMA store of the tile into the C buffer of every rank       (GEMM + all-scatter)
 //                 reduce    TMA reduce-add of the tile into the C buffer of every rank  (GEMM + atomic all-reduce)
 //                 one-shot  tile -> partial buffer (own, or pushed into an inbox slot of every rank) + per-tile flag

@@ -157,11 +157,12 @@ def plan_gemm(M: int, N: int, K: int, world: int, num_local: int, mode: str, sms
         # On where it was measured to pay: kernels that keep or push whole tiles (store / reduce), 16-bit elements,
         # at least one full wave of whole tiles before the split part, a ragged last wave.  One GPU, 8192 x N x 4096:
         # N = 3584: 192 -> 181 us, N = 7168: 380 -> 364 us, N = 14336: 654 -> 650 us.  Off where every tile would be
-        # split (fewer tiles than units: 1024 x 8192 x 8192 loses 10 %) and for the summing kernels (not measured).
+        # split (fewer than two waves of tiles: 1024 x 8192 x 8192 loses 10 - 60 %) and for the summing kernels (not
+        # measured).
         # The environment variable IRIS_STREAM_K overrides this default for A/B runs of whole programs: 0 = never,
         # 1 = wherever the kernel can (also with fewer tiles than units).
         eligible = mode in ("store", "reduce") and es == 2 and not tail_split and (ksplit or 1) == 1
-        stream_k = eligible and T >= units and T % units != 0
+        stream_k = eligible and T >= 2 * units and T % units != 0   # a wave of whole tiles stays in front of the split part
         if stream_k and store_all and world > 1:
             # Tiles pushed to every peer: where the pushes, not the MMAs, set the time, the units' ranges ending together
             # only bunches the last pushes (4 GPUs, 8192 x 3584 x 4096 per rank: 320 -> 332 us with stream-K; 2 GPUs,

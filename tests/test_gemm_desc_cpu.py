@@ -239,3 +239,33 @@ def test_planner_element_types():
     # a tail piece is a whole number of sub-tiles: int8 tiles of 256 columns split into two at most
     p = plan_gemm(2560, 2048, 256, dtype="int8", tail_split=4, ctas_per_rank=148, cta_group=1, **kw)
     assert p.tail_split in (1, 2)
+
+
+def test_stream_k_default_rule(monkeypatch):
+    """Stream-K is the default exactly where it was measured to pay: store / reduce kernels, 16-bit elements, at least
+    one full wave of whole tiles before a ragged last one, and (with tiles pushed to peers) compute time above push
+    time.  `stream_k=` and the environment variable IRIS_STREAM_K override it."""
+    monkeypatch.delenv("IRIS_STREAM_K", raising=False)
+    one = dict(world=1, num_local=1, mode="store", sms=148)
+    assert plan_gemm(8192, 3584, 4096, **one).sk_units > 0              # 6.05 waves of single-CTA tiles
+    assert plan_gemm(8192, 14336, 4096, **one).sk_units > 0             # 24.2 waves of pair tiles
+    p = plan_gemm(8192, 14336, 4096, **one)
+    assert p.dp_tiles % (p.ctas_per_rank // p.cta_group) == 0 and p.sk_tiles == p.total_tiles - p.dp_tiles
+    assert p.sk_slots == 1                                              # ranges longer than a tile: one parked piece
+    assert plan_gemm(1024, 8192, 8192, **one).sk_units == 0             # fewer than two waves: every tile would split
+    assert plan_gemm(2048, 2048, 8192, **one).sk_units == 0             # fewer tiles than units
+    assert plan_gemm(8192, 3584, 4096, dtype="int8", **one).sk_units == 0
+    assert plan_gemm(8192, 3584, 4096, stream_k=False, **one).sk_units == 0
+    for mode in ("one_shot", "two_shot"):
+        assert plan_gemm(8192, 4096, 1376, world=8, num_local=1, mode=mode, sms=148).sk_units == 0
+    # tiles pushed to peers: on while the MMAs set the time (2 ranks), off where the pushes do (4 and 8 ranks)
+    assert plan_gemm(8192, 7168, 4096, world=2, num_local=1, mode="store", sms=148, store_all=True).sk_units > 0
+    assert plan_gemm(8192, 3584, 4096, world=4, num_local=1, mode="store", sms=148, store_all=True).sk_units == 0
+    assert plan_gemm(8192, 1792, 4096, world=8, num_local=1, mode="store", sms=148, store_all=True).sk_units == 0
+    # the all-gather prologue keeps the default (tiles wait for their rows either way)
+    assert plan_gemm(16384, 3072, 4096, world=2, num_local=1, mode="store", sms=148, ag=True).sk_units > 0
+    monkeypatch.setenv("IRIS_STREAM_K", "0")
+    assert plan_gemm(8192, 3584, 4096, **one).sk_units == 0
+    monkeypatch.setenv("IRIS_STREAM_K", "1")
+    assert plan_gemm(1024, 8192, 8192, **one).sk_units > 0
+    assert plan_gemm(8192, 3584, 4096, stream_k=False, **one).sk_units == 0   # an explicit argument wins

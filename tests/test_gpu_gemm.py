@@ -454,14 +454,16 @@ def test_no_kernel_writes_outside_its_buffers():
 @pytest.mark.parametrize("world", [2, 4])
 @pytest.mark.parametrize("n_local", [256, 1536])
 def test_all_gather_gemm_emulated(world, cta_group, n_local):
-    """n_local = 1536 gives more tiles than scheduling units with a ragged last wave: the default schedule is then
-    stream-K, whose split tiles wait for their rows' chunk flags like whole tiles do."""
+    """n_local = 1536 gives more tiles than scheduling units with a ragged last wave and runs under the stream-K
+    schedule (the default for larger problems of this kind), whose split tiles wait for their rows' chunk flags like
+    whole tiles do."""
     m, k = 2048, 512
     ms = m // world
     ranks = iris.Iris.local_world(world, heap_size=256 << 20)
     a_full = _rand((m, k), 8)
     bts = [_rand((n_local, k), 20 + r, 0.05) for r in range(world)]
-    op = G.all_gather_gemm(ranks, m, bts, ag_slices=4, cta_group=cta_group)
+    op = G.all_gather_gemm(ranks, m, bts, ag_slices=4, cta_group=cta_group,
+                           stream_k=True if n_local == 1536 else None)
     assert (op.sk_units > 0) == (n_local == 1536)
     for call in range(2):
         for r in range(world):  # every rank owns only its rows; the kernel gathers the rest

@@ -38,6 +38,26 @@ def run_p2p(args):
     ranks[0].close()
 
 
+def run_mp(args):
+    """The message-passing kernel with producer and consumer blocks in ONE cooperative launch on one GPU (64 chunks of
+    1 MB): the copy, the per-slice publish and the consumer's pass, without a link in between."""
+    from iris_b200.ops import p2p
+    ranks = iris.Iris.local_world(2, heap_size=1 << 29)
+    # the same allocations, in the same order, on both simulated ranks (symmetric offsets)
+    mps = [p2p.MessagePassing(r, nchunks=64, chunk_bytes=1 << 20, producer=0, consumer=1, timeout_ms=2000)
+           for r in ranks]
+    mps[0].src.copy_(torch.arange(mps[0].src.numel(), device="cuda", dtype=torch.float32) % 1000)
+    for _ in range(args.launches):
+        for m in mps:
+            m.epoch += 1
+        mps[0].run(roles=3, advance=False)
+    torch.cuda.synchronize()
+    ranks[1].check_status()
+    assert torch.equal(mps[1].out, 2 * mps[0].src)
+    print(f"message passing on one GPU: {args.launches} hand-offs of 64 x 1 MB, {mps[0].parts} slices per chunk")
+    ranks[0].close()
+
+
 def run_elementwise(args):
     """RMSNorm, SwiGLU and residual add on 16384 x 4096 (x 11008) bf16 activations: memory-bound kernels."""
     from iris_b200.ops import elementwise as E
@@ -74,7 +94,7 @@ def run_attention(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--workload", default="gemm", choices=["gemm", "all_scatter", "atomic", "one_shot", "two_shot", "reduce_scatter", "ag", "p2p",
-                             "elementwise", "attention"])
+                             "mp", "elementwise", "attention"])
     ap.add_argument("--world", type=int, default=1)
     ap.add_argument("-m", type=int, default=8192)
     ap.add_argument("-n", type=int, default=3584)
@@ -88,6 +108,8 @@ def main():
     W = args.world
     if args.workload == "p2p":
         return run_p2p(args)
+    if args.workload == "mp":
+        return run_mp(args)
     if args.workload == "elementwise":
         return run_elementwise(args)
     if args.workload == "attention":

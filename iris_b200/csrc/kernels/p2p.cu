@@ -190,7 +190,10 @@ struct MpArgs {
   int producer, consumer;
   int roles;            // bit 0: this launch runs the producer blocks, bit 1: the consumer blocks
   int use_put;          // 1: block-cooperative put; 0: per-thread load + store of floats
-  uint32_t epoch;       // flag value that marks "chunk of this call has landed"
+  uint32_t epoch;       // flag value that marks "chunk of this call has landed"; 0: both sides count their calls in
+                        // device memory (word [nchunks] of arrive / flags: calls completed, word [nchunks + 1]:
+                        // blocks of the running launch that have left), so that a launch has no per-call argument
+                        // and can be replayed from a CUDA graph
   int parts;            // blocks per chunk: every chunk is cut into `parts` slices of whole 16-byte vectors
   uint64_t arrive_off;  // uint32 per chunk, in the producer's heap: slices of the chunk copied so far (back at 0
                         // when the chunk's flag has been raised)
@@ -207,11 +210,25 @@ struct MpArgs {
 // and puts the counter back to zero.  Consumer: every block of the chunk waits (bounded, acquire) on the chunk's flag
 // in its own memory, then writes out = 2 * landed for its slice.
 __global__ void mp_kernel(MpArgs a) {
-  __shared__ uint32_t verdict;
+  __shared__ uint32_t verdict, epoch_s;
   int b = blockIdx.x;
   const int nblk = a.nchunks * a.parts;
   const int R = a.blocks;
   const bool has_prod = a.roles & 1;
+  const bool producing = has_prod && b < R;
+  // this side's call counter: the producer's next to its arrival counters, the consumer's next to its flags
+  uint32_t* calls = reinterpret_cast<uint32_t*>(producing ? a.hb[a.producer] + a.arrive_off : a.hb[a.consumer] + a.flags_off) +
+                    a.nchunks;
+  if (threadIdx.x == 0) epoch_s = a.epoch ? a.epoch : *reinterpret_cast<volatile uint32_t*>(calls) + 1u;
+  __syncthreads();
+  const uint32_t epoch = epoch_s;
+  // the last block of a side to leave advances that side's counter (nothing to do with a host-given epoch)
+  auto leave = [&]() {
+    if (a.epoch == 0 && threadIdx.x == 0 && atomicAdd(calls + 1, 1u) + 1u == (uint32_t)R) {
+      *reinterpret_cast<volatile uint32_t*>(calls + 1) = 0u;
+      *reinterpret_cast<volatile uint32_t*>(calls) = epoch;
+    }
+  };
   // slice q of a chunk: whole 16-byte vectors, the last slice takes the remainder
   const uint64_t vecs = a.chunk_bytes / 16;
   const uint64_t per = (vecs + a.parts - 1) / a.parts;
@@ -241,10 +258,11 @@ __global__ void mp_kernel(MpArgs a) {
       if (old + 1 == (uint32_t)a.parts) {
         *cnt = 0;  // every slice has arrived: nobody touches the counter again in this call
         uint32_t* flag = reinterpret_cast<uint32_t*>(base + a.flags_off) + c;
-        signal_set(flag, a.epoch, a.producer, a.consumer, a.hb);
+        signal_set(flag, epoch, a.producer, a.consumer, a.hb);
       }
     }
    }
+    leave();
     return;
   }
   if (has_prod) b -= R;
@@ -255,11 +273,14 @@ __global__ void mp_kernel(MpArgs a) {
   const uint64_t base = a.hb[a.consumer];
   if (threadIdx.x == 0) {
     const uint32_t* flag = reinterpret_cast<const uint32_t*>(base + a.flags_off) + c;
-    verdict = wait_until_ge(flag, a.epoch, a.timeout_ns, reinterpret_cast<StatusBlock*>(base + a.status_off),
+    verdict = wait_until_ge(flag, epoch, a.timeout_ns, reinterpret_cast<StatusBlock*>(base + a.status_off),
                             /*where=*/60, (uint32_t)a.consumer, (uint32_t)c);
   }
   __syncthreads();
-  if (verdict != kOk) return;  // uniform over the block
+  if (verdict != kOk) {  // uniform over the block
+    leave();
+    return;
+  }
   const float4* in = reinterpret_cast<const float4*>(base + a.dst_off + (uint64_t)c * a.chunk_bytes);
   float4* out = reinterpret_cast<float4*>(base + a.out_off + (uint64_t)c * a.chunk_bytes);
   for (size_t i = v0 + threadIdx.x; i < v1; i += blockDim.x) {
@@ -268,6 +289,7 @@ __global__ void mp_kernel(MpArgs a) {
   }
   __syncthreads();  // everybody has read `verdict` before thread 0 writes the next one
   }
+  leave();
 }
 
 // Device-side barrier across ranks: one thread adds 1 to counter[0] of every rank (release, system scope),

@@ -144,7 +144,8 @@ class MessagePassing:
     """
 
     def __init__(self, ctx, nchunks: int, chunk_bytes: int, producer: int = 0, consumer: int = 1,
-                 timeout_ms: float = 1000.0, parts: Optional[int] = None, blocks: Optional[int] = None):
+                 timeout_ms: float = 1000.0, parts: Optional[int] = None, blocks: Optional[int] = None,
+                 device_epoch: bool = False):
         if chunk_bytes % 16:
             raise ValueError("chunk_bytes must be a multiple of 16")
         self.ctx, self.nchunks, self.chunk_bytes = ctx, nchunks, chunk_bytes
@@ -155,12 +156,16 @@ class MessagePassing:
         self.parts = max(1, int(parts))
         # thread blocks per role; fewer than one per slice makes the chunks complete in order (see mp_kernel)
         self.blocks = 0 if blocks is None else int(blocks)
-        self.arrive = ctx.zeros(nchunks, dtype=torch.int32)
+        # two words beyond the per-chunk entries: this side's call counter and its count of blocks that have left
+        self.arrive = ctx.zeros(nchunks + 2, dtype=torch.int32)
         n = nchunks * chunk_bytes // 4
         self.src = ctx.zeros(n, dtype=torch.float32)
         self.dst = ctx.zeros(n, dtype=torch.float32)
         self.out = ctx.zeros(n, dtype=torch.float32)
-        self.flags = ctx.zeros(nchunks, dtype=torch.int32)
+        self.flags = ctx.zeros(nchunks + 2, dtype=torch.int32)
+        # device_epoch: both sides count their calls in device memory instead of taking the call number as a launch
+        # argument, so that `run()` can be captured into a CUDA graph and replayed (every replay is one hand-off)
+        self.device_epoch = bool(device_epoch)
         self.timeout_ns = int(timeout_ms * 1e6)
         self.epoch = 0
         ctx.barrier()   # construction is collective: the producer must not raise a flag its owner has yet to zero
@@ -183,7 +188,7 @@ class MessagePassing:
         rc = lib.iris_k_message_passing(
             _hb(ctx), ctx.offset_of(self.src), ctx.offset_of(self.dst), ctx.offset_of(self.out),
             ctx.offset_of(self.flags), ctx.offset_of(ctx.status), self.chunk_bytes, self.nchunks, self.producer,
-            self.consumer, roles, int(use_put), self.epoch, self.timeout_ns, block, parts,
+            self.consumer, roles, int(use_put), 0 if self.device_epoch else self.epoch, self.timeout_ns, block, parts,
             ctx.offset_of(self.arrive), self.blocks, _stream(ctx, stream))
         _check(rc, "message_passing")
 

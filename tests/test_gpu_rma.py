@@ -161,6 +161,39 @@ def test_message_passing_one_launch(ranks, use_put):
         assert torch.equal(mp[1].out, 2 * mp[0].src), f"epoch {epoch}"
 
 
+def test_message_passing_replays_from_a_cuda_graph(ranks):
+    """device_epoch=True: both sides count their calls in device memory, the launch has no per-call argument, and a
+    captured hand-off replays with new data (ordinary calls before and after)."""
+    two = ranks[:2]
+    mp = [p2p.MessagePassing(c, nchunks=8, chunk_bytes=1 << 18, device_epoch=True, blocks=16) for c in two]
+
+    def fill(seed):
+        mp[0].src.copy_(torch.arange(mp[0].src.numel(), device="cuda", dtype=torch.float32) % 997 + seed)
+
+    def check():
+        torch.cuda.synchronize()
+        two[1].check_status()
+        assert torch.equal(mp[1].out, 2 * mp[0].src)
+
+    fill(1)
+    mp[0].run(roles=3)
+    check()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        mp[0].run(roles=3)
+    for i in range(3):
+        fill(10 + i)
+        mp[1].out.zero_()
+        graph.replay()
+        check()
+    fill(50)
+    mp[0].run(roles=3)
+    check()
+    n = mp[0].nchunks
+    assert int(mp[0].arrive[n]) == 5 and int(mp[1].flags[n]) == 5      # calls counted on both sides
+    assert int(mp[0].arrive[n + 1]) == 0 and int(mp[1].flags[n + 1]) == 0
+
+
 def test_bounded_wait_reports_timeout(ranks):
     """A flag that nothing sets: the consumer's wait runs out after 1 ms, the kernel returns normally and the
     host reads a time-out status; the context stays usable."""

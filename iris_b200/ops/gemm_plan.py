@@ -162,7 +162,9 @@ def plan_gemm(M: int, N: int, K: int, world: int, num_local: int, mode: str, sms
         # The environment variable IRIS_STREAM_K overrides this default for A/B runs of whole programs: 0 = never,
         # 1 = wherever the kernel can (also with fewer tiles than units).
         eligible = mode in ("store", "reduce") and es == 2 and not tail_split and (ksplit or 1) == 1
-        stream_k = eligible and T >= 2 * units and T % units != 0   # a wave of whole tiles stays in front of the split part
+        # a wave of whole tiles stays in front of the split part, and the last wave is at most half full (fuller ones
+        # measured neutral: 8192 x 5120 x 4096, 0.65 of a wave: 245 - 249 -> 247 us)
+        stream_k = eligible and T >= 2 * units and 0 < T % units <= units // 2
         if stream_k and store_all and world > 1:
             # Tiles pushed to every peer: where the pushes, not the MMAs, set the time, the units' ranges ending together
             # only bunches the last pushes (4 GPUs, 8192 x 3584 x 4096 per rank: 320 -> 332 us with stream-K; 2 GPUs,

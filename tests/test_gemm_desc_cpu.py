@@ -254,6 +254,7 @@ def test_stream_k_default_rule(monkeypatch):
     assert p.sk_slots == 1                                              # ranges longer than a tile: one parked piece
     assert plan_gemm(1024, 8192, 8192, **one).sk_units == 0             # fewer than two waves: every tile would split
     assert plan_gemm(2048, 2048, 8192, **one).sk_units == 0             # fewer tiles than units
+    assert plan_gemm(8192, 5120, 4096, **one).sk_units == 0             # last wave 0.65 full: nothing to gain
     assert plan_gemm(8192, 3584, 4096, dtype="int8", **one).sk_units == 0
     assert plan_gemm(8192, 3584, 4096, stream_k=False, **one).sk_units == 0
     for mode in ("one_shot", "two_shot"):

@@ -314,7 +314,8 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
     *ag_ok = 1;
     *never = 0;
     {
-      const uint32_t call = *reinterpret_cast<volatile uint32_t*>(flag_ptr(p, p.rank0 + blockIdx.x / p.ctas_per_rank, 2)) + 1u;
+      const int my_rank = p.rank0 + blockIdx.x / p.ctas_per_rank;
+      const uint32_t call = *reinterpret_cast<volatile uint32_t*>(flag_ptr(p, my_rank, 2)) + 1u;
       callv[0] = call;
       callv[1] = p.per_flag * call;
       callv[2] = call * (uint32_t)p.world * (uint32_t)p.ctas_per_rank;
@@ -705,26 +706,26 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
             }
           }
         } else {
-        uint32_t v[kEpiCols];
-        const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN + c * kEpiCols;
-        tmem_ld_32x32b_x32(taddr, v);
-        tmem_ld_32x32b_x32(taddr + 32, v + 32);
-        tmem_wait_ld();
+          uint32_t v[kEpiCols];
+          const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN + c * kEpiCols;
+          tmem_ld_32x32b_x32(taddr, v);
+          tmem_ld_32x32b_x32(taddr + 32, v + 32);
+          tmem_wait_ld();
 #pragma unroll 1
-        for (int s2 = 0; s2 < sk_add; ++s2) {
-          // finishing a split tile: add the pieces the other units parked (L2 reads, never through L1)
-          const float4* src = sk_ws + (size_t)s2 * (BM * BN / 4) + (size_t)(c * (kEpiCols / 4)) * BM + row;
+          for (int s2 = 0; s2 < sk_add; ++s2) {
+            // finishing a split tile: add the pieces the other units parked (L2 reads, never through L1)
+            const float4* src = sk_ws + (size_t)s2 * (BM * BN / 4) + (size_t)(c * (kEpiCols / 4)) * BM + row;
 #pragma unroll
-          for (int j = 0; j < kEpiCols / 4; ++j) {
-            const float4 f = __ldcg(src + (size_t)j * BM);
-            v[4 * j] = __float_as_uint(__uint_as_float(v[4 * j]) + f.x);
-            v[4 * j + 1] = __float_as_uint(__uint_as_float(v[4 * j + 1]) + f.y);
-            v[4 * j + 2] = __float_as_uint(__uint_as_float(v[4 * j + 2]) + f.z);
-            v[4 * j + 3] = __float_as_uint(__uint_as_float(v[4 * j + 3]) + f.w);
+            for (int j = 0; j < kEpiCols / 4; ++j) {
+              const float4 f = __ldcg(src + (size_t)j * BM);
+              v[4 * j] = __float_as_uint(__uint_as_float(v[4 * j]) + f.x);
+              v[4 * j + 1] = __float_as_uint(__uint_as_float(v[4 * j + 1]) + f.y);
+              v[4 * j + 2] = __float_as_uint(__uint_as_float(v[4 * j + 2]) + f.z);
+              v[4 * j + 3] = __float_as_uint(__uint_as_float(v[4 * j + 3]) + f.w);
+            }
           }
-        }
 #pragma unroll
-        for (int j = 0; j < 32; ++j) o[j] = pack2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]), f16);
+          for (int j = 0; j < 32; ++j) o[j] = pack2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]), f16);
         }
         if (c == nchunks - 1) {
           // The accumulator has been read completely: hand it back to the MMA warp (of the leader CTA).
@@ -747,8 +748,9 @@ __global__ void __launch_bounds__(PULL ? kThreadsPull : kThreads, 1)
         if (!direct) fence_proxy_async_smem();
         named_barrier_sync(1, 128);
         if (direct) {
-          // Copy the staged 128-row sub-tile (128 bytes per row) out with 16-byte stores: 8 lanes cover one 128-byte row segment, a warp
-          // four rows.  Element (r, j) of the buffer sits at the swizzled position the staging loop wrote it to.
+          // Copy the staged 128-row sub-tile (128 bytes per row) out with 16-byte stores: 8 lanes cover one 128-byte row
+          // segment, a warp four rows.  Element (r, j) of the buffer sits at the swizzled position the staging loop wrote
+          // it to.
           const uint32_t src = epi_base + ebuf * kEpiStageBytes;
           const int x = x_base + c * EC;
           uint4 vv[8];
@@ -1658,7 +1660,8 @@ void* iris_gemm_plan_create(const IrisGemmDesc* d) {
         const long long S = (long long)(tiles - p.dp_tiles) * kb;
         int need = 0;
         for (int t = 0; t < tiles - p.dp_tiles; ++t) {
-          const int span = sk_unit_of((long long)(t + 1) * kb - 1, S, p.sk_units) - sk_unit_of((long long)t * kb, S, p.sk_units);
+          const int span =
+              sk_unit_of((long long)(t + 1) * kb - 1, S, p.sk_units) - sk_unit_of((long long)t * kb, S, p.sk_units);
           if (span > need) need = span;
         }
         if (need > p.sk_slots || p.sk_slots > kSkSlots) {

@@ -205,7 +205,7 @@ struct MpArgs {
 // chunks still uses the whole GPU.  Block b of a role handles the (chunk, slice) pairs b, b + blocks, ... in order:
 // with blocks = nchunks * parts all chunks travel at once and land together at the end; with fewer blocks the chunks
 // complete one group after the other, and the consumer works on the early ones while the later ones are on the link.
-// Producer: copy the slice into the consumer's buffer, make it visible (barrier + one system-scope fence), count the slice on
+// Producer: copy the slice into the consumer's buffer, make it visible (barrier + one system-scope fence), count it on
 // the chunk's arrival counter; the block that completes the count raises the CONSUMER's flag with release semantics
 // and puts the counter back to zero.  Consumer: every block of the chunk waits (bounded, acquire) on the chunk's flag
 // in its own memory, then writes out = 2 * landed for its slice.
@@ -217,8 +217,8 @@ __global__ void mp_kernel(MpArgs a) {
   const bool has_prod = a.roles & 1;
   const bool producing = has_prod && b < R;
   // this side's call counter: the producer's next to its arrival counters, the consumer's next to its flags
-  uint32_t* calls = reinterpret_cast<uint32_t*>(producing ? a.hb[a.producer] + a.arrive_off : a.hb[a.consumer] + a.flags_off) +
-                    a.nchunks;
+  const uint64_t counters = producing ? a.hb[a.producer] + a.arrive_off : a.hb[a.consumer] + a.flags_off;
+  uint32_t* calls = reinterpret_cast<uint32_t*>(counters) + a.nchunks;
   if (threadIdx.x == 0) epoch_s = a.epoch ? a.epoch : *reinterpret_cast<volatile uint32_t*>(calls) + 1u;
   __syncthreads();
   const uint32_t epoch = epoch_s;
@@ -233,61 +233,61 @@ __global__ void mp_kernel(MpArgs a) {
   const uint64_t vecs = a.chunk_bytes / 16;
   const uint64_t per = (vecs + a.parts - 1) / a.parts;
   if (has_prod && b < R) {
-   for (int w = b; w < nblk; w += R) {
-    const int c = w / a.parts, q = w - c * a.parts;
-    const uint64_t v0 = per * q < vecs ? per * q : vecs, v1 = v0 + per < vecs ? v0 + per : vecs;
-    const uint64_t off = (uint64_t)c * a.chunk_bytes + v0 * 16, bytes = (v1 - v0) * 16;
-    const uint64_t base = a.hb[a.producer];
-    const char* src = reinterpret_cast<const char*>(base + a.src_off) + off;
-    char* dst_sym = reinterpret_cast<char*>(base + a.dst_off) + off;
-    if (a.use_put) {
-      put_block(src, dst_sym, bytes, a.producer, a.consumer, a.hb);
-    } else {
-      const float* s = reinterpret_cast<const float*>(src);
-      float* d = reinterpret_cast<float*>(dst_sym);
-      for (size_t i = threadIdx.x; i < bytes / 4; i += blockDim.x)
-        store(d + i, load(s + i, a.producer, a.producer, a.hb), a.producer, a.consumer, a.hb);
-    }
-    // One thread publishes for the block: the barrier orders every thread's stores before its system-scope fence
-    // (fences are cumulative), and only its warp waits for the link round trip; the others start the next slice.
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      fence_sys();
-      uint32_t* cnt = reinterpret_cast<uint32_t*>(base + a.arrive_off) + c;
-      const uint32_t old = atomic_add<Sem::acq_rel, Scope::gpu>(cnt, 1u, 0, 0, a.hb);
-      if (old + 1 == (uint32_t)a.parts) {
-        *cnt = 0;  // every slice has arrived: nobody touches the counter again in this call
-        uint32_t* flag = reinterpret_cast<uint32_t*>(base + a.flags_off) + c;
-        signal_set(flag, epoch, a.producer, a.consumer, a.hb);
+    for (int w = b; w < nblk; w += R) {
+      const int c = w / a.parts, q = w - c * a.parts;
+      const uint64_t v0 = per * q < vecs ? per * q : vecs, v1 = v0 + per < vecs ? v0 + per : vecs;
+      const uint64_t off = (uint64_t)c * a.chunk_bytes + v0 * 16, bytes = (v1 - v0) * 16;
+      const uint64_t base = a.hb[a.producer];
+      const char* src = reinterpret_cast<const char*>(base + a.src_off) + off;
+      char* dst_sym = reinterpret_cast<char*>(base + a.dst_off) + off;
+      if (a.use_put) {
+        put_block(src, dst_sym, bytes, a.producer, a.consumer, a.hb);
+      } else {
+        const float* s = reinterpret_cast<const float*>(src);
+        float* d = reinterpret_cast<float*>(dst_sym);
+        for (size_t i = threadIdx.x; i < bytes / 4; i += blockDim.x)
+          store(d + i, load(s + i, a.producer, a.producer, a.hb), a.producer, a.consumer, a.hb);
+      }
+      // One thread publishes for the block: the barrier orders every thread's stores before its system-scope fence
+      // (fences are cumulative), and only its warp waits for the link round trip; the others start the next slice.
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        fence_sys();
+        uint32_t* cnt = reinterpret_cast<uint32_t*>(base + a.arrive_off) + c;
+        const uint32_t old = atomic_add<Sem::acq_rel, Scope::gpu>(cnt, 1u, 0, 0, a.hb);
+        if (old + 1 == (uint32_t)a.parts) {
+          *cnt = 0;  // every slice has arrived: nobody touches the counter again in this call
+          uint32_t* flag = reinterpret_cast<uint32_t*>(base + a.flags_off) + c;
+          signal_set(flag, epoch, a.producer, a.consumer, a.hb);
+        }
       }
     }
-   }
     leave();
     return;
   }
   if (has_prod) b -= R;
   if (!(a.roles & 2) || b >= R) return;
   for (int w = b; w < nblk; w += R) {
-  const int c = w / a.parts, q = w - c * a.parts;
-  const uint64_t v0 = per * q < vecs ? per * q : vecs, v1 = v0 + per < vecs ? v0 + per : vecs;
-  const uint64_t base = a.hb[a.consumer];
-  if (threadIdx.x == 0) {
-    const uint32_t* flag = reinterpret_cast<const uint32_t*>(base + a.flags_off) + c;
-    verdict = wait_until_ge(flag, epoch, a.timeout_ns, reinterpret_cast<StatusBlock*>(base + a.status_off),
-                            /*where=*/60, (uint32_t)a.consumer, (uint32_t)c);
-  }
-  __syncthreads();
-  if (verdict != kOk) {  // uniform over the block
-    leave();
-    return;
-  }
-  const float4* in = reinterpret_cast<const float4*>(base + a.dst_off + (uint64_t)c * a.chunk_bytes);
-  float4* out = reinterpret_cast<float4*>(base + a.out_off + (uint64_t)c * a.chunk_bytes);
-  for (size_t i = v0 + threadIdx.x; i < v1; i += blockDim.x) {
-    float4 v = in[i];
-    out[i] = make_float4(2.f * v.x, 2.f * v.y, 2.f * v.z, 2.f * v.w);
-  }
-  __syncthreads();  // everybody has read `verdict` before thread 0 writes the next one
+    const int c = w / a.parts, q = w - c * a.parts;
+    const uint64_t v0 = per * q < vecs ? per * q : vecs, v1 = v0 + per < vecs ? v0 + per : vecs;
+    const uint64_t base = a.hb[a.consumer];
+    if (threadIdx.x == 0) {
+      const uint32_t* flag = reinterpret_cast<const uint32_t*>(base + a.flags_off) + c;
+      verdict = wait_until_ge(flag, epoch, a.timeout_ns, reinterpret_cast<StatusBlock*>(base + a.status_off),
+                              /*where=*/60, (uint32_t)a.consumer, (uint32_t)c);
+    }
+    __syncthreads();
+    if (verdict != kOk) {  // uniform over the block
+      leave();
+      return;
+    }
+    const float4* in = reinterpret_cast<const float4*>(base + a.dst_off + (uint64_t)c * a.chunk_bytes);
+    float4* out = reinterpret_cast<float4*>(base + a.out_off + (uint64_t)c * a.chunk_bytes);
+    for (size_t i = v0 + threadIdx.x; i < v1; i += blockDim.x) {
+      float4 v = in[i];
+      out[i] = make_float4(2.f * v.x, 2.f * v.y, 2.f * v.z, 2.f * v.w);
+    }
+    __syncthreads();  // everybody has read `verdict` before thread 0 writes the next one
   }
   leave();
 }

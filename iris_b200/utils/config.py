@@ -111,11 +111,12 @@ class GemmPoint:
         """The launcher command line that runs this point with validation and timing."""
         script, variant = WORKLOADS[self.workload]
         t = self.tile(table)
+        blk_n = max(t.BLK_N, 128) if self.dtype == "int8" else t.BLK_N   # an int8 sub-tile row is 128 columns
         cmd = [python, "-m", "iris_b200.launch", "-np", str(self.world), "--timeout", str(timeout_s),
                f"{root.rstrip('/')}/{script}", "-m", str(self.m), "-n", str(self.n), "-k", str(self.k), "-v", "-b",
                "--gsize_m", str(t.gsize_m), "--gemm_sms", str(t.gemm_sms), "--num_experiments",
                str(self.num_experiments), "--num_warmup", str(self.num_warmup), "--datatype", self.dtype,
-               "--BLK_N", str(t.BLK_N)]
+               "--BLK_N", str(blk_n)]
         if t.BLK_M:
             cmd += ["--BLK_M", str(t.BLK_M)]
         if t.ksplit:
@@ -133,10 +134,11 @@ class GemmPoint:
 
 
 def load_points(shapes: dict, worlds=(1, 2, 4, 8)) -> List[GemmPoint]:
-    """All points of a shape file of the form of ``configs/shapes.json`` x the given rank counts."""
+    """All points of a shape file of the form of ``configs/shapes.json`` x the given rank counts.  A shape may name
+    its element type (``"dtype"``: bf16, fp16, fp32 or int8; default bf16)."""
     pts = []
     for s in shapes["shapes"]:
         for wl in s["workloads"]:
             for w in worlds:
-                pts.append(GemmPoint(wl, s["m"], s["n"], s["k"], w, name=s["name"]))
+                pts.append(GemmPoint(wl, s["m"], s["n"], s["k"], w, name=s["name"], dtype=s.get("dtype", "bf16")))
     return pts

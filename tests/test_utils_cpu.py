@@ -193,3 +193,23 @@ def test_benchmark_points_validate_and_build_their_command():
     pts = load_points(shapes, (1, 2, 4, 8))
     assert len(pts) == 4 * sum(len(s["workloads"]) for s in shapes["shapes"])
     assert any(p.workload == "reduce_scatter" and p.world == 8 and not p.problems() for p in pts)
+
+
+def test_sweep_points_carry_their_element_type():
+    """A shape of the sweep file may name its element type; the command line passes it on, and int8 points never ask
+    for tiles narrower than one 128-column sub-tile."""
+    import json
+    import os
+    from iris_b200.utils.config import GemmPoint, load_points
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    with open(os.path.join(root, "configs", "shapes.json")) as f:
+        shapes = json.load(f)
+    pts = load_points(shapes, worlds=(1, 2))
+    by_type = {p.dtype for p in pts}
+    assert {"bf16", "fp16", "fp32", "int8"} <= by_type
+    for p in pts:
+        assert p.problems() == [], (p, p.problems())
+    table = {"default": {"BLK_N": 64}, "overrides": []}
+    cmd = GemmPoint("all_scatter", 8192, 14336, 4096, 2, dtype="int8").command("/repo", table)
+    assert cmd[cmd.index("--datatype") + 1] == "int8" and cmd[cmd.index("--BLK_N") + 1] == "128"
+    assert GemmPoint("two_shot", 8192, 4096, 11008, 2, dtype="int8").problems()

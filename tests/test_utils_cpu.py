@@ -213,3 +213,33 @@ def test_sweep_points_carry_their_element_type():
     cmd = GemmPoint("all_scatter", 8192, 14336, 4096, 2, dtype="int8").command("/repo", table)
     assert cmd[cmd.index("--datatype") + 1] == "int8" and cmd[cmd.index("--BLK_N") + 1] == "128"
     assert GemmPoint("two_shot", 8192, 4096, 11008, 2, dtype="int8").problems()
+
+
+def _example_scripts():
+    import glob
+    import os
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    pats = ["examples/[01]*/*.py", "examples/benchmark/*.py", "examples/benchmark/reference/*.py"]
+    return sorted(p for pat in pats for p in glob.glob(os.path.join(root, pat)) if not p.endswith("_common.py"))
+
+
+def test_every_example_prints_its_usage():
+    """Every example and benchmark script parses its command line before it touches a device: `-h` exits 0 on a machine
+    without a GPU and names the flags the READMEs use (a guard for edits to the shared drivers)."""
+    import os
+    import subprocess
+    import sys
+    scripts = _example_scripts()
+    assert len(scripts) >= 20
+    procs = [(s, subprocess.Popen([sys.executable, s, "-h"], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+             for s in scripts]
+    usage = {}
+    for s, p in procs:
+        out, _ = p.communicate(timeout=300)
+        assert p.returncode == 0, (s, out[-400:])
+        usage[os.path.relpath(s, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))] = out
+    for flag in ("--datatype", "--BLK_N", "--push_kind", "--all_gather", "--tail_split", "--ksplit", "--variant"):
+        assert flag in usage["examples/07_gemm_all_scatter/benchmark.py"], flag
+    assert "--cuda_graph" in usage["examples/10_tp_block/tp_block.py"] and "--attention" in usage["examples/10_tp_block/tp_block.py"]
+    assert "--blocks" in usage["examples/06_message_passing/message_passing_put.py"]
+    assert "mp" in usage["examples/benchmark/profile_case.py"]

@@ -139,6 +139,14 @@ class MessagePassing:
     least 16 KB per block), so that a hand-off of a few large chunks runs at link rate instead of at the rate of one
     SM per chunk; the block that finishes a chunk last raises its flag.
 
+    ``blocks`` (default: one per slice) is the number of thread blocks per side; with fewer, block ``b`` takes the
+    (chunk, slice) pairs ``b, b + blocks, ...`` in order, so the chunks land one group after the other and the consumer
+    works on early chunks while later ones are still on the link.  Only thread 0 of a producer block fences and
+    publishes a slice (after the block's barrier: fences are cumulative) while the other warps copy the next slice.
+
+    With ``device_epoch=True`` both sides count their calls in device memory instead of taking the call number as a
+    launch argument, so that ``run()`` can be recorded into a CUDA graph and replayed, one hand-off per replay.
+
     All three buffers, the flags and the arrival counters are allocated on the heap here, in the same order on every
     rank.
     """

@@ -7,7 +7,8 @@
 // message-passing protocol (data written with ordinary stores, flag raised with release, consumer polls with
 // acquire, then reads the data: a missing ordering shows up as a data race under the thread sanitizer), concurrent
 // atomic adds from both ranks, a bounded wait that expires, the checking pointer translation, and a model of the
-// fused GEMM's inbox protocol (cumulative flags, buffers alternating by call parity) run with random delays.
+// fused GEMM's inbox protocol (cumulative flags, buffers alternating by call parity) run with random delays, the
+// all-gather prologue, and the stream-K fix-up with the call counter kept in "device" memory.
 #include <stdint.h>
 #include <stdio.h>
 #include <string.h>
@@ -19,6 +20,7 @@
 #include <vector>
 
 #include "iris/rma_ops.cuh"
+#include "kernels/gemm_schedule.h"
 
 extern "C" {
 const char* iris_cpu_last_error();
@@ -436,6 +438,87 @@ int main() {
     for (int r = 0; r < W; ++r) ranks.emplace_back(body, r);
     for (auto& t : ranks) t.join();
     CHECK(failures.load() == 0, "all-gather protocol: %d rank(s) read rows of another call or timed out", failures.load());
+  }
+
+  // ---- 10. stream-K inside one rank: parked pieces, finisher, call counter in "device" memory ----
+  // Threads play the scheduling units of one launch and walk the kernel's own work iterator.  A piece that does not
+  // hold a tile's first k-blocks parks its partial sum in the slot sk_unit_of assigns it and counts itself on the tile
+  // (release); the unit with the first k-blocks, whose piece closes its range, waits (bounded, acquire) for the count,
+  // puts it back to zero and adds the parked values.  Every unit reads the call number at the start of a launch; the
+  // last unit to leave advances it.  Launches follow one another like kernels on a stream (join = kernel boundary).
+  {
+    using iris::gemm::kSkSlots;
+    using iris::gemm::sk_unit_of;
+    using iris::gemm::Work;
+    using iris::gemm::WorkIter;
+    constexpr int kUnits = 6, kTiles = 20, kKb = 7, kDp = 12, kLaunches = 25;   // 8 split tiles over 6 units
+    constexpr int kSk = kTiles - kDp;
+    struct State {
+      std::atomic<uint32_t> cnt[kSk];
+      int64_t ws[kSk][kSkSlots];
+      int64_t out[kTiles];
+      std::atomic<uint32_t> calls, left;
+    };
+    static State stt;
+    for (auto& c : stt.cnt) c.store(0);
+    stt.calls.store(0);
+    stt.left.store(0);
+    std::atomic<int> failures{0};
+    auto value = [](uint32_t call, int tile, int kb) { return (int64_t)call * 100000 + tile * 100 + kb; };
+    for (int launch = 1; launch <= kLaunches; ++launch) {
+      memset(stt.out, 0, sizeof(stt.out));
+      auto unit_body = [&](int unit) {
+        unsigned seed = 4242u + 31u * unit + 7u * launch;
+        auto nap = [&]() {
+          seed = seed * 1664525u + 1013904223u;
+          if ((seed >> 28) < 4) std::this_thread::sleep_for(std::chrono::microseconds((seed >> 20) & 31));
+        };
+        const uint32_t call = stt.calls.load(std::memory_order_relaxed) + 1u;   // ordered by the "kernel boundary"
+        const long long S = (long long)kSk * kKb;
+        WorkIter it(unit, kUnits, kTiles, kKb, kDp, kUnits, 1);
+        Work w;
+        while (it.next(w)) {
+          int64_t acc = 0;
+          for (int kb = w.kb0; kb < w.kb1; ++kb) acc += value(call, w.tile, kb);
+          nap();
+          if (w.kb0 == 0 && w.kb1 == kKb) {
+            stt.out[w.tile] = acc;
+            continue;
+          }
+          const int t = w.tile - kDp;
+          const int head = sk_unit_of((long long)t * kKb, S, kUnits);
+          if (w.kb0 > 0) {
+            const int slot = unit - head - 1;
+            if (slot < 0 || slot >= kSkSlots) { ++failures; return; }
+            stt.ws[t][slot] = acc;
+            stt.cnt[t].fetch_add(1u, std::memory_order_release);
+          } else {
+            const uint32_t need = (uint32_t)(sk_unit_of((long long)(t + 1) * kKb - 1, S, kUnits) - head);
+            if (unit != head || need < 1 || need > (uint32_t)kSkSlots) { ++failures; return; }
+            uint64_t polls = 0;
+            while (stt.cnt[t].load(std::memory_order_acquire) < need)
+              if (++polls > (1ull << 28)) { ++failures; return; }
+            stt.cnt[t].store(0u, std::memory_order_relaxed);
+            for (uint32_t s2 = 0; s2 < need; ++s2) acc += stt.ws[t][s2];
+            stt.out[w.tile] = acc;
+          }
+        }
+        if (stt.left.fetch_add(1u, std::memory_order_acq_rel) + 1u == call * (uint32_t)kUnits)
+          stt.calls.store(call, std::memory_order_relaxed);
+      };
+      std::vector<std::thread> units;
+      for (int u = 0; u < kUnits; ++u) units.emplace_back(unit_body, u);
+      for (auto& t : units) t.join();
+      for (int tile = 0; tile < kTiles; ++tile) {
+        int64_t want = 0;
+        for (int kb = 0; kb < kKb; ++kb) want += value((uint32_t)launch, tile, kb);
+        if (stt.out[tile] != want) ++failures;
+      }
+      if (stt.calls.load() != (uint32_t)launch) ++failures;
+      for (auto& c : stt.cnt)
+        if (c.load() != 0) ++failures;
+    }
+    CHECK(failures.load() == 0, "stream-K protocol: %d wrong sums, slots out of range, counters off or time-outs", failures.load());
   }
 
   for (int r = 0; r < kWorld; ++r) {

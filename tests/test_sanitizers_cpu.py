@@ -12,6 +12,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 SRC = [os.path.join(ROOT, "tests", "native", "cpu_backend_stress.cpp"),
        os.path.join(ROOT, "iris_b200", "csrc", "cpu", "iris_cpu_backend.cpp")]
 INC = os.path.join(ROOT, "iris_b200", "include")
+CSRC = os.path.join(ROOT, "iris_b200", "csrc")   # the schedule arithmetic shared with the kernels
 
 
 @pytest.mark.parametrize("name,flags,env", [
@@ -24,7 +25,8 @@ def test_cpu_backend_is_clean_under(name, flags, env, tmp_path):
     if cxx is None:
         pytest.skip("no g++")
     exe = str(tmp_path / f"stress_{name}")
-    build = subprocess.run([cxx, "-std=c++17", "-O1", "-g", *flags, "-I", INC, *SRC, "-o", exe, "-pthread", "-lrt"],
+    build = subprocess.run([cxx, "-std=c++17", "-O1", "-g", *flags, "-I", INC, "-I", CSRC, *SRC, "-o", exe, "-pthread",
+                            "-lrt"],
                            capture_output=True, text=True, timeout=300)
     if build.returncode != 0 and ("cannot find" in build.stderr or "unrecognized" in build.stderr):
         pytest.skip(f"{name} sanitizer runtime is not installed: {build.stderr.strip().splitlines()[-1]}")

@@ -36,7 +36,6 @@ import json
 import os
 import statistics
 import sys
-import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
